@@ -1,0 +1,184 @@
+"""ctypes front end of the CPU oracle (``oracle.c``).
+
+TEST INFRASTRUCTURE ONLY: imported by ``tests/``, by the smoke check and by the
+CPU-baseline legs of the benchmark.  The product package never imports it.
+
+All functions take and return numpy arrays (fp32 / int32 / int64, C-contiguous)
+in the reference's token-major layouts.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import subprocess
+from typing import Optional, Tuple
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_SO = os.path.join(_HERE, "liblampa_oracle.so")
+_LIB = None
+
+
+def build(force: bool = False) -> str:
+    """Compile ``oracle.c`` next to itself (gcc; OpenMP when available)."""
+    src = os.path.join(_HERE, "oracle.c")
+    if not force and os.path.exists(_SO) and os.path.getmtime(_SO) >= os.path.getmtime(src):
+        return _SO
+    base = ["-O2", "-ffp-contract=off", "-fPIC", "-shared", src, "-o", _SO, "-lm"]
+    last = None
+    for cc in ("/usr/bin/gcc", "gcc", "cc"):
+        for omp in (["-fopenmp"], []):
+            try:
+                subprocess.run([cc] + omp + base, check=True, capture_output=True)
+                return _SO
+            except (subprocess.CalledProcessError, FileNotFoundError) as e:  # try next
+                last = e
+    raise RuntimeError(f"could not build the oracle: {last}")
+
+
+def lib() -> ctypes.CDLL:
+    global _LIB
+    if _LIB is None:
+        build()
+        _LIB = ctypes.CDLL(_SO)
+    return _LIB
+
+
+def _f32(a) -> np.ndarray:
+    return np.ascontiguousarray(np.asarray(a, dtype=np.float32))
+
+
+def _p(a: Optional[np.ndarray]):
+    return None if a is None else a.ctypes.data_as(ctypes.c_void_p)
+
+
+def gdn_plain(q, k, v, g, beta, scale: Optional[float] = None, h0=None, cu_seqlens=None,
+              use_l2norm: bool = False) -> Tuple[np.ndarray, np.ndarray]:
+    """Plain gated-delta rule. q,k [T,H,K]; v [T,H,V]; g,beta [T,H]; h0 [N,H,K,V].
+
+    Returns (o [T,H,V], final_state [N,H,K,V]) in fp32.
+    """
+    q, k, v, g, beta = map(_f32, (q, k, v, g, beta))
+    T, H, K = q.shape
+    V = v.shape[-1]
+    if scale is None:
+        scale = K ** -0.5
+    cu = None if cu_seqlens is None else np.ascontiguousarray(np.asarray(cu_seqlens, dtype=np.int64))
+    nseq = 1 if cu is None else len(cu) - 1
+    h0 = None if h0 is None else _f32(h0).reshape(nseq, H, K, V)
+    o = np.empty((T, H, V), np.float32)
+    ht = np.empty((nseq, H, K, V), np.float32)
+    rc = lib().oracle_gdn_plain(_p(q), _p(k), _p(v), _p(g), _p(beta), _p(h0), _p(cu),
+                                ctypes.c_int(nseq), _p(o), _p(ht), ctypes.c_int(T), ctypes.c_int(H),
+                                ctypes.c_int(K), ctypes.c_int(V), ctypes.c_float(scale),
+                                ctypes.c_int(int(use_l2norm)))
+    if rc != 0:
+        raise RuntimeError(f"oracle_gdn_plain failed: {rc}")
+    return o, ht
+
+
+def hgdn(q, k, v, g, beta, lam, cu_seqlens=None, use_l2norm: bool = True):
+    """Hierarchical gated-delta rule. lam [T,H,L].
+
+    Returns (o [T,H,V], states [H,K,V,L], counts [L]); states/counts describe the
+    last sequence.
+    """
+    q, k, v, g, beta, lam = map(_f32, (q, k, v, g, beta, lam))
+    T, H, K = q.shape
+    V = v.shape[-1]
+    L = lam.shape[-1]
+    cu = None if cu_seqlens is None else np.ascontiguousarray(np.asarray(cu_seqlens, dtype=np.int64))
+    nseq = 1 if cu is None else len(cu) - 1
+    o = np.empty((T, H, V), np.float32)
+    states = np.zeros((H, K, V, L), np.float32)
+    counts = np.zeros((L,), np.int32)
+    rc = lib().oracle_hgdn(_p(q), _p(k), _p(v), _p(g), _p(beta), _p(lam), _p(cu), ctypes.c_int(nseq),
+                           _p(o), _p(states), _p(counts), ctypes.c_int(T), ctypes.c_int(H),
+                           ctypes.c_int(K), ctypes.c_int(V), ctypes.c_int(L),
+                           ctypes.c_int(int(use_l2norm)))
+    if rc != 0:
+        raise RuntimeError(f"oracle_hgdn failed: {rc} (not enough levels for this length?)")
+    return o, states, counts
+
+
+def lsh_ids(x, alpha, beta, w: float = 1.0, dim: Optional[int] = None, want_keys: bool = False):
+    """x [N, row] fp32 (coordinates first); alpha [heads, dim, rounds]; beta [rounds].
+
+    Returns ids int32 [rounds, heads, N] (and the float projections when want_keys).
+    """
+    x = _f32(x)
+    alpha = _f32(alpha)
+    beta = _f32(beta).reshape(-1)
+    heads, d, rounds = alpha.shape
+    dim = d if dim is None else dim
+    assert dim == d and x.shape[1] >= dim and beta.shape[0] == rounds
+    N = x.shape[0]
+    ids = np.empty((rounds, heads, N), np.int32)
+    keys = np.empty((rounds, heads, N), np.float32) if want_keys else None
+    lib().oracle_lsh_ids(_p(x), ctypes.c_int64(x.shape[1]), _p(alpha), _p(beta), ctypes.c_float(w),
+                         ctypes.c_int64(N), ctypes.c_int(heads), ctypes.c_int(rounds), ctypes.c_int(dim),
+                         _p(ids), _p(keys))
+    return (ids, keys) if want_keys else ids
+
+
+def segsort(keys, seg=None, init=None) -> np.ndarray:
+    """Stable ascending sort per segment; keys 1-D int32 or fp32; returns int64 local indices."""
+    keys = np.ascontiguousarray(keys)
+    n = keys.shape[0]
+    seg = np.array([0, n], np.int64) if seg is None else np.ascontiguousarray(np.asarray(seg, np.int64))
+    init = None if init is None else np.ascontiguousarray(np.asarray(init, np.int64))
+    perm = np.empty((n,), np.int64)
+    if keys.dtype == np.int32:
+        fn = lib().oracle_segsort_i32
+    elif keys.dtype == np.float32:
+        fn = lib().oracle_segsort_f32
+    else:
+        raise TypeError(keys.dtype)
+    fn(_p(keys), _p(seg), ctypes.c_int(len(seg) - 1), _p(init), _p(perm))
+    return perm
+
+
+def invert_perm(perm, seg=None) -> np.ndarray:
+    perm = np.ascontiguousarray(np.asarray(perm, np.int64))
+    n = perm.shape[0]
+    seg = np.array([0, n], np.int64) if seg is None else np.ascontiguousarray(np.asarray(seg, np.int64))
+    inv = np.empty_like(perm)
+    rc = lib().oracle_invert_perm(_p(perm), _p(seg), ctypes.c_int(len(seg) - 1), _p(inv))
+    if rc != 0:
+        raise ValueError("not a permutation")
+    return inv
+
+
+def permute_rows(src, perm, seg=None) -> np.ndarray:
+    src = np.ascontiguousarray(src)
+    perm = np.ascontiguousarray(np.asarray(perm, np.int64))
+    n = perm.shape[0]
+    seg = np.array([0, n], np.int64) if seg is None else np.ascontiguousarray(np.asarray(seg, np.int64))
+    dst = np.empty_like(src)
+    row_bytes = src.strides[0]
+    lib().oracle_permute_rows(_p(src), _p(perm), _p(seg), ctypes.c_int(len(seg) - 1), _p(dst),
+                              ctypes.c_int64(row_bytes))
+    return dst
+
+
+def lsh_ordering_keys(coords, alpha) -> np.ndarray:
+    """Float bucket key of LSHOrdering (models/baselines/hmamba.py:316-333) for one event.
+
+    coords [N, C] fp32; alpha [1, C, n_hashes].  With a single head the reference's
+    shift (max - min over a size-1 axis) is zero, so key = sum_i 2^i * (coords @ alpha[0,:,i]).
+    """
+    coords = _f32(coords)
+    alpha = _f32(alpha)
+    proj = coords @ alpha[0]                    # [N, n_hashes]
+    expo = (2 ** np.arange(alpha.shape[-1])).astype(np.float32)
+    return (proj * expo).sum(-1).astype(np.float32)
+
+
+def lsh_ordering(coords, alpha) -> np.ndarray:
+    """Permutation of LSHOrdering.forward for one event: norm pre-sort, then stable key sort."""
+    coords = _f32(coords)
+    key = lsh_ordering_keys(coords, alpha)
+    norm = np.sqrt((coords.astype(np.float32) ** 2).sum(-1, dtype=np.float32)).astype(np.float32)
+    norm_idx = segsort(norm)
+    return segsort(key, init=norm_idx)

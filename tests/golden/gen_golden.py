@@ -1,0 +1,146 @@
+"""Generate the golden fixtures in this directory from the reference's own code.
+
+Run once in a container where the reference checkout is mounted:
+
+    python tests/golden/gen_golden.py --reference /path/to/Lampa
+
+It executes the reference's pure-PyTorch CPU statements of the path
+(models/hattention/recurrent.py::hattention_recurrent,
+models/hattention/base.py::hattention_materialized_dplr helpers,
+models/baselines/hmamba.py::LSHOrdering / E2LSH / lsh_mapping,
+models/model_utils/hash_utils.py::invert_permutation / batched_index_select,
+models/attention/hept.py::sort_to_buckets / unsort_from_buckets) on seeded
+inputs and stores inputs + outputs as small .npz files.  Nothing from the
+reference is copied; only numbers it produced are stored.
+"""
+from __future__ import annotations
+
+import argparse
+import ast
+import importlib
+import importlib.util
+import os
+import sys
+import types
+
+import numpy as np
+import torch
+import torch.nn as nn
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def load_hattention(ref: str):
+    """Register a synthetic package over models/hattention and import base + recurrent."""
+    pkg_dir = os.path.join(ref, "models", "hattention")
+    pkg = types.ModuleType("_ref_hattention")
+    pkg.__path__ = [pkg_dir]
+    sys.modules["_ref_hattention"] = pkg
+    mods = {}
+    for name in ("base", "recurrent"):
+        spec = importlib.util.spec_from_file_location(
+            f"_ref_hattention.{name}", os.path.join(pkg_dir, f"{name}.py"))
+        m = importlib.util.module_from_spec(spec)
+        sys.modules[f"_ref_hattention.{name}"] = m
+        spec.loader.exec_module(m)
+        mods[name] = m
+    return mods["base"], mods["recurrent"]
+
+
+def load_defs(path: str, names, extra=None):
+    """Execute only the named top-level defs/classes of a file (its imports may be unavailable)."""
+    tree = ast.parse(open(path).read())
+    keep = [n for n in tree.body
+            if isinstance(n, (ast.FunctionDef, ast.ClassDef)) and n.name in names]
+    scope = {"torch": torch, "nn": nn}
+    scope.update(extra or {})
+    exec(compile(ast.Module(body=keep, type_ignores=[]), path, "exec"), scope)
+    return scope
+
+
+def gdn_inputs(seed, T, H, K, V, L=None, g_shift=2.0):
+    gen = torch.Generator().manual_seed(seed)
+    q = torch.nn.functional.normalize(torch.randn(T, H, K, generator=gen), dim=-1)
+    k = torch.nn.functional.normalize(torch.randn(T, H, K, generator=gen), dim=-1)
+    v = torch.randn(T, H, V, generator=gen)
+    beta = torch.sigmoid(torch.randn(T, H, generator=gen))
+    g = -torch.nn.functional.softplus(torch.randn(T, H, generator=gen) + g_shift)
+    lam = None if L is None else torch.nn.functional.softplus(torch.randn(T, H, L, generator=gen))
+    return q, k, v, beta, g, lam
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--reference", default="/root/reference")
+    args = ap.parse_args()
+    ref = args.reference
+    torch.set_num_threads(8)
+    base, recurrent = load_hattention(ref)
+
+    # ---- hierarchical + plain gated delta, reference token recurrence -------------
+    cases = [
+        ("hgdn_T200_H2_K16_V32_L9", 101, 200, 2, 16, 32, 9, 2.0),
+        ("hgdn_T320_H2_K32_V32_L10", 102, 320, 2, 32, 32, 10, -3.0),
+        ("hgdn_T256_H1_K64_V64_L9", 103, 256, 1, 64, 64, 9, -4.0),
+    ]
+    for name, seed, T, H, K, V, L, gs in cases:
+        q, k, v, beta, g, lam = gdn_inputs(seed, T, H, K, V, L, gs)
+        scale = K ** -0.5
+        # API layer semantics: Q = l2norm(q)*scale, L = lambda/scale (inputs are already unit-norm)
+        o, S = recurrent.hattention_recurrent(
+            Q=(q * scale)[None], K=k[None], V=v[None], A=torch.exp(g)[None], B=beta[None],
+            L=(lam / scale)[None], base=2, htype=base.HType.WEAK, hstruct=base.HStruct.GDELTA)
+        o1, S1 = recurrent.hattention_recurrent(
+            Q=(q * scale)[None], K=k[None], V=v[None], A=torch.exp(g)[None], B=beta[None],
+            L=torch.ones_like(lam)[None], base=2, htype=base.HType.WEAK, hstruct=base.HStruct.GDELTA)
+        np.savez_compressed(
+            os.path.join(HERE, name + ".npz"),
+            q=q.numpy(), k=k.numpy(), v=v.numpy(), beta=beta.numpy(), g=g.numpy(), lam=lam.numpy(),
+            o_hier=o[0].numpy(), states_hier=S.states[0].numpy(), counts_hier=S.counts.numpy(),
+            o_plain=o1[0].numpy(), final_plain=S1.states[0].sum(-1).numpy(), scale=np.float32(scale))
+        print(name, "ok", float(o.abs().max()))
+
+    # level function of the reference vs bit_length(t ^ s)
+    lv = np.array([[base.get_level_index_weak(t, s, 2) if s < t else 0 for s in range(130)]
+                   for t in range(130)], np.int32)
+    np.savez_compressed(os.path.join(HERE, "levels_weak_130.npz"), levels=lv)
+
+    # ---- LSH ordering ------------------------------------------------------------
+    hm = load_defs(os.path.join(ref, "models", "baselines", "hmamba.py"),
+                   {"lsh_mapping", "E2LSH", "LSHOrdering"})
+    sys.path.insert(0, os.path.join(ref, "models", "model_utils"))
+    hu = load_defs(os.path.join(ref, "models", "model_utils", "hash_utils.py"),
+                   {"invert_permutation", "batched_index_select"},
+                   extra={"rearrange": __import__("einops").rearrange})
+    hp = load_defs(os.path.join(ref, "models", "attention", "hept.py"),
+                   {"sort_to_buckets", "unsort_from_buckets"},
+                   extra={"rearrange": __import__("einops").rearrange,
+                          "batched_index_select": hu["batched_index_select"]})
+
+    gen = torch.Generator().manual_seed(2025)
+    Bn, Ln, D, C = 2, 1500, 8, 6
+    layer = torch.randint(0, 10, (Bn, Ln), generator=gen).float()
+    r = 30 + layer * (970.0 / 9)
+    phi = (torch.rand(Bn, Ln, generator=gen) * 2 - 1) * np.pi
+    z = (torch.rand(Bn, Ln, generator=gen) * 2 - 1) * 3000
+    coords = torch.stack([r * torch.cos(phi), r * torch.sin(phi), z, r, phi, torch.asinh(z / r)], -1)
+    points = torch.randn(Bn, Ln, D, generator=gen)
+    torch.manual_seed(7)
+    ordering = hm["LSHOrdering"](C, num_hashes=3)
+    ordered, idx = ordering(points, coords)
+    flat = coords.reshape(Bn * Ln, C).unsqueeze(0)
+    proj = ordering.e2lsh(flat)                      # [n_hashes, N, n_heads=1]
+    inv = hu["invert_permutation"](idx)
+    buckets = hp["sort_to_buckets"](points, idx[None], 100)
+    unsorted = hp["unsort_from_buckets"](buckets, inv[None])
+    np.savez_compressed(
+        os.path.join(HERE, "lsh_ordering_B2_L1500.npz"),
+        coords=coords.numpy(), points=points.numpy(), alpha=ordering.e2lsh.alpha.detach().numpy(),
+        beta=ordering.e2lsh.beta.detach().numpy(), proj=proj.numpy(), indices=idx.numpy(),
+        ordered=ordered.numpy(), inverse=inv.numpy(), buckets=buckets.numpy(),
+        unsorted=unsorted.numpy())
+    print("lsh ok", idx.shape, buckets.shape, bool((unsorted[0] == points).all()))
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,114 @@
+"""The CPU oracle against fixtures produced by the reference's own pure-PyTorch code.
+
+Fixtures: tests/golden/*.npz (made by tests/golden/gen_golden.py from
+models/hattention/recurrent.py, models/baselines/hmamba.py, models/attention/hept.py,
+models/model_utils/hash_utils.py).
+"""
+import glob
+import os
+
+import numpy as np
+import pytest
+
+from oracle import oracle
+
+
+def _cases(golden_dir):
+    return sorted(glob.glob(os.path.join(golden_dir, "hgdn_*.npz")))
+
+
+@pytest.mark.parametrize("name", ["hgdn_T200_H2_K16_V32_L9", "hgdn_T320_H2_K32_V32_L10",
+                                  "hgdn_T256_H1_K64_V64_L9"])
+def test_hier_and_plain_match_reference_recurrence(golden_dir, name):
+    z = np.load(os.path.join(golden_dir, name + ".npz"))
+    o, states, counts = oracle.hgdn(z["q"], z["k"], z["v"], z["g"], z["beta"], z["lam"], use_l2norm=False)
+    np.testing.assert_allclose(o, z["o_hier"], rtol=2e-4, atol=2e-5)
+    np.testing.assert_allclose(states, z["states_hier"], rtol=2e-4, atol=2e-5)
+    assert (counts == z["counts_hier"]).all()
+    op, ht = oracle.gdn_plain(z["q"], z["k"], z["v"], z["g"], z["beta"], scale=float(z["scale"]))
+    np.testing.assert_allclose(op, z["o_plain"], rtol=2e-4, atol=2e-5)
+    np.testing.assert_allclose(ht[0], z["final_plain"], rtol=2e-4, atol=2e-5)
+
+
+def test_level_function_is_bit_length_of_xor(golden_dir):
+    lv = np.load(os.path.join(golden_dir, "levels_weak_130.npz"))["levels"]
+    t = np.arange(130)[:, None]
+    s = np.arange(130)[None, :]
+    mine = np.where(s < t, np.floor(np.log2(np.maximum(t ^ s, 1))).astype(int) + 1, 0)
+    assert (mine == lv).all()
+
+
+def test_plain_initial_state_and_varlen_consistency():
+    rng = np.random.default_rng(0)
+    T, H, K, V = 150, 2, 16, 16
+    q, k = rng.standard_normal((2, T, H, K)).astype(np.float32)
+    v = rng.standard_normal((T, H, V)).astype(np.float32)
+    g = -np.abs(rng.standard_normal((T, H))).astype(np.float32) * 0.1
+    b = rng.uniform(0, 1, (T, H)).astype(np.float32)
+    h0 = rng.standard_normal((1, H, K, V)).astype(np.float32) * 0.1
+    o_full, ht_full = oracle.gdn_plain(q, k, v, g, b, h0=h0, use_l2norm=True)
+    # running the two halves with state hand-over equals the full run
+    o_a, ht_a = oracle.gdn_plain(q[:70], k[:70], v[:70], g[:70], b[:70], h0=h0, use_l2norm=True)
+    o_b, ht_b = oracle.gdn_plain(q[70:], k[70:], v[70:], g[70:], b[70:], h0=ht_a, use_l2norm=True)
+    np.testing.assert_allclose(np.concatenate([o_a, o_b]), o_full, rtol=1e-6, atol=1e-6)
+    np.testing.assert_allclose(ht_b, ht_full, rtol=1e-6, atol=1e-6)
+    # packed varlen == separate calls
+    cu = np.array([0, 70, 150])
+    h02 = np.concatenate([h0, h0 * 2])
+    o_v, ht_v = oracle.gdn_plain(q, k, v, g, b, h0=h02, cu_seqlens=cu, use_l2norm=True)
+    o_c, ht_c = oracle.gdn_plain(q[70:], k[70:], v[70:], g[70:], b[70:], h0=h0 * 2, use_l2norm=True)
+    np.testing.assert_array_equal(o_v[:70], o_a)
+    np.testing.assert_array_equal(o_v[70:], o_c)
+    np.testing.assert_array_equal(ht_v[1], ht_c[0])
+
+
+def test_lsh_ordering_matches_reference(golden_dir):
+    z = np.load(os.path.join(golden_dir, "lsh_ordering_B2_L1500.npz"))
+    coords, points, alpha = z["coords"], z["points"], z["alpha"]
+    Bn, Ln, _ = coords.shape
+    # E2LSH float projection (hmamba.py:275-285): [n_hashes, N, 1]
+    flat = coords.reshape(Bn * Ln, -1)
+    _, keys = oracle.lsh_ids(flat, alpha, np.zeros(3, np.float32), want_keys=True)
+    ref_proj = z["proj"][:, :, 0]                      # [3, N]
+    np.testing.assert_allclose(keys[:, 0, :], ref_proj, rtol=1e-5, atol=1e-3)
+    for b in range(Bn):
+        perm = oracle.lsh_ordering(coords[b], alpha)
+        ref = z["indices"][b]
+        agree = (perm == ref).mean()
+        # float re-association near-ties may swap a handful of neighbours
+        assert agree > 0.99, agree
+        key = oracle.lsh_ordering_keys(coords[b], alpha)
+        assert (np.diff(key[perm]) >= 0).all()
+        # same multiset, and the reference's permutation is sorted under our key up to rounding
+        assert (np.sort(perm) == np.arange(Ln)).all()
+        assert (np.diff(key[ref]) >= -1e-3 * np.abs(key).max()).all()
+        ordered = oracle.permute_rows(points[b], ref)
+        np.testing.assert_array_equal(ordered, z["ordered"][b])
+        inv = oracle.invert_perm(ref)
+        np.testing.assert_array_equal(inv, z["inverse"][b])
+        np.testing.assert_array_equal(oracle.permute_rows(ordered, inv), points[b])
+    # sort_to_buckets == row gather reshaped (hept.py:9-14)
+    np.testing.assert_array_equal(z["buckets"][0].reshape(Bn, Ln, -1), z["ordered"])
+
+
+def test_integer_ids_and_stable_sort_properties():
+    rng = np.random.default_rng(3)
+    N = 5000
+    x = rng.standard_normal((N, 24)).astype(np.float32) * 100
+    alpha = rng.standard_normal((8, 6, 3)).astype(np.float32)
+    beta = rng.uniform(0, 1, 3).astype(np.float32)
+    ids = oracle.lsh_ids(x, alpha, beta, w=1.0)
+    assert ids.shape == (3, 8, N) and ids.dtype == np.int32
+    # numpy restatement with separately rounded multiply/add
+    acc = x[:, 0, None, None] * alpha[None, :, 0, :]
+    for d in range(1, 6):
+        acc = acc + x[:, d, None, None] * alpha[None, :, d, :]
+    ref = np.floor((acc + beta[None, None, :]) / np.float32(1.0)).astype(np.int32)   # [N, heads, rounds]
+    np.testing.assert_array_equal(ids, ref.transpose(2, 1, 0))
+    row = np.ascontiguousarray(ids[1, 3])
+    perm = oracle.segsort(row)
+    np.testing.assert_array_equal(perm, np.argsort(row, kind="stable"))
+    seg = np.array([0, 100, 100, 3000, N])
+    perm_s = oracle.segsort(row, seg)
+    for a, b in zip(seg[:-1], seg[1:]):
+        np.testing.assert_array_equal(perm_s[a:b], np.argsort(row[a:b], kind="stable"))
