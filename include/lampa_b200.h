@@ -1,0 +1,165 @@
+/*
+ * lampa_b200 — C ABI of the B200 (sm_100a) implementation of Lampa's LSH ordering and
+ * (hierarchical) chunkwise gated-delta-rule forward.
+ *
+ * Conventions
+ *  - every pointer named q/k/v/.../ws/status is a DEVICE pointer unless stated otherwise;
+ *  - `stream` is a cudaStream_t passed as void*; all work is enqueued on it, asynchronously,
+ *    and no entry point synchronises the host with the device;
+ *  - the library never allocates device memory: scratch comes from the caller (`ws`), sized
+ *    by the matching *_workspace_bytes call;
+ *  - return value: LAMPA_OK or a negative LAMPA_ERR_* for problems found on the host before
+ *    any launch; problems found on the device (a wait that ran out, not enough lambda levels
+ *    for a packed sequence) are written to `status` (int32[4]: code, where, detail, unused),
+ *    which the caller zeroes once and may read after synchronising the stream;
+ *  - inputs are never written; layouts are the reference's token-major contiguous ones.
+ *
+ * "Reference" below means the Lampa repository; paths are relative to its root.
+ */
+#ifndef LAMPA_B200_H
+#define LAMPA_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* element types */
+#define LAMPA_BF16 0
+#define LAMPA_F16 1
+#define LAMPA_F32 2
+/* key types of the sort */
+#define LAMPA_KEY_I32 0
+#define LAMPA_KEY_F32 1
+
+#define LAMPA_OK 0
+#define LAMPA_ERR_ARG (-1)          /* null pointer, negative size, bad enum */
+#define LAMPA_ERR_UNSUPPORTED (-2)  /* head dims / level count outside the built set */
+#define LAMPA_ERR_WORKSPACE (-3)    /* ws too small or misaligned */
+#define LAMPA_ERR_CUDA (-4)         /* a CUDA runtime call failed (launch error) */
+#define LAMPA_ERR_TIMEOUT (-5)      /* device: a bounded wait ran out (status word only) */
+#define LAMPA_ERR_LEVELS (-6)       /* device/host: lambda has fewer levels than the sequence needs */
+#define LAMPA_ERR_BOUNDS (-7)       /* device: an index fell outside its extent (status word only) */
+
+/* Shape/type descriptor of one gated-delta forward call. */
+typedef struct lampa_gdn_desc {
+    int32_t B;          /* batch; must be 1 when cu_seqlens is given                         */
+    int32_t T;          /* tokens per batch row (total tokens when packed)                   */
+    int32_t H;          /* heads                                                             */
+    int32_t K;          /* key/query head dim: 16, 32 or 64                                  */
+    int32_t V;          /* value head dim:     16, 32 or 64                                  */
+    int32_t L;          /* hierarchical only: number of lambda levels, else 0                */
+    int32_t nseq;       /* packed input: number of sequences (len(cu_seqlens) - 1), else 0   */
+    int32_t qkv_dtype;  /* LAMPA_BF16 / LAMPA_F16 / LAMPA_F32 for q, k, v and o              */
+    int32_t gb_dtype;   /* type of g and beta                                                */
+    int32_t lam_dtype;  /* type of lambda                                                    */
+    int32_t use_l2norm; /* normalise q and k rows: x * rsqrt(sum x^2 + 1e-6)                 */
+    float scale;        /* output scale of the plain rule (K^-0.5 by default in the caller)  */
+} lampa_gdn_desc;
+
+int lampa_version(void);
+const char* lampa_error_string(int code);
+
+/*
+ * Bytes of scratch for lampa_gdn_fwd / lampa_hgdn_fwd with this descriptor (256-byte aligned
+ * pointer expected).  Replaces the reference's torch.empty intermediates (A, Ad, w, u, h, v_new:
+ * models/hattention/gated_delta_rule_ori.py:29-80, chunkwise_hgdn.py:628-760).
+ */
+int lampa_gdn_workspace_bytes(const lampa_gdn_desc* d, size_t* bytes);
+
+/*
+ * Where the per-chunk intermediates live inside the workspace, for tests that inspect them.
+ * One record per (chunk slot, head), chunk-major.  out[0] = byte offset of the first record,
+ * out[1] = bytes per record, then byte offsets inside a record of: out[2] M (bf16 [K][K+8]),
+ * out[3] B^T (bf16 [V][K+8]), out[4] Q~ (bf16 [64][K+8]), out[5] O_local (fp32 [64][V+8]),
+ * out[6] chunk-level lambda (fp32 [LC][64], hierarchical only); out[7] = LC, out[8] = number of
+ * chunk slots, out[9] = chunks per block, out[10] / out[11] = byte offsets of the block composites
+ * and of the block entry states.
+ */
+int lampa_gdn_workspace_layout(const lampa_gdn_desc* d, size_t out[12]);
+
+/*
+ * Chunkwise gated-delta-rule forward.
+ * Replaces: chunk_gated_delta_rule -> ChunkGatedDeltaRuleFunction.forward ->
+ * chunk_gated_delta_rule_fwd (models/hattention/gated_delta_rule_ori.py:235-357, 163-202, 29-80)
+ * and the Triton kernels it chains (l2norm.py:138-180, cumsum.py:386-414,
+ * chunk_scaled_dot_kkt.py:74-120, solve_tril.py:221-276, wy_fast.py:192-228,
+ * chunk_delta_h.py:397-441, chunk_o.py:433-469).
+ *   q,k [B,T,H,K]; v,o [B,T,H,V]; g,beta [B,T,H]; h0 [N,H,K,V] fp32 or NULL;
+ *   cu_seqlens int64 [nseq+1] (device) or NULL; ht [N,H,K,V] fp32 or NULL, N = nseq or B.
+ */
+int lampa_gdn_fwd(const lampa_gdn_desc* d, const void* q, const void* k, const void* v,
+                  const void* g, const void* beta, const float* h0, const int64_t* cu_seqlens,
+                  void* o, float* ht, void* ws, size_t ws_bytes, int32_t* status, void* stream);
+
+/*
+ * Hierarchical (Fenwick-level, log-linear) chunkwise gated-delta-rule forward.
+ * Replaces: chunk_h_gated_delta_rule -> hattention_kernel -> HAttentionFunction.forward (GDELTA)
+ * -> chunkwise_hgdn.chunkwise_fwd (models/hattention/gated_delta_rule_apis.py:20-134,
+ * kernel.py:338-374, 100-120, chunkwise_hgdn.py:565-791) and its per-level re-scans
+ * (fla_future/chunk_delta_h.py:34-186, chunkwise.py:473-647).
+ *   lam [B,T,H,L]: weight of level(t,s) = bit_length(t XOR s) (0 on the diagonal); a sequence of
+ *   NT chunks needs L >= 7 + ceil(log2(NT)).  q and k are l2-normalised when d->use_l2norm;
+ *   the result does not depend on d->scale (the reference multiplies q by it and divides lam by it).
+ *   Sequences (cu_seqlens) restart the hierarchy; ragged tails behave as tokens with
+ *   k = v = 0, beta = 0, g = 0.
+ */
+int lampa_hgdn_fwd(const lampa_gdn_desc* d, const void* q, const void* k, const void* v,
+                   const void* g, const void* beta, const void* lam, const int64_t* cu_seqlens,
+                   void* o, void* ws, size_t ws_bytes, int32_t* status, void* stream);
+
+/*
+ * E2LSH projection and integer bucket ids.
+ * Replaces: E2LSH.forward (models/model_utils/hash_utils.py:359-371; copies in
+ * models/baselines/hmamba.py:275-285, full_mamba2.py:128-141) — the float projection — and adds
+ * the quantisation floor((a.x + b) / w) the reference leaves out.
+ *   x: fp32 rows, `row_stride` floats apart, the first `dim` floats of a row are hashed;
+ *      head h reads rows at x + h * head_stride (0: all heads share the rows);
+ *   alpha [heads, dim, rounds] fp32, beta [rounds] fp32 (device);
+ *   ids  int32 [rounds, heads, N] or NULL;  keys fp32 [rounds, heads, N] (a.x, no offset) or NULL;
+ *   packed int32 [rounds, N] = sum_h ids[r,h,n] << h or NULL.
+ * Operation order (bit-exact contract): acc = x0*a0; acc = acc + xd*ad (d ascending, multiply
+ * and add rounded separately); id = (int32) floorf((acc + beta) / w).
+ */
+int lampa_lsh_hash(const float* x, int64_t row_stride, int64_t head_stride, const float* alpha,
+                   const float* beta, float w, int64_t N, int32_t heads, int32_t rounds, int32_t dim,
+                   int32_t* ids, float* keys, int32_t* packed, void* stream);
+
+/* Scratch bytes of lampa_segsort_stable for n_total keys. */
+int lampa_segsort_workspace_bytes(int64_t n_total, size_t* bytes);
+
+/*
+ * Stable ascending sort of each segment's keys; writes the permutation (indices local to the
+ * segment, int64 as torch.sort returns).
+ * Replaces: the per-event `argsort` / `sort(stable=True)` pair of LSHOrdering.forward
+ * (models/baselines/hmamba.py:335-346) and the `argsort(dim=-1)` of HEPT bucketing
+ * (models/attention/hept.py:138-143).
+ *   keys: int32 or fp32 [n_total]; seg_offsets int64 [nseg+1] (device) or NULL for nseg equal
+ *   segments of n_total/nseg keys; init: optional starting order per segment (local indices) —
+ *   the result is init composed with the stable sort of keys[init], i.e. norm_idx[bk_idx].
+ */
+int lampa_segsort_stable(const void* keys, int32_t key_type, int64_t n_total,
+                         const int64_t* seg_offsets, int32_t nseg, const int64_t* init,
+                         int64_t* perm, void* ws, size_t ws_bytes, int32_t* status, void* stream);
+
+/*
+ * Row gather / scatter by a per-segment permutation.
+ * Replaces: points.gather (hmamba.py:348-351), sort_to_buckets / unsort_from_buckets /
+ * batched_index_select (models/attention/hept.py:9-19, hash_utils.py:83-93).
+ *   scatter == 0: dst[s0+i] = src[s0+perm[s0+i]];  scatter != 0: dst[s0+perm[s0+i]] = src[s0+i].
+ *   row_bytes must be a multiple of 4.
+ */
+int lampa_permute_rows(const void* src, const int64_t* perm, const int64_t* seg_offsets, int32_t nseg,
+                       int64_t n_rows, int64_t row_bytes, int32_t scatter, void* dst, void* stream);
+
+/* inv[s0 + perm[s0+i]] = i.  Replaces invert_permutation (hash_utils.py:46-57) and the
+ * `perm.argsort(dim=1)` used to undo the ordering (hmamba.py:451, full_mamba2.py:678). */
+int lampa_invert_perm(const int64_t* perm, const int64_t* seg_offsets, int32_t nseg, int64_t n_total,
+                      int64_t* inv, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LAMPA_B200_H */

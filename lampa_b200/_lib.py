@@ -1,0 +1,126 @@
+"""ctypes binding of liblampa_b200.so (see include/lampa_b200.h).
+
+There is no fallback: if the library is missing or no CUDA device is present the
+public ops raise.  torch is used only for device memory and streams.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from typing import Dict, Optional
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+SO_PATH = os.path.join(_HERE, "liblampa_b200.so")
+
+LAMPA_BF16, LAMPA_F16, LAMPA_F32 = 0, 1, 2
+LAMPA_KEY_I32, LAMPA_KEY_F32 = 0, 1
+ERR_TIMEOUT, ERR_LEVELS, ERR_BOUNDS = -5, -6, -7
+
+_DTYPES = {torch.bfloat16: LAMPA_BF16, torch.float16: LAMPA_F16, torch.float32: LAMPA_F32}
+
+
+class LampaError(RuntimeError):
+    pass
+
+
+class GdnDesc(ctypes.Structure):
+    _fields_ = [("B", ctypes.c_int32), ("T", ctypes.c_int32), ("H", ctypes.c_int32), ("K", ctypes.c_int32),
+                ("V", ctypes.c_int32), ("L", ctypes.c_int32), ("nseq", ctypes.c_int32),
+                ("qkv_dtype", ctypes.c_int32), ("gb_dtype", ctypes.c_int32), ("lam_dtype", ctypes.c_int32),
+                ("use_l2norm", ctypes.c_int32), ("scale", ctypes.c_float)]
+
+
+_lib: Optional[ctypes.CDLL] = None
+EXPORTS = ["lampa_version", "lampa_error_string", "lampa_gdn_workspace_bytes", "lampa_gdn_workspace_layout",
+           "lampa_gdn_fwd", "lampa_hgdn_fwd", "lampa_lsh_hash", "lampa_segsort_workspace_bytes",
+           "lampa_segsort_stable", "lampa_permute_rows", "lampa_invert_perm"]
+
+
+def lib() -> ctypes.CDLL:
+    """Load the CUDA library; raises LampaError when it has not been built."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(SO_PATH):
+            raise LampaError(f"{SO_PATH} is missing: build it with `python -m lampa_b200.build` "
+                             "(there is no CPU or PyTorch fallback)")
+        L = ctypes.CDLL(SO_PATH)
+        L.lampa_error_string.restype = ctypes.c_char_p
+        L.lampa_error_string.argtypes = [ctypes.c_int]
+        vp, i32, i64, sz = ctypes.c_void_p, ctypes.c_int32, ctypes.c_int64, ctypes.c_size_t
+        L.lampa_gdn_workspace_bytes.argtypes = [ctypes.POINTER(GdnDesc), ctypes.POINTER(sz)]
+        L.lampa_gdn_workspace_layout.argtypes = [ctypes.POINTER(GdnDesc), ctypes.POINTER(sz)]
+        L.lampa_gdn_fwd.argtypes = [ctypes.POINTER(GdnDesc)] + [vp] * 10 + [sz, vp, vp]
+        L.lampa_hgdn_fwd.argtypes = [ctypes.POINTER(GdnDesc)] + [vp] * 9 + [sz, vp, vp]
+        L.lampa_lsh_hash.argtypes = [vp, i64, i64, vp, vp, ctypes.c_float, i64, i32, i32, i32, vp, vp, vp, vp]
+        L.lampa_segsort_workspace_bytes.argtypes = [i64, ctypes.POINTER(sz)]
+        L.lampa_segsort_stable.argtypes = [vp, i32, i64, vp, i32, vp, vp, vp, sz, vp, vp]
+        L.lampa_permute_rows.argtypes = [vp, vp, vp, i32, i64, i64, i32, vp, vp]
+        L.lampa_invert_perm.argtypes = [vp, vp, i32, i64, vp, vp]
+        for name in EXPORTS:
+            if name != "lampa_error_string":
+                getattr(L, name).restype = ctypes.c_int
+        _lib = L
+    return _lib
+
+
+def check(rc: int, what: str) -> None:
+    if rc != 0:
+        raise LampaError(f"{what}: {lib().lampa_error_string(rc).decode()} ({rc})")
+
+
+def dtype_code(dt: torch.dtype) -> int:
+    try:
+        return _DTYPES[dt]
+    except KeyError:
+        raise TypeError(f"unsupported dtype {dt}") from None
+
+
+def require_cuda(*tensors: torch.Tensor) -> torch.device:
+    dev = None
+    for t in tensors:
+        if t is None:
+            continue
+        if not t.is_cuda:
+            raise LampaError("lampa_b200 ops run on CUDA tensors only (no CPU path)")
+        if dev is not None and t.device != dev:
+            raise LampaError("all tensors must be on the same device")
+        dev = t.device
+    return dev
+
+
+def ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def stream_ptr(dev: torch.device) -> int:
+    return torch.cuda.current_stream(dev).cuda_stream
+
+
+_status: Dict[int, torch.Tensor] = {}
+
+
+def status_word(dev: torch.device) -> torch.Tensor:
+    """Device int32[4] the kernels report into (code, where, detail, -)."""
+    idx = dev.index if dev.index is not None else torch.cuda.current_device()
+    if idx not in _status:
+        _status[idx] = torch.zeros(4, dtype=torch.int32, device=dev)
+    return _status[idx]
+
+
+def check_status(dev: Optional[torch.device] = None) -> None:
+    """Synchronise and raise if a kernel reported a device-side error since the last check."""
+    devs = list(_status) if dev is None else [dev.index if dev.index is not None else torch.cuda.current_device()]
+    for idx in devs:
+        if idx not in _status:
+            continue
+        vals = _status[idx].tolist()
+        if vals[0] != 0:
+            _status[idx].zero_()
+            raise LampaError(f"device-side error: {lib().lampa_error_string(vals[0]).decode()} "
+                             f"(code {vals[0]}, where {vals[1]}, detail {vals[2]})")
+
+
+def debug_checks() -> bool:
+    return os.environ.get("LAMPA_B200_CHECK", "0") not in ("", "0")

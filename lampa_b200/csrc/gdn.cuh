@@ -1,0 +1,77 @@
+// Layout of the per-chunk and per-block intermediates of the gated-delta forward, and the
+// launchers shared between translation units.
+//
+// Algebra (per sequence and head, chunk length 64, G = inclusive cumsum of g inside the chunk,
+// E_ij = exp(G_i - G_j) for i >= j):
+//   Aw = (I + tril(diag(beta) K K^T, -1))^-1          W~ = diag(e^G) Aw diag(beta) K
+//   U  = (Aw .* E) diag(beta) V                        K~ = diag(e^{G_last - G}) K
+//   M  = e^{G_last} I - K~^T W~     B = K~^T U         Q~ = diag(e^G) Q - (tril(Q K^T) .* E) W~
+// so that one chunk acts on the running state as  S <- M S + B  and reads it as  Q~ S.
+// The prep kernel writes one record {M, B^T, Q~, O_local, lambda} per (chunk, head); the scan
+// kernels only ever multiply by those.
+#pragma once
+#include "common.cuh"
+
+namespace lampa {
+
+constexpr int BLOCK_CHUNKS = 32;     // chunks per block of the block-parallel scan
+constexpr int BLOCK_LOG = 5;         // log2(BLOCK_CHUNKS): chunk levels 0..4 live inside a block
+constexpr int NLW = 5;               // level states carried per warp in the hierarchical output pass
+constexpr int MAX_GROUPS = 3;        // 1 group of in-block levels + up to 2 groups of cross-block levels
+
+template <int KD, int VD>
+struct Rec {
+    static constexpr int KP = KD + 8;                 // bf16 row pitch (elements) of K-wide tiles
+    static constexpr int OP = VD + 8;                 // fp32 row pitch (elements) of O_local
+    static constexpr int M_OFF = 0;
+    static constexpr int M_BYTES = KD * KP * 2;       // M[k_out][k_in]
+    static constexpr int BT_OFF = M_OFF + M_BYTES;
+    static constexpr int BT_BYTES = VD * KP * 2;      // B^T[v][k]
+    static constexpr int QT_OFF = BT_OFF + BT_BYTES;
+    static constexpr int QT_BYTES = CHUNK * KP * 2;   // Q~[token][k]
+    static constexpr int OL_OFF = QT_OFF + QT_BYTES;
+    static constexpr int OL_BYTES = CHUNK * OP * 4;   // O_local[token][v]
+    static constexpr int LAM_OFF = OL_OFF + OL_BYTES; // lambda of chunk levels: [LC][64] fp32
+    static constexpr int MB_BYTES = M_BYTES + BT_BYTES;
+    __host__ __device__ static constexpr int bytes(int LC) { return LAM_OFF + LC * CHUNK * 4; }
+    // block composite: Mblk[k_out][k_in] bf16, then Bblk^T[v][k] fp32 (pitch KD + 8)
+    static constexpr int BP = KD + 8;
+    static constexpr int BLK_M_OFF = 0;
+    static constexpr int BLK_B_OFF = M_BYTES;
+    static constexpr int BLK_BYTES = M_BYTES + VD * BP * 4;
+    static constexpr int STATE_FLOATS = VD * KD;      // an S^T[v][k] fp32 state
+};
+
+struct GdnArgs {
+    const void* q; const void* k; const void* v; const void* g; const void* beta; const void* lam;
+    const float* h0; float* ht; void* o;
+    int qkv_dt, gb_dt, lam_dt;
+    int H, L, LC;
+    int use_l2norm;
+    float scale;
+    int nseq;
+    int nc_max, nb_max, nhigh_max;
+    const int64_t* tok_off; const int32_t* chunk_off; const int32_t* block_off;
+    char* rec; size_t rec_bytes;          // per (chunk, head) records
+    char* blk;                            // per (block, head) composites
+    float* entry;                         // entry states: plain [nb][H][V][K]; hier [nb][nhigh][H][V][K]
+    int32_t* status;
+};
+
+struct PlanArgs {
+    const int64_t* cu; int nseq; int B; int T; int L; int hier;
+    int64_t* tok_off; int32_t* chunk_off; int32_t* block_off; int32_t* status;
+};
+
+int launch_plan(const PlanArgs& p, cudaStream_t st);
+template <int KD, int VD> int launch_prep(const GdnArgs& a, bool hier, cudaStream_t st);
+template <int KD, int VD> int launch_scan_plain(const GdnArgs& a, cudaStream_t st);
+template <int KD, int VD> int launch_scan_hier(const GdnArgs& a, cudaStream_t st);
+
+__host__ __device__ inline int ceil_log2_int(int x) {   // smallest e with 2^e >= x (x >= 1)
+    int e = 0;
+    while ((1 << e) < x) ++e;
+    return e;
+}
+
+}  // namespace lampa

@@ -1,0 +1,447 @@
+// Per-chunk preparation of the gated-delta forward: one CTA of 4 warps per (chunk, head) turns
+// 64 tokens of q, k, v, g, beta (and lambda) into the record {M, B^T, Q~, O_local, lambda_chunk}.
+// Dense 64-wide contractions run on tensor cores (bf16 operands, fp32 accumulation); the
+// 64x64 unit-lower-triangular inverse is an fp32 substitution on CUDA cores, as in the reference
+// (models/hattention/solve_tril.py:54-61, 175-197), because bf16 there is where parity breaks.
+#include "gdn.cuh"
+
+namespace lampa {
+
+// ---- plan: token / chunk / block offsets per sequence -------------------------------------------
+__global__ void plan_kernel(PlanArgs p) {
+    if (threadIdx.x != 0 || blockIdx.x != 0) return;
+    int32_t c = 0, b = 0;
+    p.chunk_off[0] = 0;
+    p.block_off[0] = 0;
+    for (int s = 0; s < p.nseq; ++s) {
+        const int64_t t0 = p.cu ? p.cu[s] : (int64_t)s * p.T;
+        const int64_t t1 = p.cu ? p.cu[s + 1] : (int64_t)(s + 1) * p.T;
+        p.tok_off[s] = t0;
+        int64_t len = t1 - t0;
+        if (len < 0 || t1 > (int64_t)p.B * p.T) { set_status(p.status, LAMPA_ERR_BOUNDS, 1, s); len = 0; }
+        const int nch = (int)((len + CHUNK - 1) / CHUNK);
+        if (p.hier && nch > 0 && ELL0 + ceil_log2_int(nch) > p.L) set_status(p.status, LAMPA_ERR_LEVELS, 1, s);
+        c += nch;
+        b += (nch + BLOCK_CHUNKS - 1) / BLOCK_CHUNKS;
+        p.chunk_off[s + 1] = c;
+        p.block_off[s + 1] = b;
+        if (s == p.nseq - 1) p.tok_off[s + 1] = t0 + len;
+    }
+}
+
+int launch_plan(const PlanArgs& p, cudaStream_t st) {
+    plan_kernel<<<1, 32, 0, st>>>(p);
+    return cudaGetLastError() == cudaSuccess ? LAMPA_OK : LAMPA_ERR_CUDA;
+}
+
+// ---- shared-memory carve-up ---------------------------------------------------------------------
+template <int KD, int VD>
+struct PrepSmem {
+    static constexpr int KP = KD + 8, VP = VD + 8, CP = CHUNK + 8;
+    static constexpr int Q = 0;                                  // bf16 [64][KP]   q (normalised)
+    static constexpr int K = Q + CHUNK * KP * 2;                 // bf16 [64][KP]   k, later K~
+    static constexpr int KB = K + CHUNK * KP * 2;                // bf16 [64][KP]   beta*k
+    static constexpr int VB = KB + CHUNK * KP * 2;               // bf16 [64][VP]   beta*v
+    static constexpr int AT = VB + CHUNK * VP * 2;               // fp32 [64][72]   A0^T; later Aw|Au bf16 [64][CP] each
+    static constexpr int AW = AT;
+    static constexpr int AU = AT + CHUNK * CP * 2;
+    static constexpr int P = AT + CHUNK * CP * 4;                // bf16 [64][CP]   tril(QK^T) .* E
+    static constexpr int QK = P + CHUNK * CP * 2;                // bf16 [64][CP]   tril(QK^T) raw; later Pm (hier)
+    static constexpr int WT = QK + CHUNK * CP * 2;               // bf16 [64][KP]   W~
+    static constexpr int U = WT + CHUNK * KP * 2;                // bf16 [64][VP]   U
+    static constexpr int G = U + CHUNK * VP * 2;                 // fp32 [64] G, [64] beta, [64] e^G, [64] e^{Glast-G}
+    static constexpr int LAM = G + 4 * CHUNK * 4;                // fp32 [64][L+1]
+    static int bytes(int L) { return LAM + CHUNK * (L + 1) * 4; }
+};
+
+// Each of the 128 threads loads half a row (D/2 elements) of a [64][D] tile as floats.
+template <int D>
+__device__ __forceinline__ void load_half_row(const void* base, int dt, size_t elem_off, bool valid, float (&x)[D / 2]) {
+    constexpr int NE = D / 2;
+    if (!valid) {
+#pragma unroll
+        for (int i = 0; i < NE; ++i) x[i] = 0.f;
+        return;
+    }
+    if (dt == LAMPA_F32) {
+        const float4* p = reinterpret_cast<const float4*>((const float*)base + elem_off);
+#pragma unroll
+        for (int i = 0; i < NE / 4; ++i) {
+            const float4 f = __ldg(p + i);
+            x[4 * i] = f.x; x[4 * i + 1] = f.y; x[4 * i + 2] = f.z; x[4 * i + 3] = f.w;
+        }
+    } else {
+        const uint4* p = reinterpret_cast<const uint4*>((const uint16_t*)base + elem_off);
+#pragma unroll
+        for (int i = 0; i < NE / 8; ++i) {
+            const uint4 u = __ldg(p + i);
+            const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                float2 f;
+                if (dt == LAMPA_BF16) f = unpack_bf16x2(w[j]);
+                else f = __half22float2(*reinterpret_cast<const __half2*>(&w[j]));
+                x[8 * i + 2 * j] = f.x; x[8 * i + 2 * j + 1] = f.y;
+            }
+        }
+    }
+}
+
+template <int NE>
+__device__ __forceinline__ void store_half_row_bf16(__nv_bfloat16* dst, const float (&x)[NE]) {
+#pragma unroll
+    for (int i = 0; i < NE / 8; ++i) {
+        uint4 u;
+        u.x = pack_bf16x2(x[8 * i], x[8 * i + 1]);
+        u.y = pack_bf16x2(x[8 * i + 2], x[8 * i + 3]);
+        u.z = pack_bf16x2(x[8 * i + 4], x[8 * i + 5]);
+        u.w = pack_bf16x2(x[8 * i + 6], x[8 * i + 7]);
+        reinterpret_cast<uint4*>(dst)[i] = u;
+    }
+}
+
+__device__ __forceinline__ float bf16_round(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+
+template <int KD, int VD, bool HIER>
+__global__ void __launch_bounds__(128) gdn_prep_kernel(GdnArgs a) {
+    using S = PrepSmem<KD, VD>;
+    using R = Rec<KD, VD>;
+    constexpr int KP = S::KP, VP = S::VP, CP = S::CP;
+    extern __shared__ __align__(128) unsigned char smem[];
+    __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(smem + S::Q);
+    __nv_bfloat16* sK = reinterpret_cast<__nv_bfloat16*>(smem + S::K);
+    __nv_bfloat16* sKb = reinterpret_cast<__nv_bfloat16*>(smem + S::KB);
+    __nv_bfloat16* sVb = reinterpret_cast<__nv_bfloat16*>(smem + S::VB);
+    float* sAT = reinterpret_cast<float*>(smem + S::AT);
+    __nv_bfloat16* sAw = reinterpret_cast<__nv_bfloat16*>(smem + S::AW);
+    __nv_bfloat16* sAu = reinterpret_cast<__nv_bfloat16*>(smem + S::AU);
+    __nv_bfloat16* sP = reinterpret_cast<__nv_bfloat16*>(smem + S::P);
+    __nv_bfloat16* sQK = reinterpret_cast<__nv_bfloat16*>(smem + S::QK);
+    __nv_bfloat16* sWt = reinterpret_cast<__nv_bfloat16*>(smem + S::WT);
+    __nv_bfloat16* sU = reinterpret_cast<__nv_bfloat16*>(smem + S::U);
+    float* sG = reinterpret_cast<float*>(smem + S::G);
+    float* sBeta = sG + CHUNK;
+    float* sEG = sG + 2 * CHUNK;
+    float* sEGl = sG + 3 * CHUNK;
+    float* sLam = reinterpret_cast<float*>(smem + S::LAM);
+
+    const int c = blockIdx.x, h = blockIdx.y, H = a.H;
+    if (c >= a.chunk_off[a.nseq]) return;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int gq = lane >> 2, tq = lane & 3;
+    const int seq = find_seq(a.chunk_off, a.nseq, c);
+    const int64_t t0 = a.tok_off[seq] + (int64_t)(c - a.chunk_off[seq]) * CHUNK;
+    const int len = (int)min((int64_t)CHUNK, a.tok_off[seq + 1] - t0);
+    const int LP = a.L + 1;
+
+    // ---- stage 0: loads, l2norm, beta scaling, cumulative decay -------------------------------
+    {
+        const int r = tid >> 1, half = tid & 1;
+        const bool valid = r < len;
+        const size_t tok = (size_t)(t0 + r);
+        float bet = 0.f;
+        if (valid) bet = load_as_float(a.beta, tok * H + h, a.gb_dt);
+        float x[KD / 2];
+        // q
+        load_half_row<KD>(a.q, a.qkv_dt, (tok * H + h) * KD + half * (KD / 2), valid, x);
+        if (a.use_l2norm) {
+            float ss = 0.f;
+#pragma unroll
+            for (int i = 0; i < KD / 2; ++i) ss += x[i] * x[i];
+            ss += __shfl_xor_sync(0xffffffffu, ss, 1);
+            const float rn = rsqrtf(ss + 1e-6f);
+#pragma unroll
+            for (int i = 0; i < KD / 2; ++i) x[i] *= rn;
+        }
+        store_half_row_bf16<KD / 2>(sQ + r * KP + half * (KD / 2), x);
+        // k and beta*k (beta applied to the rounded k, as chunk_scaled_dot_kkt.py:60-61 does)
+        load_half_row<KD>(a.k, a.qkv_dt, (tok * H + h) * KD + half * (KD / 2), valid, x);
+        if (a.use_l2norm) {
+            float ss = 0.f;
+#pragma unroll
+            for (int i = 0; i < KD / 2; ++i) ss += x[i] * x[i];
+            ss += __shfl_xor_sync(0xffffffffu, ss, 1);
+            const float rn = rsqrtf(ss + 1e-6f);
+#pragma unroll
+            for (int i = 0; i < KD / 2; ++i) x[i] *= rn;
+        }
+        store_half_row_bf16<KD / 2>(sK + r * KP + half * (KD / 2), x);
+#pragma unroll
+        for (int i = 0; i < KD / 2; ++i) x[i] = bf16_round(x[i]) * bet;
+        store_half_row_bf16<KD / 2>(sKb + r * KP + half * (KD / 2), x);
+        // beta*v
+        float y[VD / 2];
+        load_half_row<VD>(a.v, a.qkv_dt, (tok * H + h) * VD + half * (VD / 2), valid, y);
+#pragma unroll
+        for (int i = 0; i < VD / 2; ++i) y[i] *= bet;
+        store_half_row_bf16<VD / 2>(sVb + r * VP + half * (VD / 2), y);
+    }
+    if (tid < CHUNK) {
+        const bool valid = tid < len;
+        float gv = 0.f, bv = 0.f;
+        if (valid) {
+            gv = load_as_float(a.g, (size_t)(t0 + tid) * H + h, a.gb_dt);
+            bv = load_as_float(a.beta, (size_t)(t0 + tid) * H + h, a.gb_dt);
+        }
+        float cs = gv;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const float y = __shfl_up_sync(0xffffffffu, cs, o);
+            if (lane >= o) cs += y;
+        }
+        if (tid == 31) sG[CHUNK - 1] = cs;      // borrowed as a one-float mailbox between the two warps
+        sBeta[tid] = bv;
+        asm volatile("bar.sync 1, 64;\n" ::: "memory");
+        const float carry = (warp == 1) ? sG[CHUNK - 1] : 0.f;
+        asm volatile("bar.sync 1, 64;\n" ::: "memory");
+        sG[tid] = cs + carry;
+    }
+    if (HIER) {
+        for (int idx = tid; idx < CHUNK * a.L; idx += 128) {
+            const int r = idx / a.L, l = idx - r * a.L;
+            float lv = 0.f;
+            if (r < len) lv = load_as_float(a.lam, ((size_t)(t0 + r) * H + h) * a.L + l, a.lam_dt);
+            sLam[r * LP + l] = lv;
+        }
+    }
+    __syncthreads();
+    if (tid < CHUNK) {
+        const float Gi = sG[tid], Gl = sG[CHUNK - 1];
+        sEG[tid] = __expf(Gi);
+        sEGl[tid] = __expf(Gl - Gi);
+    }
+    char* rec = a.rec + ((size_t)c * H + h) * a.rec_bytes;
+    if (HIER) {   // lambda of the chunk levels, transposed to [level][token] for the scan
+        float* lamc = reinterpret_cast<float*>(rec + R::LAM_OFF);
+        for (int idx = tid; idx < a.LC * CHUNK; idx += 128) {
+            const int l = idx >> 6, r = idx & 63;
+            lamc[idx] = (ELL0 + l < a.L) ? sLam[r * LP + ELL0 + l] : 0.f;
+        }
+    }
+
+    const int m0 = warp * 16;
+    // ---- stage 1: K K^T -> A0^T (fp32), Q K^T -> P = tril .* E and the raw tril -----------------
+    {
+        float acc[8][4];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) { acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f; }
+        warp_gemm<8, KD, false, false>(acc, sK, KP, m0, sK, KP, 0, lane, KD, m0 + 16);
+#pragma unroll
+        for (int nt = 0; nt < 8; ++nt) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int i = m0 + gq + (e >> 1) * 8, j = nt * 8 + 2 * tq + (e & 1);
+                if (nt * 8 < m0 + 16) sAT[j * CP + i] = (i > j) ? sBeta[i] * acc[nt][e] : 0.f;
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) { acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f; }
+        warp_gemm<8, KD, false, false>(acc, sQ, KP, m0, sK, KP, 0, lane, KD, m0 + 16);
+#pragma unroll
+        for (int nt = 0; nt < 8; ++nt) {
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh) {
+                const int i = m0 + gq + hh * 8, j = nt * 8 + 2 * tq;
+                const float Gi = sG[i];
+                float p0 = 0.f, p1 = 0.f, r0 = 0.f, r1 = 0.f;
+                if (i >= j) { r0 = acc[nt][2 * hh]; p0 = r0 * __expf(Gi - sG[j]); }
+                if (i >= j + 1) { r1 = acc[nt][2 * hh + 1]; p1 = r1 * __expf(Gi - sG[j + 1]); }
+                *reinterpret_cast<uint32_t*>(sP + i * CP + j) = pack_bf16x2(p0, p1);
+                if (HIER) *reinterpret_cast<uint32_t*>(sQK + i * CP + j) = pack_bf16x2(r0, r1);
+            }
+        }
+    }
+    __syncthreads();
+
+    // ---- stage 2: Aw = (I + A0)^-1 by column (threads 0..63); K~ in place (threads 64..127) -----
+    if (tid < CHUNK) {
+        const int col = tid;
+        float r[CHUNK];
+#pragma unroll
+        for (int i = 0; i < CHUNK; ++i) r[i] = (i == col) ? 1.f : 0.f;
+#pragma unroll
+        for (int j = 0; j < CHUNK - 1; ++j) {
+            const float rj = r[j];
+#pragma unroll
+            for (int i4 = ((j + 1) / 4) * 4; i4 < CHUNK; i4 += 4) {
+                const float4 av = *reinterpret_cast<const float4*>(sAT + j * CP + i4);
+                if (i4 + 0 > j) r[i4 + 0] -= av.x * rj;
+                if (i4 + 1 > j) r[i4 + 1] -= av.y * rj;
+                if (i4 + 2 > j) r[i4 + 2] -= av.z * rj;
+                if (i4 + 3 > j) r[i4 + 3] -= av.w * rj;
+            }
+        }
+        asm volatile("bar.sync 1, 64;\n" ::: "memory");   // all columns done reading A0^T before it is overwritten
+        const float Gc = sG[col];
+#pragma unroll
+        for (int i = 0; i < CHUNK; ++i) {
+            sAw[i * CP + col] = __float2bfloat16_rn(r[i]);
+            const float e = (i >= col) ? r[i] * __expf(sG[i] - Gc) : 0.f;
+            sAu[i * CP + col] = __float2bfloat16_rn(e);
+        }
+    } else {
+        const int r = tid - CHUNK;
+        const float f = sEGl[r];
+#pragma unroll
+        for (int d = 0; d < KD; d += 2) {
+            uint32_t* p = reinterpret_cast<uint32_t*>(sK + r * KP + d);
+            const float2 kv = unpack_bf16x2(*p);
+            *p = pack_bf16x2(kv.x * f, kv.y * f);
+        }
+    }
+    __syncthreads();
+
+    // ---- stage 3: W~ = diag(e^G) Aw (beta K),  U = Au (beta V) ----------------------------------
+    {
+        float acc[KD / 8][4];
+#pragma unroll
+        for (int i = 0; i < KD / 8; ++i) { acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f; }
+        warp_gemm<KD / 8, CHUNK, false, true>(acc, sAw, CP, m0, sKb, KP, 0, lane, m0 + 16, KD);
+#pragma unroll
+        for (int nt = 0; nt < KD / 8; ++nt)
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh) {
+                const int i = m0 + gq + hh * 8, j = nt * 8 + 2 * tq;
+                const float f = sEG[i];
+                *reinterpret_cast<uint32_t*>(sWt + i * KP + j) = pack_bf16x2(acc[nt][2 * hh] * f, acc[nt][2 * hh + 1] * f);
+            }
+    }
+    {
+        float acc[VD / 8][4];
+#pragma unroll
+        for (int i = 0; i < VD / 8; ++i) { acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f; }
+        warp_gemm<VD / 8, CHUNK, false, true>(acc, sAu, CP, m0, sVb, VP, 0, lane, m0 + 16, VD);
+#pragma unroll
+        for (int nt = 0; nt < VD / 8; ++nt)
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh) {
+                const int i = m0 + gq + hh * 8, j = nt * 8 + 2 * tq;
+                *reinterpret_cast<uint32_t*>(sU + i * VP + j) = pack_bf16x2(acc[nt][2 * hh], acc[nt][2 * hh + 1]);
+            }
+    }
+    __syncthreads();
+
+    // ---- stage 4: the record ---------------------------------------------------------------------
+    // M[a][b] = e^{G_last} delta_ab - sum_tok K~[tok][a] W~[tok][b]
+    if (m0 < KD) {
+        float acc[KD / 8][4];
+#pragma unroll
+        for (int i = 0; i < KD / 8; ++i) { acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f; }
+        warp_gemm<KD / 8, CHUNK, true, true>(acc, sK, KP, m0, sWt, KP, 0, lane, CHUNK, KD);
+        const float egl = sEG[CHUNK - 1];
+        __nv_bfloat16* gM = reinterpret_cast<__nv_bfloat16*>(rec + R::M_OFF);
+#pragma unroll
+        for (int nt = 0; nt < KD / 8; ++nt)
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh) {
+                const int i = m0 + gq + hh * 8, j = nt * 8 + 2 * tq;
+                const float m_0 = ((i == j) ? egl : 0.f) - acc[nt][2 * hh];
+                const float m_1 = ((i == j + 1) ? egl : 0.f) - acc[nt][2 * hh + 1];
+                *reinterpret_cast<uint32_t*>(gM + i * KP + j) = pack_bf16x2(m_0, m_1);
+            }
+    }
+    // B^T[v][a] = sum_tok U[tok][v] K~[tok][a]
+    if (m0 < VD) {
+        float acc[KD / 8][4];
+#pragma unroll
+        for (int i = 0; i < KD / 8; ++i) { acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f; }
+        warp_gemm<KD / 8, CHUNK, true, true>(acc, sU, VP, m0, sK, KP, 0, lane, CHUNK, KD);
+        __nv_bfloat16* gB = reinterpret_cast<__nv_bfloat16*>(rec + R::BT_OFF);
+#pragma unroll
+        for (int nt = 0; nt < KD / 8; ++nt)
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh) {
+                const int i = m0 + gq + hh * 8, j = nt * 8 + 2 * tq;
+                *reinterpret_cast<uint32_t*>(gB + i * KP + j) = pack_bf16x2(acc[nt][2 * hh], acc[nt][2 * hh + 1]);
+            }
+    }
+    // Q~[i][d] = s * (e^{G_i} Q[i][d] - sum_j P[i][j] W~[j][d]);  s = scale (plain) or 1 (hierarchical)
+    const float osc = HIER ? 1.f : a.scale;
+    {
+        float acc[KD / 8][4];
+#pragma unroll
+        for (int i = 0; i < KD / 8; ++i) { acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f; }
+        warp_gemm<KD / 8, CHUNK, false, true>(acc, sP, CP, m0, sWt, KP, 0, lane, m0 + 16, KD);
+        __nv_bfloat16* gQ = reinterpret_cast<__nv_bfloat16*>(rec + R::QT_OFF);
+#pragma unroll
+        for (int nt = 0; nt < KD / 8; ++nt)
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh) {
+                const int i = m0 + gq + hh * 8, j = nt * 8 + 2 * tq;
+                const float f = sEG[i];
+                const float2 qv = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(sQ + i * KP + j));
+                *reinterpret_cast<uint32_t*>(gQ + i * KP + j) =
+                    pack_bf16x2(osc * (f * qv.x - acc[nt][2 * hh]), osc * (f * qv.y - acc[nt][2 * hh + 1]));
+            }
+    }
+    // O_local
+    float* gO = reinterpret_cast<float*>(rec + R::OL_OFF);
+    if (HIER) {
+        // Pm = (tril(QK^T) Aw) .* E .* lambda[i][level(i,j)],  O_local = Pm (beta V)
+        float acc[8][4];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) { acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f; }
+        warp_gemm<8, CHUNK, false, true>(acc, sQK, CP, m0, sAw, CP, 0, lane, m0 + 16, m0 + 16);
+        __syncwarp();
+#pragma unroll
+        for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh) {
+                const int i = m0 + gq + hh * 8, j = nt * 8 + 2 * tq;
+                const float Gi = sG[i];
+                float p0 = 0.f, p1 = 0.f;
+                if (i >= j) p0 = acc[nt][2 * hh] * __expf(Gi - sG[j]) * sLam[i * LP + (32 - __clz(i ^ j))];
+                if (i >= j + 1) p1 = acc[nt][2 * hh + 1] * __expf(Gi - sG[j + 1]) * sLam[i * LP + (32 - __clz(i ^ (j + 1)))];
+                *reinterpret_cast<uint32_t*>(sQK + i * CP + j) = pack_bf16x2(p0, p1);
+            }
+        __syncwarp();
+        float acc2[VD / 8][4];
+#pragma unroll
+        for (int i = 0; i < VD / 8; ++i) { acc2[i][0] = acc2[i][1] = acc2[i][2] = acc2[i][3] = 0.f; }
+        warp_gemm<VD / 8, CHUNK, false, true>(acc2, sQK, CP, m0, sVb, VP, 0, lane, m0 + 16, VD);
+#pragma unroll
+        for (int nt = 0; nt < VD / 8; ++nt)
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh) {
+                const int i = m0 + gq + hh * 8, j = nt * 8 + 2 * tq;
+                *reinterpret_cast<float2*>(gO + i * R::OP + j) = make_float2(acc2[nt][2 * hh], acc2[nt][2 * hh + 1]);
+            }
+    } else {
+        float acc2[VD / 8][4];
+#pragma unroll
+        for (int i = 0; i < VD / 8; ++i) { acc2[i][0] = acc2[i][1] = acc2[i][2] = acc2[i][3] = 0.f; }
+        warp_gemm<VD / 8, CHUNK, false, true>(acc2, sP, CP, m0, sU, VP, 0, lane, m0 + 16, VD);
+#pragma unroll
+        for (int nt = 0; nt < VD / 8; ++nt)
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh) {
+                const int i = m0 + gq + hh * 8, j = nt * 8 + 2 * tq;
+                *reinterpret_cast<float2*>(gO + i * R::OP + j) =
+                    make_float2(osc * acc2[nt][2 * hh], osc * acc2[nt][2 * hh + 1]);
+            }
+    }
+}
+
+template <int KD, int VD>
+int launch_prep(const GdnArgs& a, bool hier, cudaStream_t st) {
+    using S = PrepSmem<KD, VD>;
+    const int smem = S::bytes(hier ? a.L : 0);
+    dim3 grid(a.nc_max, a.H);
+    cudaError_t e;
+    if (hier) {
+        e = cudaFuncSetAttribute(gdn_prep_kernel<KD, VD, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return LAMPA_ERR_CUDA;
+        gdn_prep_kernel<KD, VD, true><<<grid, 128, smem, st>>>(a);
+    } else {
+        e = cudaFuncSetAttribute(gdn_prep_kernel<KD, VD, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return LAMPA_ERR_CUDA;
+        gdn_prep_kernel<KD, VD, false><<<grid, 128, smem, st>>>(a);
+    }
+    return cudaGetLastError() == cudaSuccess ? LAMPA_OK : LAMPA_ERR_CUDA;
+}
+
+template int launch_prep<64, 64>(const GdnArgs&, bool, cudaStream_t);
+template int launch_prep<32, 32>(const GdnArgs&, bool, cudaStream_t);
+template int launch_prep<16, 32>(const GdnArgs&, bool, cudaStream_t);
+
+}  // namespace lampa

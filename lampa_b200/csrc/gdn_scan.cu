@@ -1,0 +1,613 @@
+// Block-parallel scan of the gated-delta forward over the per-chunk records {M, B^T, Q~, O_local}.
+//
+// One chunk acts on a state as S <- M S + B and reads it as Q~ S, so a block of 32 chunks acts as
+// S <- Mblk S + Bblk.  Three passes replace the reference's single sequential scan over all chunks
+// (models/hattention/chunk_delta_h.py:35-189) and its one-scan-per-level loop
+// (models/hattention/chunkwise_hgdn.py:723-789):
+//   compose : per (block, head)  run [S | P] from [0 | I] through the block -> (Mblk, Bblk)
+//   level   : per (sequence, head[, level])  scan the block composites -> state entering each block
+//   output  : per (block, head)  re-run the block from its entry state(s) and emit the outputs
+// Everything a warp owns is a 16-row slab of S^T kept in mma accumulator registers; the slab is
+// re-used as the A operand (S^T M^T) and as the B operand (Q~ S) without leaving registers, so
+// slabs never synchronise with each other.  Records stream through shared memory by bulk async
+// copies (cp.async.bulk + mbarrier), a few chunks ahead of the math.
+#include "gdn.cuh"
+
+namespace lampa {
+
+template <int KD>
+__device__ __forceinline__ void zero_state(float (&C)[KD / 8][4]) {
+#pragma unroll
+    for (int i = 0; i < KD / 8; ++i) { C[i][0] = C[i][1] = C[i][2] = C[i][3] = 0.f; }
+}
+
+// bf16 fragments of a 16 x KD slab held as mma accumulators; sp[kk] is at once the A fragment of
+// k-step kk and, pairwise, the B fragments (sp[kk][0], sp[kk][2]) / (sp[kk][1], sp[kk][3]) of the
+// slab's two 8-column halves when the slab is read as S[k][v].
+template <int KD>
+__device__ __forceinline__ void pack_state(const float (&C)[KD / 8][4], uint32_t (&sp)[KD / 16][4]) {
+#pragma unroll
+    for (int kk = 0; kk < KD / 16; ++kk) {
+        sp[kk][0] = pack_bf16x2(C[2 * kk][0], C[2 * kk][1]);
+        sp[kk][1] = pack_bf16x2(C[2 * kk][2], C[2 * kk][3]);
+        sp[kk][2] = pack_bf16x2(C[2 * kk + 1][0], C[2 * kk + 1][1]);
+        sp[kk][3] = pack_bf16x2(C[2 * kk + 1][2], C[2 * kk + 1][3]);
+    }
+}
+
+// C += slab * M^T, with sM[k_out][k_in] row-major (pitch KD + 8)
+template <int KD>
+__device__ __forceinline__ void state_times_mt(float (&C)[KD / 8][4], const uint32_t (&sp)[KD / 16][4],
+                                               const __nv_bfloat16* sM, int lane) {
+#pragma unroll
+    for (int kk = 0; kk < KD / 16; ++kk) {
+#pragma unroll
+        for (int nt = 0; nt < KD / 8; nt += 2) {
+            uint32_t b[4];
+            load_b(b, sM, KD + 8, nt * 8, kk * 16, lane);
+            mma16816(C[nt], sp[kk], b[0], b[1]);
+            mma16816(C[nt + 1], sp[kk], b[2], b[3]);
+        }
+    }
+}
+
+// C = rows row0+g, row0+g+8 of a bf16 [rows][KD + 8] tile
+template <int KD>
+__device__ __forceinline__ void load_slab_bf16(float (&C)[KD / 8][4], const __nv_bfloat16* s, int row0, int lane) {
+    const int g = lane >> 2, t = lane & 3;
+#pragma unroll
+    for (int nt = 0; nt < KD / 8; ++nt) {
+        const float2 lo = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(s + (row0 + g) * (KD + 8) + nt * 8 + 2 * t));
+        const float2 hi = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(s + (row0 + g + 8) * (KD + 8) + nt * 8 + 2 * t));
+        C[nt][0] = lo.x; C[nt][1] = lo.y; C[nt][2] = hi.x; C[nt][3] = hi.y;
+    }
+}
+// same from / to an fp32 [rows][pitch] tile (shared or global)
+template <int KD>
+__device__ __forceinline__ void load_slab_f32(float (&C)[KD / 8][4], const float* s, int pitch, int row0, int lane) {
+    const int g = lane >> 2, t = lane & 3;
+#pragma unroll
+    for (int nt = 0; nt < KD / 8; ++nt) {
+        const float2 lo = *reinterpret_cast<const float2*>(s + (size_t)(row0 + g) * pitch + nt * 8 + 2 * t);
+        const float2 hi = *reinterpret_cast<const float2*>(s + (size_t)(row0 + g + 8) * pitch + nt * 8 + 2 * t);
+        C[nt][0] = lo.x; C[nt][1] = lo.y; C[nt][2] = hi.x; C[nt][3] = hi.y;
+    }
+}
+template <int KD>
+__device__ __forceinline__ void store_slab_f32(const float (&C)[KD / 8][4], float* s, int pitch, int row0, int lane) {
+    const int g = lane >> 2, t = lane & 3;
+#pragma unroll
+    for (int nt = 0; nt < KD / 8; ++nt) {
+        *reinterpret_cast<float2*>(s + (size_t)(row0 + g) * pitch + nt * 8 + 2 * t) = make_float2(C[nt][0], C[nt][1]);
+        *reinterpret_cast<float2*>(s + (size_t)(row0 + g + 8) * pitch + nt * 8 + 2 * t) = make_float2(C[nt][2], C[nt][3]);
+    }
+}
+
+// tmp (16 tokens x 16 state columns of this slab) = Q~[16*mt .. +16, :] * S
+template <int KD>
+__device__ __forceinline__ void read_tile(float (&tmp)[2][4], const uint32_t (&sp)[KD / 16][4],
+                                          const __nv_bfloat16* sQt, int mt, int lane) {
+    tmp[0][0] = tmp[0][1] = tmp[0][2] = tmp[0][3] = 0.f;
+    tmp[1][0] = tmp[1][1] = tmp[1][2] = tmp[1][3] = 0.f;
+#pragma unroll
+    for (int kk = 0; kk < KD / 16; ++kk) {
+        uint32_t a[4];
+        load_a(a, sQt, KD + 8, mt * 16, kk * 16, lane);
+        mma16816(tmp[0], a, sp[kk][0], sp[kk][2]);
+        mma16816(tmp[1], a, sp[kk][1], sp[kk][3]);
+    }
+}
+
+// Two output values (adjacent state columns) of one token, converted to the output type.
+__device__ __forceinline__ void store_out2(void* o, int dt, size_t idx, float x, float y) {
+    if (dt == LAMPA_BF16) *reinterpret_cast<uint32_t*>((__nv_bfloat16*)o + idx) = pack_bf16x2(x, y);
+    else if (dt == LAMPA_F16) *reinterpret_cast<__half2*>((__half*)o + idx) = __floats2half2_rn(x, y);
+    else *reinterpret_cast<float2*>((float*)o + idx) = make_float2(x, y);
+}
+
+// ---- record pipeline: thread 0 issues bulk copies NST-1 steps ahead; everyone waits on the
+// stage's mbarrier.  The __syncthreads at the top of a step frees the stage consumed last step.
+template <int NST>
+struct Pipe {
+    uint64_t* bar;
+    unsigned char* stage;
+    int stage_bytes;     // distance between stages in shared memory
+    const char* src;     // record of step 0
+    size_t src_stride;   // bytes between consecutive steps' records
+    uint32_t copy_bytes;
+    int nsteps;
+    bool dead;
+    int32_t* status;
+
+    __device__ __forceinline__ void issue(int step) {
+        uint64_t* b = bar + (step % NST);
+        mbar_expect_tx(b, copy_bytes);
+        bulk_g2s(stage + (size_t)(step % NST) * stage_bytes, src + (size_t)step * src_stride, copy_bytes, b);
+    }
+    __device__ __forceinline__ void start() {
+        if (threadIdx.x == 0) {
+            for (int s = 0; s < NST; ++s) mbar_init(bar + s, 1);
+            fence_mbar_init();
+        }
+        __syncthreads();
+        if (threadIdx.x == 0)
+            for (int s = 0; s < NST - 1 && s < nsteps; ++s) issue(s);
+    }
+    // returns the stage holding step i
+    __device__ __forceinline__ const unsigned char* acquire(int i) {
+        __syncthreads();
+        if (threadIdx.x == 0 && i + NST - 1 < nsteps) issue(i + NST - 1);
+        mbar_wait(bar + (i % NST), (uint32_t)((i / NST) & 1), dead, status, 100 + (i & 0xffff));
+        return stage + (size_t)(i % NST) * stage_bytes;
+    }
+};
+
+// -------------------------------------------------------------------------------------------------
+// compose: (Mblk, Bblk) of one block of chunks
+// -------------------------------------------------------------------------------------------------
+template <int KD, int VD>
+__global__ void __launch_bounds__((KD + VD) * 2) gdn_compose_kernel(GdnArgs a) {
+    using R = Rec<KD, VD>;
+    constexpr int NST = 3;
+    constexpr int NS = VD / 16;
+    extern __shared__ __align__(128) unsigned char smem[];
+    const int gb = blockIdx.x, h = blockIdx.y;
+    if (gb >= a.block_off[a.nseq]) return;
+    const int seq = find_seq(a.block_off, a.nseq, gb);
+    const int b = gb - a.block_off[seq];
+    const int nch = a.chunk_off[seq + 1] - a.chunk_off[seq];
+    const int c0 = a.chunk_off[seq] + b * BLOCK_CHUNKS;
+    const int nsteps = min(BLOCK_CHUNKS, nch - b * BLOCK_CHUNKS);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int g = lane >> 2, t = lane & 3;
+
+    Pipe<NST> pipe;
+    pipe.bar = reinterpret_cast<uint64_t*>(smem);
+    pipe.stage = smem + 128;
+    pipe.stage_bytes = R::MB_BYTES;
+    pipe.src = a.rec + ((size_t)c0 * a.H + h) * a.rec_bytes;
+    pipe.src_stride = (size_t)a.H * a.rec_bytes;
+    pipe.copy_bytes = R::MB_BYTES;
+    pipe.nsteps = nsteps;
+    pipe.dead = false;
+    pipe.status = a.status;
+    pipe.start();
+
+    const bool is_s = warp < NS;
+    const int row0 = is_s ? warp * 16 : (warp - NS) * 16;
+    float C[KD / 8][4];
+    zero_state<KD>(C);
+    if (!is_s) {
+#pragma unroll
+        for (int nt = 0; nt < KD / 8; ++nt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+                if (row0 + g + (e >> 1) * 8 == nt * 8 + 2 * t + (e & 1)) C[nt][e] = 1.f;
+    }
+    for (int i = 0; i < nsteps; ++i) {
+        const unsigned char* st = pipe.acquire(i);
+        const __nv_bfloat16* sM = reinterpret_cast<const __nv_bfloat16*>(st + R::M_OFF);
+        const __nv_bfloat16* sBt = reinterpret_cast<const __nv_bfloat16*>(st + R::BT_OFF);
+        uint32_t sp[KD / 16][4];
+        pack_state<KD>(C, sp);
+        if (is_s) {
+            load_slab_bf16<KD>(C, sBt, row0, lane);
+            if (i > 0) state_times_mt<KD>(C, sp, sM, lane);
+        } else {
+            zero_state<KD>(C);
+            state_times_mt<KD>(C, sp, sM, lane);
+        }
+    }
+    char* blk = a.blk + ((size_t)gb * a.H + h) * R::BLK_BYTES;
+    if (is_s) {
+        store_slab_f32<KD>(C, reinterpret_cast<float*>(blk + R::BLK_B_OFF), R::BP, row0, lane);
+    } else {
+        // registers hold P^T (row = k_in, col = k_out); Mblk is stored as P[k_out][k_in]
+        __nv_bfloat16* gm = reinterpret_cast<__nv_bfloat16*>(blk + R::BLK_M_OFF);
+#pragma unroll
+        for (int nt = 0; nt < KD / 8; ++nt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int kin = row0 + g + (e >> 1) * 8, kout = nt * 8 + 2 * t + (e & 1);
+                gm[kout * R::KP + kin] = __float2bfloat16_rn(C[nt][e]);
+            }
+    }
+}
+
+// -------------------------------------------------------------------------------------------------
+// level: scan of the block composites.  Plain rule: one state per (sequence, head), seeded by h0,
+// the state entering every block is stored and the last one is the final state.  Hierarchical:
+// one CTA per cross-block level lh (chunk level 5 + lh); the level collects blocks whose bit lh is
+// 0, is read by blocks whose bit lh is 1 (its entry state is stored for those) and is cleared at
+// the end of each period of 2^(lh+1) blocks.
+// -------------------------------------------------------------------------------------------------
+template <int KD, int VD, bool HIER>
+__global__ void __launch_bounds__(VD * 2) gdn_level_kernel(GdnArgs a) {
+    using R = Rec<KD, VD>;
+    constexpr int NST = 3;
+    extern __shared__ __align__(128) unsigned char smem[];
+    const int seq = blockIdx.x, h = blockIdx.y, lh = blockIdx.z, H = a.H;
+    const int nblk = a.block_off[seq + 1] - a.block_off[seq];
+    const int gb0 = a.block_off[seq];
+    if (HIER) {
+        const int nch = a.chunk_off[seq + 1] - a.chunk_off[seq];
+        const int nlev = nch > 1 ? ceil_log2_int(nch) : 0;
+        if (lh >= nlev - BLOCK_LOG) return;
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    const int row0 = warp * 16;
+
+    Pipe<NST> pipe;
+    pipe.bar = reinterpret_cast<uint64_t*>(smem);
+    pipe.stage = smem + 128;
+    pipe.stage_bytes = R::BLK_BYTES;
+    pipe.src = a.blk + ((size_t)gb0 * H + h) * R::BLK_BYTES;
+    pipe.src_stride = (size_t)H * R::BLK_BYTES;
+    pipe.copy_bytes = R::BLK_BYTES;
+    pipe.nsteps = nblk;
+    pipe.dead = false;
+    pipe.status = a.status;
+    pipe.start();
+
+    float C[KD / 8][4];
+    zero_state<KD>(C);
+    bool nonzero = false;
+    if (!HIER && a.h0 != nullptr) {
+        const float* h0 = a.h0 + ((size_t)seq * H + h) * KD * VD;   // [K][V]
+#pragma unroll
+        for (int nt = 0; nt < KD / 8; ++nt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+                C[nt][e] = h0[(size_t)(nt * 8 + 2 * t + (e & 1)) * VD + row0 + g + (e >> 1) * 8];
+        nonzero = true;
+    }
+    for (int b = 0; b < nblk; ++b) {
+        const unsigned char* st = pipe.acquire(b);
+        const __nv_bfloat16* sM = reinterpret_cast<const __nv_bfloat16*>(st + R::BLK_M_OFF);
+        const float* sB = reinterpret_cast<const float*>(st + R::BLK_B_OFF);
+        uint32_t sp[KD / 16][4];
+        if (!HIER) {
+            float* e = a.entry + ((size_t)(gb0 + b) * H + h) * R::STATE_FLOATS;
+            store_slab_f32<KD>(C, e, KD, row0, lane);
+            pack_state<KD>(C, sp);
+            load_slab_f32<KD>(C, sB, R::BP, row0, lane);
+            if (nonzero) state_times_mt<KD>(C, sp, sM, lane);
+            nonzero = true;
+        } else {
+            const int period = 2 << lh, pos = b & (period - 1), bit = (b >> lh) & 1;
+            if (bit) {
+                float* e = a.entry + (((size_t)(gb0 + b) * a.nhigh_max + lh) * H + h) * R::STATE_FLOATS;
+                store_slab_f32<KD>(C, e, KD, row0, lane);
+            }
+            if (pos == period - 1) {
+                zero_state<KD>(C);
+            } else {
+                pack_state<KD>(C, sp);
+                if (bit == 0) load_slab_f32<KD>(C, sB, R::BP, row0, lane);
+                else zero_state<KD>(C);
+                if (pos != 0) state_times_mt<KD>(C, sp, sM, lane);
+            }
+        }
+    }
+    if (!HIER && a.ht != nullptr) {
+        float* ht = a.ht + ((size_t)seq * H + h) * KD * VD;
+#pragma unroll
+        for (int nt = 0; nt < KD / 8; ++nt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+                ht[(size_t)(nt * 8 + 2 * t + (e & 1)) * VD + row0 + g + (e >> 1) * 8] = C[nt][e];
+    }
+}
+
+// -------------------------------------------------------------------------------------------------
+// output, plain rule:  O_n = O_local + Q~ S_n ;  S_{n+1} = M S_n + B
+// -------------------------------------------------------------------------------------------------
+template <int KD, int VD>
+__global__ void __launch_bounds__(VD * 2) gdn_out_plain_kernel(GdnArgs a) {
+    using R = Rec<KD, VD>;
+    constexpr int NST = 3;
+    extern __shared__ __align__(128) unsigned char smem[];
+    const int gb = blockIdx.x, h = blockIdx.y, H = a.H;
+    if (gb >= a.block_off[a.nseq]) return;
+    const int seq = find_seq(a.block_off, a.nseq, gb);
+    const int b = gb - a.block_off[seq];
+    const int nch = a.chunk_off[seq + 1] - a.chunk_off[seq];
+    const int c0 = a.chunk_off[seq] + b * BLOCK_CHUNKS;
+    const int nsteps = min(BLOCK_CHUNKS, nch - b * BLOCK_CHUNKS);
+    const int64_t tok0 = a.tok_off[seq] + (int64_t)b * BLOCK_CHUNKS * CHUNK, tok_end = a.tok_off[seq + 1];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    const int row0 = warp * 16;
+
+    Pipe<NST> pipe;
+    pipe.bar = reinterpret_cast<uint64_t*>(smem);
+    pipe.stage = smem + 128;
+    pipe.stage_bytes = R::LAM_OFF;
+    pipe.src = a.rec + ((size_t)c0 * H + h) * a.rec_bytes;
+    pipe.src_stride = (size_t)H * a.rec_bytes;
+    pipe.copy_bytes = R::LAM_OFF;
+    pipe.nsteps = nsteps;
+    pipe.dead = false;
+    pipe.status = a.status;
+    pipe.start();
+
+    float C[KD / 8][4];
+    load_slab_f32<KD>(C, a.entry + ((size_t)gb * H + h) * R::STATE_FLOATS, KD, row0, lane);
+    for (int i = 0; i < nsteps; ++i) {
+        const unsigned char* st = pipe.acquire(i);
+        const __nv_bfloat16* sM = reinterpret_cast<const __nv_bfloat16*>(st + R::M_OFF);
+        const __nv_bfloat16* sBt = reinterpret_cast<const __nv_bfloat16*>(st + R::BT_OFF);
+        const __nv_bfloat16* sQt = reinterpret_cast<const __nv_bfloat16*>(st + R::QT_OFF);
+        const float* sOl = reinterpret_cast<const float*>(st + R::OL_OFF);
+        uint32_t sp[KD / 16][4];
+        pack_state<KD>(C, sp);
+        const int64_t t0 = tok0 + (int64_t)i * CHUNK;
+#pragma unroll
+        for (int mt = 0; mt < 4; ++mt) {
+            float tmp[2][4];
+            read_tile<KD>(tmp, sp, sQt, mt, lane);
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh) {
+                const int r = mt * 16 + g + hh * 8;
+                if (t0 + r < tok_end) {
+#pragma unroll
+                    for (int nt = 0; nt < 2; ++nt) {
+                        const int col = row0 + nt * 8 + 2 * t;
+                        const float2 ol = *reinterpret_cast<const float2*>(sOl + r * R::OP + col);
+                        store_out2(a.o, a.qkv_dt, ((size_t)(t0 + r) * H + h) * VD + col,
+                                   ol.x + tmp[nt][2 * hh], ol.y + tmp[nt][2 * hh + 1]);
+                    }
+                }
+            }
+        }
+        if (i + 1 < nsteps) {
+            load_slab_bf16<KD>(C, sBt, row0, lane);
+            state_times_mt<KD>(C, sp, sM, lane);
+        }
+    }
+}
+
+// -------------------------------------------------------------------------------------------------
+// output, hierarchical rule.  Warp = (level group, slab).  Group 0 carries chunk levels 0..4, which
+// live and die inside the block; group gi >= 1 carries cross-block levels 5*(gi-1) .. +4, seeded
+// from the level pass.  A level is read by chunk n when bit l of n is set:
+//     O_n += diag(lambda[:, 7 + l]) (Q~ S_l)
+// and then advances: cleared at the end of its period of 2^(l+1) chunks, otherwise
+//     S_l <- M S_l + [bit l of n == 0] B.
+// Partial outputs of groups >= 1 are added by group 0 through shared memory.
+// -------------------------------------------------------------------------------------------------
+template <int KD, int VD, int NG>
+__global__ void __launch_bounds__(NG * VD * 2, 1) gdn_out_hier_kernel(GdnArgs a) {
+    using R = Rec<KD, VD>;
+    constexpr int NST = 3;
+    constexpr int NS = VD / 16;
+    extern __shared__ __align__(128) unsigned char smem[];
+    const int gb = blockIdx.x, h = blockIdx.y, H = a.H;
+    if (gb >= a.block_off[a.nseq]) return;
+    const int seq = find_seq(a.block_off, a.nseq, gb);
+    const int b = gb - a.block_off[seq];
+    const int nch = a.chunk_off[seq + 1] - a.chunk_off[seq];
+    const int nlev = nch > 1 ? ceil_log2_int(nch) : 0;
+    const int nhigh = max(0, nlev - BLOCK_LOG);
+    const int c0 = a.chunk_off[seq] + b * BLOCK_CHUNKS;
+    const int nsteps = min(BLOCK_CHUNKS, nch - b * BLOCK_CHUNKS);
+    const int64_t tok0 = a.tok_off[seq] + (int64_t)b * BLOCK_CHUNKS * CHUNK, tok_end = a.tok_off[seq + 1];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    const int grp = warp / NS, slab = warp - grp * NS;
+    const int row0 = slab * 16;
+    const int rec_copy = R::bytes(a.LC);
+    const int stage_bytes = (rec_copy + 127) / 128 * 128;
+
+    Pipe<NST> pipe;
+    pipe.bar = reinterpret_cast<uint64_t*>(smem);
+    pipe.stage = smem + 128;
+    pipe.stage_bytes = stage_bytes;
+    pipe.src = a.rec + ((size_t)c0 * H + h) * a.rec_bytes;
+    pipe.src_stride = (size_t)H * a.rec_bytes;
+    pipe.copy_bytes = (uint32_t)rec_copy;
+    pipe.nsteps = nsteps;
+    pipe.dead = false;
+    pipe.status = a.status;
+    float* red = reinterpret_cast<float*>(smem + 128 + (size_t)NST * stage_bytes);   // [NG-1][NS][32 regs][32 lanes]
+    pipe.start();
+
+    float C[NLW][KD / 8][4];
+    uint32_t live = 0;   // bit x: level x of this warp holds a state that matters
+#pragma unroll
+    for (int x = 0; x < NLW; ++x) zero_state<KD>(C[x]);
+    if (grp > 0) {
+#pragma unroll
+        for (int x = 0; x < NLW; ++x) {
+            const int lh = (grp - 1) * NLW + x;
+            if (lh < nhigh && ((b >> lh) & 1)) {
+                live |= 1u << x;
+                load_slab_f32<KD>(C[x], a.entry + (((size_t)gb * a.nhigh_max + lh) * H + h) * R::STATE_FLOATS, KD, row0, lane);
+            }
+        }
+    }
+
+    for (int i = 0; i < nsteps; ++i) {
+        const unsigned char* st = pipe.acquire(i);
+        const __nv_bfloat16* sM = reinterpret_cast<const __nv_bfloat16*>(st + R::M_OFF);
+        const __nv_bfloat16* sBt = reinterpret_cast<const __nv_bfloat16*>(st + R::BT_OFF);
+        const __nv_bfloat16* sQt = reinterpret_cast<const __nv_bfloat16*>(st + R::QT_OFF);
+        const float* sOl = reinterpret_cast<const float*>(st + R::OL_OFF);
+        const float* sLam = reinterpret_cast<const float*>(st + R::LAM_OFF);
+        const int n = b * BLOCK_CHUNKS + i;
+
+        float O[4][2][4];
+#pragma unroll
+        for (int mt = 0; mt < 4; ++mt)
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt) { O[mt][nt][0] = O[mt][nt][1] = O[mt][nt][2] = O[mt][nt][3] = 0.f; }
+
+#pragma unroll
+        for (int x = 0; x < NLW; ++x) {
+            bool do_read, do_mma, add_b, clear;
+            int lam_row;
+            if (grp == 0) {
+                const int per = 2 << x, pos = n & (per - 1), bit = (n >> x) & 1;
+                do_read = bit != 0;
+                clear = pos == per - 1;
+                add_b = bit == 0;
+                do_mma = !clear && pos != 0;
+                lam_row = x;
+            } else {
+                const bool lv = (live >> x) & 1u;
+                do_read = lv;
+                clear = false;
+                add_b = false;
+                do_mma = lv && (i + 1 < nsteps);
+                lam_row = BLOCK_LOG + (grp - 1) * NLW + x;
+            }
+            if (lam_row >= a.LC) do_read = false;   // only reachable when the level check already failed
+            uint32_t sp[KD / 16][4];
+            if (do_read || do_mma) pack_state<KD>(C[x], sp);
+            if (do_read) {
+                const float* lr = sLam + lam_row * CHUNK;
+#pragma unroll
+                for (int mt = 0; mt < 4; ++mt) {
+                    float tmp[2][4];
+                    read_tile<KD>(tmp, sp, sQt, mt, lane);
+                    const float l0 = lr[mt * 16 + g], l1 = lr[mt * 16 + g + 8];
+#pragma unroll
+                    for (int nt = 0; nt < 2; ++nt) {
+                        O[mt][nt][0] += l0 * tmp[nt][0]; O[mt][nt][1] += l0 * tmp[nt][1];
+                        O[mt][nt][2] += l1 * tmp[nt][2]; O[mt][nt][3] += l1 * tmp[nt][3];
+                    }
+                }
+            }
+            if (grp == 0) {
+                if (clear) {
+                    zero_state<KD>(C[x]);
+                } else {
+                    if (add_b) load_slab_bf16<KD>(C[x], sBt, row0, lane);
+                    else zero_state<KD>(C[x]);
+                    if (do_mma) state_times_mt<KD>(C[x], sp, sM, lane);
+                }
+            } else if (do_mma) {
+                zero_state<KD>(C[x]);
+                state_times_mt<KD>(C[x], sp, sM, lane);
+            }
+        }
+
+        if (NG > 1) {
+            if (grp > 0) {
+                float* rd = red + ((size_t)(grp - 1) * NS + slab) * 1024 + lane;
+#pragma unroll
+                for (int mt = 0; mt < 4; ++mt)
+#pragma unroll
+                    for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) rd[((mt * 2 + nt) * 4 + e) * 32] = O[mt][nt][e];
+            }
+            __syncthreads();
+        }
+        if (grp == 0) {
+#pragma unroll
+            for (int gi = 1; gi < NG; ++gi) {
+                const float* rd = red + ((size_t)(gi - 1) * NS + slab) * 1024 + lane;
+#pragma unroll
+                for (int mt = 0; mt < 4; ++mt)
+#pragma unroll
+                    for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) O[mt][nt][e] += rd[((mt * 2 + nt) * 4 + e) * 32];
+            }
+            const int64_t t0 = tok0 + (int64_t)i * CHUNK;
+#pragma unroll
+            for (int mt = 0; mt < 4; ++mt)
+#pragma unroll
+                for (int hh = 0; hh < 2; ++hh) {
+                    const int r = mt * 16 + g + hh * 8;
+                    if (t0 + r < tok_end) {
+#pragma unroll
+                        for (int nt = 0; nt < 2; ++nt) {
+                            const int col = row0 + nt * 8 + 2 * t;
+                            const float2 ol = *reinterpret_cast<const float2*>(sOl + r * R::OP + col);
+                            store_out2(a.o, a.qkv_dt, ((size_t)(t0 + r) * H + h) * VD + col,
+                                       ol.x + O[mt][nt][2 * hh], ol.y + O[mt][nt][2 * hh + 1]);
+                        }
+                    }
+                }
+        }
+    }
+}
+
+// ---- launchers ------------------------------------------------------------------------------------
+template <typename KernelT>
+static int set_smem(KernelT kern, int bytes) {
+    return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) == cudaSuccess
+               ? LAMPA_OK : LAMPA_ERR_CUDA;
+}
+#define LAMPA_TRY(x) do { int rc_ = (x); if (rc_ != LAMPA_OK) return rc_; } while (0)
+#define LAMPA_LAUNCHED() do { if (cudaGetLastError() != cudaSuccess) return LAMPA_ERR_CUDA; } while (0)
+
+template <int KD, int VD>
+static int launch_compose(const GdnArgs& a, cudaStream_t st) {
+    using R = Rec<KD, VD>;
+    const int smem = 128 + 3 * R::MB_BYTES;
+    LAMPA_TRY(set_smem(gdn_compose_kernel<KD, VD>, smem));
+    gdn_compose_kernel<KD, VD><<<dim3(a.nb_max, a.H), (KD + VD) * 2, smem, st>>>(a);
+    LAMPA_LAUNCHED();
+    return LAMPA_OK;
+}
+
+template <int KD, int VD>
+int launch_scan_plain(const GdnArgs& a, cudaStream_t st) {
+    using R = Rec<KD, VD>;
+    LAMPA_TRY((launch_compose<KD, VD>(a, st)));
+    {
+        const int smem = 128 + 3 * R::BLK_BYTES;
+        LAMPA_TRY(set_smem(gdn_level_kernel<KD, VD, false>, smem));
+        gdn_level_kernel<KD, VD, false><<<dim3(a.nseq, a.H, 1), VD * 2, smem, st>>>(a);
+        LAMPA_LAUNCHED();
+    }
+    {
+        const int smem = 128 + 3 * R::LAM_OFF;
+        LAMPA_TRY(set_smem(gdn_out_plain_kernel<KD, VD>, smem));
+        gdn_out_plain_kernel<KD, VD><<<dim3(a.nb_max, a.H), VD * 2, smem, st>>>(a);
+        LAMPA_LAUNCHED();
+    }
+    return LAMPA_OK;
+}
+
+template <int KD, int VD, int NG>
+static int launch_out_hier(const GdnArgs& a, cudaStream_t st) {
+    using R = Rec<KD, VD>;
+    const int stage = (R::bytes(a.LC) + 127) / 128 * 128;
+    const int smem = 128 + 3 * stage + (NG - 1) * (VD / 16) * 4096;
+    if (smem > 227 * 1024) return LAMPA_ERR_UNSUPPORTED;
+    LAMPA_TRY(set_smem(gdn_out_hier_kernel<KD, VD, NG>, smem));
+    gdn_out_hier_kernel<KD, VD, NG><<<dim3(a.nb_max, a.H), NG * VD * 2, smem, st>>>(a);
+    LAMPA_LAUNCHED();
+    return LAMPA_OK;
+}
+
+template <int KD, int VD>
+int launch_scan_hier(const GdnArgs& a, cudaStream_t st) {
+    using R = Rec<KD, VD>;
+    const int ng = 1 + (a.nhigh_max + NLW - 1) / NLW;
+    if (ng > MAX_GROUPS) return LAMPA_ERR_UNSUPPORTED;
+    if (a.nhigh_max > 0) {
+        LAMPA_TRY((launch_compose<KD, VD>(a, st)));
+        const int smem = 128 + 3 * R::BLK_BYTES;
+        LAMPA_TRY(set_smem(gdn_level_kernel<KD, VD, true>, smem));
+        gdn_level_kernel<KD, VD, true><<<dim3(a.nseq, a.H, a.nhigh_max), VD * 2, smem, st>>>(a);
+        LAMPA_LAUNCHED();
+    }
+    if (ng == 1) return launch_out_hier<KD, VD, 1>(a, st);
+    if (ng == 2) return launch_out_hier<KD, VD, 2>(a, st);
+    return launch_out_hier<KD, VD, 3>(a, st);
+}
+
+template int launch_scan_plain<64, 64>(const GdnArgs&, cudaStream_t);
+template int launch_scan_plain<32, 32>(const GdnArgs&, cudaStream_t);
+template int launch_scan_plain<16, 32>(const GdnArgs&, cudaStream_t);
+template int launch_scan_hier<64, 64>(const GdnArgs&, cudaStream_t);
+template int launch_scan_hier<32, 32>(const GdnArgs&, cudaStream_t);
+template int launch_scan_hier<16, 32>(const GdnArgs&, cudaStream_t);
+
+}  // namespace lampa

@@ -1,0 +1,353 @@
+// E2LSH hashing, segmented stable radix sort, row permutation: the ordering half of the path.
+// All kernels are HBM/L2-bound integer and byte work; no tensor cores here by design.
+#include <cooperative_groups.h>
+
+#include <algorithm>
+
+#include "common.cuh"
+
+namespace cg = cooperative_groups;
+
+namespace lampa {
+
+// -------------------------------------------------------------------------------------------------
+// Hash: one thread per hit.  Reads dim floats of the hit's row (for the detector rows of this
+// workload 24 B of a 96 B row: one 32 B sector) and writes rounds*heads ids, each coalesced across
+// the warp.  The operation order is a contract shared with the CPU checker (see the header).
+// -------------------------------------------------------------------------------------------------
+constexpr int HASH_THREADS = 256;
+constexpr int HASH_MAX_PARAMS = 4096;   // heads*dim*rounds floats staged in shared memory
+
+template <int DIMT>   // DIMT > 0: coordinates kept in registers (dim == DIMT, shared rows)
+__global__ void __launch_bounds__(HASH_THREADS)
+lsh_hash_kernel(const float* __restrict__ x, int64_t row_stride, int64_t head_stride,
+                const float* __restrict__ alpha, const float* __restrict__ beta, float w, int64_t N,
+                int heads, int rounds, int dim, int32_t* __restrict__ ids, float* __restrict__ keys,
+                int32_t* __restrict__ packed) {
+    __shared__ float s_alpha[HASH_MAX_PARAMS];
+    __shared__ float s_beta[64];
+    const int np = heads * dim * rounds;
+    for (int i = threadIdx.x; i < np; i += HASH_THREADS) s_alpha[i] = alpha[i];
+    for (int i = threadIdx.x; i < rounds; i += HASH_THREADS) s_beta[i] = beta[i];
+    __syncthreads();
+    const int64_t n = (int64_t)blockIdx.x * HASH_THREADS + threadIdx.x;
+    if (n >= N) return;
+    float xv[DIMT > 0 ? DIMT : 1];
+    if (DIMT > 0) {
+#pragma unroll
+        for (int d = 0; d < DIMT; ++d) xv[d] = __ldg(x + n * row_stride + d);
+    }
+    for (int c = 0; c < rounds; ++c) {
+        int32_t pk = 0;
+        for (int h = 0; h < heads; ++h) {
+            const float* a = s_alpha + (size_t)h * dim * rounds + c;   // a[d*rounds]
+            float acc;
+            if (DIMT > 0) {
+                acc = __fmul_rn(xv[0], a[0]);
+#pragma unroll
+                for (int d = 1; d < DIMT; ++d) acc = __fadd_rn(acc, __fmul_rn(xv[d], a[d * rounds]));
+            } else {
+                const float* xr = x + h * head_stride + n * row_stride;
+                acc = __fmul_rn(__ldg(xr), a[0]);
+                for (int d = 1; d < dim; ++d) acc = __fadd_rn(acc, __fmul_rn(__ldg(xr + d), a[d * rounds]));
+            }
+            const size_t o = ((size_t)c * heads + h) * N + n;
+            if (keys) keys[o] = acc;
+            if (ids || packed) {
+                const int32_t id = (int32_t)floorf(__fdiv_rn(__fadd_rn(acc, s_beta[c]), w));
+                if (ids) ids[o] = id;
+                pk += (int32_t)((uint32_t)id << h);
+            }
+        }
+        if (packed) packed[(size_t)c * N + n] = pk;
+    }
+}
+
+// -------------------------------------------------------------------------------------------------
+// Segmented stable LSD radix sort.  One thread-block cluster of 8 CTAs per segment: each CTA owns
+// a contiguous eighth of the segment in its current order, digit histograms are exchanged through
+// distributed shared memory, and the passes are separated by the hardware cluster barrier (no
+// flag spinning anywhere).  Keys are reduced to (key - min) first, so only ceil(bits(range)/8)
+// passes run: two for the ~15-bit bucket ids of this workload.
+// -------------------------------------------------------------------------------------------------
+constexpr int SORT_THREADS = 1024;
+constexpr int SORT_CL = 8;
+constexpr int SORT_WARPS = SORT_THREADS / 32;
+
+__device__ __forceinline__ uint32_t key_xform(const void* keys, int key_type, int64_t i) {
+    uint32_t u = ((const uint32_t*)keys)[i];
+    if (key_type == LAMPA_KEY_I32) return u ^ 0x80000000u;
+    // float: order-preserving map; -0.0 and +0.0 compare equal in torch.sort, so fold -0 onto +0
+    if (u == 0x80000000u) u = 0u;
+    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+
+__global__ void __cluster_dims__(SORT_CL, 1, 1) __launch_bounds__(SORT_THREADS, 1)
+segsort_kernel(const void* __restrict__ keys, int key_type, int64_t n_total,
+               const int64_t* __restrict__ seg, int nseg, const int64_t* __restrict__ init,
+               int64_t* __restrict__ perm, uint32_t* kbuf0, uint32_t* kbuf1, uint32_t* ibuf0,
+               uint32_t* ibuf1) {
+    cg::cluster_group cluster = cg::this_cluster();
+    const int rank = (int)cluster.block_rank();
+    const int s = blockIdx.x / SORT_CL;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+
+    int64_t s0, n;
+    if (seg) { s0 = seg[s]; n = seg[s + 1] - s0; }
+    else { n = n_total / nseg; s0 = (int64_t)s * n; }
+    if (n < 0) n = 0;
+    const int64_t per = (n + SORT_CL - 1) / SORT_CL;
+    const int64_t lo = min((int64_t)rank * per, n), hi = min(lo + per, n);
+
+    __shared__ uint32_t hist[256];
+    __shared__ uint32_t dbase[256];
+    __shared__ uint32_t tile_tot[256];
+    __shared__ uint32_t wtot[8];
+    __shared__ uint32_t red[2];
+    __shared__ uint32_t wcount[SORT_WARPS][256];
+
+    // ---- key range over the whole segment -------------------------------------------------------
+    if (tid == 0) { red[0] = 0xFFFFFFFFu; red[1] = 0u; }
+    __syncthreads();
+    {
+        uint32_t mn = 0xFFFFFFFFu, mx = 0u;
+        for (int64_t i = lo + tid; i < hi; i += SORT_THREADS) {
+            const uint32_t u = key_xform(keys, key_type, s0 + i);
+            mn = min(mn, u); mx = max(mx, u);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            mn = min(mn, __shfl_xor_sync(0xffffffffu, mn, o));
+            mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        }
+        if (lane == 0) { atomicMin(&red[0], mn); atomicMax(&red[1], mx); }
+    }
+    __syncthreads();
+    cluster.sync();
+    uint32_t gmn = 0xFFFFFFFFu, gmx = 0u;
+    for (int r = 0; r < SORT_CL; ++r) {
+        const uint32_t* rr = cluster.map_shared_rank(red, r);
+        gmn = min(gmn, rr[0]); gmx = max(gmx, rr[1]);
+    }
+    const uint32_t range = (n > 0 && gmx >= gmn) ? (gmx - gmn) : 0u;
+    const int bits = range ? (32 - __clz(range)) : 0;
+    const int npass = (bits + 7) / 8;
+
+    if (npass == 0) {
+        for (int64_t i = lo + tid; i < hi; i += SORT_THREADS) perm[s0 + i] = init ? init[s0 + i] : i;
+    }
+
+    for (int p = 0; p < npass; ++p) {
+        const int shift = 8 * p;
+        const uint32_t* ksrc = (p & 1) ? kbuf0 : kbuf1;   // pass p reads what pass p-1 wrote
+        const uint32_t* isrc = (p & 1) ? ibuf0 : ibuf1;
+        uint32_t* kdst = (p & 1) ? kbuf1 : kbuf0;
+        uint32_t* idst = (p & 1) ? ibuf1 : ibuf0;
+        const bool last = (p == npass - 1);
+
+        // (a) digit histogram of this CTA's slice
+        for (int d = tid; d < 256; d += SORT_THREADS) hist[d] = 0;
+        __syncthreads();
+        for (int64_t i = lo + tid; i < hi; i += SORT_THREADS) {
+            const uint32_t u = (p == 0) ? (key_xform(keys, key_type, s0 + i) - gmn) : ksrc[s0 + i];
+            atomicAdd(&hist[(u >> shift) & 255u], 1u);
+        }
+        __syncthreads();
+        cluster.sync();
+
+        // (b) where each digit of this slice starts in the segment
+        uint32_t tot = 0, before = 0, incl = 0;
+        if (tid < 256) {
+            for (int r = 0; r < SORT_CL; ++r) {
+                const uint32_t h = cluster.map_shared_rank(hist, r)[tid];
+                tot += h;
+                if (r < rank) before += h;
+            }
+            incl = tot;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const uint32_t y = __shfl_up_sync(0xffffffffu, incl, o);
+                if (lane >= o) incl += y;
+            }
+            if (lane == 31) wtot[warp] = incl;
+        }
+        __syncthreads();
+        if (tid < 256) {
+            uint32_t off = 0;
+            for (int w2 = 0; w2 < warp; ++w2) off += wtot[w2];
+            dbase[tid] = off + incl - tot + before;
+        }
+        __syncthreads();
+
+        // (c) stable scatter, tile by tile in slice order
+        for (int64_t t0 = lo; t0 < hi; t0 += SORT_THREADS) {
+            const int64_t i = t0 + tid;
+            const bool valid = i < hi;
+            uint32_t u = 0, idx = 0;
+            if (valid) {
+                if (p == 0) {
+                    u = key_xform(keys, key_type, s0 + i) - gmn;
+                    idx = init ? (uint32_t)init[s0 + i] : (uint32_t)i;
+                } else {
+                    u = ksrc[s0 + i];
+                    idx = isrc[s0 + i];
+                }
+            }
+            const uint32_t digit = valid ? ((u >> shift) & 255u) : 256u;
+            for (int z = tid; z < SORT_WARPS * 256; z += SORT_THREADS) (&wcount[0][0])[z] = 0;
+            __syncthreads();
+            const uint32_t m = __match_any_sync(0xffffffffu, digit);
+            const uint32_t rank_in_warp = __popc(m & ((1u << lane) - 1u));
+            if (valid && (__ffs(m) - 1) == lane) wcount[warp][digit] = __popc(m);
+            __syncthreads();
+            if (tid < 256) {
+                uint32_t run = 0;
+#pragma unroll 4
+                for (int w2 = 0; w2 < SORT_WARPS; ++w2) {
+                    const uint32_t c = wcount[w2][tid];
+                    wcount[w2][tid] = run;
+                    run += c;
+                }
+                tile_tot[tid] = run;
+            }
+            __syncthreads();
+            if (valid) {
+                const int64_t pos = (int64_t)dbase[digit] + wcount[warp][digit] + rank_in_warp;
+                if (last) {
+                    perm[s0 + pos] = (int64_t)idx;
+                } else {
+                    kdst[s0 + pos] = u;
+                    idst[s0 + pos] = idx;
+                }
+            }
+            __syncthreads();
+            if (tid < 256) dbase[tid] += tile_tot[tid];
+        }
+        __threadfence();
+        cluster.sync();   // scattered keys visible to the whole cluster; histograms free again
+    }
+    cluster.sync();       // no CTA leaves while a peer may still read its shared memory
+}
+
+// -------------------------------------------------------------------------------------------------
+// Row gather/scatter and permutation inverse.
+// -------------------------------------------------------------------------------------------------
+__device__ __forceinline__ int find_seg64(const int64_t* off, int nseg, int64_t x) {
+    int lo = 0, hi = nseg;
+    while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (off[mid] <= x) lo = mid; else hi = mid;
+    }
+    return lo;
+}
+
+template <typename VEC>
+__global__ void __launch_bounds__(256)
+permute_rows_kernel(const VEC* __restrict__ src, const int64_t* __restrict__ perm,
+                    const int64_t* __restrict__ seg, int nseg, int64_t n_rows, int64_t units_per_row,
+                    int scatter, VEC* __restrict__ dst) {
+    const int64_t total = n_rows * units_per_row;
+    for (int64_t u = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; u < total;
+         u += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t row = u / units_per_row, col = u - row * units_per_row;
+        int64_t s0;
+        if (seg) s0 = seg[find_seg64(seg, nseg, row)];
+        else { const int64_t per = n_rows / nseg; s0 = (row / per) * per; }
+        const int64_t other = s0 + perm[row];
+        if (scatter) dst[other * units_per_row + col] = src[u];
+        else dst[u] = src[other * units_per_row + col];
+    }
+}
+
+__global__ void __launch_bounds__(256)
+invert_perm_kernel(const int64_t* __restrict__ perm, const int64_t* __restrict__ seg, int nseg,
+                   int64_t n_total, int64_t* __restrict__ inv) {
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_total;
+         i += (int64_t)gridDim.x * blockDim.x) {
+        int64_t s0;
+        if (seg) s0 = seg[find_seg64(seg, nseg, i)];
+        else { const int64_t per = n_total / nseg; s0 = (i / per) * per; }
+        inv[s0 + perm[i]] = i - s0;
+    }
+}
+
+}  // namespace lampa
+
+using namespace lampa;
+
+static inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+extern "C" int lampa_lsh_hash(const float* x, int64_t row_stride, int64_t head_stride, const float* alpha,
+                              const float* beta, float w, int64_t N, int32_t heads, int32_t rounds,
+                              int32_t dim, int32_t* ids, float* keys, int32_t* packed, void* stream) {
+    if (!x || !alpha || !beta || N < 0 || heads <= 0 || rounds <= 0 || dim <= 0) return LAMPA_ERR_ARG;
+    if (!(w > 0.f)) return LAMPA_ERR_ARG;
+    if ((int64_t)heads * dim * rounds > HASH_MAX_PARAMS || rounds > 64 || heads > 31) return LAMPA_ERR_UNSUPPORTED;
+    if (N == 0) return LAMPA_OK;
+    cudaStream_t st = (cudaStream_t)stream;
+    const unsigned grid = (unsigned)((N + HASH_THREADS - 1) / HASH_THREADS);
+    if (dim == 6 && head_stride == 0)
+        lsh_hash_kernel<6><<<grid, HASH_THREADS, 0, st>>>(x, row_stride, head_stride, alpha, beta, w, N, heads, rounds, dim, ids, keys, packed);
+    else
+        lsh_hash_kernel<0><<<grid, HASH_THREADS, 0, st>>>(x, row_stride, head_stride, alpha, beta, w, N, heads, rounds, dim, ids, keys, packed);
+    return cudaGetLastError() == cudaSuccess ? LAMPA_OK : LAMPA_ERR_CUDA;
+}
+
+extern "C" int lampa_segsort_workspace_bytes(int64_t n_total, size_t* bytes) {
+    if (n_total < 0 || !bytes) return LAMPA_ERR_ARG;
+    *bytes = 4 * align_up((size_t)n_total * 4, 256) + 256;
+    return LAMPA_OK;
+}
+
+extern "C" int lampa_segsort_stable(const void* keys, int32_t key_type, int64_t n_total,
+                                    const int64_t* seg_offsets, int32_t nseg, const int64_t* init,
+                                    int64_t* perm, void* ws, size_t ws_bytes, int32_t* status, void* stream) {
+    (void)status;
+    if (n_total < 0 || nseg <= 0 || (key_type != LAMPA_KEY_I32 && key_type != LAMPA_KEY_F32)) return LAMPA_ERR_ARG;
+    if (n_total == 0) return LAMPA_OK;
+    if (!keys || !perm || !ws) return LAMPA_ERR_ARG;
+    if (!seg_offsets && n_total % nseg != 0) return LAMPA_ERR_ARG;
+    if (n_total >= ((int64_t)1 << 32)) return LAMPA_ERR_UNSUPPORTED;
+    size_t need;
+    lampa_segsort_workspace_bytes(n_total, &need);
+    if (ws_bytes < need || ((uintptr_t)ws & 15)) return LAMPA_ERR_WORKSPACE;
+    const size_t stride = align_up((size_t)n_total * 4, 256);
+    char* base = (char*)(((uintptr_t)ws + 255) / 256 * 256);
+    uint32_t* k0 = (uint32_t*)base;
+    uint32_t* k1 = (uint32_t*)(base + stride);
+    uint32_t* i0 = (uint32_t*)(base + 2 * stride);
+    uint32_t* i1 = (uint32_t*)(base + 3 * stride);
+    segsort_kernel<<<(unsigned)nseg * SORT_CL, SORT_THREADS, 0, (cudaStream_t)stream>>>(
+        keys, key_type, n_total, seg_offsets, nseg, init, perm, k0, k1, i0, i1);
+    return cudaGetLastError() == cudaSuccess ? LAMPA_OK : LAMPA_ERR_CUDA;
+}
+
+extern "C" int lampa_permute_rows(const void* src, const int64_t* perm, const int64_t* seg_offsets,
+                                  int32_t nseg, int64_t n_rows, int64_t row_bytes, int32_t scatter,
+                                  void* dst, void* stream) {
+    if (n_rows < 0 || row_bytes <= 0 || (row_bytes & 3) || nseg <= 0) return LAMPA_ERR_ARG;
+    if (n_rows == 0) return LAMPA_OK;
+    if (!src || !perm || !dst) return LAMPA_ERR_ARG;
+    if (!seg_offsets && n_rows % nseg != 0) return LAMPA_ERR_ARG;
+    cudaStream_t st = (cudaStream_t)stream;
+    const bool v16 = (row_bytes % 16 == 0) && (((uintptr_t)src | (uintptr_t)dst) % 16 == 0);
+    const int64_t upr = v16 ? row_bytes / 16 : row_bytes / 4;
+    const int64_t total = n_rows * upr;
+    const unsigned grid = (unsigned)std::min<int64_t>((total + 255) / 256, 148 * 32);
+    if (v16)
+        permute_rows_kernel<uint4><<<grid, 256, 0, st>>>((const uint4*)src, perm, seg_offsets, nseg, n_rows, upr, scatter, (uint4*)dst);
+    else
+        permute_rows_kernel<uint32_t><<<grid, 256, 0, st>>>((const uint32_t*)src, perm, seg_offsets, nseg, n_rows, upr, scatter, (uint32_t*)dst);
+    return cudaGetLastError() == cudaSuccess ? LAMPA_OK : LAMPA_ERR_CUDA;
+}
+
+extern "C" int lampa_invert_perm(const int64_t* perm, const int64_t* seg_offsets, int32_t nseg,
+                                 int64_t n_total, int64_t* inv, void* stream) {
+    if (n_total < 0 || nseg <= 0) return LAMPA_ERR_ARG;
+    if (n_total == 0) return LAMPA_OK;
+    if (!perm || !inv) return LAMPA_ERR_ARG;
+    if (!seg_offsets && n_total % nseg != 0) return LAMPA_ERR_ARG;
+    const unsigned grid = (unsigned)std::min<int64_t>((n_total + 255) / 256, 148 * 32);
+    invert_perm_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(perm, seg_offsets, nseg, n_total, inv);
+    return cudaGetLastError() == cudaSuccess ? LAMPA_OK : LAMPA_ERR_CUDA;
+}

@@ -1,0 +1,233 @@
+"""Drop-in host side of the gated-delta forward ops.
+
+Same names, argument meaning and error behaviour as the reference entry points:
+  chunk_gated_delta_rule    models/hattention/gated_delta_rule_ori.py:235-357
+  chunk_h_gated_delta_rule  models/hattention/gated_delta_rule_apis.py:20-134
+  hattention_kernel         models/hattention/kernel.py:338-374
+Forward only (no autograd graph is recorded).  Everything runs in the CUDA library on
+the current torch stream; there is no PyTorch or CPU fallback.
+"""
+from __future__ import annotations
+
+import ctypes
+import enum
+import math
+import warnings
+from typing import Optional, Tuple
+
+import torch
+
+from . import _lib as L
+
+
+class HType(enum.Enum):
+    """Hierarchy type (models/hattention/base.py); only WEAK is implemented, as in the GDELTA path."""
+    WEAK = "weak"
+    STRONG = "strong"
+
+
+class HStruct(enum.Enum):
+    """State structure (models/hattention/base.py); only GDELTA is implemented here."""
+    MAMBA2 = "mamba2"
+    GDELTA = "gdelta"
+
+
+CHUNK = 64
+ELL0 = 7   # intra-chunk levels: get_num_levels(64, 2) (models/hattention/base.py:37-38)
+
+
+def num_levels_required(T: int) -> int:
+    """Levels lambda must provide for a sequence of T tokens: 7 + ceil(log2(ceil(T/64)))
+    (the check at models/hattention/chunkwise_hgdn.py:723-726)."""
+    nt = (T + CHUNK - 1) // CHUNK
+    return ELL0 + (math.ceil(math.log2(nt)) if nt > 1 else 0)
+
+
+def _common_checks(q, k, v, beta, head_first, cu_seqlens, initial_state):
+    assert q.dtype == k.dtype == v.dtype
+    assert len(beta.shape) == 3, "beta must be of shape [B, T, H] if head_first=False, or [B, H, T] otherwise."
+    if head_first:
+        raise DeprecationWarning(
+            "head_first is deprecated and will be removed in a future version. "
+            "Please use head_first=False for now instead."
+        )
+    if q.shape[1] < q.shape[2]:
+        warnings.warn(
+            f"Input tensor shape suggests potential format mismatch: seq_len ({q.shape[1]}) < num_heads ({q.shape[2]}). "
+            "This may indicate the inputs were passed in head-first format [B, H, T, ...] "
+            "when head_first=False was specified. "
+            "Please verify your input tensor format matches the expected shape [B, T, H, ...]."
+        )
+    if cu_seqlens is not None:
+        if q.shape[0] != 1:
+            raise ValueError(
+                f"The batch size is expected to be 1 rather than {q.shape[0]} when using `cu_seqlens`."
+                f"Please flatten variable-length inputs before processing."
+            )
+        if initial_state is not None and initial_state.shape[0] != len(cu_seqlens) - 1:
+            raise ValueError(
+                f"The number of initial states is expected to be equal to the number of input sequences, "
+                f"i.e., {len(cu_seqlens) - 1} rather than {initial_state.shape[0]}."
+            )
+
+
+def _desc(q, v, g, lam, cu_seqlens, use_l2norm, scale) -> L.GdnDesc:
+    B, T, H, K = q.shape
+    return L.GdnDesc(B=B, T=T, H=H, K=K, V=v.shape[-1], L=0 if lam is None else lam.shape[-1],
+                     nseq=0 if cu_seqlens is None else len(cu_seqlens) - 1,
+                     qkv_dtype=L.dtype_code(q.dtype), gb_dtype=L.dtype_code(g.dtype),
+                     lam_dtype=L.LAMPA_F32 if lam is None else L.dtype_code(lam.dtype),
+                     use_l2norm=int(bool(use_l2norm)), scale=float(scale))
+
+
+def _workspace(desc: L.GdnDesc, dev: torch.device) -> torch.Tensor:
+    n = ctypes.c_size_t(0)
+    L.check(L.lib().lampa_gdn_workspace_bytes(ctypes.byref(desc), ctypes.byref(n)), "lampa_gdn_workspace_bytes")
+    return torch.empty(max(n.value, 256), dtype=torch.uint8, device=dev)
+
+
+def _prep_inputs(q, k, v, g, beta, lam, cu_seqlens):
+    dev = L.require_cuda(q, k, v, g, beta, lam, cu_seqlens)
+    if v.shape[:3] != q.shape[:3] or k.shape != q.shape or g.shape != q.shape[:3] or beta.shape != q.shape[:3]:
+        raise ValueError("q/k [B,T,H,K], v [B,T,H,V], g/beta [B,T,H] expected")
+    q, k, v, g, beta = (x.contiguous() for x in (q, k, v, g, beta))
+    if g.dtype != beta.dtype:
+        beta = beta.to(g.dtype)
+    if lam is not None:
+        if lam.shape[:3] != q.shape[:3]:
+            raise ValueError("l must be [B,T,H,L]")
+        lam = lam.contiguous()
+    if cu_seqlens is not None:
+        cu_seqlens = cu_seqlens.to(device=dev, dtype=torch.int64).contiguous()
+    return dev, q, k, v, g, beta, lam, cu_seqlens
+
+
+@torch.no_grad()
+def chunk_gated_delta_rule(
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    g: torch.Tensor,
+    beta: torch.Tensor,
+    scale: float = None,
+    initial_state: torch.Tensor = None,
+    output_final_state: bool = False,
+    cu_seqlens: Optional[torch.LongTensor] = None,
+    head_first: bool = False,
+    use_qk_l2norm_in_kernel: bool = False,
+) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
+    """Chunkwise gated-delta-rule forward.
+
+    q, k: [B,T,H,K]; v: [B,T,H,V]; g (log decay), beta: [B,T,H]; initial_state: [N,H,K,V];
+    cu_seqlens: [N+1] with B == 1.  Returns (o [B,T,H,V] in q's dtype, final_state [N,H,K,V]
+    fp32 or None).  Unlike the reference (gated_delta_rule_ori.py:313) fp32 q/k/v are accepted;
+    they are rounded to bf16 as tensor-core operands.
+    """
+    _common_checks(q, k, v, beta, head_first, cu_seqlens, initial_state)
+    if scale is None:
+        scale = k.shape[-1] ** -0.5
+    dev, q, k, v, g, beta, _, cu = _prep_inputs(q, k, v, g, beta, None, cu_seqlens)
+    B, T, H, K = q.shape
+    V = v.shape[-1]
+    N = B if cu is None else len(cu) - 1
+    h0 = None
+    if initial_state is not None:
+        L.require_cuda(initial_state)
+        if tuple(initial_state.shape) != (N, H, K, V):
+            raise ValueError(f"initial_state must be [{N},{H},{K},{V}]")
+        h0 = initial_state.to(torch.float32).contiguous()
+    desc = _desc(q, v, g, None, cu, use_qk_l2norm_in_kernel, scale)
+    o = torch.empty(B, T, H, V, dtype=q.dtype, device=dev)
+    ht = torch.empty(N, H, K, V, dtype=torch.float32, device=dev) if output_final_state else None
+    ws = _workspace(desc, dev)
+    st = L.status_word(dev)
+    rc = L.lib().lampa_gdn_fwd(ctypes.byref(desc), L.ptr(q), L.ptr(k), L.ptr(v), L.ptr(g), L.ptr(beta),
+                               L.ptr(h0), L.ptr(cu), L.ptr(o), L.ptr(ht), L.ptr(ws), ws.numel(),
+                               L.ptr(st), L.stream_ptr(dev))
+    L.check(rc, "lampa_gdn_fwd")
+    if L.debug_checks():
+        L.check_status(dev)
+    return o, ht
+
+
+@torch.no_grad()
+def _hgdn(q, k, v, g, beta, lam, cu_seqlens, use_l2norm):
+    dev, q, k, v, g, beta, lam, cu = _prep_inputs(q, k, v, g, beta, lam, cu_seqlens)
+    B, T, H, K = q.shape
+    V = v.shape[-1]
+    if cu is None and lam.shape[-1] < num_levels_required(T):
+        raise ValueError(f"l has {lam.shape[-1]} levels, a sequence of {T} tokens needs {num_levels_required(T)}")
+    if K > 256:
+        raise NotImplementedError("current kernel does not support head dimension larger than 256.")
+    desc = _desc(q, v, g, lam, cu, use_l2norm, 1.0)
+    o = torch.empty(B, T, H, V, dtype=q.dtype, device=dev)
+    ws = _workspace(desc, dev)
+    st = L.status_word(dev)
+    rc = L.lib().lampa_hgdn_fwd(ctypes.byref(desc), L.ptr(q), L.ptr(k), L.ptr(v), L.ptr(g), L.ptr(beta),
+                                L.ptr(lam), L.ptr(cu), L.ptr(o), L.ptr(ws), ws.numel(), L.ptr(st),
+                                L.stream_ptr(dev))
+    L.check(rc, "lampa_hgdn_fwd")
+    if L.debug_checks():
+        L.check_status(dev)
+    return o
+
+
+def chunk_h_gated_delta_rule(
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    g: torch.Tensor,
+    l: torch.Tensor,
+    beta: torch.Tensor,
+    scale: float = None,
+    initial_state=None,
+    output_final_state: bool = False,
+    cu_seqlens: Optional[torch.LongTensor] = None,
+    head_first: bool = False,
+    use_qk_l2norm_in_kernel: bool = False,
+):
+    """Hierarchical (Fenwick-level) chunkwise gated-delta-rule forward.
+
+    l: [B,T,H,L] level weights.  The reference divides l by `scale` and multiplies the
+    normalised q by it (gated_delta_rule_apis.py:68-70, kernel.py:109-111); the two cancel, so
+    the kernel takes l as given and the result does not depend on `scale`.
+    Beyond the reference: `cu_seqlens` and T not a multiple of 64 are accepted.
+    `output_final_state=True` (the HState prefill/step branches, kernel.py:377-633) is not
+    implemented yet.
+    """
+    _common_checks(q, k, v, beta, head_first, cu_seqlens, None)
+    assert use_qk_l2norm_in_kernel is True
+    if output_final_state or initial_state is not None:
+        raise NotImplementedError("hierarchical final/initial state (HState) is not implemented")
+    return _hgdn(q, k, v, g, beta, l, cu_seqlens, True), None
+
+
+def hattention_kernel(
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    b: Optional[torch.Tensor],
+    g: torch.Tensor,
+    l: torch.Tensor,
+    scale: Optional[float],
+    head_first: bool,
+    level_base: int,
+    htype,
+    hstruct,
+    chunk_sizes=None,
+    chunkwise: bool = True,
+    use_qk_l2norm_in_kernel: bool = False,
+) -> torch.Tensor:
+    """The GDELTA / WEAK / base-2 / chunkwise branch of hattention_kernel (kernel.py:100-120):
+    o = sum over levels of l * (l2norm(q) * scale)^T (...).  Other branches raise, as there."""
+    if getattr(hstruct, "name", hstruct) != "GDELTA" or not chunkwise:
+        raise NotImplementedError
+    if getattr(htype, "name", htype) != "WEAK" or level_base != 2:
+        raise NotImplementedError
+    if b is None:
+        raise ValueError
+    if chunk_sizes is not None and (chunk_sizes[0] != chunk_sizes[1] or chunk_sizes[0] != CHUNK):
+        raise NotImplementedError
+    if not use_qk_l2norm_in_kernel or scale is None or head_first:
+        raise NotImplementedError
+    return _hgdn(q, k, v, g, b, l * scale, None, True)
