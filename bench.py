@@ -1,0 +1,299 @@
+#!/usr/bin/env python
+"""Benchmark of the LSH ordering + hierarchical gated-delta forward on B200.
+
+One step = one pass of the hot path over one synthetic 60k-hit event:
+  E2LSH bucket ids (3 rounds x 8 hashes) -> 24 stable row sorts -> gather of the hit rows by the
+  layer's ordering -> hierarchical (Fenwick-level) chunkwise gated-delta forward (T = 60000 padded
+  to 61440, H = 8, K = V = 64, L = 17, bf16) -> scatter of the mixer output back to hit order.
+Each rank owns one event (event sharding, no data-path collective).
+
+    python bench.py --gpus N --steps K --warmup W            # this library
+    python bench.py --impl reference --steps K --warmup W    # CPU restatement of the reference path
+
+Prints one JSON line (rank 0).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+import numpy as np
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+N_HITS = 60000
+T_PAD = 61440
+H, K, V, LEVELS = 8, 64, 64, 17
+ROUNDS, HEADS = 3, 8
+METRIC = "hits/sec, 60k-hit event LSH+hier. gated-delta fwd"
+WORKLOAD = ("config 3 + config 2: E2LSH ids (3x8) + 24 stable sorts + row gather, then hierarchical "
+            "gated-delta fwd T=60000 (padded 61440) H=8 K=V=64 L=17 bf16, output scattered back")
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"],
+                "bf16_tflops_sustained": d.get("bf16_tflops_sustained", d["bf16_tflops"]), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+def make_event(seed: int):
+    from lampa_b200 import synth
+    inp = synth.gdn_inputs(seed, T_PAD, H, K, V, L=LEVELS, g_shift=2.0)
+    for key in ("k", "v", "beta", "g", "lam"):          # padded tokens are inert
+        inp[key][:, N_HITS:] = 0
+    inp["lam"] = inp["lam"].to(torch.bfloat16)
+    hits = synth.detector_hits(seed + 1000, N_HITS)
+    alpha, beta = synth.lsh_params(seed + 2000, heads=HEADS, dim=6, rounds=ROUNDS)
+    return dict(inp, hits=hits, alpha=alpha, lsh_beta=beta)
+
+
+# ---- clocks sampler (read-only NVML) ----------------------------------------------------------------
+class ClockSampler(threading.Thread):
+    REASONS = {0x1: "gpu_idle", 0x2: "applications_clocks_setting", 0x4: "sw_power_cap", 0x8: "hw_slowdown",
+               0x10: "sync_boost", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown",
+               0x80: "hw_power_brake_slowdown", 0x100: "display_clock_setting"}
+
+    def __init__(self, index: int):
+        super().__init__(daemon=True)
+        self.index, self.samples, self.stop_flag, self.ok = index, [], False, False
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_sm = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+            self.ok = True
+        except Exception:
+            self.max_sm = None
+
+    def run(self):
+        while self.ok and not self.stop_flag:
+            try:
+                sm = self.nv.nvmlDeviceGetClockInfo(self.h, self.nv.NVML_CLOCK_SM)
+                rs = self.nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                self.samples.append((time.perf_counter(), sm, rs))
+            except Exception:
+                pass
+            time.sleep(0.01)
+
+    def summary(self, t0: float, t1: float):
+        if not self.ok:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "note": "NVML unavailable"}
+        inside = [s for s in self.samples if t0 <= s[0] <= t1] or self.samples[-3:]
+        mask = 0
+        for s in inside:
+            mask |= s[2]
+        reasons = [n for b, n in self.REASONS.items() if mask & b and n != "gpu_idle"]
+        return {"sm_mhz": float(np.median([s[1] for s in inside])) if inside else None,
+                "sm_max_mhz": float(self.max_sm), "reasons": reasons, "samples": len(inside)}
+
+
+# ---- CPU restatement of the reference path (checker code, timed as the baseline) ---------------------
+def cpu_pass(ev, n_tokens: int):
+    """One pass of the path over the first n_tokens hits on the host cores; returns seconds."""
+    from oracle import oracle
+    a = [ev[k][0, :n_tokens].float().numpy() for k in ("q", "k", "v", "g", "beta", "lam")]
+    hits = ev["hits"][:n_tokens].numpy()
+    t0 = time.perf_counter()
+    ids = oracle.lsh_ids(hits, ev["alpha"].numpy(), ev["lsh_beta"].numpy(), 1.0)
+    perms = [oracle.segsort(np.ascontiguousarray(ids[r, h])) for r in range(ROUNDS) for h in range(HEADS)]
+    oracle.permute_rows(hits, perms[0])
+    o, _, _ = oracle.hgdn(*a, use_l2norm=True)
+    oracle.permute_rows(o.reshape(n_tokens, -1), oracle.invert_perm(perms[0]))
+    return time.perf_counter() - t0
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    ev = make_event(20252)
+    cores = os.cpu_count() or 1
+    probe_n = 2048
+    probe = cpu_pass(ev, probe_n)
+    budget = 150.0 / max(1, args.steps + args.warmup)
+    n = int(min(N_HITS, max(512, probe_n * budget / max(probe, 1e-6) * 0.6)))
+    n = max(64, n // 64 * 64) if n < N_HITS else N_HITS
+    for _ in range(args.warmup):
+        cpu_pass(ev, n)
+    t = [cpu_pass(ev, n) for _ in range(args.steps)]
+    tot = float(np.sum(t))
+    val = n * args.steps / tot
+    sample = (f"first {n} of {N_HITS} hits of the event per step (fewer hits => fewer Fenwick levels, so this "
+              f"flatters the CPU); C restatement of the reference's token recurrence, OpenMP over heads")
+    line = {"impl": "reference", "metric": METRIC, "value": val, "unit": "hits/s", "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * tot / args.steps,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+            "data": "synthetic", "config": {"workload": WORKLOAD},
+            "cpu_baseline": {"value": val, "unit": "hits/s", "cores": min(cores, H), "kind": "port", "sample": sample},
+            "e2e": {"value": val, "unit": "hits/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+# ---- this library ------------------------------------------------------------------------------------
+def run_ours(args):
+    import torch.distributed as dist
+    import lampa_b200
+    from lampa_b200 import _lib as L
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU path in this library)")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    ev = make_event(20252 + rank)
+    d = {k: v.to(dev) for k, v in ev.items()}
+    pinned = {k: v.pin_memory() for k, v in ev.items() if k not in ("alpha", "lsh_beta")}
+    stage = {k: torch.empty_like(v, device=dev) for k, v in pinned.items()}
+    o_host = torch.empty(N_HITS, H * V, dtype=torch.bfloat16).pin_memory()
+    perm_host = torch.empty(N_HITS, dtype=torch.int64).pin_memory()
+
+    def step(t):
+        ids = lampa_b200.lsh_hash(t["hits"], d["alpha"], d["lsh_beta"], 1.0)["ids"]
+        perm = lampa_b200.segmented_sort(ids, nseg=ROUNDS * HEADS).view(ROUNDS, HEADS, N_HITS)
+        order = perm[0, 0]
+        lampa_b200.permute_rows(t["hits"], order)
+        o, _ = lampa_b200.chunk_h_gated_delta_rule(t["q"], t["k"], t["v"], t["g"], t["lam"], t["beta"],
+                                                   use_qk_l2norm_in_kernel=True)
+        out = lampa_b200.permute_rows(o[0, :N_HITS].reshape(N_HITS, H * V), order, scatter=True)
+        return out, order
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0 = time.perf_counter()
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        barrier()
+        t1 = time.perf_counter()
+        ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item()), t0, t1
+
+    def e2e_step():
+        for kk, hv in pinned.items():
+            stage[kk].copy_(hv, non_blocking=True)
+        out, order = step(stage)
+        o_host.copy_(out, non_blocking=True)
+        perm_host.copy_(order, non_blocking=True)
+
+    sampler = ClockSampler(local)
+    sampler.start()
+    for _ in range(max(args.warmup, 3)):
+        step(d)
+    ms, t0, t1 = timed(lambda: step(d), args.steps)
+    clocks = sampler.summary(t0, t1)
+    L.check_status(dev)
+
+    e2e_steps = max(3, min(args.steps, 50))
+    for _ in range(3):
+        e2e_step()
+    ms_e2e, _, _ = timed(e2e_step, e2e_steps)
+    sampler.stop_flag = True
+
+    # per-kernel durations (CUDA events recorded by the library around each of its launches)
+    prof_steps = max(3, min(args.steps, 20))
+    torch.cuda.synchronize()
+    L.profile_enable(True)
+    for _ in range(prof_steps):
+        step(d)
+    torch.cuda.synchronize()
+    prof = L.profile_read()
+    L.profile_enable(False)
+    L.check_status(dev)
+
+    if rank == 0:
+        pk = peaks()
+        per_kernel = {n: {"ms_per_launch": r["ms"] / r["launches"], "launches_per_step": r["launches"] / prof_steps,
+                          "ms_per_step": r["ms"] / prof_steps} for n, r in prof.items()}
+        tot_k = sum(v["ms_per_step"] for v in per_kernel.values())
+        for v in per_kernel.values():
+            v["share"] = v["ms_per_step"] / tot_k
+        dom = max(per_kernel, key=lambda n: per_kernel[n]["ms_per_step"])
+        n_chunks = T_PAD // 64
+        n_lev = 10
+        alg = {   # algorithmic cost of one launch of each kernel on this workload
+            "gdn_prep_hier": ("tensor", H * n_chunks * (7 * 524288 + 2 * 174763)),
+            "gdn_out_hier": ("tensor", H * n_chunks * (n_lev * 2.5 * 524288)),
+            "gdn_compose": ("tensor", H * n_chunks * 2 * 2 * 64 ** 3),
+            "gdn_level_hier": ("tensor", H * (n_chunks // 32) * 5 * 2 * 64 ** 3),
+            "lsh_hash": ("hbm", N_HITS * 120),
+            "segsort": ("hbm", N_HITS * ROUNDS * HEADS * 68),
+            "permute_rows": ("hbm", N_HITS * (16 + 2 * (96 + H * V * 2)) / 2),
+            "gdn_plan": ("hbm", 64),
+        }
+        bound, units = alg.get(dom, ("hbm", 0))
+        dur_s = per_kernel[dom]["ms_per_launch"] * 1e-3
+        if bound == "tensor":
+            achieved, peak, unit = units / dur_s / 1e12, pk["bf16_tflops"], "TFLOP/s"
+        else:
+            achieved, peak, unit = units / dur_s / 1e9, pk["hbm_gbs"], "GB/s"
+        h2d = int(sum(v.numel() * v.element_size() for v in pinned.values()))
+        d2h = int(o_host.numel() * o_host.element_size() + perm_host.numel() * 8)
+        line = {
+            "metric": METRIC, "value": world * N_HITS * args.steps / (ms * 1e-3), "unit": "hits/s",
+            "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "sharding": "one event per rank, no collective",
+                       "l2": "inputs (~215 MB/step) and intermediates (~375 MB) exceed the 126 MB L2"},
+            "clocks": clocks,
+            "e2e": {"value": world * N_HITS * e2e_steps / (ms_e2e * 1e-3), "unit": "hits/s",
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps},
+            "gpu_launches": int(round(sum(v["launches_per_step"] for v in per_kernel.values()) * args.steps)),
+            "roofline": {"kernel": dom, "bound": bound, "achieved": achieved, "peak": peak, "unit": unit,
+                         "frac": achieved / peak, "traffic": None, "peak_source": pk["source"],
+                         "whole_step_hbm_gbs": N_HITS * 4432 / (ms / args.steps * 1e-3) / 1e9},
+            "kernels": per_kernel,
+        }
+        if world == 1 and not args.no_cpu:
+            cores = os.cpu_count() or 1
+            n = N_HITS if not args.cpu_sample else args.cpu_sample
+            sec = cpu_pass(ev, n)
+            line["cpu_baseline"] = {"value": n / sec, "unit": "hits/s", "cores": min(cores, H), "kind": "port",
+                                    "sample": f"one pass over {n} of {N_HITS} hits of the same event ({sec:.1f} s); "
+                                              "C restatement of the reference's token recurrence, OpenMP over heads"}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=100)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--cpu-sample", type=int, default=0, help="hits in the CPU baseline pass (default: all)")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -159,6 +159,17 @@ int lampa_permute_rows(const void* src, const int64_t* perm, const int64_t* seg_
 int lampa_invert_perm(const int64_t* perm, const int64_t* seg_offsets, int32_t nseg, int64_t n_total,
                       int64_t* inv, void* stream);
 
+/*
+ * Per-kernel timing for benchmarks (no counterpart in the reference, which has no timing code).
+ * lampa_profile_enable(1) makes every later launch of this library record a pair of CUDA events
+ * on its stream; lampa_profile_enable(0) stops and clears.  lampa_profile_read synchronises on
+ * the recorded events and returns, per kernel name ('\n'-separated in `names`), the summed
+ * milliseconds and the number of launches.  Host-side only; not for concurrent use.
+ */
+int lampa_profile_enable(int on);
+int lampa_profile_read(char* names, size_t names_cap, float* total_ms, int32_t* launches,
+                       int32_t max_kernels, int32_t* n_kernels);
+
 #ifdef __cplusplus
 }
 #endif

@@ -35,7 +35,8 @@ class GdnDesc(ctypes.Structure):
 _lib: Optional[ctypes.CDLL] = None
 EXPORTS = ["lampa_version", "lampa_error_string", "lampa_gdn_workspace_bytes", "lampa_gdn_workspace_layout",
            "lampa_gdn_fwd", "lampa_hgdn_fwd", "lampa_lsh_hash", "lampa_segsort_workspace_bytes",
-           "lampa_segsort_stable", "lampa_permute_rows", "lampa_invert_perm"]
+           "lampa_segsort_stable", "lampa_permute_rows", "lampa_invert_perm", "lampa_profile_enable",
+           "lampa_profile_read"]
 
 
 def lib() -> ctypes.CDLL:
@@ -58,6 +59,9 @@ def lib() -> ctypes.CDLL:
         L.lampa_segsort_stable.argtypes = [vp, i32, i64, vp, i32, vp, vp, vp, sz, vp, vp]
         L.lampa_permute_rows.argtypes = [vp, vp, vp, i32, i64, i64, i32, vp, vp]
         L.lampa_invert_perm.argtypes = [vp, vp, i32, i64, vp, vp]
+        L.lampa_profile_enable.argtypes = [ctypes.c_int]
+        L.lampa_profile_read.argtypes = [ctypes.c_char_p, sz, ctypes.POINTER(ctypes.c_float),
+                                         ctypes.POINTER(i32), i32, ctypes.POINTER(i32)]
         for name in EXPORTS:
             if name != "lampa_error_string":
                 getattr(L, name).restype = ctypes.c_int
@@ -124,3 +128,21 @@ def check_status(dev: Optional[torch.device] = None) -> None:
 
 def debug_checks() -> bool:
     return os.environ.get("LAMPA_B200_CHECK", "0") not in ("", "0")
+
+
+def profile_enable(on: bool) -> None:
+    """Turn per-kernel CUDA-event timing inside the library on or off (clears earlier records)."""
+    check(lib().lampa_profile_enable(int(on)), "lampa_profile_enable")
+
+
+def profile_read() -> Dict[str, Dict[str, float]]:
+    """{kernel name: {"ms": summed milliseconds, "launches": count}} since profiling was enabled."""
+    names = ctypes.create_string_buffer(4096)
+    ms = (ctypes.c_float * 64)()
+    cnt = (ctypes.c_int32 * 64)()
+    n = ctypes.c_int32(0)
+    check(lib().lampa_profile_read(names, 4096, ms, cnt, 64, ctypes.byref(n)), "lampa_profile_read")
+    out = {}
+    for i, nm in enumerate(names.value.decode().split("\n")[: n.value]):
+        out[nm] = {"ms": float(ms[i]), "launches": int(cnt[i])}
+    return out

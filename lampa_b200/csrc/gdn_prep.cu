@@ -4,6 +4,7 @@
 // 64x64 unit-lower-triangular inverse is an fp32 substitution on CUDA cores, as in the reference
 // (models/hattention/solve_tril.py:54-61, 175-197), because bf16 there is where parity breaks.
 #include "gdn.cuh"
+#include "profile.cuh"
 
 namespace lampa {
 
@@ -30,6 +31,7 @@ __global__ void plan_kernel(PlanArgs p) {
 }
 
 int launch_plan(const PlanArgs& p, cudaStream_t st) {
+    ProfScope prof("gdn_plan", st);
     plan_kernel<<<1, 32, 0, st>>>(p);
     return cudaGetLastError() == cudaSuccess ? LAMPA_OK : LAMPA_ERR_CUDA;
 }
@@ -428,6 +430,7 @@ int launch_prep(const GdnArgs& a, bool hier, cudaStream_t st) {
     const int smem = S::bytes(hier ? a.L : 0);
     dim3 grid(a.nc_max, a.H);
     cudaError_t e;
+    ProfScope prof(hier ? "gdn_prep_hier" : "gdn_prep_plain", st);
     if (hier) {
         e = cudaFuncSetAttribute(gdn_prep_kernel<KD, VD, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return LAMPA_ERR_CUDA;

@@ -12,6 +12,7 @@
 // slabs never synchronise with each other.  Records stream through shared memory by bulk async
 // copies (cp.async.bulk + mbarrier), a few chunks ahead of the math.
 #include "gdn.cuh"
+#include "profile.cuh"
 
 namespace lampa {
 
@@ -550,6 +551,7 @@ static int launch_compose(const GdnArgs& a, cudaStream_t st) {
     using R = Rec<KD, VD>;
     const int smem = 128 + 3 * R::MB_BYTES;
     LAMPA_TRY(set_smem(gdn_compose_kernel<KD, VD>, smem));
+    ProfScope prof("gdn_compose", st);
     gdn_compose_kernel<KD, VD><<<dim3(a.nb_max, a.H), (KD + VD) * 2, smem, st>>>(a);
     LAMPA_LAUNCHED();
     return LAMPA_OK;
@@ -562,12 +564,14 @@ int launch_scan_plain(const GdnArgs& a, cudaStream_t st) {
     {
         const int smem = 128 + 3 * R::BLK_BYTES;
         LAMPA_TRY(set_smem(gdn_level_kernel<KD, VD, false>, smem));
+        ProfScope prof("gdn_level_plain", st);
         gdn_level_kernel<KD, VD, false><<<dim3(a.nseq, a.H, 1), VD * 2, smem, st>>>(a);
         LAMPA_LAUNCHED();
     }
     {
         const int smem = 128 + 3 * R::LAM_OFF;
         LAMPA_TRY(set_smem(gdn_out_plain_kernel<KD, VD>, smem));
+        ProfScope prof("gdn_out_plain", st);
         gdn_out_plain_kernel<KD, VD><<<dim3(a.nb_max, a.H), VD * 2, smem, st>>>(a);
         LAMPA_LAUNCHED();
     }
@@ -581,6 +585,7 @@ static int launch_out_hier(const GdnArgs& a, cudaStream_t st) {
     const int smem = 128 + 3 * stage + (NG - 1) * (VD / 16) * 4096;
     if (smem > 227 * 1024) return LAMPA_ERR_UNSUPPORTED;
     LAMPA_TRY(set_smem(gdn_out_hier_kernel<KD, VD, NG>, smem));
+    ProfScope prof("gdn_out_hier", st);
     gdn_out_hier_kernel<KD, VD, NG><<<dim3(a.nb_max, a.H), NG * VD * 2, smem, st>>>(a);
     LAMPA_LAUNCHED();
     return LAMPA_OK;
@@ -595,6 +600,7 @@ int launch_scan_hier(const GdnArgs& a, cudaStream_t st) {
         LAMPA_TRY((launch_compose<KD, VD>(a, st)));
         const int smem = 128 + 3 * R::BLK_BYTES;
         LAMPA_TRY(set_smem(gdn_level_kernel<KD, VD, true>, smem));
+        ProfScope prof("gdn_level_hier", st);
         gdn_level_kernel<KD, VD, true><<<dim3(a.nseq, a.H, a.nhigh_max), VD * 2, smem, st>>>(a);
         LAMPA_LAUNCHED();
     }

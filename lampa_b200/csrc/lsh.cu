@@ -5,6 +5,7 @@
 #include <algorithm>
 
 #include "common.cuh"
+#include "profile.cuh"
 
 namespace cg = cooperative_groups;
 
@@ -286,6 +287,7 @@ extern "C" int lampa_lsh_hash(const float* x, int64_t row_stride, int64_t head_s
     if (N == 0) return LAMPA_OK;
     cudaStream_t st = (cudaStream_t)stream;
     const unsigned grid = (unsigned)((N + HASH_THREADS - 1) / HASH_THREADS);
+    ProfScope prof("lsh_hash", st);
     if (dim == 6 && head_stride == 0)
         lsh_hash_kernel<6><<<grid, HASH_THREADS, 0, st>>>(x, row_stride, head_stride, alpha, beta, w, N, heads, rounds, dim, ids, keys, packed);
     else
@@ -317,6 +319,7 @@ extern "C" int lampa_segsort_stable(const void* keys, int32_t key_type, int64_t 
     uint32_t* k1 = (uint32_t*)(base + stride);
     uint32_t* i0 = (uint32_t*)(base + 2 * stride);
     uint32_t* i1 = (uint32_t*)(base + 3 * stride);
+    ProfScope prof("segsort", (cudaStream_t)stream);
     segsort_kernel<<<(unsigned)nseg * SORT_CL, SORT_THREADS, 0, (cudaStream_t)stream>>>(
         keys, key_type, n_total, seg_offsets, nseg, init, perm, k0, k1, i0, i1);
     return cudaGetLastError() == cudaSuccess ? LAMPA_OK : LAMPA_ERR_CUDA;
@@ -334,6 +337,7 @@ extern "C" int lampa_permute_rows(const void* src, const int64_t* perm, const in
     const int64_t upr = v16 ? row_bytes / 16 : row_bytes / 4;
     const int64_t total = n_rows * upr;
     const unsigned grid = (unsigned)std::min<int64_t>((total + 255) / 256, 148 * 32);
+    ProfScope prof("permute_rows", st);
     if (v16)
         permute_rows_kernel<uint4><<<grid, 256, 0, st>>>((const uint4*)src, perm, seg_offsets, nseg, n_rows, upr, scatter, (uint4*)dst);
     else
@@ -348,6 +352,7 @@ extern "C" int lampa_invert_perm(const int64_t* perm, const int64_t* seg_offsets
     if (!perm || !inv) return LAMPA_ERR_ARG;
     if (!seg_offsets && n_total % nseg != 0) return LAMPA_ERR_ARG;
     const unsigned grid = (unsigned)std::min<int64_t>((n_total + 255) / 256, 148 * 32);
+    ProfScope prof("invert_perm", (cudaStream_t)stream);
     invert_perm_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(perm, seg_offsets, nseg, n_total, inv);
     return cudaGetLastError() == cudaSuccess ? LAMPA_OK : LAMPA_ERR_CUDA;
 }

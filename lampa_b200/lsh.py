@@ -75,7 +75,7 @@ def segmented_sort(keys: torch.Tensor, seg_offsets: Optional[torch.Tensor] = Non
     indices local to each segment.  With `init` (a starting order per segment) the result is
     init[stable_sort(keys[init])] — the norm pre-sort followed by the key sort of LSHOrdering.
     """
-    dev = L.require_cuda(keys, seg_offsets, init)
+    dev = L.require_cuda(keys, init)
     if keys.dtype == torch.int32:
         kt = L.LAMPA_KEY_I32
     elif keys.dtype == torch.float32:
@@ -105,7 +105,7 @@ def segmented_sort(keys: torch.Tensor, seg_offsets: Optional[torch.Tensor] = Non
 def permute_rows(src: torch.Tensor, perm: torch.Tensor, seg_offsets: Optional[torch.Tensor] = None,
                  nseg: int = 1, scatter: bool = False) -> torch.Tensor:
     """dst[s0+i] = src[s0+perm[s0+i]] per segment (or the scatter form); src is [rows, ...]."""
-    dev = L.require_cuda(src, perm, seg_offsets)
+    dev = L.require_cuda(src, perm)
     src = src.contiguous()
     rows = perm.numel()
     if src.shape[0] != rows:
