@@ -36,6 +36,14 @@ WORKLOAD = ("config 3 + config 2: E2LSH ids (3x8) + 24 stable sorts + row gather
             "gated-delta fwd T=60000 (padded 61440) H=8 K=V=64 L=17 bf16, output scattered back")
 
 
+def set_event_size(n_hits: int) -> None:
+    """Scale the event down (profiler captures, quick checks); the default is the 60k-hit workload."""
+    global N_HITS, T_PAD, WORKLOAD
+    N_HITS = n_hits
+    T_PAD = (n_hits + 1023) // 1024 * 1024
+    WORKLOAD = WORKLOAD.replace("T=60000 (padded 61440)", f"T={N_HITS} (padded {T_PAD})") + " [reduced event]"
+
+
 def peaks():
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(p):
@@ -209,9 +217,11 @@ def run_ours(args):
     L.check_status(dev)
 
     e2e_steps = max(3, min(args.steps, 50))
-    for _ in range(3):
-        e2e_step()
-    ms_e2e, _, _ = timed(e2e_step, e2e_steps)
+    ms_e2e = None
+    if not args.no_e2e:
+        for _ in range(3):
+            e2e_step()
+        ms_e2e, _, _ = timed(e2e_step, e2e_steps)
     sampler.stop_flag = True
 
     # per-kernel durations (CUDA events recorded by the library around each of its launches)
@@ -234,7 +244,7 @@ def run_ours(args):
             v["share"] = v["ms_per_step"] / tot_k
         dom = max(per_kernel, key=lambda n: per_kernel[n]["ms_per_step"])
         n_chunks = T_PAD // 64
-        n_lev = 10
+        n_lev = max(1, (n_chunks - 1).bit_length())
         alg = {   # algorithmic cost of one launch of each kernel on this workload
             "gdn_prep_hier": ("tensor", H * n_chunks * (7 * 524288 + 2 * 174763)),
             "gdn_out_hier": ("tensor", H * n_chunks * (n_lev * 2.5 * 524288)),
@@ -260,8 +270,9 @@ def run_ours(args):
             "config": {"workload": WORKLOAD, "sharding": "one event per rank, no collective",
                        "l2": "inputs (~215 MB/step) and intermediates (~375 MB) exceed the 126 MB L2"},
             "clocks": clocks,
-            "e2e": {"value": world * N_HITS * e2e_steps / (ms_e2e * 1e-3), "unit": "hits/s",
-                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps},
+            "e2e": None if ms_e2e is None else {
+                "value": world * N_HITS * e2e_steps / (ms_e2e * 1e-3), "unit": "hits/s",
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps},
             "gpu_launches": int(round(sum(v["launches_per_step"] for v in per_kernel.values()) * args.steps)),
             "roofline": {"kernel": dom, "bound": bound, "achieved": achieved, "peak": peak, "unit": unit,
                          "frac": achieved / peak, "traffic": None, "peak_source": pk["source"],
@@ -288,7 +299,11 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--cpu-sample", type=int, default=0, help="hits in the CPU baseline pass (default: all)")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer (end-to-end) leg")
+    ap.add_argument("--hits", type=int, default=N_HITS, help="hits of the event (default: the 60k-hit workload)")
     args = ap.parse_args()
+    if args.hits != N_HITS:
+        set_event_size(args.hits)
     if args.impl == "reference":
         run_reference(args)
     else:

@@ -150,7 +150,9 @@ segsort_kernel(const void* __restrict__ keys, int key_type, int64_t n_total,
         for (int d = tid; d < 256; d += SORT_THREADS) hist[d] = 0;
         __syncthreads();
         for (int64_t i = lo + tid; i < hi; i += SORT_THREADS) {
-            const uint32_t u = (p == 0) ? (key_xform(keys, key_type, s0 + i) - gmn) : ksrc[s0 + i];
+            uint32_t u;
+            if (p == 0) u = key_xform(keys, key_type, s0 + (init ? init[s0 + i] : i)) - gmn;   // position i holds element init[i]
+            else u = ksrc[s0 + i];
             atomicAdd(&hist[(u >> shift) & 255u], 1u);
         }
         __syncthreads();
@@ -187,8 +189,8 @@ segsort_kernel(const void* __restrict__ keys, int key_type, int64_t n_total,
             uint32_t u = 0, idx = 0;
             if (valid) {
                 if (p == 0) {
-                    u = key_xform(keys, key_type, s0 + i) - gmn;
                     idx = init ? (uint32_t)init[s0 + i] : (uint32_t)i;
+                    u = key_xform(keys, key_type, s0 + idx) - gmn;
                 } else {
                     u = ksrc[s0 + i];
                     idx = isrc[s0 + i];
