@@ -128,6 +128,30 @@ __device__ __forceinline__ void warp_gemm(float (&acc)[NT8][4], const __nv_bfloa
     }
 }
 
+// Same with the A operand already in registers: afrag[kk] is the A fragment of k-step kk (for a
+// 16-row tile held as accumulators C[nt][4], afrag[kk] = {pack(C[2kk][0..1]), pack(C[2kk][2..3]),
+// pack(C[2kk+1][0..1]), pack(C[2kk+1][2..3])}).
+template <int NT8, int KSTEPS, bool B_T>
+__device__ __forceinline__ void warp_gemm_ra(float (&acc)[NT8][4], const uint32_t (&afrag)[KSTEPS][4],
+                                             const __nv_bfloat16* sB, int ldb, int n0, int lane,
+                                             int k_end = KSTEPS * 16, int n_end = NT8 * 8) {
+    static_assert(NT8 % 2 == 0, "tile shape");
+#pragma unroll
+    for (int kk = 0; kk < KSTEPS; ++kk) {
+        if (kk * 16 < k_end) {
+#pragma unroll
+            for (int nt = 0; nt < NT8; nt += 2) {
+                if (nt * 8 < n_end) {
+                    uint32_t b[4];
+                    if (B_T) load_b_t(b, sB, ldb, n0 + nt * 8, kk * 16, lane); else load_b(b, sB, ldb, n0 + nt * 8, kk * 16, lane);
+                    mma16816(acc[nt], afrag[kk], b[0], b[1]);
+                    mma16816(acc[nt + 1], afrag[kk], b[2], b[3]);
+                }
+            }
+        }
+    }
+}
+
 // ---- mbarrier + bulk async copy (TMA, untiled form) -------------------------------------------
 __device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" :: "r"(smem_u32(bar)), "r"(count));

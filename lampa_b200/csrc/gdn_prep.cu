@@ -40,18 +40,15 @@ int launch_plan(const PlanArgs& p, cudaStream_t st) {
 template <int KD, int VD>
 struct PrepSmem {
     static constexpr int KP = KD + 8, VP = VD + 8, CP = CHUNK + 8;
-    static constexpr int Q = 0;                                  // bf16 [64][KP]   q (normalised)
-    static constexpr int K = Q + CHUNK * KP * 2;                 // bf16 [64][KP]   k, later K~
-    static constexpr int KB = K + CHUNK * KP * 2;                // bf16 [64][KP]   beta*k
-    static constexpr int VB = KB + CHUNK * KP * 2;               // bf16 [64][VP]   beta*v
-    static constexpr int AT = VB + CHUNK * VP * 2;               // fp32 [64][72]   A0^T; later Aw|Au bf16 [64][CP] each
+    static constexpr int Q = 0;                                  // bf16 [64][KP]   q (normalised); later W (rows are warp-private)
+    static constexpr int K = Q + CHUNK * KP * 2;                 // bf16 [64][KP]   k (normalised)
+    static constexpr int V = K + CHUNK * KP * 2;                 // bf16 [64][VP]   v
+    static constexpr int AT = V + CHUNK * VP * 2;                // fp32 [64][72]   A0^T; later Awb|Aub bf16 [64][CP] each
     static constexpr int AW = AT;
     static constexpr int AU = AT + CHUNK * CP * 2;
-    static constexpr int P = AT + CHUNK * CP * 4;                // bf16 [64][CP]   tril(QK^T) .* E
-    static constexpr int QK = P + CHUNK * CP * 2;                // bf16 [64][CP]   tril(QK^T) raw; later Pm (hier)
-    static constexpr int WT = QK + CHUNK * CP * 2;               // bf16 [64][KP]   W~
-    static constexpr int U = WT + CHUNK * KP * 2;                // bf16 [64][VP]   U
-    static constexpr int G = U + CHUNK * VP * 2;                 // fp32 [64] G, [64] beta, [64] e^G, [64] e^{Glast-G}
+    static constexpr int QK = AT + CHUNK * CP * 4;               // bf16 [64][CP]   tril(Q K^T)
+    static constexpr int UH = QK + CHUNK * CP * 2;               // bf16 [64][VP]   diag(e^{Glast-G}) U
+    static constexpr int G = UH + CHUNK * VP * 2;                // fp32 [64] G, [64] beta, [64] e^G, [64] e^{Glast-G}
     static constexpr int LAM = G + 4 * CHUNK * 4;                // fp32 [64][L+1]
     static int bytes(int L) { return LAM + CHUNK * (L + 1) * 4; }
 };
@@ -102,25 +99,34 @@ __device__ __forceinline__ void store_half_row_bf16(__nv_bfloat16* dst, const fl
     }
 }
 
-__device__ __forceinline__ float bf16_round(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+template <int N>
+__device__ __forceinline__ void zero_acc(float (&acc)[N][4]) {
+#pragma unroll
+    for (int i = 0; i < N; ++i) { acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f; }
+}
 
+// With beta folded into the columns of the inverse (Awb = (I + A0)^-1 diag(beta), Aub = Awb .* E):
+//   W  = Awb K                    M   = e^{G_last} (I - K^T W)
+//   U^ = diag(e^{G_last-G}) Aub V B^T = U^^T K
+//   R  = tril(Q K^T) Awb          Q~  = s diag(e^G) (Q - R K)
+//   O_local = s ((R .* E .* lambda[i][level(i,j)]) V)
+// (s = scale and lambda = 1 for the plain rule; s = 1 for the hierarchical one).  These equal
+// the definitions in gdn.cuh: every e^{G_last-G_tok} e^{G_tok} pair collapses to e^{G_last}.
 template <int KD, int VD, bool HIER>
-__global__ void __launch_bounds__(128) gdn_prep_kernel(GdnArgs a) {
+__global__ void __launch_bounds__(128, 3) gdn_prep_kernel(GdnArgs a) {
     using S = PrepSmem<KD, VD>;
     using R = Rec<KD, VD>;
     constexpr int KP = S::KP, VP = S::VP, CP = S::CP;
     extern __shared__ __align__(128) unsigned char smem[];
     __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(smem + S::Q);
+    __nv_bfloat16* sW = sQ;
     __nv_bfloat16* sK = reinterpret_cast<__nv_bfloat16*>(smem + S::K);
-    __nv_bfloat16* sKb = reinterpret_cast<__nv_bfloat16*>(smem + S::KB);
-    __nv_bfloat16* sVb = reinterpret_cast<__nv_bfloat16*>(smem + S::VB);
+    __nv_bfloat16* sV = reinterpret_cast<__nv_bfloat16*>(smem + S::V);
     float* sAT = reinterpret_cast<float*>(smem + S::AT);
     __nv_bfloat16* sAw = reinterpret_cast<__nv_bfloat16*>(smem + S::AW);
     __nv_bfloat16* sAu = reinterpret_cast<__nv_bfloat16*>(smem + S::AU);
-    __nv_bfloat16* sP = reinterpret_cast<__nv_bfloat16*>(smem + S::P);
     __nv_bfloat16* sQK = reinterpret_cast<__nv_bfloat16*>(smem + S::QK);
-    __nv_bfloat16* sWt = reinterpret_cast<__nv_bfloat16*>(smem + S::WT);
-    __nv_bfloat16* sU = reinterpret_cast<__nv_bfloat16*>(smem + S::U);
+    __nv_bfloat16* sUh = reinterpret_cast<__nv_bfloat16*>(smem + S::UH);
     float* sG = reinterpret_cast<float*>(smem + S::G);
     float* sBeta = sG + CHUNK;
     float* sEG = sG + 2 * CHUNK;
@@ -136,15 +142,12 @@ __global__ void __launch_bounds__(128) gdn_prep_kernel(GdnArgs a) {
     const int len = (int)min((int64_t)CHUNK, a.tok_off[seq + 1] - t0);
     const int LP = a.L + 1;
 
-    // ---- stage 0: loads, l2norm, beta scaling, cumulative decay -------------------------------
+    // ---- stage 0: loads, l2norm, cumulative decay -------------------------------------------------
     {
         const int r = tid >> 1, half = tid & 1;
         const bool valid = r < len;
         const size_t tok = (size_t)(t0 + r);
-        float bet = 0.f;
-        if (valid) bet = load_as_float(a.beta, tok * H + h, a.gb_dt);
         float x[KD / 2];
-        // q
         load_half_row<KD>(a.q, a.qkv_dt, (tok * H + h) * KD + half * (KD / 2), valid, x);
         if (a.use_l2norm) {
             float ss = 0.f;
@@ -156,7 +159,6 @@ __global__ void __launch_bounds__(128) gdn_prep_kernel(GdnArgs a) {
             for (int i = 0; i < KD / 2; ++i) x[i] *= rn;
         }
         store_half_row_bf16<KD / 2>(sQ + r * KP + half * (KD / 2), x);
-        // k and beta*k (beta applied to the rounded k, as chunk_scaled_dot_kkt.py:60-61 does)
         load_half_row<KD>(a.k, a.qkv_dt, (tok * H + h) * KD + half * (KD / 2), valid, x);
         if (a.use_l2norm) {
             float ss = 0.f;
@@ -168,15 +170,13 @@ __global__ void __launch_bounds__(128) gdn_prep_kernel(GdnArgs a) {
             for (int i = 0; i < KD / 2; ++i) x[i] *= rn;
         }
         store_half_row_bf16<KD / 2>(sK + r * KP + half * (KD / 2), x);
-#pragma unroll
-        for (int i = 0; i < KD / 2; ++i) x[i] = bf16_round(x[i]) * bet;
-        store_half_row_bf16<KD / 2>(sKb + r * KP + half * (KD / 2), x);
-        // beta*v
         float y[VD / 2];
         load_half_row<VD>(a.v, a.qkv_dt, (tok * H + h) * VD + half * (VD / 2), valid, y);
-#pragma unroll
-        for (int i = 0; i < VD / 2; ++i) y[i] *= bet;
-        store_half_row_bf16<VD / 2>(sVb + r * VP + half * (VD / 2), y);
+        store_half_row_bf16<VD / 2>(sV + r * VP + half * (VD / 2), y);
+        if (HIER) {
+            for (int l = half; l < a.L; l += 2)
+                sLam[r * LP + l] = valid ? load_as_float(a.lam, (tok * H + h) * a.L + l, a.lam_dt) : 0.f;
+        }
     }
     if (tid < CHUNK) {
         const bool valid = tid < len;
@@ -191,20 +191,12 @@ __global__ void __launch_bounds__(128) gdn_prep_kernel(GdnArgs a) {
             const float y = __shfl_up_sync(0xffffffffu, cs, o);
             if (lane >= o) cs += y;
         }
-        if (tid == 31) sG[CHUNK - 1] = cs;      // borrowed as a one-float mailbox between the two warps
+        if (tid == 31) sG[CHUNK - 1] = cs;      // one-float mailbox between the two warps
         sBeta[tid] = bv;
         asm volatile("bar.sync 1, 64;\n" ::: "memory");
         const float carry = (warp == 1) ? sG[CHUNK - 1] : 0.f;
         asm volatile("bar.sync 1, 64;\n" ::: "memory");
         sG[tid] = cs + carry;
-    }
-    if (HIER) {
-        for (int idx = tid; idx < CHUNK * a.L; idx += 128) {
-            const int r = idx / a.L, l = idx - r * a.L;
-            float lv = 0.f;
-            if (r < len) lv = load_as_float(a.lam, ((size_t)(t0 + r) * H + h) * a.L + l, a.lam_dt);
-            sLam[r * LP + l] = lv;
-        }
     }
     __syncthreads();
     if (tid < CHUNK) {
@@ -222,11 +214,10 @@ __global__ void __launch_bounds__(128) gdn_prep_kernel(GdnArgs a) {
     }
 
     const int m0 = warp * 16;
-    // ---- stage 1: K K^T -> A0^T (fp32), Q K^T -> P = tril .* E and the raw tril -----------------
+    // ---- stage 1: K K^T -> A0^T (fp32, strictly lower, rows scaled by beta); Q K^T -> tril, bf16 ---
     {
         float acc[8][4];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) { acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f; }
+        zero_acc<8>(acc);
         warp_gemm<8, KD, false, false>(acc, sK, KP, m0, sK, KP, 0, lane, KD, m0 + 16);
 #pragma unroll
         for (int nt = 0; nt < 8; ++nt) {
@@ -236,100 +227,165 @@ __global__ void __launch_bounds__(128) gdn_prep_kernel(GdnArgs a) {
                 if (nt * 8 < m0 + 16) sAT[j * CP + i] = (i > j) ? sBeta[i] * acc[nt][e] : 0.f;
             }
         }
-#pragma unroll
-        for (int i = 0; i < 8; ++i) { acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f; }
+        zero_acc<8>(acc);
         warp_gemm<8, KD, false, false>(acc, sQ, KP, m0, sK, KP, 0, lane, KD, m0 + 16);
 #pragma unroll
         for (int nt = 0; nt < 8; ++nt) {
 #pragma unroll
             for (int hh = 0; hh < 2; ++hh) {
                 const int i = m0 + gq + hh * 8, j = nt * 8 + 2 * tq;
-                const float Gi = sG[i];
-                float p0 = 0.f, p1 = 0.f, r0 = 0.f, r1 = 0.f;
-                if (i >= j) { r0 = acc[nt][2 * hh]; p0 = r0 * __expf(Gi - sG[j]); }
-                if (i >= j + 1) { r1 = acc[nt][2 * hh + 1]; p1 = r1 * __expf(Gi - sG[j + 1]); }
-                *reinterpret_cast<uint32_t*>(sP + i * CP + j) = pack_bf16x2(p0, p1);
-                if (HIER) *reinterpret_cast<uint32_t*>(sQK + i * CP + j) = pack_bf16x2(r0, r1);
+                const float r0 = (i >= j) ? acc[nt][2 * hh] : 0.f;
+                const float r1 = (i >= j + 1) ? acc[nt][2 * hh + 1] : 0.f;
+                *reinterpret_cast<uint32_t*>(sQK + i * CP + j) = pack_bf16x2(r0, r1);
             }
         }
     }
     __syncthreads();
 
-    // ---- stage 2: Aw = (I + A0)^-1 by column (threads 0..63); K~ in place (threads 64..127) -----
-    if (tid < CHUNK) {
-        const int col = tid;
-        float r[CHUNK];
+    // ---- stage 2: X = (I + A0)^-1, two threads per column (lanes 2c, 2c+1 split the rows in
+    // alternating groups of four); right-looking substitution: once x_j is final, every later
+    // row takes its update x_i -= A0[i][j] x_j, all independent of each other.
+    {
+        const int col = tid >> 1, half = tid & 1;
+        float r[8][4];
 #pragma unroll
-        for (int i = 0; i < CHUNK; ++i) r[i] = (i == col) ? 1.f : 0.f;
+        for (int m = 0; m < 8; ++m)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) r[m][e] = (8 * m + 4 * half + e == col) ? 1.f : 0.f;
 #pragma unroll
         for (int j = 0; j < CHUNK - 1; ++j) {
-            const float rj = r[j];
+            const int mb = j >> 3, hj = (j >> 2) & 1, ej = j & 3;
+            const float rj = __shfl_sync(0xffffffffu, r[mb][ej], (lane & ~1) | hj);
+            {
+                const int i0 = 8 * mb + 4 * half;
+                const float4 av = *reinterpret_cast<const float4*>(sAT + j * CP + i0);
+                r[mb][0] -= (i0 + 0 > j ? av.x : 0.f) * rj;
+                r[mb][1] -= (i0 + 1 > j ? av.y : 0.f) * rj;
+                r[mb][2] -= (i0 + 2 > j ? av.z : 0.f) * rj;
+                r[mb][3] -= (i0 + 3 > j ? av.w : 0.f) * rj;
+            }
 #pragma unroll
-            for (int i4 = ((j + 1) / 4) * 4; i4 < CHUNK; i4 += 4) {
-                const float4 av = *reinterpret_cast<const float4*>(sAT + j * CP + i4);
-                if (i4 + 0 > j) r[i4 + 0] -= av.x * rj;
-                if (i4 + 1 > j) r[i4 + 1] -= av.y * rj;
-                if (i4 + 2 > j) r[i4 + 2] -= av.z * rj;
-                if (i4 + 3 > j) r[i4 + 3] -= av.w * rj;
+            for (int m = mb + 1; m < 8; ++m) {
+                const float4 av = *reinterpret_cast<const float4*>(sAT + j * CP + 8 * m + 4 * half);
+                r[m][0] -= av.x * rj; r[m][1] -= av.y * rj; r[m][2] -= av.z * rj; r[m][3] -= av.w * rj;
             }
         }
-        asm volatile("bar.sync 1, 64;\n" ::: "memory");   // all columns done reading A0^T before it is overwritten
-        const float Gc = sG[col];
+        __syncthreads();   // everyone is done reading A0^T; its storage now takes Awb and Aub
+        const float Gc = sG[col], bc = sBeta[col];
 #pragma unroll
-        for (int i = 0; i < CHUNK; ++i) {
-            sAw[i * CP + col] = __float2bfloat16_rn(r[i]);
-            const float e = (i >= col) ? r[i] * __expf(sG[i] - Gc) : 0.f;
-            sAu[i * CP + col] = __float2bfloat16_rn(e);
-        }
-    } else {
-        const int r = tid - CHUNK;
-        const float f = sEGl[r];
+        for (int m = 0; m < 8; ++m)
 #pragma unroll
-        for (int d = 0; d < KD; d += 2) {
-            uint32_t* p = reinterpret_cast<uint32_t*>(sK + r * KP + d);
-            const float2 kv = unpack_bf16x2(*p);
-            *p = pack_bf16x2(kv.x * f, kv.y * f);
-        }
-    }
-    __syncthreads();
-
-    // ---- stage 3: W~ = diag(e^G) Aw (beta K),  U = Au (beta V) ----------------------------------
-    {
-        float acc[KD / 8][4];
-#pragma unroll
-        for (int i = 0; i < KD / 8; ++i) { acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f; }
-        warp_gemm<KD / 8, CHUNK, false, true>(acc, sAw, CP, m0, sKb, KP, 0, lane, m0 + 16, KD);
-#pragma unroll
-        for (int nt = 0; nt < KD / 8; ++nt)
-#pragma unroll
-            for (int hh = 0; hh < 2; ++hh) {
-                const int i = m0 + gq + hh * 8, j = nt * 8 + 2 * tq;
-                const float f = sEG[i];
-                *reinterpret_cast<uint32_t*>(sWt + i * KP + j) = pack_bf16x2(acc[nt][2 * hh] * f, acc[nt][2 * hh + 1] * f);
-            }
-    }
-    {
-        float acc[VD / 8][4];
-#pragma unroll
-        for (int i = 0; i < VD / 8; ++i) { acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f; }
-        warp_gemm<VD / 8, CHUNK, false, true>(acc, sAu, CP, m0, sVb, VP, 0, lane, m0 + 16, VD);
-#pragma unroll
-        for (int nt = 0; nt < VD / 8; ++nt)
-#pragma unroll
-            for (int hh = 0; hh < 2; ++hh) {
-                const int i = m0 + gq + hh * 8, j = nt * 8 + 2 * tq;
-                *reinterpret_cast<uint32_t*>(sU + i * VP + j) = pack_bf16x2(acc[nt][2 * hh], acc[nt][2 * hh + 1]);
+            for (int e = 0; e < 4; ++e) {
+                const int i = 8 * m + 4 * half + e;
+                const float x = r[m][e] * bc;
+                sAw[i * CP + col] = __float2bfloat16_rn(x);
+                sAu[i * CP + col] = __float2bfloat16_rn((i >= col) ? x * __expf(sG[i] - Gc) : 0.f);
             }
     }
     __syncthreads();
 
-    // ---- stage 4: the record ---------------------------------------------------------------------
-    // M[a][b] = e^{G_last} delta_ab - sum_tok K~[tok][a] W~[tok][b]
+    const float osc = HIER ? 1.f : a.scale;
+    // ---- stage 3 (rows m0..m0+15 of everything; nothing leaves the warp) --------------------------
+    {
+        // R = tril(QK^T) Awb, kept as accumulators and re-used as an A operand twice
+        float racc[8][4];
+        zero_acc<8>(racc);
+        warp_gemm<8, CHUNK, false, true>(racc, sQK, CP, m0, sAw, CP, 0, lane, m0 + 16, m0 + 16);
+        uint32_t ra[4][4];
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) {
+            ra[kk][0] = pack_bf16x2(racc[2 * kk][0], racc[2 * kk][1]);
+            ra[kk][1] = pack_bf16x2(racc[2 * kk][2], racc[2 * kk][3]);
+            ra[kk][2] = pack_bf16x2(racc[2 * kk + 1][0], racc[2 * kk + 1][1]);
+            ra[kk][3] = pack_bf16x2(racc[2 * kk + 1][2], racc[2 * kk + 1][3]);
+        }
+        // Q~ = s e^G (Q - R K)
+        {
+            float acc[KD / 8][4];
+            zero_acc<KD / 8>(acc);
+            warp_gemm_ra<KD / 8, 4, true>(acc, ra, sK, KP, 0, lane, m0 + 16, KD);
+            __nv_bfloat16* gQ = reinterpret_cast<__nv_bfloat16*>(rec + R::QT_OFF);
+#pragma unroll
+            for (int nt = 0; nt < KD / 8; ++nt)
+#pragma unroll
+                for (int hh = 0; hh < 2; ++hh) {
+                    const int i = m0 + gq + hh * 8, j = nt * 8 + 2 * tq;
+                    const float f = osc * sEG[i];
+                    const float2 qv = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(sQ + i * KP + j));
+                    *reinterpret_cast<uint32_t*>(gQ + i * KP + j) =
+                        pack_bf16x2(f * (qv.x - acc[nt][2 * hh]), f * (qv.y - acc[nt][2 * hh + 1]));
+                }
+        }
+        // Pm = R .* E .* lambda, as A fragments;  O_local = s Pm V
+        {
+#pragma unroll
+            for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int i = m0 + gq + (e >> 1) * 8, j = nt * 8 + 2 * tq + (e & 1);
+                    float p = 0.f;
+                    if (i >= j && nt * 8 < m0 + 16) {
+                        p = racc[nt][e] * __expf(sG[i] - sG[j]);
+                        if (HIER) p *= sLam[i * LP + (32 - __clz(i ^ j))];
+                    }
+                    racc[nt][e] = p;
+                }
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk) {
+                ra[kk][0] = pack_bf16x2(racc[2 * kk][0], racc[2 * kk][1]);
+                ra[kk][1] = pack_bf16x2(racc[2 * kk][2], racc[2 * kk][3]);
+                ra[kk][2] = pack_bf16x2(racc[2 * kk + 1][0], racc[2 * kk + 1][1]);
+                ra[kk][3] = pack_bf16x2(racc[2 * kk + 1][2], racc[2 * kk + 1][3]);
+            }
+            float acc[VD / 8][4];
+            zero_acc<VD / 8>(acc);
+            warp_gemm_ra<VD / 8, 4, true>(acc, ra, sV, VP, 0, lane, m0 + 16, VD);
+            float* gO = reinterpret_cast<float*>(rec + R::OL_OFF);
+#pragma unroll
+            for (int nt = 0; nt < VD / 8; ++nt)
+#pragma unroll
+                for (int hh = 0; hh < 2; ++hh) {
+                    const int i = m0 + gq + hh * 8, j = nt * 8 + 2 * tq;
+                    *reinterpret_cast<float2*>(gO + i * R::OP + j) =
+                        make_float2(osc * acc[nt][2 * hh], osc * acc[nt][2 * hh + 1]);
+                }
+        }
+        // U^ = diag(e^{Glast-G}) Aub V
+        {
+            float acc[VD / 8][4];
+            zero_acc<VD / 8>(acc);
+            warp_gemm<VD / 8, CHUNK, false, true>(acc, sAu, CP, m0, sV, VP, 0, lane, m0 + 16, VD);
+#pragma unroll
+            for (int nt = 0; nt < VD / 8; ++nt)
+#pragma unroll
+                for (int hh = 0; hh < 2; ++hh) {
+                    const int i = m0 + gq + hh * 8, j = nt * 8 + 2 * tq;
+                    const float f = sEGl[i];
+                    *reinterpret_cast<uint32_t*>(sUh + i * VP + j) = pack_bf16x2(f * acc[nt][2 * hh], f * acc[nt][2 * hh + 1]);
+                }
+        }
+        // W = Awb K, written over this warp's own rows of Q (no longer needed)
+        {
+            float acc[KD / 8][4];
+            zero_acc<KD / 8>(acc);
+            warp_gemm<KD / 8, CHUNK, false, true>(acc, sAw, CP, m0, sK, KP, 0, lane, m0 + 16, KD);
+            __syncwarp();
+#pragma unroll
+            for (int nt = 0; nt < KD / 8; ++nt)
+#pragma unroll
+                for (int hh = 0; hh < 2; ++hh) {
+                    const int i = m0 + gq + hh * 8, j = nt * 8 + 2 * tq;
+                    *reinterpret_cast<uint32_t*>(sW + i * KP + j) = pack_bf16x2(acc[nt][2 * hh], acc[nt][2 * hh + 1]);
+                }
+        }
+    }
+    __syncthreads();
+
+    // ---- stage 4: M[a][b] = e^{G_last} (delta_ab - sum_tok K[tok][a] W[tok][b]);  B^T = U^^T K -----
     if (m0 < KD) {
         float acc[KD / 8][4];
-#pragma unroll
-        for (int i = 0; i < KD / 8; ++i) { acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f; }
-        warp_gemm<KD / 8, CHUNK, true, true>(acc, sK, KP, m0, sWt, KP, 0, lane, CHUNK, KD);
+        zero_acc<KD / 8>(acc);
+        warp_gemm<KD / 8, CHUNK, true, true>(acc, sK, KP, m0, sW, KP, 0, lane, CHUNK, KD);
         const float egl = sEG[CHUNK - 1];
         __nv_bfloat16* gM = reinterpret_cast<__nv_bfloat16*>(rec + R::M_OFF);
 #pragma unroll
@@ -337,17 +393,15 @@ __global__ void __launch_bounds__(128) gdn_prep_kernel(GdnArgs a) {
 #pragma unroll
             for (int hh = 0; hh < 2; ++hh) {
                 const int i = m0 + gq + hh * 8, j = nt * 8 + 2 * tq;
-                const float m_0 = ((i == j) ? egl : 0.f) - acc[nt][2 * hh];
-                const float m_1 = ((i == j + 1) ? egl : 0.f) - acc[nt][2 * hh + 1];
+                const float m_0 = egl * (((i == j) ? 1.f : 0.f) - acc[nt][2 * hh]);
+                const float m_1 = egl * (((i == j + 1) ? 1.f : 0.f) - acc[nt][2 * hh + 1]);
                 *reinterpret_cast<uint32_t*>(gM + i * KP + j) = pack_bf16x2(m_0, m_1);
             }
     }
-    // B^T[v][a] = sum_tok U[tok][v] K~[tok][a]
     if (m0 < VD) {
         float acc[KD / 8][4];
-#pragma unroll
-        for (int i = 0; i < KD / 8; ++i) { acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f; }
-        warp_gemm<KD / 8, CHUNK, true, true>(acc, sU, VP, m0, sK, KP, 0, lane, CHUNK, KD);
+        zero_acc<KD / 8>(acc);
+        warp_gemm<KD / 8, CHUNK, true, true>(acc, sUh, VP, m0, sK, KP, 0, lane, CHUNK, KD);
         __nv_bfloat16* gB = reinterpret_cast<__nv_bfloat16*>(rec + R::BT_OFF);
 #pragma unroll
         for (int nt = 0; nt < KD / 8; ++nt)
@@ -355,71 +409,6 @@ __global__ void __launch_bounds__(128) gdn_prep_kernel(GdnArgs a) {
             for (int hh = 0; hh < 2; ++hh) {
                 const int i = m0 + gq + hh * 8, j = nt * 8 + 2 * tq;
                 *reinterpret_cast<uint32_t*>(gB + i * KP + j) = pack_bf16x2(acc[nt][2 * hh], acc[nt][2 * hh + 1]);
-            }
-    }
-    // Q~[i][d] = s * (e^{G_i} Q[i][d] - sum_j P[i][j] W~[j][d]);  s = scale (plain) or 1 (hierarchical)
-    const float osc = HIER ? 1.f : a.scale;
-    {
-        float acc[KD / 8][4];
-#pragma unroll
-        for (int i = 0; i < KD / 8; ++i) { acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f; }
-        warp_gemm<KD / 8, CHUNK, false, true>(acc, sP, CP, m0, sWt, KP, 0, lane, m0 + 16, KD);
-        __nv_bfloat16* gQ = reinterpret_cast<__nv_bfloat16*>(rec + R::QT_OFF);
-#pragma unroll
-        for (int nt = 0; nt < KD / 8; ++nt)
-#pragma unroll
-            for (int hh = 0; hh < 2; ++hh) {
-                const int i = m0 + gq + hh * 8, j = nt * 8 + 2 * tq;
-                const float f = sEG[i];
-                const float2 qv = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(sQ + i * KP + j));
-                *reinterpret_cast<uint32_t*>(gQ + i * KP + j) =
-                    pack_bf16x2(osc * (f * qv.x - acc[nt][2 * hh]), osc * (f * qv.y - acc[nt][2 * hh + 1]));
-            }
-    }
-    // O_local
-    float* gO = reinterpret_cast<float*>(rec + R::OL_OFF);
-    if (HIER) {
-        // Pm = (tril(QK^T) Aw) .* E .* lambda[i][level(i,j)],  O_local = Pm (beta V)
-        float acc[8][4];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) { acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f; }
-        warp_gemm<8, CHUNK, false, true>(acc, sQK, CP, m0, sAw, CP, 0, lane, m0 + 16, m0 + 16);
-        __syncwarp();
-#pragma unroll
-        for (int nt = 0; nt < 8; ++nt)
-#pragma unroll
-            for (int hh = 0; hh < 2; ++hh) {
-                const int i = m0 + gq + hh * 8, j = nt * 8 + 2 * tq;
-                const float Gi = sG[i];
-                float p0 = 0.f, p1 = 0.f;
-                if (i >= j) p0 = acc[nt][2 * hh] * __expf(Gi - sG[j]) * sLam[i * LP + (32 - __clz(i ^ j))];
-                if (i >= j + 1) p1 = acc[nt][2 * hh + 1] * __expf(Gi - sG[j + 1]) * sLam[i * LP + (32 - __clz(i ^ (j + 1)))];
-                *reinterpret_cast<uint32_t*>(sQK + i * CP + j) = pack_bf16x2(p0, p1);
-            }
-        __syncwarp();
-        float acc2[VD / 8][4];
-#pragma unroll
-        for (int i = 0; i < VD / 8; ++i) { acc2[i][0] = acc2[i][1] = acc2[i][2] = acc2[i][3] = 0.f; }
-        warp_gemm<VD / 8, CHUNK, false, true>(acc2, sQK, CP, m0, sVb, VP, 0, lane, m0 + 16, VD);
-#pragma unroll
-        for (int nt = 0; nt < VD / 8; ++nt)
-#pragma unroll
-            for (int hh = 0; hh < 2; ++hh) {
-                const int i = m0 + gq + hh * 8, j = nt * 8 + 2 * tq;
-                *reinterpret_cast<float2*>(gO + i * R::OP + j) = make_float2(acc2[nt][2 * hh], acc2[nt][2 * hh + 1]);
-            }
-    } else {
-        float acc2[VD / 8][4];
-#pragma unroll
-        for (int i = 0; i < VD / 8; ++i) { acc2[i][0] = acc2[i][1] = acc2[i][2] = acc2[i][3] = 0.f; }
-        warp_gemm<VD / 8, CHUNK, false, true>(acc2, sP, CP, m0, sU, VP, 0, lane, m0 + 16, VD);
-#pragma unroll
-        for (int nt = 0; nt < VD / 8; ++nt)
-#pragma unroll
-            for (int hh = 0; hh < 2; ++hh) {
-                const int i = m0 + gq + hh * 8, j = nt * 8 + 2 * tq;
-                *reinterpret_cast<float2*>(gO + i * R::OP + j) =
-                    make_float2(osc * acc2[nt][2 * hh], osc * acc2[nt][2 * hh + 1]);
             }
     }
 }
