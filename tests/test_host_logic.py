@@ -1,0 +1,111 @@
+"""CPU-side checks: the C-ABI library loads and exports what the header declares, host-side
+argument validation, and the multi-rank sharding plan (2 gloo ranks)."""
+import os
+import re
+import socket
+import sys
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_library_exports_every_declared_symbol():
+    from lampa_b200 import _lib, build
+    build.build()
+    hdr = open(os.path.join(ROOT, "include", "lampa_b200.h")).read()
+    declared = sorted(set(re.findall(r"\b(lampa_[a-z0-9_]+)\s*\(", hdr)))
+    assert declared, "no declarations found"
+    lib = _lib.lib()
+    for name in declared:
+        assert hasattr(lib, name), f"{name} declared in the header but not exported"
+    assert lib.lampa_version() >= 100
+    assert lib.lampa_error_string(-6).decode().startswith("lambda")
+
+
+def test_host_side_argument_errors_without_a_gpu():
+    import ctypes
+    from lampa_b200 import _lib
+    lib = _lib.lib()
+    n = ctypes.c_size_t(0)
+    bad = _lib.GdnDesc(B=1, T=128, H=2, K=48, V=64, L=0, nseq=0, qkv_dtype=0, gb_dtype=2, lam_dtype=2, use_l2norm=1, scale=0.1)
+    assert lib.lampa_gdn_workspace_bytes(ctypes.byref(bad), ctypes.byref(n)) == -2          # unsupported head dim
+    ok = _lib.GdnDesc(B=1, T=61440, H=8, K=64, V=64, L=17, nseq=0, qkv_dtype=0, gb_dtype=2, lam_dtype=0, use_l2norm=1, scale=0.1)
+    assert lib.lampa_gdn_workspace_bytes(ctypes.byref(ok), ctypes.byref(n)) == 0
+    assert 300e6 < n.value < 600e6
+    lay = (ctypes.c_size_t * 12)()
+    assert lib.lampa_gdn_workspace_layout(ctypes.byref(ok), lay) == 0
+    assert lay[1] % 128 == 0 and lay[7] == 10 and lay[9] == 32
+    assert lib.lampa_segsort_workspace_bytes(-1, ctypes.byref(n)) == -1
+    assert lib.lampa_lsh_hash(None, 24, 0, None, None, 1.0, 10, 8, 3, 6, None, None, None, None) == -1
+    assert lib.lampa_permute_rows(None, None, None, 1, 10, 6, 0, None, None) == -1            # row bytes not /4
+
+
+def test_python_api_rejects_cpu_tensors_and_bad_shapes():
+    import lampa_b200
+    q = torch.randn(1, 128, 2, 64)
+    with pytest.raises(lampa_b200.LampaError):
+        lampa_b200.chunk_gated_delta_rule(q, q, q, torch.zeros(1, 128, 2), torch.zeros(1, 128, 2))
+    with pytest.raises(DeprecationWarning):
+        lampa_b200.chunk_gated_delta_rule(q, q, q, torch.zeros(1, 128, 2), torch.zeros(1, 128, 2), head_first=True)
+    with pytest.raises(AssertionError):
+        lampa_b200.chunk_gated_delta_rule(q, q.half(), q, torch.zeros(1, 128, 2), torch.zeros(1, 128, 2))
+    with pytest.raises(lampa_b200.LampaError):
+        lampa_b200.segmented_sort(torch.zeros(10, dtype=torch.int32))
+    assert lampa_b200.num_levels_required(61440) == 17 and lampa_b200.num_levels_required(64) == 7
+    assert lampa_b200.num_levels_required(65536) == 17 and lampa_b200.num_levels_required(65537) == 18
+
+
+def test_lpt_plan_properties():
+    from lampa_b200 import sharding, synth
+    lens = synth.event_sizes(20254, 64).tolist()
+    for g in (1, 2, 4, 8):
+        plan = sharding.lpt_assign(lens, g)
+        assert sorted(e for o in plan for e in o) == list(range(64))
+        assert sharding.imbalance(lens, plan) < 1.03
+    cu, spans = sharding.pack_events(lens, plan[3])
+    assert cu[-1].item() == sum(lens[e] for e in plan[3]) and len(spans) == len(plan[3])
+    assert sharding.head_slice(8, 3, 4) == (6, 8)
+    with pytest.raises(ValueError):
+        sharding.head_slice(6, 0, 4)
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _rank_main(rank, world, port, lens):
+    sys.path.insert(0, ROOT)
+    from lampa_b200 import sharding
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        # rank 1 starts from different (wrong) lengths: the plan must come from rank 0
+        mine = torch.tensor(lens if rank == 0 else [1] * len(lens), dtype=torch.int64)
+        plan = sharding.agree_on_plan(mine)
+        assert plan == sharding.lpt_assign(lens, world)
+        owned = plan[rank]
+        # each event's "output" is its global row index: after the gather every rank holds 0..N-1
+        starts = [0]
+        for n in lens:
+            starts.append(starts[-1] + n)
+        local = torch.cat([torch.arange(starts[e], starts[e + 1], dtype=torch.float32)[:, None].repeat(1, 3)
+                           for e in owned]) if owned else torch.zeros(0, 3)
+        full = sharding.gather_event_outputs(local, lens, plan)
+        assert torch.equal(full[:, 0], torch.arange(starts[-1], dtype=torch.float32))
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_rank_plan_and_gather_over_gloo():
+    lens = [700, 60, 1500, 333, 64, 900, 5]
+    mp.spawn(_rank_main, args=(2, _free_port(), lens), nprocs=2, join=True)
