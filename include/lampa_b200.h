@@ -42,6 +42,7 @@ extern "C" {
 #define LAMPA_ERR_TIMEOUT (-5)      /* device: a bounded wait ran out (status word only) */
 #define LAMPA_ERR_LEVELS (-6)       /* device/host: lambda has fewer levels than the sequence needs */
 #define LAMPA_ERR_BOUNDS (-7)       /* device: an index fell outside its extent (status word only) */
+#define LAMPA_ERR_TOO_LARGE (-8)    /* input exceeds the fixed capacity of an allocation-free entry point */
 
 /* Shape/type descriptor of one gated-delta forward call. */
 typedef struct lampa_gdn_desc {
@@ -143,6 +144,31 @@ int lampa_segsort_workspace_bytes(int64_t n_total, size_t* bytes);
 int lampa_segsort_stable(const void* keys, int32_t key_type, int64_t n_total,
                          const int64_t* seg_offsets, int32_t nseg, const int64_t* init,
                          int64_t* perm, void* ws, size_t ws_bytes, int32_t* status, void* stream);
+
+/*
+ * lampa_segsort_stable for hosts that may not allocate device memory when they call it.
+ * No counterpart in the reference (its sorts allocate through torch on every call).
+ *
+ * Who needs it: an online reconstruction / trigger-style loop that reserves all of its device
+ * memory at start-up and forbids cudaMalloc afterwards (it synchronises the device and can fail
+ * late), or a host process whose device memory belongs to an allocator this library cannot reach,
+ * so that it has no workspace pointer to hand over.  Same arguments and results as
+ * lampa_segsort_stable minus `ws`: the ping-pong buffers are a fixed array inside the library
+ * image, 16 bytes x LAMPA_SEGSORT_STATIC_MAX_KEYS = 24 MiB, resident on every GPU that loads the
+ * library until the process exits.
+ *   - n_total > LAMPA_SEGSORT_STATIC_MAX_KEYS returns LAMPA_ERR_TOO_LARGE and launches nothing;
+ *   - neither this call nor anything it uses calls cudaMalloc/cudaFree or an allocating routine;
+ *   - the first call on a device looks up the array's address there (cudaGetSymbolAddress, with
+ *     that device current) and caches it: make that first call outside any stream capture;
+ *   - all calls on a device share the one array and it keeps the previous call's contents; the
+ *     sort never reads what it has not just written, so nothing is cleared, but two calls that
+ *     overlap on the GPU (different streams, or threads without ordering) race on it: keep
+ *     calls on one stream or order them with events.
+ */
+#define LAMPA_SEGSORT_STATIC_MAX_KEYS 1572864
+int lampa_segsort_stable_static(const void* keys, int32_t key_type, int64_t n_total,
+                                const int64_t* seg_offsets, int32_t nseg, const int64_t* init,
+                                int64_t* perm, int32_t* status, void* stream);
 
 /*
  * Row gather / scatter by a per-segment permutation.

@@ -16,7 +16,8 @@ SO_PATH = os.path.join(_HERE, "liblampa_b200.so")
 
 LAMPA_BF16, LAMPA_F16, LAMPA_F32 = 0, 1, 2
 LAMPA_KEY_I32, LAMPA_KEY_F32 = 0, 1
-ERR_TIMEOUT, ERR_LEVELS, ERR_BOUNDS = -5, -6, -7
+ERR_TIMEOUT, ERR_LEVELS, ERR_BOUNDS, ERR_TOO_LARGE = -5, -6, -7, -8
+SEGSORT_STATIC_MAX_KEYS = 1572864
 
 _DTYPES = {torch.bfloat16: LAMPA_BF16, torch.float16: LAMPA_F16, torch.float32: LAMPA_F32}
 
@@ -35,7 +36,8 @@ class GdnDesc(ctypes.Structure):
 _lib: Optional[ctypes.CDLL] = None
 EXPORTS = ["lampa_version", "lampa_error_string", "lampa_gdn_workspace_bytes", "lampa_gdn_workspace_layout",
            "lampa_gdn_fwd", "lampa_hgdn_fwd", "lampa_lsh_hash", "lampa_segsort_workspace_bytes",
-           "lampa_segsort_stable", "lampa_permute_rows", "lampa_invert_perm", "lampa_profile_enable",
+           "lampa_segsort_stable", "lampa_permute_rows", "lampa_invert_perm", "lampa_segsort_stable_static",
+           "lampa_profile_enable",
            "lampa_profile_read"]
 
 
@@ -57,6 +59,7 @@ def lib() -> ctypes.CDLL:
         L.lampa_lsh_hash.argtypes = [vp, i64, i64, vp, vp, ctypes.c_float, i64, i32, i32, i32, vp, vp, vp, vp]
         L.lampa_segsort_workspace_bytes.argtypes = [i64, ctypes.POINTER(sz)]
         L.lampa_segsort_stable.argtypes = [vp, i32, i64, vp, i32, vp, vp, vp, sz, vp, vp]
+        L.lampa_segsort_stable_static.argtypes = [vp, i32, i64, vp, i32, vp, vp, vp, vp]
         L.lampa_permute_rows.argtypes = [vp, vp, vp, i32, i64, i64, i32, vp, vp]
         L.lampa_invert_perm.argtypes = [vp, vp, i32, i64, vp, vp]
         L.lampa_profile_enable.argtypes = [ctypes.c_int]

@@ -128,6 +128,7 @@ extern "C" const char* lampa_error_string(int code) {
         case LAMPA_ERR_TIMEOUT: return "device wait ran out";
         case LAMPA_ERR_LEVELS: return "lambda has fewer levels than 7 + ceil(log2(chunks))";
         case LAMPA_ERR_BOUNDS: return "index outside its extent (bad cu_seqlens?)";
+        case LAMPA_ERR_TOO_LARGE: return "input larger than the fixed capacity of this allocation-free entry point";
         default: return "unknown error";
     }
 }

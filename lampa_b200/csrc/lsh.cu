@@ -3,6 +3,7 @@
 #include <cooperative_groups.h>
 
 #include <algorithm>
+#include <mutex>
 
 #include "common.cuh"
 #include "profile.cuh"
@@ -356,5 +357,59 @@ extern "C" int lampa_invert_perm(const int64_t* perm, const int64_t* seg_offsets
     const unsigned grid = (unsigned)std::min<int64_t>((n_total + 255) / 256, 148 * 32);
     ProfScope prof("invert_perm", (cudaStream_t)stream);
     invert_perm_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(perm, seg_offsets, nseg, n_total, inv);
+    return cudaGetLastError() == cudaSuccess ? LAMPA_OK : LAMPA_ERR_CUDA;
+}
+
+// -------------------------------------------------------------------------------------------------
+// Sort without any caller- or library-side allocation: the four ping-pong buffers live in a
+// fixed array that is part of the loaded module (24 MiB per GPU that loads the library, held
+// until the process exits).  Host code cannot use the symbol g_sort_scratch as a pointer — on
+// the host it is only a handle — so its device address is looked up once per device with
+// cudaGetSymbolAddress and cached.
+// -------------------------------------------------------------------------------------------------
+namespace {
+constexpr size_t kStaticSortStride = (size_t)LAMPA_SEGSORT_STATIC_MAX_KEYS * 4;   // bytes per buffer, multiple of 256
+constexpr int kMaxDevices = 64;
+std::mutex g_scratch_mu;
+void* g_scratch_addr[kMaxDevices] = {nullptr};
+}  // namespace
+
+static __device__ __align__(256) unsigned char g_sort_scratch[4 * kStaticSortStride];
+
+// Device address of g_sort_scratch on the CURRENT device (looked up on first use there).
+static int static_sort_scratch(void** out) {
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess) return LAMPA_ERR_CUDA;
+    if (dev < 0 || dev >= kMaxDevices) return LAMPA_ERR_UNSUPPORTED;
+    std::lock_guard<std::mutex> lk(g_scratch_mu);
+    if (g_scratch_addr[dev] == nullptr) {
+        void* p = nullptr;
+        if (cudaGetSymbolAddress(&p, g_sort_scratch) != cudaSuccess || p == nullptr) return LAMPA_ERR_CUDA;
+        g_scratch_addr[dev] = p;
+    }
+    *out = g_scratch_addr[dev];
+    return LAMPA_OK;
+}
+
+extern "C" int lampa_segsort_stable_static(const void* keys, int32_t key_type, int64_t n_total,
+                                           const int64_t* seg_offsets, int32_t nseg, const int64_t* init,
+                                           int64_t* perm, int32_t* status, void* stream) {
+    (void)status;
+    if (n_total < 0 || nseg <= 0 || (key_type != LAMPA_KEY_I32 && key_type != LAMPA_KEY_F32)) return LAMPA_ERR_ARG;
+    if (n_total > (int64_t)LAMPA_SEGSORT_STATIC_MAX_KEYS) return LAMPA_ERR_TOO_LARGE;
+    if (n_total == 0) return LAMPA_OK;
+    if (!keys || !perm) return LAMPA_ERR_ARG;
+    if (!seg_offsets && n_total % nseg != 0) return LAMPA_ERR_ARG;
+    void* base_v = nullptr;
+    const int rc = static_sort_scratch(&base_v);
+    if (rc != LAMPA_OK) return rc;
+    char* base = (char*)base_v;
+    // No buffer needs clearing between calls: every pass writes positions [0, n) of its
+    // destination pair before the next pass reads them, and nothing beyond n is ever read.
+    ProfScope prof("segsort_static", (cudaStream_t)stream);
+    segsort_kernel<<<(unsigned)nseg * SORT_CL, SORT_THREADS, 0, (cudaStream_t)stream>>>(
+        keys, key_type, n_total, seg_offsets, nseg, init, perm, (uint32_t*)base,
+        (uint32_t*)(base + kStaticSortStride), (uint32_t*)(base + 2 * kStaticSortStride),
+        (uint32_t*)(base + 3 * kStaticSortStride));
     return cudaGetLastError() == cudaSuccess ? LAMPA_OK : LAMPA_ERR_CUDA;
 }
