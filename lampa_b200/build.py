@@ -35,12 +35,13 @@ def build(force: bool = False, verbose: bool = False) -> str:
     if not force and not _stale():
         return SO
     nvcc = _nvcc()
+    extra = os.environ.get("LAMPA_NVCC_EXTRA", "").split()   # e.g. -DLAMPA_PREP_TIMING for stage timing builds
     objdir = os.path.join(HERE, "build")
     os.makedirs(objdir, exist_ok=True)
 
     def compile_one(src: str) -> str:
         obj = os.path.join(objdir, src.replace(".cu", ".o"))
-        cmd = [nvcc] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-c", os.path.join(CSRC, src), "-o", obj]
+        cmd = [nvcc] + NVCC_FLAGS + extra + (["-Xptxas", "-v"] if verbose else []) + ["-c", os.path.join(CSRC, src), "-o", obj]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if verbose or r.returncode != 0:
             sys.stderr.write(r.stdout + r.stderr)

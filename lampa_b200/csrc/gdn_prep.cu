@@ -43,10 +43,9 @@ struct PrepSmem {
     static constexpr int Q = 0;                                  // bf16 [64][KP]   q (normalised); later W (rows are warp-private)
     static constexpr int K = Q + CHUNK * KP * 2;                 // bf16 [64][KP]   k (normalised)
     static constexpr int V = K + CHUNK * KP * 2;                 // bf16 [64][VP]   v
-    static constexpr int AT = V + CHUNK * VP * 2;                // fp32 [64][72]   A0^T; later Awb|Aub bf16 [64][CP] each
-    static constexpr int AW = AT;
-    static constexpr int AU = AT + CHUNK * CP * 2;
-    static constexpr int QK = AT + CHUNK * CP * 4;               // bf16 [64][CP]   tril(Q K^T)
+    static constexpr int AW = V + CHUNK * VP * 2;                // bf16 [64][CP]   Awb = (I + A0)^-1 diag(beta)
+    static constexpr int AU = AW + CHUNK * CP * 2;               // bf16 [64][CP]   Awb .* E
+    static constexpr int QK = AU + CHUNK * CP * 2;               // bf16 [64][CP]   tril(Q K^T)
     static constexpr int UH = QK + CHUNK * CP * 2;               // bf16 [64][VP]   diag(e^{Glast-G}) U
     static constexpr int G = UH + CHUNK * VP * 2;                // fp32 [64] G, [64] beta, [64] e^G, [64] e^{Glast-G}
     static constexpr int LAM = G + 4 * CHUNK * 4;                // fp32 [64][L+1]
@@ -86,6 +85,28 @@ __device__ __forceinline__ void load_half_row(const void* base, int dt, size_t e
     }
 }
 
+// Raw 16-byte loads of half a row of a 2-byte-element tile (issued early, converted later).
+template <int D>
+__device__ __forceinline__ void issue_half_row(const void* base, size_t elem_off, bool valid, uint4 (&u)[D / 16]) {
+    const uint4* p = reinterpret_cast<const uint4*>((const uint16_t*)base + elem_off);
+#pragma unroll
+    for (int i = 0; i < D / 16; ++i) u[i] = valid ? __ldg(p + i) : make_uint4(0u, 0u, 0u, 0u);
+}
+template <int D>
+__device__ __forceinline__ void convert_half_row(const uint4 (&u)[D / 16], int dt, float (&x)[D / 2]) {
+#pragma unroll
+    for (int i = 0; i < D / 16; ++i) {
+        const uint32_t w[4] = {u[i].x, u[i].y, u[i].z, u[i].w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            float2 f;
+            if (dt == LAMPA_BF16) f = unpack_bf16x2(w[j]);
+            else f = __half22float2(*reinterpret_cast<const __half2*>(&w[j]));
+            x[8 * i + 2 * j] = f.x; x[8 * i + 2 * j + 1] = f.y;
+        }
+    }
+}
+
 template <int NE>
 __device__ __forceinline__ void store_half_row_bf16(__nv_bfloat16* dst, const float (&x)[NE]) {
 #pragma unroll
@@ -105,6 +126,103 @@ __device__ __forceinline__ void zero_acc(float (&acc)[N][4]) {
     for (int i = 0; i < N; ++i) { acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f; }
 }
 
+// -------------------------------------------------------------------------------------------------
+// Solve kernel: one CTA of 2 warps per (chunk, head) computes A0 = tril(diag(beta) K K^T, -1) on
+// tensor cores and X = (I + A0)^-1 by an fp32 right-looking substitution, one thread per column
+// (once x_j is final every later row takes x_i -= A0[i][j] x_j, all independent).  It is its own
+// kernel because it needs 28 KB of shared memory and ~100 registers, so 8 of these CTAs share an SM
+// and hide each other's 63-step dependency chain, which the 70 KB preparation kernel cannot.
+// Awb = X diag(beta) goes, as bf16 [64][72], into the record's O_local slot (rewritten later).
+// -------------------------------------------------------------------------------------------------
+template <int KD>
+struct SolveSmem {
+    static constexpr int KP = KD + 8, CP = CHUNK + 8;
+    static constexpr int K = 0;
+    static constexpr int AT = K + CHUNK * KP * 2;      // fp32 [64][72]: A0 transposed
+    static constexpr int BETA = AT + CHUNK * CP * 4;
+    static constexpr int BYTES = BETA + CHUNK * 4;
+};
+
+template <int KD, int VD>
+__global__ void __launch_bounds__(64) gdn_solve_kernel(GdnArgs a) {
+    using S = SolveSmem<KD>;
+    using R = Rec<KD, VD>;
+    constexpr int KP = S::KP, CP = S::CP;
+    extern __shared__ __align__(128) unsigned char smem[];
+    __nv_bfloat16* sK = reinterpret_cast<__nv_bfloat16*>(smem + S::K);
+    float* sAT = reinterpret_cast<float*>(smem + S::AT);
+    float* sBeta = reinterpret_cast<float*>(smem + S::BETA);
+    const int h = blockIdx.x, c = blockIdx.y, H = a.H;
+    if (c >= a.chunk_off[a.nseq]) return;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int gq = lane >> 2, tq = lane & 3;
+    const int seq = find_seq(a.chunk_off, a.nseq, c);
+    const int64_t t0 = a.tok_off[seq] + (int64_t)(c - a.chunk_off[seq]) * CHUNK;
+    const int len = (int)min((int64_t)CHUNK, a.tok_off[seq + 1] - t0);
+    {
+        const bool valid = tid < len;
+        const size_t tok = (size_t)(t0 + tid);
+        float bv = 0.f;
+        if (valid) bv = load_as_float(a.beta, tok * H + h, a.gb_dt);
+        float x[KD / 2], y[KD / 2];
+        load_half_row<KD>(a.k, a.qkv_dt, (tok * H + h) * KD, valid, x);
+        load_half_row<KD>(a.k, a.qkv_dt, (tok * H + h) * KD + KD / 2, valid, y);
+        if (a.use_l2norm) {
+            float ss = 0.f;
+#pragma unroll
+            for (int i = 0; i < KD / 2; ++i) ss += x[i] * x[i];
+            // same summation order as the preparation kernel (half rows first), so both see the same K
+            float ss2 = 0.f;
+#pragma unroll
+            for (int i = 0; i < KD / 2; ++i) ss2 += y[i] * y[i];
+            const float rn = rsqrtf(ss + ss2 + 1e-6f);
+#pragma unroll
+            for (int i = 0; i < KD / 2; ++i) { x[i] *= rn; y[i] *= rn; }
+        }
+        store_half_row_bf16<KD / 2>(sK + tid * KP, x);
+        store_half_row_bf16<KD / 2>(sK + tid * KP + KD / 2, y);
+        sBeta[tid] = bv;
+    }
+    __syncthreads();
+    // A0^T[j][i] = beta_i (k_i . k_j) for i > j; warp 0 takes row tiles 0 and 3, warp 1 tiles 1 and 2
+#pragma unroll
+    for (int q = 0; q < 2; ++q) {
+        const int m0 = 16 * (q == 0 ? warp : 3 - warp);
+        float acc[8][4];
+        zero_acc<8>(acc);
+        warp_gemm<8, KD, false, false>(acc, sK, KP, m0, sK, KP, 0, lane, KD, m0 + 16);
+#pragma unroll
+        for (int nt = 0; nt < 8; ++nt) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int i = m0 + gq + (e >> 1) * 8, j = nt * 8 + 2 * tq + (e & 1);
+                if (nt * 8 < m0 + 16) sAT[j * CP + i] = (i > j) ? sBeta[i] * acc[nt][e] : 0.f;
+            }
+        }
+    }
+    __syncthreads();
+    const int col = tid;
+    float r[CHUNK];
+#pragma unroll
+    for (int i = 0; i < CHUNK; ++i) r[i] = (i == col) ? 1.f : 0.f;
+#pragma unroll
+    for (int j = 0; j < CHUNK - 1; ++j) {
+        const float rj = r[j];
+#pragma unroll
+        for (int i4 = ((j + 1) / 4) * 4; i4 < CHUNK; i4 += 4) {
+            const float4 av = *reinterpret_cast<const float4*>(sAT + j * CP + i4);
+            if (i4 + 0 > j) r[i4 + 0] -= av.x * rj;
+            if (i4 + 1 > j) r[i4 + 1] -= av.y * rj;
+            if (i4 + 2 > j) r[i4 + 2] -= av.z * rj;
+            if (i4 + 3 > j) r[i4 + 3] -= av.w * rj;
+        }
+    }
+    __nv_bfloat16* gA = reinterpret_cast<__nv_bfloat16*>(a.rec + ((size_t)c * H + h) * a.rec_bytes + R::OL_OFF);
+    const float bc = sBeta[col];
+#pragma unroll
+    for (int i = 0; i < CHUNK; ++i) gA[i * CP + col] = __float2bfloat16_rn(r[i] * bc);
+}
+
 // With beta folded into the columns of the inverse (Awb = (I + A0)^-1 diag(beta), Aub = Awb .* E):
 //   W  = Awb K                    M   = e^{G_last} (I - K^T W)
 //   U^ = diag(e^{G_last-G}) Aub V B^T = U^^T K
@@ -112,6 +230,16 @@ __device__ __forceinline__ void zero_acc(float (&acc)[N][4]) {
 //   O_local = s ((R .* E .* lambda[i][level(i,j)]) V)
 // (s = scale and lambda = 1 for the plain rule; s = 1 for the hierarchical one).  These equal
 // the definitions in gdn.cuh: every e^{G_last-G_tok} e^{G_tok} pair collapses to e^{G_last}.
+// Stage timing for tuning builds only (-DLAMPA_PREP_TIMING): thread 0 of the first 1024 CTAs of
+// head 0 stores clock64() at each stage boundary behind the status word, which the caller of such
+// a build must size as int32[4 + 2 * 8 * 1024].
+#ifdef LAMPA_PREP_TIMING
+#define PREP_TICK(slot) do { if (threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y < 1024) \
+    reinterpret_cast<long long*>(a.status + 4)[blockIdx.y * 8 + (slot)] = clock64(); } while (0)
+#else
+#define PREP_TICK(slot) do { } while (0)
+#endif
+
 template <int KD, int VD, bool HIER>
 __global__ void __launch_bounds__(128, 3) gdn_prep_kernel(GdnArgs a) {
     using S = PrepSmem<KD, VD>;
@@ -122,7 +250,6 @@ __global__ void __launch_bounds__(128, 3) gdn_prep_kernel(GdnArgs a) {
     __nv_bfloat16* sW = sQ;
     __nv_bfloat16* sK = reinterpret_cast<__nv_bfloat16*>(smem + S::K);
     __nv_bfloat16* sV = reinterpret_cast<__nv_bfloat16*>(smem + S::V);
-    float* sAT = reinterpret_cast<float*>(smem + S::AT);
     __nv_bfloat16* sAw = reinterpret_cast<__nv_bfloat16*>(smem + S::AW);
     __nv_bfloat16* sAu = reinterpret_cast<__nv_bfloat16*>(smem + S::AU);
     __nv_bfloat16* sQK = reinterpret_cast<__nv_bfloat16*>(smem + S::QK);
@@ -133,7 +260,9 @@ __global__ void __launch_bounds__(128, 3) gdn_prep_kernel(GdnArgs a) {
     float* sEGl = sG + 3 * CHUNK;
     float* sLam = reinterpret_cast<float*>(smem + S::LAM);
 
-    const int c = blockIdx.x, h = blockIdx.y, H = a.H;
+    // head is the fastest grid index: the H CTAs of one chunk run together and between them read
+    // whole contiguous token rows of q, k, v (one head alone touches 128 B out of every H*128 B)
+    const int h = blockIdx.x, c = blockIdx.y, H = a.H;
     if (c >= a.chunk_off[a.nseq]) return;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int gq = lane >> 2, tq = lane & 3;
@@ -141,14 +270,72 @@ __global__ void __launch_bounds__(128, 3) gdn_prep_kernel(GdnArgs a) {
     const int64_t t0 = a.tok_off[seq] + (int64_t)(c - a.chunk_off[seq]) * CHUNK;
     const int len = (int)min((int64_t)CHUNK, a.tok_off[seq + 1] - t0);
     const int LP = a.L + 1;
+    PREP_TICK(0);
 
     // ---- stage 0: loads, l2norm, cumulative decay -------------------------------------------------
+    // Every global load of the chunk is issued before any of them is consumed (one DRAM round trip
+    // instead of four), and the rows of a chunk some 600 CTAs ahead are pulled into L2.
     {
         const int r = tid >> 1, half = tid & 1;
         const bool valid = r < len;
         const size_t tok = (size_t)(t0 + r);
+        const bool two_byte = a.qkv_dt != LAMPA_F32;
+        uint4 rq[KD / 16], rk[KD / 16], rv[VD / 16];
+        if (two_byte) {
+            issue_half_row<KD>(a.q, (tok * H + h) * KD + half * (KD / 2), valid, rq);
+            issue_half_row<KD>(a.k, (tok * H + h) * KD + half * (KD / 2), valid, rk);
+            issue_half_row<VD>(a.v, (tok * H + h) * VD + half * (VD / 2), valid, rv);
+        }
+        uint4 raw_aw[5];   // Awb tile written by the solve kernel into the record's O_local slot
+        {
+            const uint4* ga = reinterpret_cast<const uint4*>(a.rec + ((size_t)c * H + h) * a.rec_bytes + R::OL_OFF);
+#pragma unroll
+            for (int i = 0; i < 5; ++i) {
+                const int idx = tid + 128 * i;
+                raw_aw[i] = (idx < CHUNK * CP / 8) ? __ldg(ga + idx) : make_uint4(0u, 0u, 0u, 0u);
+            }
+        }
+        float gv = 0.f, bv = 0.f;
+        if (tid < len) {   // len <= 64: threads 0..len-1 carry g and beta of token tid
+            gv = load_as_float(a.g, (size_t)(t0 + tid) * H + h, a.gb_dt);
+            bv = load_as_float(a.beta, (size_t)(t0 + tid) * H + h, a.gb_dt);
+        }
+        if (HIER) {   // all of the row's loads in flight before the first store (L <= 40)
+            float lv[20];
+#pragma unroll
+            for (int i = 0; i < 20; ++i) {
+                const int l = half + 2 * i;
+                lv[i] = (valid && l < a.L) ? load_as_float(a.lam, (tok * H + h) * a.L + l, a.lam_dt) : 0.f;
+            }
+#pragma unroll
+            for (int i = 0; i < 20; ++i) {
+                const int l = half + 2 * i;
+                if (l < a.L) sLam[r * LP + l] = lv[i];
+            }
+        }
+        {   // L2 prefetch of the token rows of a chunk ~80 chunks ahead (all heads: thread pairs split the row)
+            const int c2 = c + 80;
+            if (c2 < a.chunk_off[a.nseq] && h == 0) {
+                const int s2 = find_seq(a.chunk_off, a.nseq, c2);
+                const int64_t t2 = a.tok_off[s2] + (int64_t)(c2 - a.chunk_off[s2]) * CHUNK + r;
+                if (t2 < a.tok_off[s2 + 1]) {
+                    const int eb = dtype_bytes(a.qkv_dt);
+                    const size_t rowq = (size_t)H * KD * eb, rowv = (size_t)H * VD * eb;
+                    const char* pq = (const char*)a.q + (size_t)t2 * rowq;
+                    const char* pk = (const char*)a.k + (size_t)t2 * rowq;
+                    const char* pv = (const char*)a.v + (size_t)t2 * rowv;
+                    for (size_t off = (size_t)half * 128; off < rowq; off += 256) {
+                        asm volatile("prefetch.global.L2 [%0];\n" :: "l"(pq + off));
+                        asm volatile("prefetch.global.L2 [%0];\n" :: "l"(pk + off));
+                    }
+                    for (size_t off = (size_t)half * 128; off < rowv; off += 256)
+                        asm volatile("prefetch.global.L2 [%0];\n" :: "l"(pv + off));
+                }
+            }
+        }
         float x[KD / 2];
-        load_half_row<KD>(a.q, a.qkv_dt, (tok * H + h) * KD + half * (KD / 2), valid, x);
+        if (two_byte) convert_half_row<KD>(rq, a.qkv_dt, x);
+        else load_half_row<KD>(a.q, a.qkv_dt, (tok * H + h) * KD + half * (KD / 2), valid, x);
         if (a.use_l2norm) {
             float ss = 0.f;
 #pragma unroll
@@ -159,7 +346,8 @@ __global__ void __launch_bounds__(128, 3) gdn_prep_kernel(GdnArgs a) {
             for (int i = 0; i < KD / 2; ++i) x[i] *= rn;
         }
         store_half_row_bf16<KD / 2>(sQ + r * KP + half * (KD / 2), x);
-        load_half_row<KD>(a.k, a.qkv_dt, (tok * H + h) * KD + half * (KD / 2), valid, x);
+        if (two_byte) convert_half_row<KD>(rk, a.qkv_dt, x);
+        else load_half_row<KD>(a.k, a.qkv_dt, (tok * H + h) * KD + half * (KD / 2), valid, x);
         if (a.use_l2norm) {
             float ss = 0.f;
 #pragma unroll
@@ -171,32 +359,29 @@ __global__ void __launch_bounds__(128, 3) gdn_prep_kernel(GdnArgs a) {
         }
         store_half_row_bf16<KD / 2>(sK + r * KP + half * (KD / 2), x);
         float y[VD / 2];
-        load_half_row<VD>(a.v, a.qkv_dt, (tok * H + h) * VD + half * (VD / 2), valid, y);
+        if (two_byte) convert_half_row<VD>(rv, a.qkv_dt, y);
+        else load_half_row<VD>(a.v, a.qkv_dt, (tok * H + h) * VD + half * (VD / 2), valid, y);
         store_half_row_bf16<VD / 2>(sV + r * VP + half * (VD / 2), y);
-        if (HIER) {
-            for (int l = half; l < a.L; l += 2)
-                sLam[r * LP + l] = valid ? load_as_float(a.lam, (tok * H + h) * a.L + l, a.lam_dt) : 0.f;
-        }
-    }
-    if (tid < CHUNK) {
-        const bool valid = tid < len;
-        float gv = 0.f, bv = 0.f;
-        if (valid) {
-            gv = load_as_float(a.g, (size_t)(t0 + tid) * H + h, a.gb_dt);
-            bv = load_as_float(a.beta, (size_t)(t0 + tid) * H + h, a.gb_dt);
-        }
-        float cs = gv;
 #pragma unroll
-        for (int o = 1; o < 32; o <<= 1) {
-            const float y = __shfl_up_sync(0xffffffffu, cs, o);
-            if (lane >= o) cs += y;
+        for (int i = 0; i < 5; ++i) {
+            const int idx = tid + 128 * i;
+            if (idx < CHUNK * CP / 8) reinterpret_cast<uint4*>(sAw)[idx] = raw_aw[i];
         }
-        if (tid == 31) sG[CHUNK - 1] = cs;      // one-float mailbox between the two warps
-        sBeta[tid] = bv;
-        asm volatile("bar.sync 1, 64;\n" ::: "memory");
-        const float carry = (warp == 1) ? sG[CHUNK - 1] : 0.f;
-        asm volatile("bar.sync 1, 64;\n" ::: "memory");
-        sG[tid] = cs + carry;
+
+        if (tid < CHUNK) {
+            float cs = gv;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const float yy = __shfl_up_sync(0xffffffffu, cs, o);
+                if (lane >= o) cs += yy;
+            }
+            if (tid == 31) sG[CHUNK - 1] = cs;      // one-float mailbox between the two warps
+            sBeta[tid] = bv;
+            asm volatile("bar.sync 1, 64;\n" ::: "memory");
+            const float carry = (warp == 1) ? sG[CHUNK - 1] : 0.f;
+            asm volatile("bar.sync 1, 64;\n" ::: "memory");
+            sG[tid] = cs + carry;
+        }
     }
     __syncthreads();
     if (tid < CHUNK) {
@@ -214,19 +399,10 @@ __global__ void __launch_bounds__(128, 3) gdn_prep_kernel(GdnArgs a) {
     }
 
     const int m0 = warp * 16;
-    // ---- stage 1: K K^T -> A0^T (fp32, strictly lower, rows scaled by beta); Q K^T -> tril, bf16 ---
+    PREP_TICK(1);
+    // ---- stage 1: Q K^T -> tril, bf16 -------------------------------------------------------------
     {
         float acc[8][4];
-        zero_acc<8>(acc);
-        warp_gemm<8, KD, false, false>(acc, sK, KP, m0, sK, KP, 0, lane, KD, m0 + 16);
-#pragma unroll
-        for (int nt = 0; nt < 8; ++nt) {
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const int i = m0 + gq + (e >> 1) * 8, j = nt * 8 + 2 * tq + (e & 1);
-                if (nt * 8 < m0 + 16) sAT[j * CP + i] = (i > j) ? sBeta[i] * acc[nt][e] : 0.f;
-            }
-        }
         zero_acc<8>(acc);
         warp_gemm<8, KD, false, false>(acc, sQ, KP, m0, sK, KP, 0, lane, KD, m0 + 16);
 #pragma unroll
@@ -240,50 +416,22 @@ __global__ void __launch_bounds__(128, 3) gdn_prep_kernel(GdnArgs a) {
             }
         }
     }
-    __syncthreads();
-
-    // ---- stage 2: X = (I + A0)^-1, two threads per column (lanes 2c, 2c+1 split the rows in
-    // alternating groups of four); right-looking substitution: once x_j is final, every later
-    // row takes its update x_i -= A0[i][j] x_j, all independent of each other.
+    // ---- stage 2: Aub = Awb .* E (Awb came from the solve kernel) ---------------------------------
     {
-        const int col = tid >> 1, half = tid & 1;
-        float r[8][4];
+        const int r = tid >> 1, half = tid & 1;
+        const float Gr = sG[r];
 #pragma unroll
-        for (int m = 0; m < 8; ++m)
-#pragma unroll
-            for (int e = 0; e < 4; ++e) r[m][e] = (8 * m + 4 * half + e == col) ? 1.f : 0.f;
-#pragma unroll
-        for (int j = 0; j < CHUNK - 1; ++j) {
-            const int mb = j >> 3, hj = (j >> 2) & 1, ej = j & 3;
-            const float rj = __shfl_sync(0xffffffffu, r[mb][ej], (lane & ~1) | hj);
-            {
-                const int i0 = 8 * mb + 4 * half;
-                const float4 av = *reinterpret_cast<const float4*>(sAT + j * CP + i0);
-                r[mb][0] -= (i0 + 0 > j ? av.x : 0.f) * rj;
-                r[mb][1] -= (i0 + 1 > j ? av.y : 0.f) * rj;
-                r[mb][2] -= (i0 + 2 > j ? av.z : 0.f) * rj;
-                r[mb][3] -= (i0 + 3 > j ? av.w : 0.f) * rj;
-            }
-#pragma unroll
-            for (int m = mb + 1; m < 8; ++m) {
-                const float4 av = *reinterpret_cast<const float4*>(sAT + j * CP + 8 * m + 4 * half);
-                r[m][0] -= av.x * rj; r[m][1] -= av.y * rj; r[m][2] -= av.z * rj; r[m][3] -= av.w * rj;
-            }
+        for (int cc = 0; cc < CHUNK / 2; cc += 2) {
+            const int col = half * (CHUNK / 2) + cc;
+            const float2 w = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(sAw + r * CP + col));
+            const float u0 = (r >= col) ? w.x * __expf(Gr - sG[col]) : 0.f;
+            const float u1 = (r >= col + 1) ? w.y * __expf(Gr - sG[col + 1]) : 0.f;
+            *reinterpret_cast<uint32_t*>(sAu + r * CP + col) = pack_bf16x2(u0, u1);
         }
-        __syncthreads();   // everyone is done reading A0^T; its storage now takes Awb and Aub
-        const float Gc = sG[col], bc = sBeta[col];
-#pragma unroll
-        for (int m = 0; m < 8; ++m)
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const int i = 8 * m + 4 * half + e;
-                const float x = r[m][e] * bc;
-                sAw[i * CP + col] = __float2bfloat16_rn(x);
-                sAu[i * CP + col] = __float2bfloat16_rn((i >= col) ? x * __expf(sG[i] - Gc) : 0.f);
-            }
     }
     __syncthreads();
 
+    PREP_TICK(4);
     const float osc = HIER ? 1.f : a.scale;
     // ---- stage 3 (rows m0..m0+15 of everything; nothing leaves the warp) --------------------------
     {
@@ -380,6 +528,7 @@ __global__ void __launch_bounds__(128, 3) gdn_prep_kernel(GdnArgs a) {
         }
     }
     __syncthreads();
+    PREP_TICK(5);
 
     // ---- stage 4: M[a][b] = e^{G_last} (delta_ab - sum_tok K[tok][a] W[tok][b]);  B^T = U^^T K -----
     if (m0 < KD) {
@@ -411,14 +560,20 @@ __global__ void __launch_bounds__(128, 3) gdn_prep_kernel(GdnArgs a) {
                 *reinterpret_cast<uint32_t*>(gB + i * KP + j) = pack_bf16x2(acc[nt][2 * hh], acc[nt][2 * hh + 1]);
             }
     }
+    PREP_TICK(6);
 }
 
 template <int KD, int VD>
 int launch_prep(const GdnArgs& a, bool hier, cudaStream_t st) {
     using S = PrepSmem<KD, VD>;
     const int smem = S::bytes(hier ? a.L : 0);
-    dim3 grid(a.nc_max, a.H);
+    dim3 grid(a.H, a.nc_max);
     cudaError_t e;
+    {
+        ProfScope prof_s("gdn_solve", st);
+        gdn_solve_kernel<KD, VD><<<grid, 64, SolveSmem<KD>::BYTES, st>>>(a);
+        if (cudaGetLastError() != cudaSuccess) return LAMPA_ERR_CUDA;
+    }
     ProfScope prof(hier ? "gdn_prep_hier" : "gdn_prep_plain", st);
     if (hier) {
         e = cudaFuncSetAttribute(gdn_prep_kernel<KD, VD, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);

@@ -22,6 +22,20 @@
 
 #define MAXD 256
 
+#ifdef _OPENMP
+#include <omp.h>
+#endif
+/* Number of host threads the parallel loops use (0 or less: leave as is); returns the setting. */
+int oracle_set_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+    return omp_get_max_threads();
+#else
+    (void)n;
+    return 1;
+#endif
+}
+
 /* l2norm as models/hattention/l2norm.py:99-103: x * rsqrt(sum(x^2) + 1e-6). */
 static void l2norm_row(const float* x, float* y, int d) {
     float s = 0.f;

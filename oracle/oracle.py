@@ -45,6 +45,11 @@ def lib() -> ctypes.CDLL:
     return _LIB
 
 
+def set_threads(n: int) -> int:
+    """Set the OpenMP thread count of the oracle's loops; returns the count in effect."""
+    return int(lib().oracle_set_threads(ctypes.c_int(int(n))))
+
+
 def _f32(a) -> np.ndarray:
     return np.ascontiguousarray(np.asarray(a, dtype=np.float32))
 
