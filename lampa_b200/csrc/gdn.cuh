@@ -50,6 +50,8 @@ struct GdnArgs {
     int use_l2norm;
     float scale;
     int nseq;
+    int fixed_T;        // tokens per sequence when there is no cu_seqlens (0 otherwise)
+    int fixed_cps;      // chunks per sequence in that case: positions follow by arithmetic, no plan loads
     int nc_max, nb_max, nhigh_max;
     const int64_t* tok_off; const int32_t* chunk_off; const int32_t* block_off;
     char* rec; size_t rec_bytes;          // per (chunk, head) records
@@ -67,6 +69,24 @@ int launch_plan(const PlanArgs& p, cudaStream_t st);
 template <int KD, int VD> int launch_prep(const GdnArgs& a, bool hier, cudaStream_t st);
 template <int KD, int VD> int launch_scan_plain(const GdnArgs& a, cudaStream_t st);
 template <int KD, int VD> int launch_scan_hier(const GdnArgs& a, cudaStream_t st);
+
+// Where chunk slot c lives: sequence, first token, number of valid tokens.  False for unused slots.
+struct ChunkLoc { int seq; int64_t t0; int len; };
+__device__ __forceinline__ bool locate_chunk(const GdnArgs& a, int c, ChunkLoc& loc) {
+    if (a.fixed_T > 0) {
+        if (c >= a.nseq * a.fixed_cps) return false;
+        loc.seq = c / a.fixed_cps;
+        const int local = c - loc.seq * a.fixed_cps;
+        loc.t0 = (int64_t)loc.seq * a.fixed_T + (int64_t)local * CHUNK;
+        loc.len = min(CHUNK, a.fixed_T - local * CHUNK);
+        return true;
+    }
+    if (c >= a.chunk_off[a.nseq]) return false;
+    loc.seq = find_seq(a.chunk_off, a.nseq, c);
+    loc.t0 = a.tok_off[loc.seq] + (int64_t)(c - a.chunk_off[loc.seq]) * CHUNK;
+    loc.len = (int)min((int64_t)CHUNK, a.tok_off[loc.seq + 1] - loc.t0);
+    return true;
+}
 
 __host__ __device__ inline int ceil_log2_int(int x) {   // smallest e with 2^e >= x (x >= 1)
     int e = 0;

@@ -95,6 +95,8 @@ int run(const lampa_gdn_desc* d, bool hier, const void* q, const void* k, const 
     a.qkv_dt = d->qkv_dtype; a.gb_dt = d->gb_dtype; a.lam_dt = d->lam_dtype;
     a.H = d->H; a.L = hier ? d->L : 0; a.LC = l.LC;
     a.use_l2norm = d->use_l2norm; a.scale = d->scale;
+    a.fixed_T = cu ? 0 : d->T;
+    a.fixed_cps = cu ? 0 : (d->T + CHUNK - 1) / CHUNK;
     a.nseq = l.nseq; a.nc_max = l.nc_max; a.nb_max = l.nb_max; a.nhigh_max = l.nhigh_max;
     a.tok_off = p.tok_off; a.chunk_off = p.chunk_off; a.block_off = p.block_off;
     a.rec = base + l.off_rec; a.rec_bytes = l.rec_bytes;

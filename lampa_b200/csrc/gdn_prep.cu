@@ -44,9 +44,7 @@ struct PrepSmem {
     static constexpr int K = Q + CHUNK * KP * 2;                 // bf16 [64][KP]   k (normalised)
     static constexpr int V = K + CHUNK * KP * 2;                 // bf16 [64][VP]   v
     static constexpr int AW = V + CHUNK * VP * 2;                // bf16 [64][CP]   Awb = (I + A0)^-1 diag(beta)
-    static constexpr int AU = AW + CHUNK * CP * 2;               // bf16 [64][CP]   Awb .* E
-    static constexpr int QK = AU + CHUNK * CP * 2;               // bf16 [64][CP]   tril(Q K^T)
-    static constexpr int UH = QK + CHUNK * CP * 2;               // bf16 [64][VP]   diag(e^{Glast-G}) U
+    static constexpr int UH = AW + CHUNK * CP * 2;               // bf16 [64][VP]   diag(e^{Glast-G}) U
     static constexpr int G = UH + CHUNK * VP * 2;                // fp32 [64] G, [64] beta, [64] e^G, [64] e^{Glast-G}
     static constexpr int LAM = G + 4 * CHUNK * 4;                // fp32 [64][L+1]
     static int bytes(int L) { return LAM + CHUNK * (L + 1) * 4; }
@@ -127,24 +125,27 @@ __device__ __forceinline__ void zero_acc(float (&acc)[N][4]) {
 }
 
 // -------------------------------------------------------------------------------------------------
-// Solve kernel: one CTA of 2 warps per (chunk, head) computes A0 = tril(diag(beta) K K^T, -1) on
-// tensor cores and X = (I + A0)^-1 by an fp32 right-looking substitution, one thread per column
-// (once x_j is final every later row takes x_i -= A0[i][j] x_j, all independent).  It is its own
-// kernel because it needs 28 KB of shared memory and ~100 registers, so 8 of these CTAs share an SM
-// and hide each other's 63-step dependency chain, which the 70 KB preparation kernel cannot.
-// Awb = X diag(beta) goes, as bf16 [64][72], into the record's O_local slot (rewritten later).
+// Solve kernel: one warp per (chunk, head) computes A0 = tril(diag(beta) K K^T, -1) on tensor
+// cores and X = (I + A0)^-1 by an fp32 right-looking substitution (once x_j is final every later
+// row takes x_i -= A0[i][j] x_j, all independent).  Lane c owns columns c and c + 32; the second
+// is zero above row 32, so it only joins for j >= 32 and re-uses the A0 values already loaded for
+// column c: the substitution is bound by shared-memory wavefronts (one broadcast load per FMA
+// group), and this halves them.  It is its own kernel because it needs 18.7 KB of shared memory and
+// ~130 registers for 32 threads, so 12 of these CTAs share an SM and hide each other's 63-step
+// dependency chain.  Awb = X diag(beta) goes, as bf16 [64][72], into the record's O_local slot
+// (consumed and then overwritten by the preparation kernel).
 // -------------------------------------------------------------------------------------------------
 template <int KD>
 struct SolveSmem {
     static constexpr int KP = KD + 8, CP = CHUNK + 8;
-    static constexpr int K = 0;
-    static constexpr int AT = K + CHUNK * KP * 2;      // fp32 [64][72]: A0 transposed
+    static constexpr int K = 0;                        // bf16 [64][KP], dead once K K^T is in registers
+    static constexpr int AT = 0;                       // fp32 [64][72]: A0 transposed (aliases K)
     static constexpr int BETA = AT + CHUNK * CP * 4;
     static constexpr int BYTES = BETA + CHUNK * 4;
 };
 
 template <int KD, int VD>
-__global__ void __launch_bounds__(64) gdn_solve_kernel(GdnArgs a) {
+__global__ void __launch_bounds__(32) gdn_solve_kernel(GdnArgs a) {
     using S = SolveSmem<KD>;
     using R = Rec<KD, VD>;
     constexpr int KP = S::KP, CP = S::CP;
@@ -153,74 +154,91 @@ __global__ void __launch_bounds__(64) gdn_solve_kernel(GdnArgs a) {
     float* sAT = reinterpret_cast<float*>(smem + S::AT);
     float* sBeta = reinterpret_cast<float*>(smem + S::BETA);
     const int h = blockIdx.x, c = blockIdx.y, H = a.H;
-    if (c >= a.chunk_off[a.nseq]) return;
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    ChunkLoc loc;
+    if (!locate_chunk(a, c, loc)) return;
+    const int lane = threadIdx.x;
     const int gq = lane >> 2, tq = lane & 3;
-    const int seq = find_seq(a.chunk_off, a.nseq, c);
-    const int64_t t0 = a.tok_off[seq] + (int64_t)(c - a.chunk_off[seq]) * CHUNK;
-    const int len = (int)min((int64_t)CHUNK, a.tok_off[seq + 1] - t0);
-    {
-        const bool valid = tid < len;
-        const size_t tok = (size_t)(t0 + tid);
+    const int64_t t0 = loc.t0;
+    const int len = loc.len;
+#pragma unroll
+    for (int rr = 0; rr < 2; ++rr) {
+        const int row = lane + 32 * rr;
+        const bool valid = row < len;
+        const size_t tok = (size_t)(t0 + row);
         float bv = 0.f;
         if (valid) bv = load_as_float(a.beta, tok * H + h, a.gb_dt);
         float x[KD / 2], y[KD / 2];
         load_half_row<KD>(a.k, a.qkv_dt, (tok * H + h) * KD, valid, x);
         load_half_row<KD>(a.k, a.qkv_dt, (tok * H + h) * KD + KD / 2, valid, y);
         if (a.use_l2norm) {
-            float ss = 0.f;
+            // same summation order as the preparation kernel (half rows first), so both see the same K
+            float ss = 0.f, ss2 = 0.f;
 #pragma unroll
             for (int i = 0; i < KD / 2; ++i) ss += x[i] * x[i];
-            // same summation order as the preparation kernel (half rows first), so both see the same K
-            float ss2 = 0.f;
 #pragma unroll
             for (int i = 0; i < KD / 2; ++i) ss2 += y[i] * y[i];
             const float rn = rsqrtf(ss + ss2 + 1e-6f);
 #pragma unroll
             for (int i = 0; i < KD / 2; ++i) { x[i] *= rn; y[i] *= rn; }
         }
-        store_half_row_bf16<KD / 2>(sK + tid * KP, x);
-        store_half_row_bf16<KD / 2>(sK + tid * KP + KD / 2, y);
-        sBeta[tid] = bv;
+        store_half_row_bf16<KD / 2>(sK + row * KP, x);
+        store_half_row_bf16<KD / 2>(sK + row * KP + KD / 2, y);
+        sBeta[row] = bv;
     }
-    __syncthreads();
-    // A0^T[j][i] = beta_i (k_i . k_j) for i > j; warp 0 takes row tiles 0 and 3, warp 1 tiles 1 and 2
-#pragma unroll
-    for (int q = 0; q < 2; ++q) {
-        const int m0 = 16 * (q == 0 ? warp : 3 - warp);
-        float acc[8][4];
-        zero_acc<8>(acc);
-        warp_gemm<8, KD, false, false>(acc, sK, KP, m0, sK, KP, 0, lane, KD, m0 + 16);
-#pragma unroll
-        for (int nt = 0; nt < 8; ++nt) {
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const int i = m0 + gq + (e >> 1) * 8, j = nt * 8 + 2 * tq + (e & 1);
-                if (nt * 8 < m0 + 16) sAT[j * CP + i] = (i > j) ? sBeta[i] * acc[nt][e] : 0.f;
-            }
-        }
+    __syncwarp();
+    // A0^T[j][i] = beta_i (k_i . k_j) for i > j.  All lower tiles are accumulated first: the fp32
+    // matrix then takes over the storage of K (18.4 KB per CTA instead of 27.6 KB: 12 CTAs per SM).
+    float acc0[2][4], acc1[4][4], acc2[6][4], acc3[8][4];
+    zero_acc<2>(acc0); zero_acc<4>(acc1); zero_acc<6>(acc2); zero_acc<8>(acc3);
+    warp_gemm<2, KD, false, false>(acc0, sK, KP, 0, sK, KP, 0, lane);
+    warp_gemm<4, KD, false, false>(acc1, sK, KP, 16, sK, KP, 0, lane);
+    warp_gemm<6, KD, false, false>(acc2, sK, KP, 32, sK, KP, 0, lane);
+    warp_gemm<8, KD, false, false>(acc3, sK, KP, 48, sK, KP, 0, lane);
+    const float bi[8] = {sBeta[gq], sBeta[gq + 8], sBeta[16 + gq], sBeta[24 + gq],
+                         sBeta[32 + gq], sBeta[40 + gq], sBeta[48 + gq], sBeta[56 + gq]};
+    __syncwarp();
+#define LAMPA_PUT_A0(ACC, NT, M0)                                                              \
+    _Pragma("unroll") for (int nt = 0; nt < NT; ++nt) {                                        \
+        _Pragma("unroll") for (int e = 0; e < 4; ++e) {                                        \
+            const int i = M0 + gq + (e >> 1) * 8, j = nt * 8 + 2 * tq + (e & 1);               \
+            sAT[j * CP + i] = (i > j) ? bi[M0 / 8 + (e >> 1)] * ACC[nt][e] : 0.f;              \
+        }                                                                                      \
     }
-    __syncthreads();
-    const int col = tid;
-    float r[CHUNK];
+    LAMPA_PUT_A0(acc0, 2, 0)
+    LAMPA_PUT_A0(acc1, 4, 16)
+    LAMPA_PUT_A0(acc2, 6, 32)
+    LAMPA_PUT_A0(acc3, 8, 48)
+#undef LAMPA_PUT_A0
+    __syncwarp();
+    float r[CHUNK], s2[CHUNK / 2];
 #pragma unroll
-    for (int i = 0; i < CHUNK; ++i) r[i] = (i == col) ? 1.f : 0.f;
+    for (int i = 0; i < CHUNK; ++i) r[i] = (i == lane) ? 1.f : 0.f;
+#pragma unroll
+    for (int i = 0; i < CHUNK / 2; ++i) s2[i] = (i == lane) ? 1.f : 0.f;
 #pragma unroll
     for (int j = 0; j < CHUNK - 1; ++j) {
         const float rj = r[j];
+        const float sj = (j >= CHUNK / 2) ? s2[j >= CHUNK / 2 ? j - CHUNK / 2 : 0] : 0.f;
 #pragma unroll
         for (int i4 = ((j + 1) / 4) * 4; i4 < CHUNK; i4 += 4) {
             const float4 av = *reinterpret_cast<const float4*>(sAT + j * CP + i4);
-            if (i4 + 0 > j) r[i4 + 0] -= av.x * rj;
-            if (i4 + 1 > j) r[i4 + 1] -= av.y * rj;
-            if (i4 + 2 > j) r[i4 + 2] -= av.z * rj;
-            if (i4 + 3 > j) r[i4 + 3] -= av.w * rj;
+            const float ae[4] = {av.x, av.y, av.z, av.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                if (i4 + e > j) {
+                    r[i4 + e] -= ae[e] * rj;
+                    if (j >= CHUNK / 2) s2[i4 + e - CHUNK / 2 >= 0 ? i4 + e - CHUNK / 2 : 0] -= ae[e] * sj;
+                }
+            }
         }
     }
     __nv_bfloat16* gA = reinterpret_cast<__nv_bfloat16*>(a.rec + ((size_t)c * H + h) * a.rec_bytes + R::OL_OFF);
-    const float bc = sBeta[col];
+    const float b0 = sBeta[lane], b1 = sBeta[lane + 32];
 #pragma unroll
-    for (int i = 0; i < CHUNK; ++i) gA[i * CP + col] = __float2bfloat16_rn(r[i] * bc);
+    for (int i = 0; i < CHUNK; ++i) {
+        gA[i * CP + lane] = __float2bfloat16_rn(r[i] * b0);
+        gA[i * CP + lane + 32] = __float2bfloat16_rn(i >= CHUNK / 2 ? s2[i >= CHUNK / 2 ? i - CHUNK / 2 : 0] * b1 : 0.f);
+    }
 }
 
 // With beta folded into the columns of the inverse (Awb = (I + A0)^-1 diag(beta), Aub = Awb .* E):
@@ -241,7 +259,7 @@ __global__ void __launch_bounds__(64) gdn_solve_kernel(GdnArgs a) {
 #endif
 
 template <int KD, int VD, bool HIER>
-__global__ void __launch_bounds__(128, 3) gdn_prep_kernel(GdnArgs a) {
+__global__ void __launch_bounds__(128, 4) gdn_prep_kernel(GdnArgs a) {
     using S = PrepSmem<KD, VD>;
     using R = Rec<KD, VD>;
     constexpr int KP = S::KP, VP = S::VP, CP = S::CP;
@@ -251,8 +269,6 @@ __global__ void __launch_bounds__(128, 3) gdn_prep_kernel(GdnArgs a) {
     __nv_bfloat16* sK = reinterpret_cast<__nv_bfloat16*>(smem + S::K);
     __nv_bfloat16* sV = reinterpret_cast<__nv_bfloat16*>(smem + S::V);
     __nv_bfloat16* sAw = reinterpret_cast<__nv_bfloat16*>(smem + S::AW);
-    __nv_bfloat16* sAu = reinterpret_cast<__nv_bfloat16*>(smem + S::AU);
-    __nv_bfloat16* sQK = reinterpret_cast<__nv_bfloat16*>(smem + S::QK);
     __nv_bfloat16* sUh = reinterpret_cast<__nv_bfloat16*>(smem + S::UH);
     float* sG = reinterpret_cast<float*>(smem + S::G);
     float* sBeta = sG + CHUNK;
@@ -263,12 +279,12 @@ __global__ void __launch_bounds__(128, 3) gdn_prep_kernel(GdnArgs a) {
     // head is the fastest grid index: the H CTAs of one chunk run together and between them read
     // whole contiguous token rows of q, k, v (one head alone touches 128 B out of every H*128 B)
     const int h = blockIdx.x, c = blockIdx.y, H = a.H;
-    if (c >= a.chunk_off[a.nseq]) return;
+    ChunkLoc loc;
+    if (!locate_chunk(a, c, loc)) return;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int gq = lane >> 2, tq = lane & 3;
-    const int seq = find_seq(a.chunk_off, a.nseq, c);
-    const int64_t t0 = a.tok_off[seq] + (int64_t)(c - a.chunk_off[seq]) * CHUNK;
-    const int len = (int)min((int64_t)CHUNK, a.tok_off[seq + 1] - t0);
+    const int64_t t0 = loc.t0;
+    const int len = loc.len;
     const int LP = a.L + 1;
     PREP_TICK(0);
 
@@ -313,24 +329,20 @@ __global__ void __launch_bounds__(128, 3) gdn_prep_kernel(GdnArgs a) {
                 if (l < a.L) sLam[r * LP + l] = lv[i];
             }
         }
-        {   // L2 prefetch of the token rows of a chunk ~80 chunks ahead (all heads: thread pairs split the row)
-            const int c2 = c + 80;
-            if (c2 < a.chunk_off[a.nseq] && h == 0) {
-                const int s2 = find_seq(a.chunk_off, a.nseq, c2);
-                const int64_t t2 = a.tok_off[s2] + (int64_t)(c2 - a.chunk_off[s2]) * CHUNK + r;
-                if (t2 < a.tok_off[s2 + 1]) {
-                    const int eb = dtype_bytes(a.qkv_dt);
-                    const size_t rowq = (size_t)H * KD * eb, rowv = (size_t)H * VD * eb;
-                    const char* pq = (const char*)a.q + (size_t)t2 * rowq;
-                    const char* pk = (const char*)a.k + (size_t)t2 * rowq;
-                    const char* pv = (const char*)a.v + (size_t)t2 * rowv;
-                    for (size_t off = (size_t)half * 128; off < rowq; off += 256) {
-                        asm volatile("prefetch.global.L2 [%0];\n" :: "l"(pq + off));
-                        asm volatile("prefetch.global.L2 [%0];\n" :: "l"(pk + off));
-                    }
-                    for (size_t off = (size_t)half * 128; off < rowv; off += 256)
-                        asm volatile("prefetch.global.L2 [%0];\n" :: "l"(pv + off));
+        if (h == 0) {   // L2 prefetch of the token rows (all heads) of a chunk ~80 chunks ahead
+            ChunkLoc l2;
+            if (locate_chunk(a, c + 80, l2) && r < l2.len) {
+                const int eb = dtype_bytes(a.qkv_dt);
+                const size_t rowq = (size_t)H * KD * eb, rowv = (size_t)H * VD * eb;
+                const char* pq = (const char*)a.q + (size_t)(l2.t0 + r) * rowq;
+                const char* pk = (const char*)a.k + (size_t)(l2.t0 + r) * rowq;
+                const char* pv = (const char*)a.v + (size_t)(l2.t0 + r) * rowv;
+                for (size_t off = (size_t)half * 128; off < rowq; off += 256) {
+                    asm volatile("prefetch.global.L2 [%0];\n" :: "l"(pq + off));
+                    asm volatile("prefetch.global.L2 [%0];\n" :: "l"(pk + off));
                 }
+                for (size_t off = (size_t)half * 128; off < rowv; off += 256)
+                    asm volatile("prefetch.global.L2 [%0];\n" :: "l"(pv + off));
             }
         }
         float x[KD / 2];
@@ -400,46 +412,31 @@ __global__ void __launch_bounds__(128, 3) gdn_prep_kernel(GdnArgs a) {
 
     const int m0 = warp * 16;
     PREP_TICK(1);
-    // ---- stage 1: Q K^T -> tril, bf16 -------------------------------------------------------------
-    {
-        float acc[8][4];
-        zero_acc<8>(acc);
-        warp_gemm<8, KD, false, false>(acc, sQ, KP, m0, sK, KP, 0, lane, KD, m0 + 16);
-#pragma unroll
-        for (int nt = 0; nt < 8; ++nt) {
-#pragma unroll
-            for (int hh = 0; hh < 2; ++hh) {
-                const int i = m0 + gq + hh * 8, j = nt * 8 + 2 * tq;
-                const float r0 = (i >= j) ? acc[nt][2 * hh] : 0.f;
-                const float r1 = (i >= j + 1) ? acc[nt][2 * hh + 1] : 0.f;
-                *reinterpret_cast<uint32_t*>(sQK + i * CP + j) = pack_bf16x2(r0, r1);
-            }
-        }
-    }
-    // ---- stage 2: Aub = Awb .* E (Awb came from the solve kernel) ---------------------------------
-    {
-        const int r = tid >> 1, half = tid & 1;
-        const float Gr = sG[r];
-#pragma unroll
-        for (int cc = 0; cc < CHUNK / 2; cc += 2) {
-            const int col = half * (CHUNK / 2) + cc;
-            const float2 w = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(sAw + r * CP + col));
-            const float u0 = (r >= col) ? w.x * __expf(Gr - sG[col]) : 0.f;
-            const float u1 = (r >= col + 1) ? w.y * __expf(Gr - sG[col + 1]) : 0.f;
-            *reinterpret_cast<uint32_t*>(sAu + r * CP + col) = pack_bf16x2(u0, u1);
-        }
-    }
-    __syncthreads();
-
-    PREP_TICK(4);
     const float osc = HIER ? 1.f : a.scale;
-    // ---- stage 3 (rows m0..m0+15 of everything; nothing leaves the warp) --------------------------
+    // ---- per-warp part (rows m0..m0+15 of everything; nothing leaves the warp) --------------------
     {
-        // R = tril(QK^T) Awb, kept as accumulators and re-used as an A operand twice
+        // tril(Q K^T) as A fragments, straight from its accumulators
+        uint32_t ra[4][4];
         float racc[8][4];
         zero_acc<8>(racc);
-        warp_gemm<8, CHUNK, false, true>(racc, sQK, CP, m0, sAw, CP, 0, lane, m0 + 16, m0 + 16);
-        uint32_t ra[4][4];
+        warp_gemm<8, KD, false, false>(racc, sQ, KP, m0, sK, KP, 0, lane, KD, m0 + 16);
+#pragma unroll
+        for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int i = m0 + gq + (e >> 1) * 8, j = nt * 8 + 2 * tq + (e & 1);
+                if (i < j) racc[nt][e] = 0.f;
+            }
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) {
+            ra[kk][0] = pack_bf16x2(racc[2 * kk][0], racc[2 * kk][1]);
+            ra[kk][1] = pack_bf16x2(racc[2 * kk][2], racc[2 * kk][3]);
+            ra[kk][2] = pack_bf16x2(racc[2 * kk + 1][0], racc[2 * kk + 1][1]);
+            ra[kk][3] = pack_bf16x2(racc[2 * kk + 1][2], racc[2 * kk + 1][3]);
+        }
+        // R = tril(QK^T) Awb, kept as accumulators and re-used as an A operand twice
+        zero_acc<8>(racc);
+        warp_gemm_ra<8, 4, true>(racc, ra, sAw, CP, 0, lane, m0 + 16, m0 + 16);
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk) {
             ra[kk][0] = pack_bf16x2(racc[2 * kk][0], racc[2 * kk][1]);
@@ -498,11 +495,34 @@ __global__ void __launch_bounds__(128, 3) gdn_prep_kernel(GdnArgs a) {
                         make_float2(osc * acc[nt][2 * hh], osc * acc[nt][2 * hh + 1]);
                 }
         }
-        // U^ = diag(e^{Glast-G}) Aub V
+        // U^ = diag(e^{Glast-G}) (Awb .* E) V: the decay is applied to the A fragments in registers
         {
             float acc[VD / 8][4];
             zero_acc<VD / 8>(acc);
-            warp_gemm<VD / 8, CHUNK, false, true>(acc, sAu, CP, m0, sV, VP, 0, lane, m0 + 16, VD);
+            const float g_lo = sG[m0 + gq], g_hi = sG[m0 + gq + 8];
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk) {
+                if (kk * 16 < m0 + 16) {
+                    uint32_t af[4];
+                    load_a(af, sAw, CP, m0, kk * 16, lane);
+#pragma unroll
+                    for (int x = 0; x < 4; ++x) {
+                        const int i = m0 + gq + (x & 1) * 8, j = kk * 16 + (x >> 1) * 8 + 2 * tq;
+                        const float gi = (x & 1) ? g_hi : g_lo;
+                        const float2 w = unpack_bf16x2(af[x]);
+                        const float u0 = (i >= j) ? w.x * __expf(gi - sG[j]) : 0.f;
+                        const float u1 = (i >= j + 1) ? w.y * __expf(gi - sG[j + 1]) : 0.f;
+                        af[x] = pack_bf16x2(u0, u1);
+                    }
+#pragma unroll
+                    for (int nt = 0; nt < VD / 8; nt += 2) {
+                        uint32_t b[4];
+                        load_b_t(b, sV, VP, nt * 8, kk * 16, lane);
+                        mma16816(acc[nt], af, b[0], b[1]);
+                        mma16816(acc[nt + 1], af, b[2], b[3]);
+                    }
+                }
+            }
 #pragma unroll
             for (int nt = 0; nt < VD / 8; ++nt)
 #pragma unroll
@@ -571,7 +591,7 @@ int launch_prep(const GdnArgs& a, bool hier, cudaStream_t st) {
     cudaError_t e;
     {
         ProfScope prof_s("gdn_solve", st);
-        gdn_solve_kernel<KD, VD><<<grid, 64, SolveSmem<KD>::BYTES, st>>>(a);
+        gdn_solve_kernel<KD, VD><<<grid, 32, SolveSmem<KD>::BYTES, st>>>(a);
         if (cudaGetLastError() != cudaSuccess) return LAMPA_ERR_CUDA;
     }
     ProfScope prof(hier ? "gdn_prep_hier" : "gdn_prep_plain", st);
