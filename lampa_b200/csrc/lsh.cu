@@ -66,15 +66,20 @@ lsh_hash_kernel(const float* __restrict__ x, int64_t row_stride, int64_t head_st
 }
 
 // -------------------------------------------------------------------------------------------------
-// Segmented stable LSD radix sort.  One thread-block cluster of 8 CTAs per segment: each CTA owns
-// a contiguous eighth of the segment in its current order, digit histograms are exchanged through
-// distributed shared memory, and the passes are separated by the hardware cluster barrier (no
-// flag spinning anywhere).  Keys are reduced to (key - min) first, so only ceil(bits(range)/8)
-// passes run: two for the ~15-bit bucket ids of this workload.
+// Segmented stable LSD radix sort.  One thread-block cluster (up to 8 CTAs, sized at launch so that
+// all clusters are resident at once) per segment: each CTA owns a contiguous slice of the segment
+// in its current order, digit histograms are exchanged through distributed shared memory, and the
+// passes are separated by the hardware cluster barrier (no flag spinning anywhere).  Keys are
+// reduced to (key - min) first, so only ceil(bits(range)/8) passes run: two for the ~15-bit bucket
+// ids of this workload.  Inside a pass a CTA walks its slice in tiles of 4096 keys; a warp takes
+// 128 consecutive keys as four rounds of 32, ranking each round with match_any on top of a
+// per-warp digit histogram, so the order (round, lane) is the key order and the sort is stable.
 // -------------------------------------------------------------------------------------------------
 constexpr int SORT_THREADS = 1024;
-constexpr int SORT_CL = 8;
+constexpr int SORT_MAX_CL = 8;
 constexpr int SORT_WARPS = SORT_THREADS / 32;
+constexpr int SORT_ITEMS = 4;
+constexpr int SORT_TILE = SORT_THREADS * SORT_ITEMS;
 
 __device__ __forceinline__ uint32_t key_xform(const void* keys, int key_type, int64_t i) {
     uint32_t u = ((const uint32_t*)keys)[i];
@@ -84,21 +89,22 @@ __device__ __forceinline__ uint32_t key_xform(const void* keys, int key_type, in
     return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
 }
 
-__global__ void __cluster_dims__(SORT_CL, 1, 1) __launch_bounds__(SORT_THREADS, 1)
+__global__ void __launch_bounds__(SORT_THREADS, 1)
 segsort_kernel(const void* __restrict__ keys, int key_type, int64_t n_total,
                const int64_t* __restrict__ seg, int nseg, const int64_t* __restrict__ init,
                int64_t* __restrict__ perm, uint32_t* kbuf0, uint32_t* kbuf1, uint32_t* ibuf0,
                uint32_t* ibuf1) {
     cg::cluster_group cluster = cg::this_cluster();
     const int rank = (int)cluster.block_rank();
-    const int s = blockIdx.x / SORT_CL;
+    const int ncl = (int)cluster.num_blocks();
+    const int s = blockIdx.x / ncl;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
 
     int64_t s0, n;
     if (seg) { s0 = seg[s]; n = seg[s + 1] - s0; }
     else { n = n_total / nseg; s0 = (int64_t)s * n; }
     if (n < 0) n = 0;
-    const int64_t per = (n + SORT_CL - 1) / SORT_CL;
+    const int64_t per = (n + ncl - 1) / ncl;
     const int64_t lo = min((int64_t)rank * per, n), hi = min(lo + per, n);
 
     __shared__ uint32_t hist[256];
@@ -127,7 +133,7 @@ segsort_kernel(const void* __restrict__ keys, int key_type, int64_t n_total,
     __syncthreads();
     cluster.sync();
     uint32_t gmn = 0xFFFFFFFFu, gmx = 0u;
-    for (int r = 0; r < SORT_CL; ++r) {
+    for (int r = 0; r < ncl; ++r) {
         const uint32_t* rr = cluster.map_shared_rank(red, r);
         gmn = min(gmn, rr[0]); gmx = max(gmx, rr[1]);
     }
@@ -162,10 +168,10 @@ segsort_kernel(const void* __restrict__ keys, int key_type, int64_t n_total,
         // (b) where each digit of this slice starts in the segment
         uint32_t tot = 0, before = 0, incl = 0;
         if (tid < 256) {
-            for (int r = 0; r < SORT_CL; ++r) {
-                const uint32_t h = cluster.map_shared_rank(hist, r)[tid];
-                tot += h;
-                if (r < rank) before += h;
+            for (int r = 0; r < ncl; ++r) {
+                const uint32_t hv = cluster.map_shared_rank(hist, r)[tid];
+                tot += hv;
+                if (r < rank) before += hv;
             }
             incl = tot;
 #pragma unroll
@@ -184,25 +190,37 @@ segsort_kernel(const void* __restrict__ keys, int key_type, int64_t n_total,
         __syncthreads();
 
         // (c) stable scatter, tile by tile in slice order
-        for (int64_t t0 = lo; t0 < hi; t0 += SORT_THREADS) {
-            const int64_t i = t0 + tid;
-            const bool valid = i < hi;
-            uint32_t u = 0, idx = 0;
-            if (valid) {
-                if (p == 0) {
-                    idx = init ? (uint32_t)init[s0 + i] : (uint32_t)i;
-                    u = key_xform(keys, key_type, s0 + idx) - gmn;
+        for (int64_t t0 = lo; t0 < hi; t0 += SORT_TILE) {
+            uint32_t u[SORT_ITEMS], idx[SORT_ITEMS], rnk[SORT_ITEMS], dg[SORT_ITEMS];
+#pragma unroll
+            for (int it = 0; it < SORT_ITEMS; ++it) {
+                const int64_t i = t0 + warp * (32 * SORT_ITEMS) + it * 32 + lane;
+                u[it] = 0; idx[it] = 0;
+                if (i < hi) {
+                    if (p == 0) {
+                        idx[it] = init ? (uint32_t)init[s0 + i] : (uint32_t)i;
+                        u[it] = key_xform(keys, key_type, s0 + idx[it]) - gmn;
+                    } else {
+                        u[it] = ksrc[s0 + i];
+                        idx[it] = isrc[s0 + i];
+                    }
+                    dg[it] = (u[it] >> shift) & 255u;
                 } else {
-                    u = ksrc[s0 + i];
-                    idx = isrc[s0 + i];
+                    dg[it] = 256u;
                 }
             }
-            const uint32_t digit = valid ? ((u >> shift) & 255u) : 256u;
             for (int z = tid; z < SORT_WARPS * 256; z += SORT_THREADS) (&wcount[0][0])[z] = 0;
             __syncthreads();
-            const uint32_t m = __match_any_sync(0xffffffffu, digit);
-            const uint32_t rank_in_warp = __popc(m & ((1u << lane) - 1u));
-            if (valid && (__ffs(m) - 1) == lane) wcount[warp][digit] = __popc(m);
+#pragma unroll
+            for (int it = 0; it < SORT_ITEMS; ++it) {
+                const uint32_t m = __match_any_sync(0xffffffffu, dg[it]);
+                const bool valid = dg[it] < 256u;
+                const uint32_t basecnt = valid ? wcount[warp][dg[it]] : 0u;
+                rnk[it] = basecnt + __popc(m & ((1u << lane) - 1u));
+                __syncwarp();
+                if (valid && (__ffs(m) - 1) == lane) wcount[warp][dg[it]] = basecnt + __popc(m);
+                __syncwarp();
+            }
             __syncthreads();
             if (tid < 256) {
                 uint32_t run = 0;
@@ -215,13 +233,16 @@ segsort_kernel(const void* __restrict__ keys, int key_type, int64_t n_total,
                 tile_tot[tid] = run;
             }
             __syncthreads();
-            if (valid) {
-                const int64_t pos = (int64_t)dbase[digit] + wcount[warp][digit] + rank_in_warp;
-                if (last) {
-                    perm[s0 + pos] = (int64_t)idx;
-                } else {
-                    kdst[s0 + pos] = u;
-                    idst[s0 + pos] = idx;
+#pragma unroll
+            for (int it = 0; it < SORT_ITEMS; ++it) {
+                if (dg[it] < 256u) {
+                    const int64_t pos = (int64_t)dbase[dg[it]] + wcount[warp][dg[it]] + rnk[it];
+                    if (last) {
+                        perm[s0 + pos] = (int64_t)idx[it];
+                    } else {
+                        kdst[s0 + pos] = u[it];
+                        idst[s0 + pos] = idx[it];
+                    }
                 }
             }
             __syncthreads();
@@ -231,6 +252,37 @@ segsort_kernel(const void* __restrict__ keys, int key_type, int64_t n_total,
         cluster.sync();   // scattered keys visible to the whole cluster; histograms free again
     }
     cluster.sync();       // no CTA leaves while a peer may still read its shared memory
+}
+
+// Cluster size for nseg segments: as large as possible (<= 8) while all clusters fit the GPU at once.
+static int sort_cluster_size(int nseg) {
+    int dev = 0, sms = 148;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    int cl = sms / (nseg > 0 ? nseg : 1);
+    if (cl > SORT_MAX_CL) cl = SORT_MAX_CL;
+    if (cl < 1) cl = 1;
+    return cl;
+}
+
+static int launch_segsort(const void* keys, int key_type, int64_t n_total, const int64_t* seg, int nseg,
+                          const int64_t* init, int64_t* perm, uint32_t* k0, uint32_t* k1, uint32_t* i0,
+                          uint32_t* i1, cudaStream_t st) {
+    const int cl = sort_cluster_size(nseg);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)nseg * cl, 1, 1);
+    cfg.blockDim = dim3(SORT_THREADS, 1, 1);
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = cl;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, segsort_kernel, keys, key_type, n_total, seg, nseg, init, perm,
+                                             k0, k1, i0, i1);
+    return e == cudaSuccess ? LAMPA_OK : LAMPA_ERR_CUDA;
 }
 
 // -------------------------------------------------------------------------------------------------
@@ -323,9 +375,7 @@ extern "C" int lampa_segsort_stable(const void* keys, int32_t key_type, int64_t 
     uint32_t* i0 = (uint32_t*)(base + 2 * stride);
     uint32_t* i1 = (uint32_t*)(base + 3 * stride);
     ProfScope prof("segsort", (cudaStream_t)stream);
-    segsort_kernel<<<(unsigned)nseg * SORT_CL, SORT_THREADS, 0, (cudaStream_t)stream>>>(
-        keys, key_type, n_total, seg_offsets, nseg, init, perm, k0, k1, i0, i1);
-    return cudaGetLastError() == cudaSuccess ? LAMPA_OK : LAMPA_ERR_CUDA;
+    return launch_segsort(keys, key_type, n_total, seg_offsets, nseg, init, perm, k0, k1, i0, i1, (cudaStream_t)stream);
 }
 
 extern "C" int lampa_permute_rows(const void* src, const int64_t* perm, const int64_t* seg_offsets,
@@ -407,9 +457,7 @@ extern "C" int lampa_segsort_stable_static(const void* keys, int32_t key_type, i
     // No buffer needs clearing between calls: every pass writes positions [0, n) of its
     // destination pair before the next pass reads them, and nothing beyond n is ever read.
     ProfScope prof("segsort_static", (cudaStream_t)stream);
-    segsort_kernel<<<(unsigned)nseg * SORT_CL, SORT_THREADS, 0, (cudaStream_t)stream>>>(
-        keys, key_type, n_total, seg_offsets, nseg, init, perm, (uint32_t*)base,
-        (uint32_t*)(base + kStaticSortStride), (uint32_t*)(base + 2 * kStaticSortStride),
-        (uint32_t*)(base + 3 * kStaticSortStride));
-    return cudaGetLastError() == cudaSuccess ? LAMPA_OK : LAMPA_ERR_CUDA;
+    return launch_segsort(keys, key_type, n_total, seg_offsets, nseg, init, perm, (uint32_t*)base,
+                          (uint32_t*)(base + kStaticSortStride), (uint32_t*)(base + 2 * kStaticSortStride),
+                          (uint32_t*)(base + 3 * kStaticSortStride), (cudaStream_t)stream);
 }
