@@ -299,6 +299,7 @@ def run_ours(args):
         alg = {   # algorithmic cost of one launch of each kernel on this workload
             "gdn_prep_hier": ("tensor", H * n_chunks * (7 * 524288 + 2 * 174763)),
             "gdn_out_hier": ("tensor", H * n_chunks * (n_lev * 2.5 * 524288)),
+            "gdn_solve": ("hbm", H * n_chunks * (64 * 64 * 2 + 64 * 72 * 2 + 64 * 4)),   # reads k, beta; writes Awb
             "gdn_compose": ("tensor", H * n_chunks * 2 * 2 * 64 ** 3),
             "gdn_level_hier": ("tensor", H * (n_chunks // 32) * 5 * 2 * 64 ** 3),
             "lsh_hash": ("hbm", N_HITS * 120),
@@ -306,6 +307,10 @@ def run_ours(args):
             "permute_rows": ("hbm", N_HITS * (16 + 2 * (96 + H * V * 2)) / 2),
             "gdn_plan": ("hbm", 64),
         }
+        # DRAM bytes (read + write) per launch on the default workload, from the committed ncu capture
+        # profiles/kernels_bench_60k_hier.md
+        ncu_traffic = {"gdn_prep_hier": 639.4e6, "gdn_out_hier": 435.2e6, "gdn_solve": 104.6e6, "gdn_compose": 145.4e6,
+                       "gdn_level_hier": 6.6e6, "segsort": 5.8e6, "lsh_hash": 5.8e6, "permute_rows": 6.3e6}
         bound, units = alg.get(dom, ("hbm", 0))
         dur_s = per_kernel[dom]["ms_per_launch"] * 1e-3
         if bound == "tensor":
@@ -326,7 +331,8 @@ def run_ours(args):
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps},
             "gpu_launches": int(round(sum(v["launches_per_step"] for v in per_kernel.values()) * args.steps)),
             "roofline": {"kernel": dom, "bound": bound, "achieved": achieved, "peak": peak, "unit": unit,
-                         "frac": achieved / peak, "traffic": None, "peak_source": pk["source"],
+                         "frac": achieved / peak,
+                         "traffic": ncu_traffic.get(dom) if N_HITS == 60000 else None, "peak_source": pk["source"],
                          "whole_step_hbm_gbs": N_HITS * 4432 / (ms / args.steps * 1e-3) / 1e9},
             "kernels": per_kernel,
         }
