@@ -64,7 +64,7 @@ int lampa_version(void);
 const char* lampa_error_string(int code);
 
 /*
- * Bytes of scratch for lampa_gdn_fwd / lampa_hgdn_fwd with this descriptor (256-byte aligned
+ * Bytes of scratch for lampa_gdn_fwd / lampa_hgdn_fwd with this descriptor (1024-byte aligned
  * pointer expected).  Replaces the reference's torch.empty intermediates (A, Ad, w, u, h, v_new:
  * models/hattention/gated_delta_rule_ori.py:29-80, chunkwise_hgdn.py:628-760).
  */
@@ -73,8 +73,9 @@ int lampa_gdn_workspace_bytes(const lampa_gdn_desc* d, size_t* bytes);
 /*
  * Where the per-chunk intermediates live inside the workspace, for tests that inspect them.
  * One record per (chunk slot, head), chunk-major.  out[0] = byte offset of the first record,
- * out[1] = bytes per record, then byte offsets inside a record of: out[2] M (bf16 [K][K+8]),
- * out[3] B^T (bf16 [V][K+8]), out[4] Q~ (bf16 [64][K+8]), out[5] O_local (fp32 [64][V+8]),
+ * out[1] = bytes per record, then byte offsets inside a record of the bf16 tiles out[2] M [K][K],
+ * out[3] B^T [V][K], out[4] Q~ [64][K] (row pitch K+8 elements, except K = 64: dense 128-byte rows
+ * with the 16-byte chunk index XORed with row%8), out[5] O_local (fp32 [64][V+8]),
  * out[6] chunk-level lambda (fp32 [LC][64], hierarchical only); out[7] = LC, out[8] = number of
  * chunk slots, out[9] = chunks per block, out[10] / out[11] = byte offsets of the block composites
  * and of the block entry states.

@@ -19,26 +19,42 @@ constexpr int BLOCK_LOG = 5;         // log2(BLOCK_CHUNKS): chunk levels 0..4 li
 constexpr int NLW = 5;               // level states carried per warp in the hierarchical output pass
 constexpr int MAX_GROUPS = 3;        // 1 group of in-block levels + up to 2 groups of cross-block levels
 
+// Layout of a K-wide bf16 tile ([rows][KD]) inside a record.  For KD = 64 rows are dense 128-byte
+// lines whose eight 16-byte chunks are XOR-swizzled with the row index (the 128B-swizzle pattern
+// tcgen05.mma and ldmatrix both read without bank conflicts); other widths use a padded pitch.
+template <int KD>
+struct Tile {
+    static constexpr bool SWZ = (KD == 64);
+    static constexpr int PITCH = SWZ ? 64 : KD + 8;
+    __host__ __device__ static constexpr int off(int r, int c) {
+        return SWZ ? r * 64 + ((((c >> 3) ^ r) & 7) << 3) + (c & 7) : r * PITCH + c;
+    }
+    __host__ __device__ static constexpr int bytes(int rows) { return rows * PITCH * 2; }
+};
+
 template <int KD, int VD>
 struct Rec {
-    static constexpr int KP = KD + 8;                 // bf16 row pitch (elements) of K-wide tiles
+    using T = Tile<KD>;
+    static constexpr int KP = KD + 8;                 // padded bf16 row pitch (block composites)
     static constexpr int OP = VD + 8;                 // fp32 row pitch (elements) of O_local
     static constexpr int M_OFF = 0;
-    static constexpr int M_BYTES = KD * KP * 2;       // M[k_out][k_in]
-    static constexpr int BT_OFF = M_OFF + M_BYTES;
-    static constexpr int BT_BYTES = VD * KP * 2;      // B^T[v][k]
-    static constexpr int QT_OFF = BT_OFF + BT_BYTES;
-    static constexpr int QT_BYTES = CHUNK * KP * 2;   // Q~[token][k]
-    static constexpr int OL_OFF = QT_OFF + QT_BYTES;
+    static constexpr int M_BYTES = T::bytes(KD);      // M[k_out][k_in]
+    static constexpr int QT_OFF = M_OFF + M_BYTES;    // M and Q~ are adjacent: together they are one 128-row B operand
+    static constexpr int QT_BYTES = T::bytes(CHUNK);  // Q~[token][k]
+    static constexpr int BT_OFF = QT_OFF + QT_BYTES;
+    static constexpr int BT_BYTES = T::bytes(VD);     // B^T[v][k]
+    static constexpr int OL_OFF = BT_OFF + BT_BYTES;
     static constexpr int OL_BYTES = CHUNK * OP * 4;   // O_local[token][v]
     static constexpr int LAM_OFF = OL_OFF + OL_BYTES; // lambda of chunk levels: [LC][64] fp32
-    static constexpr int MB_BYTES = M_BYTES + BT_BYTES;
+    static constexpr int PRE_BYTES = OL_OFF;          // M, Q~, B^T: what the compose pass streams
+    static constexpr int ALIGN = T::SWZ ? 1024 : 128; // records and shared-memory stages
     __host__ __device__ static constexpr int bytes(int LC) { return LAM_OFF + LC * CHUNK * 4; }
-    // block composite: Mblk[k_out][k_in] bf16, then Bblk^T[v][k] fp32 (pitch KD + 8)
+    // block composite: Mblk[k_out][k_in] bf16 (padded pitch), then Bblk^T[v][k] fp32 (pitch KD + 8)
     static constexpr int BP = KD + 8;
     static constexpr int BLK_M_OFF = 0;
-    static constexpr int BLK_B_OFF = M_BYTES;
-    static constexpr int BLK_BYTES = M_BYTES + VD * BP * 4;
+    static constexpr int BLK_M_BYTES = KD * KP * 2;
+    static constexpr int BLK_B_OFF = BLK_M_BYTES;
+    static constexpr int BLK_BYTES = BLK_M_BYTES + VD * BP * 4;
     static constexpr int STATE_FLOATS = VD * KD;      // an S^T[v][k] fp32 state
 };
 

@@ -16,7 +16,7 @@ struct Layout {
 template <int KD, int VD>
 void fill_sizes(Layout& l) {
     using R = Rec<KD, VD>;
-    l.rec_bytes = align_up((size_t)R::bytes(l.LC), 128);
+    l.rec_bytes = align_up((size_t)R::bytes(l.LC), R::ALIGN);
     l.blk_bytes = R::BLK_BYTES;
     l.state_bytes = (size_t)R::STATE_FLOATS * 4;
 }
@@ -57,6 +57,7 @@ int make_layout(const lampa_gdn_desc* d, bool hier, Layout& l) {
     l.off_tok = off;   off = align_up(off + (size_t)(l.nseq + 1) * 8, 256);
     l.off_chunk = off; off = align_up(off + (size_t)(l.nseq + 1) * 4, 256);
     l.off_block = off; off = align_up(off + (size_t)(l.nseq + 1) * 4, 256);
+    off = align_up(off, 1024);
     l.off_rec = off;   off = align_up(off + (size_t)l.nc_max * d->H * l.rec_bytes, 256);
     l.off_blk = off;   off = align_up(off + (size_t)l.nb_max * d->H * l.blk_bytes, 256);
     l.off_entry = off;
@@ -74,7 +75,7 @@ int run(const lampa_gdn_desc* d, bool hier, const void* q, const void* k, const 
     if ((int64_t)d->B * d->T == 0) return LAMPA_OK;
     if (!q || !k || !v || !g || !beta || !o || !ws || (hier && !lam)) return LAMPA_ERR_ARG;
     if (d->nseq > 0 && !cu) return LAMPA_ERR_ARG;
-    if (ws_bytes < l.total || ((uintptr_t)ws & 255)) return LAMPA_ERR_WORKSPACE;
+    if (ws_bytes < l.total || ((uintptr_t)ws & 1023)) return LAMPA_ERR_WORKSPACE;
     if ((((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)o) & 15)) return LAMPA_ERR_ARG;
     if (hier && !cu && d->L < ELL0 + ((d->T + CHUNK - 1) / CHUNK > 1 ? ceil_log2_int((d->T + CHUNK - 1) / CHUNK) : 0))
         return LAMPA_ERR_LEVELS;
@@ -125,7 +126,7 @@ extern "C" const char* lampa_error_string(int code) {
         case LAMPA_OK: return "ok";
         case LAMPA_ERR_ARG: return "invalid argument";
         case LAMPA_ERR_UNSUPPORTED: return "unsupported shape (head dims must be 64/64, 32/32 or 16/32; sequence too long)";
-        case LAMPA_ERR_WORKSPACE: return "workspace too small or not 256-byte aligned";
+        case LAMPA_ERR_WORKSPACE: return "workspace too small or not 1024-byte aligned";
         case LAMPA_ERR_CUDA: return "CUDA runtime error at launch";
         case LAMPA_ERR_TIMEOUT: return "device wait ran out";
         case LAMPA_ERR_LEVELS: return "lambda has fewer levels than 7 + ceil(log2(chunks))";

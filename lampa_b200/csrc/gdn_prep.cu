@@ -457,7 +457,7 @@ __global__ void __launch_bounds__(128, 4) gdn_prep_kernel(GdnArgs a) {
                     const int i = m0 + gq + hh * 8, j = nt * 8 + 2 * tq;
                     const float f = osc * sEG[i];
                     const float2 qv = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(sQ + i * KP + j));
-                    *reinterpret_cast<uint32_t*>(gQ + i * KP + j) =
+                    *reinterpret_cast<uint32_t*>(gQ + R::T::off(i, j)) =
                         pack_bf16x2(f * (qv.x - acc[nt][2 * hh]), f * (qv.y - acc[nt][2 * hh + 1]));
                 }
         }
@@ -564,7 +564,7 @@ __global__ void __launch_bounds__(128, 4) gdn_prep_kernel(GdnArgs a) {
                 const int i = m0 + gq + hh * 8, j = nt * 8 + 2 * tq;
                 const float m_0 = egl * (((i == j) ? 1.f : 0.f) - acc[nt][2 * hh]);
                 const float m_1 = egl * (((i == j + 1) ? 1.f : 0.f) - acc[nt][2 * hh + 1]);
-                *reinterpret_cast<uint32_t*>(gM + i * KP + j) = pack_bf16x2(m_0, m_1);
+                *reinterpret_cast<uint32_t*>(gM + R::T::off(i, j)) = pack_bf16x2(m_0, m_1);
             }
     }
     if (m0 < VD) {
@@ -577,7 +577,7 @@ __global__ void __launch_bounds__(128, 4) gdn_prep_kernel(GdnArgs a) {
 #pragma unroll
             for (int hh = 0; hh < 2; ++hh) {
                 const int i = m0 + gq + hh * 8, j = nt * 8 + 2 * tq;
-                *reinterpret_cast<uint32_t*>(gB + i * KP + j) = pack_bf16x2(acc[nt][2 * hh], acc[nt][2 * hh + 1]);
+                *reinterpret_cast<uint32_t*>(gB + R::T::off(i, j)) = pack_bf16x2(acc[nt][2 * hh], acc[nt][2 * hh + 1]);
             }
     }
     PREP_TICK(6);

@@ -36,30 +36,38 @@ __device__ __forceinline__ void pack_state(const float (&C)[KD / 8][4], uint32_t
     }
 }
 
-// C += slab * M^T, with sM[k_out][k_in] row-major (pitch KD + 8)
+// Element offset inside a bf16 tile: TL is Tile<KD> (record tiles, swizzled for KD = 64) or Padded<KD>
+// (block composites).
 template <int KD>
+struct Padded {
+    __device__ static constexpr int off(int r, int c) { return r * (KD + 8) + c; }
+};
+
+// C += slab * M^T, with sM[k_out][k_in]
+template <int KD, class TL>
 __device__ __forceinline__ void state_times_mt(float (&C)[KD / 8][4], const uint32_t (&sp)[KD / 16][4],
                                                const __nv_bfloat16* sM, int lane) {
+    const int mi = lane >> 3, r = lane & 7;
 #pragma unroll
     for (int kk = 0; kk < KD / 16; ++kk) {
 #pragma unroll
         for (int nt = 0; nt < KD / 8; nt += 2) {
             uint32_t b[4];
-            load_b(b, sM, KD + 8, nt * 8, kk * 16, lane);
+            ldsm_x4(b, smem_u32(sM + TL::off(nt * 8 + r + (mi >> 1) * 8, kk * 16 + (mi & 1) * 8)));
             mma16816(C[nt], sp[kk], b[0], b[1]);
             mma16816(C[nt + 1], sp[kk], b[2], b[3]);
         }
     }
 }
 
-// C = rows row0+g, row0+g+8 of a bf16 [rows][KD + 8] tile
+// C = rows row0+g, row0+g+8 of a bf16 [rows][KD] record tile
 template <int KD>
 __device__ __forceinline__ void load_slab_bf16(float (&C)[KD / 8][4], const __nv_bfloat16* s, int row0, int lane) {
     const int g = lane >> 2, t = lane & 3;
 #pragma unroll
     for (int nt = 0; nt < KD / 8; ++nt) {
-        const float2 lo = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(s + (row0 + g) * (KD + 8) + nt * 8 + 2 * t));
-        const float2 hi = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(s + (row0 + g + 8) * (KD + 8) + nt * 8 + 2 * t));
+        const float2 lo = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(s + Tile<KD>::off(row0 + g, nt * 8 + 2 * t)));
+        const float2 hi = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(s + Tile<KD>::off(row0 + g + 8, nt * 8 + 2 * t)));
         C[nt][0] = lo.x; C[nt][1] = lo.y; C[nt][2] = hi.x; C[nt][3] = hi.y;
     }
 }
@@ -93,7 +101,10 @@ __device__ __forceinline__ void read_tile(float (&tmp)[2][4], const uint32_t (&s
 #pragma unroll
     for (int kk = 0; kk < KD / 16; ++kk) {
         uint32_t a[4];
-        load_a(a, sQt, KD + 8, mt * 16, kk * 16, lane);
+        {
+            const int mi = lane >> 3, r = lane & 7;
+            ldsm_x4(a, smem_u32(sQt + Tile<KD>::off(mt * 16 + r + (mi & 1) * 8, kk * 16 + (mi >> 1) * 8)));
+        }
         mma16816(tmp[0], a, sp[kk][0], sp[kk][2]);
         mma16816(tmp[1], a, sp[kk][1], sp[kk][3]);
     }
@@ -151,7 +162,7 @@ __global__ void __launch_bounds__((KD + VD) * 2) gdn_compose_kernel(GdnArgs a) {
     using R = Rec<KD, VD>;
     constexpr int NST = 3;
     constexpr int NS = VD / 16;
-    extern __shared__ __align__(128) unsigned char smem[];
+    extern __shared__ __align__(1024) unsigned char smem[];
     const int gb = blockIdx.x, h = blockIdx.y;
     if (gb >= a.block_off[a.nseq]) return;
     const int seq = find_seq(a.block_off, a.nseq, gb);
@@ -164,11 +175,11 @@ __global__ void __launch_bounds__((KD + VD) * 2) gdn_compose_kernel(GdnArgs a) {
 
     Pipe<NST> pipe;
     pipe.bar = reinterpret_cast<uint64_t*>(smem);
-    pipe.stage = smem + 128;
-    pipe.stage_bytes = R::MB_BYTES;
+    pipe.stage = smem + 1024;
+    pipe.stage_bytes = R::PRE_BYTES;
     pipe.src = a.rec + ((size_t)c0 * a.H + h) * a.rec_bytes;
     pipe.src_stride = (size_t)a.H * a.rec_bytes;
-    pipe.copy_bytes = R::MB_BYTES;
+    pipe.copy_bytes = R::PRE_BYTES;
     pipe.nsteps = nsteps;
     pipe.dead = false;
     pipe.status = a.status;
@@ -193,10 +204,10 @@ __global__ void __launch_bounds__((KD + VD) * 2) gdn_compose_kernel(GdnArgs a) {
         pack_state<KD>(C, sp);
         if (is_s) {
             load_slab_bf16<KD>(C, sBt, row0, lane);
-            if (i > 0) state_times_mt<KD>(C, sp, sM, lane);
+            if (i > 0) state_times_mt<KD, Tile<KD>>(C, sp, sM, lane);
         } else {
             zero_state<KD>(C);
-            state_times_mt<KD>(C, sp, sM, lane);
+            state_times_mt<KD, Tile<KD>>(C, sp, sM, lane);
         }
     }
     char* blk = a.blk + ((size_t)gb * a.H + h) * R::BLK_BYTES;
@@ -210,7 +221,7 @@ __global__ void __launch_bounds__((KD + VD) * 2) gdn_compose_kernel(GdnArgs a) {
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 const int kin = row0 + g + (e >> 1) * 8, kout = nt * 8 + 2 * t + (e & 1);
-                gm[kout * R::KP + kin] = __float2bfloat16_rn(C[nt][e]);
+                gm[kout * R::KP + kin] = __float2bfloat16_rn(C[nt][e]);   // block composites keep the padded pitch
             }
     }
 }
@@ -226,7 +237,7 @@ template <int KD, int VD, bool HIER>
 __global__ void __launch_bounds__(VD * 2) gdn_level_kernel(GdnArgs a) {
     using R = Rec<KD, VD>;
     constexpr int NST = 3;
-    extern __shared__ __align__(128) unsigned char smem[];
+    extern __shared__ __align__(1024) unsigned char smem[];
     const int seq = blockIdx.x, h = blockIdx.y, lh = blockIdx.z, H = a.H;
     const int nblk = a.block_off[seq + 1] - a.block_off[seq];
     const int gb0 = a.block_off[seq];
@@ -241,7 +252,7 @@ __global__ void __launch_bounds__(VD * 2) gdn_level_kernel(GdnArgs a) {
 
     Pipe<NST> pipe;
     pipe.bar = reinterpret_cast<uint64_t*>(smem);
-    pipe.stage = smem + 128;
+    pipe.stage = smem + 1024;
     pipe.stage_bytes = R::BLK_BYTES;
     pipe.src = a.blk + ((size_t)gb0 * H + h) * R::BLK_BYTES;
     pipe.src_stride = (size_t)H * R::BLK_BYTES;
@@ -273,7 +284,7 @@ __global__ void __launch_bounds__(VD * 2) gdn_level_kernel(GdnArgs a) {
             store_slab_f32<KD>(C, e, KD, row0, lane);
             pack_state<KD>(C, sp);
             load_slab_f32<KD>(C, sB, R::BP, row0, lane);
-            if (nonzero) state_times_mt<KD>(C, sp, sM, lane);
+            if (nonzero) state_times_mt<KD, Padded<KD>>(C, sp, sM, lane);
             nonzero = true;
         } else {
             const int period = 2 << lh, pos = b & (period - 1), bit = (b >> lh) & 1;
@@ -287,7 +298,7 @@ __global__ void __launch_bounds__(VD * 2) gdn_level_kernel(GdnArgs a) {
                 pack_state<KD>(C, sp);
                 if (bit == 0) load_slab_f32<KD>(C, sB, R::BP, row0, lane);
                 else zero_state<KD>(C);
-                if (pos != 0) state_times_mt<KD>(C, sp, sM, lane);
+                if (pos != 0) state_times_mt<KD, Padded<KD>>(C, sp, sM, lane);
             }
         }
     }
@@ -308,7 +319,7 @@ template <int KD, int VD>
 __global__ void __launch_bounds__(VD * 2) gdn_out_plain_kernel(GdnArgs a) {
     using R = Rec<KD, VD>;
     constexpr int NST = 3;
-    extern __shared__ __align__(128) unsigned char smem[];
+    extern __shared__ __align__(1024) unsigned char smem[];
     const int gb = blockIdx.x, h = blockIdx.y, H = a.H;
     if (gb >= a.block_off[a.nseq]) return;
     const int seq = find_seq(a.block_off, a.nseq, gb);
@@ -323,7 +334,7 @@ __global__ void __launch_bounds__(VD * 2) gdn_out_plain_kernel(GdnArgs a) {
 
     Pipe<NST> pipe;
     pipe.bar = reinterpret_cast<uint64_t*>(smem);
-    pipe.stage = smem + 128;
+    pipe.stage = smem + 1024;
     pipe.stage_bytes = R::LAM_OFF;
     pipe.src = a.rec + ((size_t)c0 * H + h) * a.rec_bytes;
     pipe.src_stride = (size_t)H * a.rec_bytes;
@@ -364,7 +375,7 @@ __global__ void __launch_bounds__(VD * 2) gdn_out_plain_kernel(GdnArgs a) {
         }
         if (i + 1 < nsteps) {
             load_slab_bf16<KD>(C, sBt, row0, lane);
-            state_times_mt<KD>(C, sp, sM, lane);
+            state_times_mt<KD, Tile<KD>>(C, sp, sM, lane);
         }
     }
 }
@@ -383,7 +394,7 @@ __global__ void __launch_bounds__(NG * VD * 2, 1) gdn_out_hier_kernel(GdnArgs a)
     using R = Rec<KD, VD>;
     constexpr int NST = 3;
     constexpr int NS = VD / 16;
-    extern __shared__ __align__(128) unsigned char smem[];
+    extern __shared__ __align__(1024) unsigned char smem[];
     const int gb = blockIdx.x, h = blockIdx.y, H = a.H;
     if (gb >= a.block_off[a.nseq]) return;
     const int seq = find_seq(a.block_off, a.nseq, gb);
@@ -399,11 +410,11 @@ __global__ void __launch_bounds__(NG * VD * 2, 1) gdn_out_hier_kernel(GdnArgs a)
     const int grp = warp / NS, slab = warp - grp * NS;
     const int row0 = slab * 16;
     const int rec_copy = R::bytes(a.LC);
-    const int stage_bytes = (rec_copy + 127) / 128 * 128;
+    const int stage_bytes = (rec_copy + 1023) / 1024 * 1024;
 
     Pipe<NST> pipe;
     pipe.bar = reinterpret_cast<uint64_t*>(smem);
-    pipe.stage = smem + 128;
+    pipe.stage = smem + 1024;
     pipe.stage_bytes = stage_bytes;
     pipe.src = a.rec + ((size_t)c0 * H + h) * a.rec_bytes;
     pipe.src_stride = (size_t)H * a.rec_bytes;
@@ -411,7 +422,7 @@ __global__ void __launch_bounds__(NG * VD * 2, 1) gdn_out_hier_kernel(GdnArgs a)
     pipe.nsteps = nsteps;
     pipe.dead = false;
     pipe.status = a.status;
-    float* red = reinterpret_cast<float*>(smem + 128 + (size_t)NST * stage_bytes);   // [NG-1][NS][32 regs][32 lanes]
+    float* red = reinterpret_cast<float*>(smem + 1024 + (size_t)NST * stage_bytes);   // [NG-1][NS][32 regs][32 lanes]
     pipe.start();
 
     float C[NLW][KD / 8][4];
@@ -486,11 +497,11 @@ __global__ void __launch_bounds__(NG * VD * 2, 1) gdn_out_hier_kernel(GdnArgs a)
                 } else {
                     if (add_b) load_slab_bf16<KD>(C[x], sBt, row0, lane);
                     else zero_state<KD>(C[x]);
-                    if (do_mma) state_times_mt<KD>(C[x], sp, sM, lane);
+                    if (do_mma) state_times_mt<KD, Tile<KD>>(C[x], sp, sM, lane);
                 }
             } else if (do_mma) {
                 zero_state<KD>(C[x]);
-                state_times_mt<KD>(C[x], sp, sM, lane);
+                state_times_mt<KD, Tile<KD>>(C[x], sp, sM, lane);
             }
         }
 
@@ -549,7 +560,7 @@ static int set_smem(KernelT kern, int bytes) {
 template <int KD, int VD>
 static int launch_compose(const GdnArgs& a, cudaStream_t st) {
     using R = Rec<KD, VD>;
-    const int smem = 128 + 3 * R::MB_BYTES;
+    const int smem = 1024 + 3 * R::PRE_BYTES;
     LAMPA_TRY(set_smem(gdn_compose_kernel<KD, VD>, smem));
     ProfScope prof("gdn_compose", st);
     gdn_compose_kernel<KD, VD><<<dim3(a.nb_max, a.H), (KD + VD) * 2, smem, st>>>(a);
@@ -562,14 +573,14 @@ int launch_scan_plain(const GdnArgs& a, cudaStream_t st) {
     using R = Rec<KD, VD>;
     LAMPA_TRY((launch_compose<KD, VD>(a, st)));
     {
-        const int smem = 128 + 3 * R::BLK_BYTES;
+        const int smem = 1024 + 3 * R::BLK_BYTES;
         LAMPA_TRY(set_smem(gdn_level_kernel<KD, VD, false>, smem));
         ProfScope prof("gdn_level_plain", st);
         gdn_level_kernel<KD, VD, false><<<dim3(a.nseq, a.H, 1), VD * 2, smem, st>>>(a);
         LAMPA_LAUNCHED();
     }
     {
-        const int smem = 128 + 3 * R::LAM_OFF;
+        const int smem = 1024 + 3 * R::LAM_OFF;
         LAMPA_TRY(set_smem(gdn_out_plain_kernel<KD, VD>, smem));
         ProfScope prof("gdn_out_plain", st);
         gdn_out_plain_kernel<KD, VD><<<dim3(a.nb_max, a.H), VD * 2, smem, st>>>(a);
@@ -581,8 +592,8 @@ int launch_scan_plain(const GdnArgs& a, cudaStream_t st) {
 template <int KD, int VD, int NG>
 static int launch_out_hier(const GdnArgs& a, cudaStream_t st) {
     using R = Rec<KD, VD>;
-    const int stage = (R::bytes(a.LC) + 127) / 128 * 128;
-    const int smem = 128 + 3 * stage + (NG - 1) * (VD / 16) * 4096;
+    const int stage = (R::bytes(a.LC) + 1023) / 1024 * 1024;
+    const int smem = 1024 + 3 * stage + (NG - 1) * (VD / 16) * 4096;
     if (smem > 227 * 1024) return LAMPA_ERR_UNSUPPORTED;
     LAMPA_TRY(set_smem(gdn_out_hier_kernel<KD, VD, NG>, smem));
     ProfScope prof("gdn_out_hier", st);
@@ -598,7 +609,7 @@ int launch_scan_hier(const GdnArgs& a, cudaStream_t st) {
     if (ng > MAX_GROUPS) return LAMPA_ERR_UNSUPPORTED;
     if (a.nhigh_max > 0) {
         LAMPA_TRY((launch_compose<KD, VD>(a, st)));
-        const int smem = 128 + 3 * R::BLK_BYTES;
+        const int smem = 1024 + 3 * R::BLK_BYTES;
         LAMPA_TRY(set_smem(gdn_level_kernel<KD, VD, true>, smem));
         ProfScope prof("gdn_level_hier", st);
         gdn_level_kernel<KD, VD, true><<<dim3(a.nseq, a.H, a.nhigh_max), VD * 2, smem, st>>>(a);

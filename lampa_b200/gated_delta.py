@@ -83,7 +83,9 @@ def _desc(q, v, g, lam, cu_seqlens, use_l2norm, scale) -> L.GdnDesc:
 def _workspace(desc: L.GdnDesc, dev: torch.device) -> torch.Tensor:
     n = ctypes.c_size_t(0)
     L.check(L.lib().lampa_gdn_workspace_bytes(ctypes.byref(desc), ctypes.byref(n)), "lampa_gdn_workspace_bytes")
-    return torch.empty(max(n.value, 256), dtype=torch.uint8, device=dev)
+    buf = torch.empty(max(n.value, 256) + 1024, dtype=torch.uint8, device=dev)
+    skip = (-buf.data_ptr()) % 1024          # the library wants a 1024-byte aligned workspace
+    return buf[skip: skip + max(n.value, 256)]
 
 
 def _prep_inputs(q, k, v, g, beta, lam, cu_seqlens):
