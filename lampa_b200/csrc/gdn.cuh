@@ -74,6 +74,7 @@ struct GdnArgs {
     char* blk;                            // per (block, head) composites
     float* entry;                         // entry states: plain [nb][H][V][K]; hier [nb][nhigh][H][V][K]
     int32_t* status;
+    int use_umma;                         // hierarchical output pass on tcgen05 (K = V = 64)
 };
 
 struct PlanArgs {
@@ -103,6 +104,15 @@ __device__ __forceinline__ bool locate_chunk(const GdnArgs& a, int c, ChunkLoc& 
     loc.len = (int)min((int64_t)CHUNK, a.tok_off[loc.seq + 1] - loc.t0);
     return true;
 }
+
+// Two output values (adjacent state columns) of one token, converted to the output type.
+__device__ __forceinline__ void store_out2(void* o, int dt, size_t idx, float x, float y) {
+    if (dt == LAMPA_BF16) *reinterpret_cast<uint32_t*>((__nv_bfloat16*)o + idx) = pack_bf16x2(x, y);
+    else if (dt == LAMPA_F16) *reinterpret_cast<__half2*>((__half*)o + idx) = __floats2half2_rn(x, y);
+    else *reinterpret_cast<float2*>((float*)o + idx) = make_float2(x, y);
+}
+
+int launch_out_hier_umma(const GdnArgs& a, cudaStream_t st);
 
 __host__ __device__ inline int ceil_log2_int(int x) {   // smallest e with 2^e >= x (x >= 1)
     int e = 0;

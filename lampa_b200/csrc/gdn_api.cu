@@ -1,5 +1,6 @@
 // C ABI of the gated-delta forward: argument checks, workspace carve-up, kernel dispatch.
 #include "gdn.cuh"
+#include <cstdlib>
 
 using namespace lampa;
 
@@ -104,6 +105,7 @@ int run(const lampa_gdn_desc* d, bool hier, const void* q, const void* k, const 
     a.blk = base + l.off_blk;
     a.entry = (float*)(base + l.off_entry);
     a.status = status;
+    { const char* e = getenv("LAMPA_B200_NO_UMMA"); a.use_umma = (e && e[0] == '1') ? 0 : 1; }
 
 #define LAMPA_DISPATCH(KD, VD)                                         \
     do {                                                               \

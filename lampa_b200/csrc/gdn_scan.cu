@@ -110,13 +110,6 @@ __device__ __forceinline__ void read_tile(float (&tmp)[2][4], const uint32_t (&s
     }
 }
 
-// Two output values (adjacent state columns) of one token, converted to the output type.
-__device__ __forceinline__ void store_out2(void* o, int dt, size_t idx, float x, float y) {
-    if (dt == LAMPA_BF16) *reinterpret_cast<uint32_t*>((__nv_bfloat16*)o + idx) = pack_bf16x2(x, y);
-    else if (dt == LAMPA_F16) *reinterpret_cast<__half2*>((__half*)o + idx) = __floats2half2_rn(x, y);
-    else *reinterpret_cast<float2*>((float*)o + idx) = make_float2(x, y);
-}
-
 // ---- record pipeline: thread 0 issues bulk copies NST-1 steps ahead; everyone waits on the
 // stage's mbarrier.  The __syncthreads at the top of a step frees the stage consumed last step.
 template <int NST>
@@ -615,6 +608,7 @@ int launch_scan_hier(const GdnArgs& a, cudaStream_t st) {
         gdn_level_kernel<KD, VD, true><<<dim3(a.nseq, a.H, a.nhigh_max), VD * 2, smem, st>>>(a);
         LAMPA_LAUNCHED();
     }
+    if (KD == 64 && VD == 64 && a.nhigh_max <= 5 && a.use_umma) return launch_out_hier_umma(a, st);
     if (ng == 1) return launch_out_hier<KD, VD, 1>(a, st);
     if (ng == 2) return launch_out_hier<KD, VD, 2>(a, st);
     return launch_out_hier<KD, VD, 3>(a, st);

@@ -1,0 +1,307 @@
+// Hierarchical output pass on the 5th-generation tensor cores (tcgen05.mma, accumulators in TMEM)
+// for K = V = 64.
+//
+// Per (block of 32 chunks, head) one CTA of 4 warps keeps every level state the block touches as
+// rows of bf16 A operands in shared memory: slot s holds S_l^T (64 rows v x 64 columns k), two slots
+// per 128-row operand ("pair").  Slots 0..4 are the chunk levels that live inside the block,
+// the following ones the cross-block levels this block reads (seeded from the level pass).
+// A chunk is one record {M | Q~ | B^T | O_local | lambda}; its first 16 KB, the M and Q~ tiles back to
+// back, are a single 128-row K-major B operand, so ONE accumulating MMA per pair,
+//     D[128 x 128] = [S_a^T ; S_b^T] (128 x 64)  x  [M ; Q~]^T (64 x 128),
+// yields both the advanced states (columns 0..63: S^T M^T) and the levels' contributions to the
+// output (columns 64..127: S^T Q~^T = (Q~ S)^T).  The epilogue, one thread per TMEM lane (= state
+// row), scales the contribution by lambda and accumulates it over the pairs, adds B^T where the
+// level is collecting, clears it at the end of its period, and writes the bf16 row back into the A
+// operand for the next chunk.  Records arrive by bulk async copies two stages deep; MMA completion
+// is tracked by tcgen05.commit on one mbarrier per pair; every wait is bounded.
+#include "gdn.cuh"
+#include "profile.cuh"
+
+namespace lampa {
+
+namespace {
+
+constexpr int UKD = 64, UVD = 64;
+constexpr int UNP = 5;                       // pairs of slots: 5 in-block levels + up to 5 cross-block levels
+constexpr int UTHREADS = 128;
+using UR = Rec<UKD, UVD>;
+
+// shared-memory map (bytes); everything that tcgen05 reads is 1024-byte aligned
+constexpr int SM_BAR = 0;                    // full[2], mma[UNP] mbarriers, TMEM slot
+constexpr int SM_A = 1024;                   // UNP operands of 128 x 64 bf16 (16 KB each)
+constexpr int SM_OT = SM_A + UNP * 16384;    // fp32 [2][64 tokens][64 v]: output transpose / pair-half sum
+constexpr int SM_STAGE = SM_OT + 2 * 64 * 64 * 4;
+
+__device__ __forceinline__ uint64_t umma_desc_k128(uint32_t saddr) {   // K-major, 128B swizzle, 8-row groups 1024 B apart
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr >> 4) & 0x3FFF);
+    d |= (uint64_t)1 << 16;                 // leading byte offset (ignored for swizzled K-major): 16 B
+    d |= (uint64_t)(1024 >> 4) << 32;       // stride byte offset
+    d |= (uint64_t)1 << 46;                 // descriptor version
+    d |= (uint64_t)2 << 61;                 // SWIZZLE_128B
+    return d;
+}
+// instruction descriptor: D fp32, A/B bf16, both K-major, M = 128, N = 128
+constexpr uint32_t UMMA_IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
+
+__device__ __forceinline__ void umma_f16_ss(uint32_t d_tmem, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+                 :: "r"(d_tmem), "l"(da), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" :: "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }
+
+// 64 consecutive fp32 columns of this thread's TMEM lane
+__device__ __forceinline__ void tmem_ld64(float (&x)[64], uint32_t taddr) {
+    uint32_t* r = reinterpret_cast<uint32_t*>(x);
+#define LAMPA_LD16(o)                                                                                                     \
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];\n" \
+                 : "=r"(r[o + 0]), "=r"(r[o + 1]), "=r"(r[o + 2]), "=r"(r[o + 3]), "=r"(r[o + 4]), "=r"(r[o + 5]),          \
+                   "=r"(r[o + 6]), "=r"(r[o + 7]), "=r"(r[o + 8]), "=r"(r[o + 9]), "=r"(r[o + 10]), "=r"(r[o + 11]),       \
+                   "=r"(r[o + 12]), "=r"(r[o + 13]), "=r"(r[o + 14]), "=r"(r[o + 15])                                     \
+                 : "r"(taddr + o));
+    LAMPA_LD16(0) LAMPA_LD16(16) LAMPA_LD16(32) LAMPA_LD16(48)
+#undef LAMPA_LD16
+    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+}
+
+// write 64 floats as one bf16 row (row index R of a 128B-swizzled tile)
+__device__ __forceinline__ void store_row_bf16(unsigned char* tile, int R, const float (&x)[64]) {
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+        uint4 u;
+        u.x = pack_bf16x2(x[8 * c], x[8 * c + 1]);
+        u.y = pack_bf16x2(x[8 * c + 2], x[8 * c + 3]);
+        u.z = pack_bf16x2(x[8 * c + 4], x[8 * c + 5]);
+        u.w = pack_bf16x2(x[8 * c + 6], x[8 * c + 7]);
+        *reinterpret_cast<uint4*>(tile + R * 128 + ((c ^ (R & 7)) << 4)) = u;
+    }
+}
+
+__global__ void __launch_bounds__(UTHREADS, 1) gdn_out_hier_umma_kernel(GdnArgs a) {
+    extern __shared__ __align__(1024) unsigned char smem[];
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + SM_BAR);
+    uint64_t* mbar = full + 2;
+    uint32_t* tslot = reinterpret_cast<uint32_t*>(smem + SM_BAR + 128);
+    float* sOT = reinterpret_cast<float*>(smem + SM_OT);
+
+    const int gb = blockIdx.x, h = blockIdx.y, H = a.H;
+    if (gb >= a.block_off[a.nseq]) return;
+    const int seq = find_seq(a.block_off, a.nseq, gb);
+    const int b = gb - a.block_off[seq];
+    const int nch = a.chunk_off[seq + 1] - a.chunk_off[seq];
+    const int nlev = nch > 1 ? ceil_log2_int(nch) : 0;
+    const int nhigh = max(0, nlev - BLOCK_LOG);
+    const int c0 = a.chunk_off[seq] + b * BLOCK_CHUNKS;
+    const int nsteps = min(BLOCK_CHUNKS, nch - b * BLOCK_CHUNKS);
+    const int64_t tok0 = a.tok_off[seq] + (int64_t)b * BLOCK_CHUNKS * CHUNK, tok_end = a.tok_off[seq + 1];
+    const int tid = threadIdx.x, warp = tid >> 5;
+    const int u = tid >> 6, v = tid & 63;            // which slot of the pair, which state row
+    const int rec_copy = UR::bytes(a.LC);
+    const int stage_bytes = (rec_copy + 1023) / 1024 * 1024;
+    unsigned char* stage0 = smem + SM_STAGE;
+    const char* rec0 = a.rec + ((size_t)c0 * H + h) * a.rec_bytes;
+    const size_t rec_stride = (size_t)H * a.rec_bytes;
+
+    // cross-block levels this block reads, compacted into slots 5, 6, ...
+    int live_lh[UNP];
+    int nlive = 0;
+#pragma unroll
+    for (int j = 0; j < UNP; ++j) live_lh[j] = -1;
+    for (int lh = 0; lh < nhigh; ++lh)
+        if ((b >> lh) & 1) {
+#pragma unroll
+            for (int j = 0; j < UNP; ++j)
+                if (j == nlive) live_lh[j] = lh;
+            ++nlive;
+        }
+    const int nslots = BLOCK_LOG + nlive;
+    const int npairs = (nslots + 1) >> 1;
+
+    if (tid == 0) {
+        mbar_init(full + 0, 1);
+        mbar_init(full + 1, 1);
+#pragma unroll
+        for (int p = 0; p < UNP; ++p) mbar_init(mbar + p, 1);
+        fence_mbar_init();
+    }
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" :: "r"(smem_u32(tslot)), "r"(512) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+    }
+    // initial states: zero for the in-block levels, the block's entry state for the cross-block ones
+#pragma unroll
+    for (int p = 0; p < UNP; ++p) {
+        const int s = 2 * p + u;
+        float x[64];
+#pragma unroll
+        for (int i = 0; i < 64; ++i) x[i] = 0.f;
+        if (s >= BLOCK_LOG && s < nslots) {
+            int lh = 0;
+#pragma unroll
+            for (int j = 0; j < UNP; ++j)
+                if (j == s - BLOCK_LOG) lh = live_lh[j];
+            const float4* e = reinterpret_cast<const float4*>(
+                a.entry + (((size_t)gb * a.nhigh_max + lh) * H + h) * UR::STATE_FLOATS + (size_t)v * UKD);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                const float4 f = e[i];
+                x[4 * i] = f.x; x[4 * i + 1] = f.y; x[4 * i + 2] = f.z; x[4 * i + 3] = f.w;
+            }
+        }
+        if (p < npairs) store_row_bf16(smem + SM_A + p * 16384, tid, x);
+    }
+    fence_async_smem();
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t taddr = *tslot;
+    const uint32_t tlane = taddr + ((uint32_t)(warp * 32) << 16);
+
+    bool dead = false;
+    if (tid == 0) {
+        mbar_expect_tx(full + 0, (uint32_t)rec_copy);
+        bulk_g2s(stage0, rec0, (uint32_t)rec_copy, full + 0);
+    }
+
+    // issue the MMA of pair p for the record in `st` (thread 0 only)
+    auto issue_pair = [&](int p, const unsigned char* st) {
+        const uint32_t a_base = smem_u32(smem + SM_A + p * 16384);
+        const uint32_t b_base = smem_u32(st + UR::M_OFF);
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk)
+            umma_f16_ss(taddr + (uint32_t)((p & 3) * 128), umma_desc_k128(a_base + kk * 32), umma_desc_k128(b_base + kk * 32),
+                        UMMA_IDESC, kk > 0 ? 1u : 0u);
+        umma_commit(mbar + p);
+    };
+
+    for (int i = 0; i < nsteps; ++i) {
+        const int sidx = i & 1;
+        const unsigned char* st = stage0 + (size_t)sidx * stage_bytes;
+        __syncthreads();                       // previous chunk fully consumed: its stage and all D buffers are free
+        if (tid == 0 && i + 1 < nsteps) {
+            mbar_expect_tx(full + (sidx ^ 1), (uint32_t)rec_copy);
+            bulk_g2s(stage0 + (size_t)(sidx ^ 1) * stage_bytes, rec0 + (size_t)(i + 1) * rec_stride, (uint32_t)rec_copy, full + (sidx ^ 1));
+        }
+        mbar_wait(full + sidx, (uint32_t)((i >> 1) & 1), dead, a.status, 200 + i);
+        if (tid == 0) {
+            tc_fence_after();
+            for (int p = 0; p < npairs && p < 4; ++p) issue_pair(p, st);
+        }
+        const float* sLam = reinterpret_cast<const float*>(st + UR::LAM_OFF);
+        const unsigned char* sBt = st + UR::BT_OFF;
+        const float* sOl = reinterpret_cast<const float*>(st + UR::OL_OFF);
+        const int n = b * BLOCK_CHUNKS + i;
+
+        float oacc[64];
+#pragma unroll
+        for (int j = 0; j < 64; ++j) oacc[j] = 0.f;
+
+        for (int p = 0; p < npairs; ++p) {
+            mbar_wait(mbar + p, (uint32_t)(i & 1), dead, a.status, 300 + p);
+            tc_fence_after();
+            const int s = 2 * p + u;
+            bool do_read = false, clear = false, add_b = false, active = s < nslots;
+            int lam_row = 0;
+            if (s < BLOCK_LOG) {
+                const int per = 2 << s, pos = n & (per - 1), bit = (n >> s) & 1;
+                do_read = bit != 0;
+                clear = pos == per - 1;
+                add_b = bit == 0;
+                lam_row = s;
+            } else if (active) {
+                int lh = 0;
+#pragma unroll
+                for (int j = 0; j < UNP; ++j)
+                    if (j == s - BLOCK_LOG) lh = live_lh[j];
+                do_read = true;
+                lam_row = BLOCK_LOG + lh;
+            }
+            if (lam_row >= a.LC) do_read = false;      // only reachable when the level check already failed
+            const uint32_t tcol = tlane + (uint32_t)((p & 3) * 128);
+            if (do_read) {
+                float y[64];
+                tmem_ld64(y, tcol + 64);
+                const float4* lr = reinterpret_cast<const float4*>(sLam + lam_row * CHUNK);
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    const float4 l4 = lr[j];
+                    oacc[4 * j] += l4.x * y[4 * j]; oacc[4 * j + 1] += l4.y * y[4 * j + 1];
+                    oacc[4 * j + 2] += l4.z * y[4 * j + 2]; oacc[4 * j + 3] += l4.w * y[4 * j + 3];
+                }
+            }
+            if (active && i + 1 < nsteps) {
+                float x[64];
+                if (clear) {
+#pragma unroll
+                    for (int j = 0; j < 64; ++j) x[j] = 0.f;
+                } else {
+                    tmem_ld64(x, tcol);
+                    if (add_b) {
+#pragma unroll
+                        for (int c = 0; c < 8; ++c) {
+                            const uint4 q4 = *reinterpret_cast<const uint4*>(sBt + v * 128 + ((c ^ (v & 7)) << 4));
+                            const float2 f0 = unpack_bf16x2(q4.x), f1 = unpack_bf16x2(q4.y), f2 = unpack_bf16x2(q4.z), f3 = unpack_bf16x2(q4.w);
+                            x[8 * c] += f0.x; x[8 * c + 1] += f0.y; x[8 * c + 2] += f1.x; x[8 * c + 3] += f1.y;
+                            x[8 * c + 4] += f2.x; x[8 * c + 5] += f2.y; x[8 * c + 6] += f3.x; x[8 * c + 7] += f3.y;
+                        }
+                    }
+                }
+                store_row_bf16(smem + SM_A + p * 16384, tid, x);
+            }
+            if (p + 4 < npairs) {              // a fifth pair re-uses the first accumulator buffer
+                tc_fence_before();
+                __syncthreads();
+                if (tid == 0) {
+                    tc_fence_after();
+                    issue_pair(p + 4, st);
+                }
+            }
+        }
+
+        // output: sum the two halves of the pairs, add O_local, transpose to token-major
+#pragma unroll
+        for (int j = 0; j < 64; ++j) sOT[(u * 64 + j) * 64 + v] = oacc[j];
+        fence_async_smem();                    // the A rows written above are read by next chunk's MMAs
+        tc_fence_before();
+        __syncthreads();
+        {
+            const int tok = tid >> 1, hf = tid & 1;
+            const int64_t t = tok0 + (int64_t)i * CHUNK + tok;
+            if (t < tok_end) {
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    const int col = hf * 32 + c * 4;
+                    const float4 o0 = *reinterpret_cast<const float4*>(sOT + (0 * 64 + tok) * 64 + col);
+                    const float4 o1 = *reinterpret_cast<const float4*>(sOT + (1 * 64 + tok) * 64 + col);
+                    const float4 ol = *reinterpret_cast<const float4*>(sOl + tok * UR::OP + col);
+                    const size_t idx = ((size_t)t * H + h) * UVD + col;
+                    store_out2(a.o, a.qkv_dt, idx, o0.x + o1.x + ol.x, o0.y + o1.y + ol.y);
+                    store_out2(a.o, a.qkv_dt, idx + 2, o0.z + o1.z + ol.z, o0.w + o1.w + ol.w);
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" :: "r"(taddr), "r"(512) : "memory");
+}
+
+}  // namespace
+
+int launch_out_hier_umma(const GdnArgs& a, cudaStream_t st) {
+    const int stage = (UR::bytes(a.LC) + 1023) / 1024 * 1024;
+    const int smem = SM_STAGE + 2 * stage;
+    if (smem > 227 * 1024 || a.nhigh_max > UNP) return LAMPA_ERR_UNSUPPORTED;
+    if (cudaFuncSetAttribute(gdn_out_hier_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+        return LAMPA_ERR_CUDA;
+    ProfScope prof("gdn_out_hier_umma", st);
+    gdn_out_hier_umma_kernel<<<dim3(a.nb_max, a.H), UTHREADS, smem, st>>>(a);
+    return cudaGetLastError() == cudaSuccess ? LAMPA_OK : LAMPA_ERR_CUDA;
+}
+
+}  // namespace lampa
