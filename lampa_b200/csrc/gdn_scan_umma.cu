@@ -23,14 +23,17 @@ namespace {
 
 constexpr int UKD = 64, UVD = 64;
 constexpr int UNP = 5;                       // pairs of slots: 5 in-block levels + up to 5 cross-block levels
-constexpr int UTHREADS = 128;
+constexpr int UTHREADS = 512;                // 4 warpgroups: two advance the states (32 columns each), two read them
+constexpr int UNST = 3;                      // record stages
 using UR = Rec<UKD, UVD>;
 
 // shared-memory map (bytes); everything that tcgen05 reads is 1024-byte aligned
-constexpr int SM_BAR = 0;                    // full[2], mma[UNP] mbarriers, TMEM slot
+constexpr int SM_BAR = 0;                    // full[UNST], mma[UNP] mbarriers, TMEM slot
 constexpr int SM_A = 1024;                   // UNP operands of 128 x 64 bf16 (16 KB each)
 constexpr int SM_OT = SM_A + UNP * 16384;    // fp32 [2][64 tokens][64 v]: output transpose / pair-half sum
 constexpr int SM_STAGE = SM_OT + 2 * 64 * 64 * 4;
+constexpr int STAGE_TILES = UR::PRE_BYTES;   // M | Q~ | B^T, then the lambda rows
+__host__ __device__ constexpr int ustage_bytes(int LC) { return (STAGE_TILES + LC * CHUNK * 4 + 1023) / 1024 * 1024; }
 
 __device__ __forceinline__ uint64_t umma_desc_k128(uint32_t saddr) {   // K-major, 128B swizzle, 8-row groups 1024 B apart
     uint64_t d = 0;
@@ -55,8 +58,8 @@ __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence:
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }
 
-// 64 consecutive fp32 columns of this thread's TMEM lane
-__device__ __forceinline__ void tmem_ld64(float (&x)[64], uint32_t taddr) {
+// 32 consecutive fp32 columns of this thread's TMEM lane
+__device__ __forceinline__ void tmem_ld32(float (&x)[32], uint32_t taddr) {
     uint32_t* r = reinterpret_cast<uint32_t*>(x);
 #define LAMPA_LD16(o)                                                                                                     \
     asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];\n" \
@@ -64,28 +67,28 @@ __device__ __forceinline__ void tmem_ld64(float (&x)[64], uint32_t taddr) {
                    "=r"(r[o + 6]), "=r"(r[o + 7]), "=r"(r[o + 8]), "=r"(r[o + 9]), "=r"(r[o + 10]), "=r"(r[o + 11]),       \
                    "=r"(r[o + 12]), "=r"(r[o + 13]), "=r"(r[o + 14]), "=r"(r[o + 15])                                     \
                  : "r"(taddr + o));
-    LAMPA_LD16(0) LAMPA_LD16(16) LAMPA_LD16(32) LAMPA_LD16(48)
+    LAMPA_LD16(0) LAMPA_LD16(16)
 #undef LAMPA_LD16
     asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
 }
 
-// write 64 floats as one bf16 row (row index R of a 128B-swizzled tile)
-__device__ __forceinline__ void store_row_bf16(unsigned char* tile, int R, const float (&x)[64]) {
+// write 32 floats as half a bf16 row (row R of a 128B-swizzled tile, 16-byte chunks 4*half .. 4*half+3)
+__device__ __forceinline__ void store_half_row_sw(unsigned char* tile, int R, int half, const float (&x)[32]) {
 #pragma unroll
-    for (int c = 0; c < 8; ++c) {
+    for (int c = 0; c < 4; ++c) {
         uint4 u;
         u.x = pack_bf16x2(x[8 * c], x[8 * c + 1]);
         u.y = pack_bf16x2(x[8 * c + 2], x[8 * c + 3]);
         u.z = pack_bf16x2(x[8 * c + 4], x[8 * c + 5]);
         u.w = pack_bf16x2(x[8 * c + 6], x[8 * c + 7]);
-        *reinterpret_cast<uint4*>(tile + R * 128 + ((c ^ (R & 7)) << 4)) = u;
+        *reinterpret_cast<uint4*>(tile + R * 128 + (((4 * half + c) ^ (R & 7)) << 4)) = u;
     }
 }
 
 __global__ void __launch_bounds__(UTHREADS, 1) gdn_out_hier_umma_kernel(GdnArgs a) {
     extern __shared__ __align__(1024) unsigned char smem[];
     uint64_t* full = reinterpret_cast<uint64_t*>(smem + SM_BAR);
-    uint64_t* mbar = full + 2;
+    uint64_t* mbar = full + UNST;
     uint32_t* tslot = reinterpret_cast<uint32_t*>(smem + SM_BAR + 128);
     float* sOT = reinterpret_cast<float*>(smem + SM_OT);
 
@@ -99,32 +102,28 @@ __global__ void __launch_bounds__(UTHREADS, 1) gdn_out_hier_umma_kernel(GdnArgs 
     const int c0 = a.chunk_off[seq] + b * BLOCK_CHUNKS;
     const int nsteps = min(BLOCK_CHUNKS, nch - b * BLOCK_CHUNKS);
     const int64_t tok0 = a.tok_off[seq] + (int64_t)b * BLOCK_CHUNKS * CHUNK, tok_end = a.tok_off[seq + 1];
-    const int tid = threadIdx.x, warp = tid >> 5;
-    const int u = tid >> 6, v = tid & 63;            // which slot of the pair, which state row
-    const int rec_copy = UR::bytes(a.LC);
-    const int stage_bytes = (rec_copy + 1023) / 1024 * 1024;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int wg = warp >> 2;                          // 0,1: advance columns 32*wg..; 2,3: read tokens 32*(wg-2)..
+    const int row = (warp & 3) * 32 + lane;            // TMEM lane = row of the pair's A operand
+    const int u = row >> 6, v = row & 63;              // which slot of the pair, which state row
+    const int half = wg & 1;
+    const int lam_bytes = a.LC * CHUNK * 4;
+    const int stage_bytes = ustage_bytes(a.LC);
     unsigned char* stage0 = smem + SM_STAGE;
     const char* rec0 = a.rec + ((size_t)c0 * H + h) * a.rec_bytes;
     const size_t rec_stride = (size_t)H * a.rec_bytes;
 
     // cross-block levels this block reads, compacted into slots 5, 6, ...
-    int live_lh[UNP];
     int nlive = 0;
-#pragma unroll
-    for (int j = 0; j < UNP; ++j) live_lh[j] = -1;
+    uint32_t live_pack = 0;                            // 4 bits per compact slot: the level index
     for (int lh = 0; lh < nhigh; ++lh)
-        if ((b >> lh) & 1) {
-#pragma unroll
-            for (int j = 0; j < UNP; ++j)
-                if (j == nlive) live_lh[j] = lh;
-            ++nlive;
-        }
+        if ((b >> lh) & 1) { live_pack |= (uint32_t)lh << (4 * nlive); ++nlive; }
     const int nslots = BLOCK_LOG + nlive;
     const int npairs = (nslots + 1) >> 1;
 
     if (tid == 0) {
-        mbar_init(full + 0, 1);
-        mbar_init(full + 1, 1);
+#pragma unroll
+        for (int s = 0; s < UNST; ++s) mbar_init(full + s, 1);
 #pragma unroll
         for (int p = 0; p < UNP; ++p) mbar_init(mbar + p, 1);
         fence_mbar_init();
@@ -134,39 +133,43 @@ __global__ void __launch_bounds__(UTHREADS, 1) gdn_out_hier_umma_kernel(GdnArgs 
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
     }
     // initial states: zero for the in-block levels, the block's entry state for the cross-block ones
+    if (wg < 2) {
+        for (int p = 0; p < npairs; ++p) {
+            const int s = 2 * p + u;
+            float x[32];
 #pragma unroll
-    for (int p = 0; p < UNP; ++p) {
-        const int s = 2 * p + u;
-        float x[64];
+            for (int i = 0; i < 32; ++i) x[i] = 0.f;
+            if (s >= BLOCK_LOG && s < nslots) {
+                const int lh = (live_pack >> (4 * (s - BLOCK_LOG))) & 15;
+                const float4* e = reinterpret_cast<const float4*>(
+                    a.entry + (((size_t)gb * a.nhigh_max + lh) * H + h) * UR::STATE_FLOATS + (size_t)v * UKD + 32 * half);
 #pragma unroll
-        for (int i = 0; i < 64; ++i) x[i] = 0.f;
-        if (s >= BLOCK_LOG && s < nslots) {
-            int lh = 0;
-#pragma unroll
-            for (int j = 0; j < UNP; ++j)
-                if (j == s - BLOCK_LOG) lh = live_lh[j];
-            const float4* e = reinterpret_cast<const float4*>(
-                a.entry + (((size_t)gb * a.nhigh_max + lh) * H + h) * UR::STATE_FLOATS + (size_t)v * UKD);
-#pragma unroll
-            for (int i = 0; i < 16; ++i) {
-                const float4 f = e[i];
-                x[4 * i] = f.x; x[4 * i + 1] = f.y; x[4 * i + 2] = f.z; x[4 * i + 3] = f.w;
+                for (int i = 0; i < 8; ++i) {
+                    const float4 f = e[i];
+                    x[4 * i] = f.x; x[4 * i + 1] = f.y; x[4 * i + 2] = f.z; x[4 * i + 3] = f.w;
+                }
             }
+            store_half_row_sw(smem + SM_A + p * 16384, row, half, x);
         }
-        if (p < npairs) store_row_bf16(smem + SM_A + p * 16384, tid, x);
     }
     fence_async_smem();
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t taddr = *tslot;
-    const uint32_t tlane = taddr + ((uint32_t)(warp * 32) << 16);
+    const uint32_t tlane = taddr + ((uint32_t)((warp & 3) * 32) << 16);
 
     bool dead = false;
-    if (tid == 0) {
-        mbar_expect_tx(full + 0, (uint32_t)rec_copy);
-        bulk_g2s(stage0, rec0, (uint32_t)rec_copy, full + 0);
-    }
+    auto load_record = [&](int step) {      // thread 0: tiles and lambda rows of one chunk into stage step % UNST
+        uint64_t* fb = full + (step % UNST);
+        unsigned char* dst = stage0 + (size_t)(step % UNST) * stage_bytes;
+        const char* src = rec0 + (size_t)step * rec_stride;
+        mbar_expect_tx(fb, (uint32_t)(STAGE_TILES + lam_bytes));
+        bulk_g2s(dst, src, (uint32_t)STAGE_TILES, fb);
+        bulk_g2s(dst + STAGE_TILES, src + UR::LAM_OFF, (uint32_t)lam_bytes, fb);
+    };
+    if (tid == 0)
+        for (int s = 0; s < UNST - 1 && s < nsteps; ++s) load_record(s);
 
     // issue the MMA of pair p for the record in `st` (thread 0 only)
     auto issue_pair = [&](int p, const unsigned char* st) {
@@ -180,32 +183,36 @@ __global__ void __launch_bounds__(UTHREADS, 1) gdn_out_hier_umma_kernel(GdnArgs 
     };
 
     for (int i = 0; i < nsteps; ++i) {
-        const int sidx = i & 1;
-        const unsigned char* st = stage0 + (size_t)sidx * stage_bytes;
+        const unsigned char* st = stage0 + (size_t)(i % UNST) * stage_bytes;
         __syncthreads();                       // previous chunk fully consumed: its stage and all D buffers are free
-        if (tid == 0 && i + 1 < nsteps) {
-            mbar_expect_tx(full + (sidx ^ 1), (uint32_t)rec_copy);
-            bulk_g2s(stage0 + (size_t)(sidx ^ 1) * stage_bytes, rec0 + (size_t)(i + 1) * rec_stride, (uint32_t)rec_copy, full + (sidx ^ 1));
-        }
-        mbar_wait(full + sidx, (uint32_t)((i >> 1) & 1), dead, a.status, 200 + i);
+        if (tid == 0 && i + UNST - 1 < nsteps) load_record(i + UNST - 1);
+        mbar_wait(full + (i % UNST), (uint32_t)((i / UNST) & 1), dead, a.status, 200 + i);
         if (tid == 0) {
             tc_fence_after();
             for (int p = 0; p < npairs && p < 4; ++p) issue_pair(p, st);
         }
-        const float* sLam = reinterpret_cast<const float*>(st + UR::LAM_OFF);
+        const float* sLam = reinterpret_cast<const float*>(st + STAGE_TILES);
         const unsigned char* sBt = st + UR::BT_OFF;
-        const float* sOl = reinterpret_cast<const float*>(st + UR::OL_OFF);
         const int n = b * BLOCK_CHUNKS + i;
+        const int64_t t_out = tok0 + (int64_t)i * CHUNK + (tid >> 3);
+        // O_local of this thread's 8 outputs, straight from the record in global memory
+        float4 ol0 = make_float4(0.f, 0.f, 0.f, 0.f), ol1 = ol0;
+        {
+            const float* gol = reinterpret_cast<const float*>(rec0 + (size_t)i * rec_stride + UR::OL_OFF) + (tid >> 3) * UR::OP + (tid & 7) * 8;
+            ol0 = __ldg(reinterpret_cast<const float4*>(gol));
+            ol1 = __ldg(reinterpret_cast<const float4*>(gol) + 1);
+        }
 
-        float oacc[64];
+        float oacc[32];
 #pragma unroll
-        for (int j = 0; j < 64; ++j) oacc[j] = 0.f;
+        for (int j = 0; j < 32; ++j) oacc[j] = 0.f;
 
         for (int p = 0; p < npairs; ++p) {
             mbar_wait(mbar + p, (uint32_t)(i & 1), dead, a.status, 300 + p);
             tc_fence_after();
             const int s = 2 * p + u;
-            bool do_read = false, clear = false, add_b = false, active = s < nslots;
+            const bool active = s < nslots;
+            bool do_read = false, clear = false, add_b = false;
             int lam_row = 0;
             if (s < BLOCK_LOG) {
                 const int per = 2 << s, pos = n & (per - 1), bit = (n >> s) & 1;
@@ -214,44 +221,41 @@ __global__ void __launch_bounds__(UTHREADS, 1) gdn_out_hier_umma_kernel(GdnArgs 
                 add_b = bit == 0;
                 lam_row = s;
             } else if (active) {
-                int lh = 0;
-#pragma unroll
-                for (int j = 0; j < UNP; ++j)
-                    if (j == s - BLOCK_LOG) lh = live_lh[j];
                 do_read = true;
-                lam_row = BLOCK_LOG + lh;
+                lam_row = BLOCK_LOG + ((live_pack >> (4 * (s - BLOCK_LOG))) & 15);
             }
             if (lam_row >= a.LC) do_read = false;      // only reachable when the level check already failed
             const uint32_t tcol = tlane + (uint32_t)((p & 3) * 128);
-            if (do_read) {
-                float y[64];
-                tmem_ld64(y, tcol + 64);
-                const float4* lr = reinterpret_cast<const float4*>(sLam + lam_row * CHUNK);
+            if (wg >= 2) {
+                if (do_read) {
+                    float y[32];
+                    tmem_ld32(y, tcol + 64 + 32 * half);
+                    const float4* lr = reinterpret_cast<const float4*>(sLam + lam_row * CHUNK + 32 * half);
 #pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    const float4 l4 = lr[j];
-                    oacc[4 * j] += l4.x * y[4 * j]; oacc[4 * j + 1] += l4.y * y[4 * j + 1];
-                    oacc[4 * j + 2] += l4.z * y[4 * j + 2]; oacc[4 * j + 3] += l4.w * y[4 * j + 3];
+                    for (int j = 0; j < 8; ++j) {
+                        const float4 l4 = lr[j];
+                        oacc[4 * j] += l4.x * y[4 * j]; oacc[4 * j + 1] += l4.y * y[4 * j + 1];
+                        oacc[4 * j + 2] += l4.z * y[4 * j + 2]; oacc[4 * j + 3] += l4.w * y[4 * j + 3];
+                    }
                 }
-            }
-            if (active && i + 1 < nsteps) {
-                float x[64];
+            } else if (active && i + 1 < nsteps) {
+                float x[32];
                 if (clear) {
 #pragma unroll
-                    for (int j = 0; j < 64; ++j) x[j] = 0.f;
+                    for (int j = 0; j < 32; ++j) x[j] = 0.f;
                 } else {
-                    tmem_ld64(x, tcol);
+                    tmem_ld32(x, tcol + 32 * half);
                     if (add_b) {
 #pragma unroll
-                        for (int c = 0; c < 8; ++c) {
-                            const uint4 q4 = *reinterpret_cast<const uint4*>(sBt + v * 128 + ((c ^ (v & 7)) << 4));
+                        for (int c = 0; c < 4; ++c) {
+                            const uint4 q4 = *reinterpret_cast<const uint4*>(sBt + v * 128 + (((4 * half + c) ^ (v & 7)) << 4));
                             const float2 f0 = unpack_bf16x2(q4.x), f1 = unpack_bf16x2(q4.y), f2 = unpack_bf16x2(q4.z), f3 = unpack_bf16x2(q4.w);
                             x[8 * c] += f0.x; x[8 * c + 1] += f0.y; x[8 * c + 2] += f1.x; x[8 * c + 3] += f1.y;
                             x[8 * c + 4] += f2.x; x[8 * c + 5] += f2.y; x[8 * c + 6] += f3.x; x[8 * c + 7] += f3.y;
                         }
                     }
                 }
-                store_row_bf16(smem + SM_A + p * 16384, tid, x);
+                store_half_row_sw(smem + SM_A + p * 16384, row, half, x);
             }
             if (p + 4 < npairs) {              // a fifth pair re-uses the first accumulator buffer
                 tc_fence_before();
@@ -264,26 +268,24 @@ __global__ void __launch_bounds__(UTHREADS, 1) gdn_out_hier_umma_kernel(GdnArgs 
         }
 
         // output: sum the two halves of the pairs, add O_local, transpose to token-major
+        if (wg >= 2) {
 #pragma unroll
-        for (int j = 0; j < 64; ++j) sOT[(u * 64 + j) * 64 + v] = oacc[j];
+            for (int j = 0; j < 32; ++j) sOT[(u * 64 + 32 * half + j) * 64 + v] = oacc[j];
+        }
         fence_async_smem();                    // the A rows written above are read by next chunk's MMAs
         tc_fence_before();
         __syncthreads();
-        {
-            const int tok = tid >> 1, hf = tid & 1;
-            const int64_t t = tok0 + (int64_t)i * CHUNK + tok;
-            if (t < tok_end) {
-#pragma unroll
-                for (int c = 0; c < 8; ++c) {
-                    const int col = hf * 32 + c * 4;
-                    const float4 o0 = *reinterpret_cast<const float4*>(sOT + (0 * 64 + tok) * 64 + col);
-                    const float4 o1 = *reinterpret_cast<const float4*>(sOT + (1 * 64 + tok) * 64 + col);
-                    const float4 ol = *reinterpret_cast<const float4*>(sOl + tok * UR::OP + col);
-                    const size_t idx = ((size_t)t * H + h) * UVD + col;
-                    store_out2(a.o, a.qkv_dt, idx, o0.x + o1.x + ol.x, o0.y + o1.y + ol.y);
-                    store_out2(a.o, a.qkv_dt, idx + 2, o0.z + o1.z + ol.z, o0.w + o1.w + ol.w);
-                }
-            }
+        if (t_out < tok_end) {
+            const int tok = tid >> 3, col = (tid & 7) * 8;
+            const float4 p0 = *reinterpret_cast<const float4*>(sOT + (0 * 64 + tok) * 64 + col);
+            const float4 p1 = *reinterpret_cast<const float4*>(sOT + (0 * 64 + tok) * 64 + col + 4);
+            const float4 q0 = *reinterpret_cast<const float4*>(sOT + (1 * 64 + tok) * 64 + col);
+            const float4 q1 = *reinterpret_cast<const float4*>(sOT + (1 * 64 + tok) * 64 + col + 4);
+            const size_t idx = ((size_t)t_out * H + h) * UVD + col;
+            store_out2(a.o, a.qkv_dt, idx, p0.x + q0.x + ol0.x, p0.y + q0.y + ol0.y);
+            store_out2(a.o, a.qkv_dt, idx + 2, p0.z + q0.z + ol0.z, p0.w + q0.w + ol0.w);
+            store_out2(a.o, a.qkv_dt, idx + 4, p1.x + q1.x + ol1.x, p1.y + q1.y + ol1.y);
+            store_out2(a.o, a.qkv_dt, idx + 6, p1.z + q1.z + ol1.z, p1.w + q1.w + ol1.w);
         }
     }
     tc_fence_before();
@@ -294,8 +296,7 @@ __global__ void __launch_bounds__(UTHREADS, 1) gdn_out_hier_umma_kernel(GdnArgs 
 }  // namespace
 
 int launch_out_hier_umma(const GdnArgs& a, cudaStream_t st) {
-    const int stage = (UR::bytes(a.LC) + 1023) / 1024 * 1024;
-    const int smem = SM_STAGE + 2 * stage;
+    const int smem = SM_STAGE + UNST * ustage_bytes(a.LC);
     if (smem > 227 * 1024 || a.nhigh_max > UNP) return LAMPA_ERR_UNSUPPORTED;
     if (cudaFuncSetAttribute(gdn_out_hier_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
         return LAMPA_ERR_CUDA;
