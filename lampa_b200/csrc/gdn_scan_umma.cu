@@ -12,8 +12,12 @@
 // output (columns 64..127: S^T Q~^T = (Q~ S)^T).  The epilogue, one thread per TMEM lane (= state
 // row), scales the contribution by lambda and accumulates it over the pairs, adds B^T where the
 // level is collecting, clears it at the end of its period, and writes the bf16 row back into the A
-// operand for the next chunk.  Records arrive by bulk async copies two stages deep; MMA completion
-// is tracked by tcgen05.commit on one mbarrier per pair; every wait is bounded.
+// operand for the next chunk.  Warp-specialised: 16 epilogue warps (two warpgroups advance the states,
+// 32 columns each; two read them and also transpose and store the output) and one control warp whose
+// first lane streams the records in (bulk async copies, three stages) and issues the MMAs.  A pair's
+// MMA for the next chunk is issued as soon as that pair's epilogue has handed its operand back
+// (mbarriers only, no block-wide barrier on the state path), so the tensor core runs ahead of the
+// epilogues.  MMA completion is tracked by tcgen05.commit on one mbarrier per pair; every wait is bounded.
 #include "gdn.cuh"
 #include "profile.cuh"
 
@@ -23,7 +27,8 @@ namespace {
 
 constexpr int UKD = 64, UVD = 64;
 constexpr int UNP = 5;                       // pairs of slots: 5 in-block levels + up to 5 cross-block levels
-constexpr int UTHREADS = 512;                // 4 warpgroups: two advance the states (32 columns each), two read them
+constexpr int UEPI_WARPS = 16;               // 4 warpgroups: two advance the states (32 columns each), two read them
+constexpr int UTHREADS = (UEPI_WARPS + 1) * 32;   // plus one control warp
 constexpr int UNST = 3;                      // record stages
 using UR = Rec<UKD, UVD>;
 
@@ -85,11 +90,17 @@ __device__ __forceinline__ void store_half_row_sw(unsigned char* tile, int R, in
     }
 }
 
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" :: "r"(smem_u32(bar)) : "memory");
+}
+
 __global__ void __launch_bounds__(UTHREADS, 1) gdn_out_hier_umma_kernel(GdnArgs a) {
     extern __shared__ __align__(1024) unsigned char smem[];
-    uint64_t* full = reinterpret_cast<uint64_t*>(smem + SM_BAR);
-    uint64_t* mbar = full + UNST;
-    uint32_t* tslot = reinterpret_cast<uint32_t*>(smem + SM_BAR + 128);
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + SM_BAR);      // record landed            (tx count)
+    uint64_t* sfree = full + UNST;                                      // stage consumed           (16 warps)
+    uint64_t* mdone = sfree + UNST;                                     // pair's MMA complete      (commit)
+    uint64_t* aready = mdone + UNP;                                     // pair's operand rewritten (16 warps)
+    uint32_t* tslot = reinterpret_cast<uint32_t*>(smem + SM_BAR + 256);
     float* sOT = reinterpret_cast<float*>(smem + SM_OT);
 
     const int gb = blockIdx.x, h = blockIdx.y, H = a.H;
@@ -103,7 +114,7 @@ __global__ void __launch_bounds__(UTHREADS, 1) gdn_out_hier_umma_kernel(GdnArgs 
     const int nsteps = min(BLOCK_CHUNKS, nch - b * BLOCK_CHUNKS);
     const int64_t tok0 = a.tok_off[seq] + (int64_t)b * BLOCK_CHUNKS * CHUNK, tok_end = a.tok_off[seq + 1];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int wg = warp >> 2;                          // 0,1: advance columns 32*wg..; 2,3: read tokens 32*(wg-2)..
+    const int wg = warp >> 2;                          // 0,1: advance columns 32*wg..; 2,3: read tokens 32*(wg-2)..; 4: control
     const int row = (warp & 3) * 32 + lane;            // TMEM lane = row of the pair's A operand
     const int u = row >> 6, v = row & 63;              // which slot of the pair, which state row
     const int half = wg & 1;
@@ -123,9 +134,9 @@ __global__ void __launch_bounds__(UTHREADS, 1) gdn_out_hier_umma_kernel(GdnArgs 
 
     if (tid == 0) {
 #pragma unroll
-        for (int s = 0; s < UNST; ++s) mbar_init(full + s, 1);
+        for (int s = 0; s < UNST; ++s) { mbar_init(full + s, 1); mbar_init(sfree + s, UEPI_WARPS); }
 #pragma unroll
-        for (int p = 0; p < UNP; ++p) mbar_init(mbar + p, 1);
+        for (int p = 0; p < UNP; ++p) { mbar_init(mdone + p, 1); mbar_init(aready + p, UEPI_WARPS); }
         fence_mbar_init();
     }
     if (warp == 0) {
@@ -158,134 +169,158 @@ __global__ void __launch_bounds__(UTHREADS, 1) gdn_out_hier_umma_kernel(GdnArgs 
     tc_fence_after();
     const uint32_t taddr = *tslot;
     const uint32_t tlane = taddr + ((uint32_t)((warp & 3) * 32) << 16);
-
     bool dead = false;
-    auto load_record = [&](int step) {      // thread 0: tiles and lambda rows of one chunk into stage step % UNST
-        uint64_t* fb = full + (step % UNST);
-        unsigned char* dst = stage0 + (size_t)(step % UNST) * stage_bytes;
-        const char* src = rec0 + (size_t)step * rec_stride;
-        mbar_expect_tx(fb, (uint32_t)(STAGE_TILES + lam_bytes));
-        bulk_g2s(dst, src, (uint32_t)STAGE_TILES, fb);
-        bulk_g2s(dst + STAGE_TILES, src + UR::LAM_OFF, (uint32_t)lam_bytes, fb);
-    };
-    if (tid == 0)
-        for (int s = 0; s < UNST - 1 && s < nsteps; ++s) load_record(s);
 
-    // issue the MMA of pair p for the record in `st` (thread 0 only)
-    auto issue_pair = [&](int p, const unsigned char* st) {
-        const uint32_t a_base = smem_u32(smem + SM_A + p * 16384);
-        const uint32_t b_base = smem_u32(st + UR::M_OFF);
+    if (wg == 4) {
+        // ---- control warp: one lane streams records and issues MMAs --------------------------------
+        if (lane == 0) {
+            auto load_record = [&](int step) {
+                uint64_t* fb = full + (step % UNST);
+                unsigned char* dst = stage0 + (size_t)(step % UNST) * stage_bytes;
+                const char* src = rec0 + (size_t)step * rec_stride;
+                mbar_expect_tx(fb, (uint32_t)(STAGE_TILES + lam_bytes));
+                bulk_g2s(dst, src, (uint32_t)STAGE_TILES, fb);
+                bulk_g2s(dst + STAGE_TILES, src + UR::LAM_OFF, (uint32_t)lam_bytes, fb);
+            };
+            for (int s = 0; s < UNST - 1 && s < nsteps; ++s) load_record(s);
+            for (int i = 0; i < nsteps; ++i) {
+                const unsigned char* st = stage0 + (size_t)(i % UNST) * stage_bytes;
+                mbar_wait(full + (i % UNST), (uint32_t)((i / UNST) & 1), dead, a.status, 200 + i);
+                for (int p = 0; p < npairs; ++p) {
+                    // the pair's operand rewritten by the previous chunk, and the accumulator buffer drained
+                    if (i > 0) mbar_wait(aready + p, (uint32_t)((i - 1) & 1), dead, a.status, 400 + p);
+                    if (p >= 4) mbar_wait(aready + (p - 4), (uint32_t)(i & 1), dead, a.status, 410 + p);
+                    else if (i > 0 && p + 4 < npairs) mbar_wait(aready + (p + 4), (uint32_t)((i - 1) & 1), dead, a.status, 420 + p);
+                    tc_fence_after();
+                    const uint32_t a_base = smem_u32(smem + SM_A + p * 16384);
+                    const uint32_t b_base = smem_u32(st + UR::M_OFF);
 #pragma unroll
-        for (int kk = 0; kk < 4; ++kk)
-            umma_f16_ss(taddr + (uint32_t)((p & 3) * 128), umma_desc_k128(a_base + kk * 32), umma_desc_k128(b_base + kk * 32),
-                        UMMA_IDESC, kk > 0 ? 1u : 0u);
-        umma_commit(mbar + p);
-    };
-
-    for (int i = 0; i < nsteps; ++i) {
-        const unsigned char* st = stage0 + (size_t)(i % UNST) * stage_bytes;
-        __syncthreads();                       // previous chunk fully consumed: its stage and all D buffers are free
-        if (tid == 0 && i + UNST - 1 < nsteps) load_record(i + UNST - 1);
-        mbar_wait(full + (i % UNST), (uint32_t)((i / UNST) & 1), dead, a.status, 200 + i);
-        if (tid == 0) {
-            tc_fence_after();
-            for (int p = 0; p < npairs && p < 4; ++p) issue_pair(p, st);
-        }
-        const float* sLam = reinterpret_cast<const float*>(st + STAGE_TILES);
-        const unsigned char* sBt = st + UR::BT_OFF;
-        const int n = b * BLOCK_CHUNKS + i;
-        const int64_t t_out = tok0 + (int64_t)i * CHUNK + (tid >> 3);
-        // O_local of this thread's 8 outputs, straight from the record in global memory
-        float4 ol0 = make_float4(0.f, 0.f, 0.f, 0.f), ol1 = ol0;
-        {
-            const float* gol = reinterpret_cast<const float*>(rec0 + (size_t)i * rec_stride + UR::OL_OFF) + (tid >> 3) * UR::OP + (tid & 7) * 8;
-            ol0 = __ldg(reinterpret_cast<const float4*>(gol));
-            ol1 = __ldg(reinterpret_cast<const float4*>(gol) + 1);
-        }
-
-        float oacc[32];
-#pragma unroll
-        for (int j = 0; j < 32; ++j) oacc[j] = 0.f;
-
-        for (int p = 0; p < npairs; ++p) {
-            mbar_wait(mbar + p, (uint32_t)(i & 1), dead, a.status, 300 + p);
-            tc_fence_after();
-            const int s = 2 * p + u;
-            const bool active = s < nslots;
-            bool do_read = false, clear = false, add_b = false;
-            int lam_row = 0;
-            if (s < BLOCK_LOG) {
-                const int per = 2 << s, pos = n & (per - 1), bit = (n >> s) & 1;
-                do_read = bit != 0;
-                clear = pos == per - 1;
-                add_b = bit == 0;
-                lam_row = s;
-            } else if (active) {
-                do_read = true;
-                lam_row = BLOCK_LOG + ((live_pack >> (4 * (s - BLOCK_LOG))) & 15);
-            }
-            if (lam_row >= a.LC) do_read = false;      // only reachable when the level check already failed
-            const uint32_t tcol = tlane + (uint32_t)((p & 3) * 128);
-            if (wg >= 2) {
-                if (do_read) {
-                    float y[32];
-                    tmem_ld32(y, tcol + 64 + 32 * half);
-                    const float4* lr = reinterpret_cast<const float4*>(sLam + lam_row * CHUNK + 32 * half);
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        const float4 l4 = lr[j];
-                        oacc[4 * j] += l4.x * y[4 * j]; oacc[4 * j + 1] += l4.y * y[4 * j + 1];
-                        oacc[4 * j + 2] += l4.z * y[4 * j + 2]; oacc[4 * j + 3] += l4.w * y[4 * j + 3];
-                    }
+                    for (int kk = 0; kk < 4; ++kk)
+                        umma_f16_ss(taddr + (uint32_t)((p & 3) * 128), umma_desc_k128(a_base + kk * 32),
+                                    umma_desc_k128(b_base + kk * 32), UMMA_IDESC, kk > 0 ? 1u : 0u);
+                    umma_commit(mdone + p);
                 }
-            } else if (active && i + 1 < nsteps) {
-                float x[32];
-                if (clear) {
+                if (i + UNST - 1 < nsteps) {       // refill the stage chunk i-1 used, once everyone is done with it
+                    if (i >= 1) mbar_wait(sfree + ((i - 1) % UNST), (uint32_t)(((i - 1) / UNST) & 1), dead, a.status, 500 + i);
+                    load_record(i + UNST - 1);
+                }
+            }
+        }
+    } else {
+        // ---- epilogue warps ---------------------------------------------------------------------------
+        for (int i = 0; i < nsteps; ++i) {
+            const unsigned char* st = stage0 + (size_t)(i % UNST) * stage_bytes;
+            const float* sLam = reinterpret_cast<const float*>(st + STAGE_TILES);
+            const unsigned char* sBt = st + UR::BT_OFF;
+            const int n = b * BLOCK_CHUNKS + i;
+            const int otid = tid - 256;                       // output thread index of the read warpgroups
+            const int64_t t_out = tok0 + (int64_t)i * CHUNK + (otid >> 2);
+            float4 ol[4];
+            if (wg >= 2) {   // O_local of this thread's 16 outputs, straight from the record in global memory
+                const float4* gol = reinterpret_cast<const float4*>(
+                    reinterpret_cast<const float*>(rec0 + (size_t)i * rec_stride + UR::OL_OFF) + (otid >> 2) * UR::OP + (otid & 3) * 16);
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) x[j] = 0.f;
-                } else {
-                    tmem_ld32(x, tcol + 32 * half);
-                    if (add_b) {
+                for (int q = 0; q < 4; ++q) ol[q] = __ldg(gol + q);
+            }
+            mbar_wait(full + (i % UNST), (uint32_t)((i / UNST) & 1), dead, a.status, 250 + i);
+
+            float oacc[32];
 #pragma unroll
-                        for (int c = 0; c < 4; ++c) {
-                            const uint4 q4 = *reinterpret_cast<const uint4*>(sBt + v * 128 + (((4 * half + c) ^ (v & 7)) << 4));
-                            const float2 f0 = unpack_bf16x2(q4.x), f1 = unpack_bf16x2(q4.y), f2 = unpack_bf16x2(q4.z), f3 = unpack_bf16x2(q4.w);
-                            x[8 * c] += f0.x; x[8 * c + 1] += f0.y; x[8 * c + 2] += f1.x; x[8 * c + 3] += f1.y;
-                            x[8 * c + 4] += f2.x; x[8 * c + 5] += f2.y; x[8 * c + 6] += f3.x; x[8 * c + 7] += f3.y;
+            for (int j = 0; j < 32; ++j) oacc[j] = 0.f;
+
+            for (int p = 0; p < npairs; ++p) {
+                mbar_wait(mdone + p, (uint32_t)(i & 1), dead, a.status, 300 + p);
+                tc_fence_after();
+                const int s = 2 * p + u;
+                const bool active = s < nslots;
+                bool do_read = false, clear = false, add_b = false;
+                int lam_row = 0;
+                if (s < BLOCK_LOG) {
+                    const int per = 2 << s, pos = n & (per - 1), bit = (n >> s) & 1;
+                    do_read = bit != 0;
+                    clear = pos == per - 1;
+                    add_b = bit == 0;
+                    lam_row = s;
+                } else if (active) {
+                    do_read = true;
+                    lam_row = BLOCK_LOG + ((live_pack >> (4 * (s - BLOCK_LOG))) & 15);
+                }
+                if (lam_row >= a.LC) do_read = false;      // only reachable when the level check already failed
+                const uint32_t tcol = tlane + (uint32_t)((p & 3) * 128);
+                if (wg >= 2) {
+                    if (do_read) {
+                        float y[32];
+                        tmem_ld32(y, tcol + 64 + 32 * half);
+                        const float4* lr = reinterpret_cast<const float4*>(sLam + lam_row * CHUNK + 32 * half);
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            const float4 l4 = lr[j];
+                            oacc[4 * j] += l4.x * y[4 * j]; oacc[4 * j + 1] += l4.y * y[4 * j + 1];
+                            oacc[4 * j + 2] += l4.z * y[4 * j + 2]; oacc[4 * j + 3] += l4.w * y[4 * j + 3];
                         }
                     }
-                }
-                store_half_row_sw(smem + SM_A + p * 16384, row, half, x);
-            }
-            if (p + 4 < npairs) {              // a fifth pair re-uses the first accumulator buffer
-                tc_fence_before();
-                __syncthreads();
-                if (tid == 0) {
-                    tc_fence_after();
-                    issue_pair(p + 4, st);
-                }
-            }
-        }
-
-        // output: sum the two halves of the pairs, add O_local, transpose to token-major
-        if (wg >= 2) {
+                } else if (active && i + 1 < nsteps) {
+                    float x[32];
+                    if (clear) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) sOT[(u * 64 + 32 * half + j) * 64 + v] = oacc[j];
-        }
-        fence_async_smem();                    // the A rows written above are read by next chunk's MMAs
-        tc_fence_before();
-        __syncthreads();
-        if (t_out < tok_end) {
-            const int tok = tid >> 3, col = (tid & 7) * 8;
-            const float4 p0 = *reinterpret_cast<const float4*>(sOT + (0 * 64 + tok) * 64 + col);
-            const float4 p1 = *reinterpret_cast<const float4*>(sOT + (0 * 64 + tok) * 64 + col + 4);
-            const float4 q0 = *reinterpret_cast<const float4*>(sOT + (1 * 64 + tok) * 64 + col);
-            const float4 q1 = *reinterpret_cast<const float4*>(sOT + (1 * 64 + tok) * 64 + col + 4);
-            const size_t idx = ((size_t)t_out * H + h) * UVD + col;
-            store_out2(a.o, a.qkv_dt, idx, p0.x + q0.x + ol0.x, p0.y + q0.y + ol0.y);
-            store_out2(a.o, a.qkv_dt, idx + 2, p0.z + q0.z + ol0.z, p0.w + q0.w + ol0.w);
-            store_out2(a.o, a.qkv_dt, idx + 4, p1.x + q1.x + ol1.x, p1.y + q1.y + ol1.y);
-            store_out2(a.o, a.qkv_dt, idx + 6, p1.z + q1.z + ol1.z, p1.w + q1.w + ol1.w);
+                        for (int j = 0; j < 32; ++j) x[j] = 0.f;
+                    } else {
+                        tmem_ld32(x, tcol + 32 * half);
+                        if (add_b) {
+#pragma unroll
+                            for (int c = 0; c < 4; ++c) {
+                                const uint4 q4 = *reinterpret_cast<const uint4*>(sBt + v * 128 + (((4 * half + c) ^ (v & 7)) << 4));
+                                const float2 f0 = unpack_bf16x2(q4.x), f1 = unpack_bf16x2(q4.y), f2 = unpack_bf16x2(q4.z), f3 = unpack_bf16x2(q4.w);
+                                x[8 * c] += f0.x; x[8 * c + 1] += f0.y; x[8 * c + 2] += f1.x; x[8 * c + 3] += f1.y;
+                                x[8 * c + 4] += f2.x; x[8 * c + 5] += f2.y; x[8 * c + 6] += f3.x; x[8 * c + 7] += f3.y;
+                            }
+                        }
+                    }
+                    store_half_row_sw(smem + SM_A + p * 16384, row, half, x);
+                    fence_async_smem();                    // the row is read by the tensor core next
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(aready + p);
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(sfree + (i % UNST));
+
+            if (wg >= 2) {
+                // output (read warpgroups only): sum the two halves of the pairs, add O_local, transpose
+                asm volatile("bar.sync 1, 256;\n" ::: "memory");       // previous chunk's transpose buffer fully read
+#pragma unroll
+                for (int j = 0; j < 32; ++j) sOT[(u * 64 + 32 * half + j) * 64 + v] = oacc[j];
+                asm volatile("bar.sync 1, 256;\n" ::: "memory");
+                if (t_out < tok_end) {
+                    const int tok = otid >> 2, col = (otid & 3) * 16;
+                    const size_t idx = ((size_t)t_out * H + h) * UVD + col;
+                    float r[16];
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        const float4 p0 = *reinterpret_cast<const float4*>(sOT + (0 * 64 + tok) * 64 + col + 4 * q);
+                        const float4 q0 = *reinterpret_cast<const float4*>(sOT + (1 * 64 + tok) * 64 + col + 4 * q);
+                        r[4 * q] = p0.x + q0.x; r[4 * q + 1] = p0.y + q0.y; r[4 * q + 2] = p0.z + q0.z; r[4 * q + 3] = p0.w + q0.w;
+                    }
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) { r[4 * q] += ol[q].x; r[4 * q + 1] += ol[q].y; r[4 * q + 2] += ol[q].z; r[4 * q + 3] += ol[q].w; }
+                    if (a.qkv_dt == LAMPA_F32) {
+                        float4* o4 = reinterpret_cast<float4*>((float*)a.o + idx);
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) o4[q] = make_float4(r[4 * q], r[4 * q + 1], r[4 * q + 2], r[4 * q + 3]);
+                    } else {
+                        uint32_t w[8];
+#pragma unroll
+                        for (int q = 0; q < 8; ++q) {
+                            if (a.qkv_dt == LAMPA_BF16) w[q] = pack_bf16x2(r[2 * q], r[2 * q + 1]);
+                            else { const __half2 hh = __floats2half2_rn(r[2 * q], r[2 * q + 1]); w[q] = *reinterpret_cast<const uint32_t*>(&hh); }
+                        }
+                        uint4* o4 = reinterpret_cast<uint4*>((uint16_t*)a.o + idx);
+                        o4[0] = make_uint4(w[0], w[1], w[2], w[3]);
+                        o4[1] = make_uint4(w[4], w[5], w[6], w[7]);
+                    }
+                }
+            }
         }
     }
     tc_fence_before();
