@@ -29,13 +29,16 @@ constexpr int UKD = 64, UVD = 64;
 constexpr int UNP = 5;                       // pairs of slots: 5 in-block levels + up to 5 cross-block levels
 constexpr int UEPI_WARPS = 16;               // 4 warpgroups: two advance the states (32 columns each), two read them
 constexpr int UTHREADS = (UEPI_WARPS + 1) * 32;   // plus one control warp
-constexpr int UNST = 3;                      // record stages
+constexpr int UNST = 4;                      // record stages
 using UR = Rec<UKD, UVD>;
 
 // shared-memory map (bytes); everything that tcgen05 reads is 1024-byte aligned
 constexpr int SM_BAR = 0;                    // full[UNST], mma[UNP] mbarriers, TMEM slot
-constexpr int SM_A = 1024;                   // UNP operands of 128 x 64 bf16 (16 KB each)
-constexpr int SM_OT = SM_A + UNP * 16384;    // fp32 [2][64 tokens][64 v]: output transpose / pair-half sum
+constexpr int SM_OT = 1024;                  // fp32 [2][64 tokens][64 v]: output transpose / pair-half sum
+// TMEM columns (512 allocated): the states as bf16 A operands, 32 columns per pair, then two
+// 128-column accumulator buffers used by the pairs in turn
+constexpr int TM_A = 0;
+constexpr int TM_D = 192;
 constexpr int SM_STAGE = SM_OT + 2 * 64 * 64 * 4;
 constexpr int STAGE_TILES = UR::PRE_BYTES;   // M | Q~ | B^T, then the lambda rows
 __host__ __device__ constexpr int ustage_bytes(int LC) { return (STAGE_TILES + LC * CHUNK * 4 + 1023) / 1024 * 1024; }
@@ -55,6 +58,11 @@ constexpr uint32_t UMMA_IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((128u >> 3
 __device__ __forceinline__ void umma_f16_ss(uint32_t d_tmem, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
     asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
                  :: "r"(d_tmem), "l"(da), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
+}
+// same with the A operand in TMEM (lane = row, packed bf16 pairs, 8 columns per k-step of 16)
+__device__ __forceinline__ void umma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n"
+                 :: "r"(d_tmem), "r"(a_tmem), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
 }
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" :: "r"(smem_u32(bar)) : "memory");
@@ -77,17 +85,15 @@ __device__ __forceinline__ void tmem_ld32(float (&x)[32], uint32_t taddr) {
     asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
 }
 
-// write 32 floats as half a bf16 row (row R of a 128B-swizzled tile, 16-byte chunks 4*half .. 4*half+3)
-__device__ __forceinline__ void store_half_row_sw(unsigned char* tile, int R, int half, const float (&x)[32]) {
+// write 32 floats as 16 columns of packed bf16 pairs of this thread's TMEM lane (half a row of an A operand)
+__device__ __forceinline__ void tmem_st_bf16x32(uint32_t taddr, const float (&x)[32]) {
+    uint32_t w[16];
 #pragma unroll
-    for (int c = 0; c < 4; ++c) {
-        uint4 u;
-        u.x = pack_bf16x2(x[8 * c], x[8 * c + 1]);
-        u.y = pack_bf16x2(x[8 * c + 2], x[8 * c + 3]);
-        u.z = pack_bf16x2(x[8 * c + 4], x[8 * c + 5]);
-        u.w = pack_bf16x2(x[8 * c + 6], x[8 * c + 7]);
-        *reinterpret_cast<uint4*>(tile + R * 128 + (((4 * half + c) ^ (R & 7)) << 4)) = u;
-    }
+    for (int c = 0; c < 16; ++c) w[c] = pack_bf16x2(x[2 * c], x[2 * c + 1]);
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};\n"
+                 :: "r"(taddr), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7]),
+                    "r"(w[8]), "r"(w[9]), "r"(w[10]), "r"(w[11]), "r"(w[12]), "r"(w[13]), "r"(w[14]), "r"(w[15]) : "memory");
+    asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
 }
 
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
@@ -143,6 +149,12 @@ __global__ void __launch_bounds__(UTHREADS, 1) gdn_out_hier_umma_kernel(GdnArgs 
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" :: "r"(smem_u32(tslot)), "r"(512) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
     }
+    fence_async_smem();
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t taddr = *tslot;
+    const uint32_t tlane = taddr + ((uint32_t)((warp & 3) * 32) << 16);
     // initial states: zero for the in-block levels, the block's entry state for the cross-block ones
     if (wg < 2) {
         for (int p = 0; p < npairs; ++p) {
@@ -160,15 +172,12 @@ __global__ void __launch_bounds__(UTHREADS, 1) gdn_out_hier_umma_kernel(GdnArgs 
                     x[4 * i] = f.x; x[4 * i + 1] = f.y; x[4 * i + 2] = f.z; x[4 * i + 3] = f.w;
                 }
             }
-            store_half_row_sw(smem + SM_A + p * 16384, row, half, x);
+            tmem_st_bf16x32(tlane + TM_A + 32 * p + 16 * half, x);
         }
     }
-    fence_async_smem();
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    const uint32_t taddr = *tslot;
-    const uint32_t tlane = taddr + ((uint32_t)((warp & 3) * 32) << 16);
     bool dead = false;
 
     if (wg == 4) {
@@ -187,16 +196,20 @@ __global__ void __launch_bounds__(UTHREADS, 1) gdn_out_hier_umma_kernel(GdnArgs 
                 const unsigned char* st = stage0 + (size_t)(i % UNST) * stage_bytes;
                 mbar_wait(full + (i % UNST), (uint32_t)((i / UNST) & 1), dead, a.status, 200 + i);
                 for (int p = 0; p < npairs; ++p) {
-                    // the pair's operand rewritten by the previous chunk, and the accumulator buffer drained
+                    // the pair's operand rewritten by the previous chunk ...
                     if (i > 0) mbar_wait(aready + p, (uint32_t)((i - 1) & 1), dead, a.status, 400 + p);
-                    if (p >= 4) mbar_wait(aready + (p - 4), (uint32_t)(i & 1), dead, a.status, 410 + p);
-                    else if (i > 0 && p + 4 < npairs) mbar_wait(aready + (p + 4), (uint32_t)((i - 1) & 1), dead, a.status, 420 + p);
+                    // ... and the accumulator buffer (p & 1) drained by the pair that used it last
+                    if (p >= 2) {
+                        mbar_wait(aready + (p - 2), (uint32_t)(i & 1), dead, a.status, 410 + p);
+                    } else if (i > 0) {
+                        const int q = ((npairs - 1) & 1) == p ? npairs - 1 : npairs - 2;
+                        if (q > p) mbar_wait(aready + q, (uint32_t)((i - 1) & 1), dead, a.status, 420 + p);
+                    }
                     tc_fence_after();
-                    const uint32_t a_base = smem_u32(smem + SM_A + p * 16384);
                     const uint32_t b_base = smem_u32(st + UR::M_OFF);
 #pragma unroll
                     for (int kk = 0; kk < 4; ++kk)
-                        umma_f16_ss(taddr + (uint32_t)((p & 3) * 128), umma_desc_k128(a_base + kk * 32),
+                        umma_f16_ts(taddr + (uint32_t)(TM_D + (p & 1) * 128), taddr + (uint32_t)(TM_A + 32 * p + 8 * kk),
                                     umma_desc_k128(b_base + kk * 32), UMMA_IDESC, kk > 0 ? 1u : 0u);
                     umma_commit(mdone + p);
                 }
@@ -246,7 +259,7 @@ __global__ void __launch_bounds__(UTHREADS, 1) gdn_out_hier_umma_kernel(GdnArgs 
                     lam_row = BLOCK_LOG + ((live_pack >> (4 * (s - BLOCK_LOG))) & 15);
                 }
                 if (lam_row >= a.LC) do_read = false;      // only reachable when the level check already failed
-                const uint32_t tcol = tlane + (uint32_t)((p & 3) * 128);
+                const uint32_t tcol = tlane + (uint32_t)(TM_D + (p & 1) * 128);
                 if (wg >= 2) {
                     if (do_read) {
                         float y[32];
@@ -276,8 +289,7 @@ __global__ void __launch_bounds__(UTHREADS, 1) gdn_out_hier_umma_kernel(GdnArgs 
                             }
                         }
                     }
-                    store_half_row_sw(smem + SM_A + p * 16384, row, half, x);
-                    fence_async_smem();                    // the row is read by the tensor core next
+                    tmem_st_bf16x32(tlane + TM_A + 32 * p + 16 * half, x);
                 }
                 tc_fence_before();
                 __syncwarp();
