@@ -29,7 +29,7 @@ constexpr int UKD = 64, UVD = 64;
 constexpr int UNP = 5;                       // pairs of slots: 5 in-block levels + up to 5 cross-block levels
 constexpr int UEPI_WARPS = 16;               // 4 warpgroups: two advance the states (32 columns each), two read them
 constexpr int UTHREADS = (UEPI_WARPS + 1) * 32;   // plus one control warp
-constexpr int UNST = 4;                      // record stages
+constexpr int UNST = 3;                      // record stages
 using UR = Rec<UKD, UVD>;
 
 // shared-memory map (bytes); everything that tcgen05 reads is 1024-byte aligned
@@ -40,7 +40,7 @@ constexpr int SM_OT = 1024;                  // fp32 [2][64 tokens][64 v]: outpu
 constexpr int TM_A = 0;
 constexpr int TM_D = 192;
 constexpr int SM_STAGE = SM_OT + 2 * 64 * 64 * 4;
-constexpr int STAGE_TILES = UR::PRE_BYTES;   // M | Q~ | B^T, then the lambda rows
+constexpr int STAGE_TILES = UR::LAM_OFF;     // M | Q~ | B^T | O_local, then the lambda rows: the whole record
 __host__ __device__ constexpr int ustage_bytes(int LC) { return (STAGE_TILES + LC * CHUNK * 4 + 1023) / 1024 * 1024; }
 
 __device__ __forceinline__ uint64_t umma_desc_k128(uint32_t saddr) {   // K-major, 128B swizzle, 8-row groups 1024 B apart
@@ -188,8 +188,7 @@ __global__ void __launch_bounds__(UTHREADS, 1) gdn_out_hier_umma_kernel(GdnArgs 
                 unsigned char* dst = stage0 + (size_t)(step % UNST) * stage_bytes;
                 const char* src = rec0 + (size_t)step * rec_stride;
                 mbar_expect_tx(fb, (uint32_t)(STAGE_TILES + lam_bytes));
-                bulk_g2s(dst, src, (uint32_t)STAGE_TILES, fb);
-                bulk_g2s(dst + STAGE_TILES, src + UR::LAM_OFF, (uint32_t)lam_bytes, fb);
+                bulk_g2s(dst, src, (uint32_t)(STAGE_TILES + lam_bytes), fb);
             };
             for (int s = 0; s < UNST - 1 && s < nsteps; ++s) load_record(s);
             for (int i = 0; i < nsteps; ++i) {
@@ -228,13 +227,7 @@ __global__ void __launch_bounds__(UTHREADS, 1) gdn_out_hier_umma_kernel(GdnArgs 
             const int n = b * BLOCK_CHUNKS + i;
             const int otid = tid - 256;                       // output thread index of the read warpgroups
             const int64_t t_out = tok0 + (int64_t)i * CHUNK + (otid >> 2);
-            float4 ol[4];
-            if (wg >= 2) {   // O_local of this thread's 16 outputs, straight from the record in global memory
-                const float4* gol = reinterpret_cast<const float4*>(
-                    reinterpret_cast<const float*>(rec0 + (size_t)i * rec_stride + UR::OL_OFF) + (otid >> 2) * UR::OP + (otid & 3) * 16);
-#pragma unroll
-                for (int q = 0; q < 4; ++q) ol[q] = __ldg(gol + q);
-            }
+            const float* sOl = reinterpret_cast<const float*>(st + UR::OL_OFF);
             mbar_wait(full + (i % UNST), (uint32_t)((i / UNST) & 1), dead, a.status, 250 + i);
 
             float oacc[32];
@@ -295,9 +288,10 @@ __global__ void __launch_bounds__(UTHREADS, 1) gdn_out_hier_umma_kernel(GdnArgs 
                 __syncwarp();
                 if (lane == 0) mbar_arrive(aready + p);
             }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(sfree + (i % UNST));
-
+            if (wg < 2) {
+                __syncwarp();
+                if (lane == 0) mbar_arrive(sfree + (i % UNST));
+            }
             if (wg >= 2) {
                 // output (read warpgroups only): sum the two halves of the pairs, add O_local, transpose
                 asm volatile("bar.sync 1, 256;\n" ::: "memory");       // previous chunk's transpose buffer fully read
@@ -315,7 +309,10 @@ __global__ void __launch_bounds__(UTHREADS, 1) gdn_out_hier_umma_kernel(GdnArgs 
                         r[4 * q] = p0.x + q0.x; r[4 * q + 1] = p0.y + q0.y; r[4 * q + 2] = p0.z + q0.z; r[4 * q + 3] = p0.w + q0.w;
                     }
 #pragma unroll
-                    for (int q = 0; q < 4; ++q) { r[4 * q] += ol[q].x; r[4 * q + 1] += ol[q].y; r[4 * q + 2] += ol[q].z; r[4 * q + 3] += ol[q].w; }
+                    for (int q = 0; q < 4; ++q) {
+                        const float4 o4 = *reinterpret_cast<const float4*>(sOl + tok * UR::OP + col + 4 * q);
+                        r[4 * q] += o4.x; r[4 * q + 1] += o4.y; r[4 * q + 2] += o4.z; r[4 * q + 3] += o4.w;
+                    }
                     if (a.qkv_dt == LAMPA_F32) {
                         float4* o4 = reinterpret_cast<float4*>((float*)a.o + idx);
 #pragma unroll
@@ -332,6 +329,8 @@ __global__ void __launch_bounds__(UTHREADS, 1) gdn_out_hier_umma_kernel(GdnArgs 
                         o4[1] = make_uint4(w[4], w[5], w[6], w[7]);
                     }
                 }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(sfree + (i % UNST));   // O_local of this stage has been read
             }
         }
     }
