@@ -349,6 +349,45 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def run_plain(args):
+    """Configuration 1 on one GPU: timing of the plain chunkwise rule (not the headline metric)."""
+    import lampa_b200
+    from lampa_b200 import _lib as L, synth
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    T = 65536
+    d = {k: v.to(dev) for k, v in synth.gdn_inputs(20251, T, H, K, V, g_shift=2.0, h0=True).items()}
+
+    def step():
+        return lampa_b200.chunk_gated_delta_rule(d["q"], d["k"], d["v"], d["g"], d["beta"], initial_state=d["h0"],
+                                                 output_final_state=True, use_qk_l2norm_in_kernel=True)
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    L.profile_enable(True)
+    for _ in range(5):
+        step()
+    torch.cuda.synchronize()
+    prof = L.profile_read()
+    L.profile_enable(False)
+    L.check_status(dev)
+    print(json.dumps({
+        "metric": "tokens/sec, plain chunkwise gated-delta fwd", "value": T * args.steps / (ms * 1e-3), "unit": "tokens/s",
+        "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps,
+        "higher_is_better": True, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "config 1: chunk_gated_delta_rule T=65536 H=8 K=V=64 bf16, h0 + final state"},
+        "hbm_gbs_algorithmic": T * 4160 / (ms / args.steps * 1e-3) / 1e9,
+        "kernels": {n: {"ms_per_launch": r["ms"] / r["launches"]} for n, r in prof.items()}}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -359,10 +398,15 @@ def main():
     ap.add_argument("--cpu-sample", type=int, default=0, help="hits in the CPU baseline pass (default: all)")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer (end-to-end) leg")
     ap.add_argument("--hits", type=int, default=N_HITS, help="hits of the event (default: the 60k-hit workload)")
+    ap.add_argument("--workload", default="event", choices=["event", "plain"],
+                    help="event: the headline LSH + hierarchical step; plain: configuration 1 "
+                         "(chunk_gated_delta_rule, T=65536, H=8, K=V=64, initial and final state), device-resident only")
     args = ap.parse_args()
     if args.hits != N_HITS:
         set_event_size(args.hits)
-    if args.impl == "reference":
+    if args.workload == "plain":
+        run_plain(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)

@@ -289,3 +289,45 @@ def test_error_conventions(lb):
     with pytest.raises(lb.LampaError):
         lb.chunk_h_gated_delta_rule(d["q"], d["k"], d["v"], d["g"], d["lam"][..., :7].contiguous(), d["beta"],
                                     cu_seqlens=torch.tensor([0, 128]).cuda(), use_qk_l2norm_in_kernel=True)
+
+
+def test_packed_events_like_config4(lb):
+    """Benchmark configuration 4's mixer shape: many events of ragged length packed with cu_seqlens,
+    H = 4, K = V = 32 (a subset of events keeps the CPU check short); each event restarts the hierarchy."""
+    from lampa_b200 import synth
+    H, K, V = 4, 32, 32
+    lens = synth.event_sizes(20254, 64)[:12].tolist()
+    lens = [n // 8 for n in lens]                      # 750 .. 7500 hits per event
+    cu = np.concatenate([[0], np.cumsum(lens)]).astype(np.int64)
+    T = int(cu[-1])
+    Lv = lb.num_levels_required(max(lens))
+    inp = synth.gdn_inputs(20254, T, H, K, V, L=Lv, g_shift=-3.0)
+    d = _cuda(inp)
+    cu_d = torch.from_numpy(cu).cuda()
+    o, _ = lb.chunk_h_gated_delta_rule(d["q"], d["k"], d["v"], d["g"], d["lam"], d["beta"], cu_seqlens=cu_d,
+                                       use_qk_l2norm_in_kernel=True)
+    assert_close_bf16(to_np(o[0]), _hier_ref(inp, cu=cu), "o hier, packed events")
+    op, ht = lb.chunk_gated_delta_rule(d["q"], d["k"], d["v"], d["g"], d["beta"], cu_seqlens=cu_d,
+                                       output_final_state=True, use_qk_l2norm_in_kernel=True)
+    oref, htref = _plain_ref(inp, cu=cu)
+    assert_close_bf16(to_np(op[0]), oref, "o plain, packed events")
+    assert_close_bf16(to_np(ht), htref, "final states, packed events")
+    # K = V = 64 packed events go through the tcgen05 output pass
+    inp = synth.gdn_inputs(20255, T, 2, 64, 64, L=Lv, g_shift=-3.0)
+    d = _cuda(inp)
+    o, _ = lb.chunk_h_gated_delta_rule(d["q"], d["k"], d["v"], d["g"], d["lam"], d["beta"], cu_seqlens=cu_d,
+                                       use_qk_l2norm_in_kernel=True)
+    assert_close_bf16(to_np(o[0]), _hier_ref(inp, cu=cu), "o hier, packed events, K=V=64")
+
+
+def test_tensor_core_paths_agree(lb, monkeypatch):
+    """The tcgen05 output pass and the mma.sync one (selected by LAMPA_B200_NO_UMMA=1) on the same input."""
+    from lampa_b200 import synth
+    T, H = 8192 + 640, 2
+    inp = _cuda(synth.gdn_inputs(31, T, H, 64, 64, L=lb.num_levels_required(T), g_shift=-4.0))
+    args = (inp["q"], inp["k"], inp["v"], inp["g"], inp["lam"], inp["beta"])
+    o_t, _ = lb.chunk_h_gated_delta_rule(*args, use_qk_l2norm_in_kernel=True)
+    monkeypatch.setenv("LAMPA_B200_NO_UMMA", "1")
+    o_m, _ = lb.chunk_h_gated_delta_rule(*args, use_qk_l2norm_in_kernel=True)
+    monkeypatch.delenv("LAMPA_B200_NO_UMMA")
+    assert_close_bf16(to_np(o_t), to_np(o_m), "tcgen05 vs mma.sync output pass")
