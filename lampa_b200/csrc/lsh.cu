@@ -112,7 +112,11 @@ segsort_kernel(const void* __restrict__ keys, int key_type, int64_t n_total,
     __shared__ uint32_t tile_tot[256];
     __shared__ uint32_t wtot[8];
     __shared__ uint32_t red[2];
-    __shared__ uint32_t wcount[SORT_WARPS][256];
+    __shared__ uint32_t wcount[SORT_WARPS][257];   // +1: a column (one digit across the warps) is conflict-free
+    __shared__ uint32_t tstart[256];
+    extern __shared__ uint32_t sort_dyn[];         // [SORT_TILE] keys, [SORT_TILE] indices of the tile, grouped by digit
+    uint32_t* skey = sort_dyn;
+    uint32_t* sidx = sort_dyn + SORT_TILE;
 
     // ---- key range over the whole segment -------------------------------------------------------
     if (tid == 0) { red[0] = 0xFFFFFFFFu; red[1] = 0u; }
@@ -209,11 +213,17 @@ segsort_kernel(const void* __restrict__ keys, int key_type, int64_t n_total,
                     dg[it] = 256u;
                 }
             }
-            for (int z = tid; z < SORT_WARPS * 256; z += SORT_THREADS) (&wcount[0][0])[z] = 0;
+            for (int z = tid; z < SORT_WARPS * 257; z += SORT_THREADS) (&wcount[0][0])[z] = 0;
             __syncthreads();
 #pragma unroll
             for (int it = 0; it < SORT_ITEMS; ++it) {
-                const uint32_t m = __match_any_sync(0xffffffffu, dg[it]);
+                // lanes holding the same digit: eight ballots (one per bit) instead of match.any
+                uint32_t m = 0xffffffffu;
+#pragma unroll
+                for (int bit = 0; bit < 9; ++bit) {
+                    const uint32_t bal = __ballot_sync(0xffffffffu, (dg[it] >> bit) & 1u);
+                    m &= ((dg[it] >> bit) & 1u) ? bal : ~bal;
+                }
                 const bool valid = dg[it] < 256u;
                 const uint32_t basecnt = valid ? wcount[warp][dg[it]] : 0u;
                 rnk[it] = basecnt + __popc(m & ((1u << lane) - 1u));
@@ -222,26 +232,64 @@ segsort_kernel(const void* __restrict__ keys, int key_type, int64_t n_total,
                 __syncwarp();
             }
             __syncthreads();
-            if (tid < 256) {
-                uint32_t run = 0;
-#pragma unroll 4
-                for (int w2 = 0; w2 < SORT_WARPS; ++w2) {
-                    const uint32_t c = wcount[w2][tid];
-                    wcount[w2][tid] = run;
-                    run += c;
+            // exclusive scan over the warps, per digit: warp w takes digits w, w + 32, ...; lane = source warp
+#pragma unroll
+            for (int q = 0; q < 256 / SORT_WARPS; ++q) {
+                const int d = warp + q * SORT_WARPS;
+                const uint32_t c = wcount[lane][d];
+                uint32_t incl2 = c;
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) {
+                    const uint32_t y = __shfl_up_sync(0xffffffffu, incl2, o);
+                    if (lane >= o) incl2 += y;
                 }
-                tile_tot[tid] = run;
+                wcount[lane][d] = incl2 - c;
+                if (lane == 31) tile_tot[d] = incl2;
             }
             __syncthreads();
+            // where each digit starts inside the tile (exclusive scan of the tile's digit counts)
+            uint32_t tt = 0, ti = 0;
+            if (tid < 256) {
+                tt = tile_tot[tid];
+                ti = tt;
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) {
+                    const uint32_t y = __shfl_up_sync(0xffffffffu, ti, o);
+                    if (lane >= o) ti += y;
+                }
+                if (lane == 31) wtot[warp] = ti;
+            }
+            __syncthreads();
+            if (tid < 256) {
+                uint32_t off = 0;
+                for (int w2 = 0; w2 < warp; ++w2) off += wtot[w2];
+                tstart[tid] = off + ti - tt;
+            }
+            __syncthreads();
+            // group the tile by digit in shared memory, so that the global writes below are runs of
+            // consecutive addresses (a direct scatter costs one 32-byte sector per key)
 #pragma unroll
             for (int it = 0; it < SORT_ITEMS; ++it) {
                 if (dg[it] < 256u) {
-                    const int64_t pos = (int64_t)dbase[dg[it]] + wcount[warp][dg[it]] + rnk[it];
+                    const uint32_t lp = tstart[dg[it]] + wcount[warp][dg[it]] + rnk[it];
+                    skey[lp] = u[it];
+                    sidx[lp] = idx[it];
+                }
+            }
+            __syncthreads();
+            const int ntile = (int)min((int64_t)SORT_TILE, hi - t0);
+#pragma unroll
+            for (int it = 0; it < SORT_ITEMS; ++it) {
+                const int lp = it * SORT_THREADS + tid;
+                if (lp < ntile) {
+                    const uint32_t ku = skey[lp], ki = sidx[lp];
+                    const uint32_t d = (ku >> shift) & 255u;
+                    const int64_t pos = (int64_t)dbase[d] + (lp - tstart[d]);
                     if (last) {
-                        perm[s0 + pos] = (int64_t)idx[it];
+                        perm[s0 + pos] = (int64_t)ki;
                     } else {
-                        kdst[s0 + pos] = u[it];
-                        idst[s0 + pos] = idx[it];
+                        kdst[s0 + pos] = ku;
+                        idst[s0 + pos] = ki;
                     }
                 }
             }
@@ -271,8 +319,10 @@ static int launch_segsort(const void* keys, int key_type, int64_t n_total, const
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)nseg * cl, 1, 1);
     cfg.blockDim = dim3(SORT_THREADS, 1, 1);
-    cfg.dynamicSmemBytes = 0;
+    cfg.dynamicSmemBytes = 2 * SORT_TILE * sizeof(uint32_t);
     cfg.stream = st;
+    if (cudaFuncSetAttribute(segsort_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)cfg.dynamicSmemBytes) != cudaSuccess)
+        return LAMPA_ERR_CUDA;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = cl;
