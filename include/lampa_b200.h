@@ -113,6 +113,41 @@ int lampa_hgdn_fwd(const lampa_gdn_desc* d, const void* q, const void* k, const 
                    void* o, void* ws, size_t ws_bytes, int32_t* status, void* stream);
 
 /*
+ * Fenwick state left by a hierarchical forward: call after lampa_hgdn_fwd with the same
+ * descriptor, inputs, cu_seqlens and workspace (the per-chunk records and block entry states it
+ * left there are read again; nothing in the workspace is changed).
+ * Replaces: hattention_prefill's state half — HAttentionPrefillFunction's per-level `_ht` and
+ * postprocess_prefill_hstate_ (models/hattention/kernel.py:377-560, chunkwise_hgdn.py:738-739) —
+ * which the reference reaches through chunk_h_gated_delta_rule(output_final_state=True)
+ * (gated_delta_rule_apis.py:87-101).
+ *   states fp32 [N][H][K][V][L] (N = nseq or B): the HState.states layout of
+ *   models/hattention/recurrent.py:9-40; level 0 holds the last token, level l >= 1 holds
+ *   2^(l-1) tokens when bit l-1 of T-1 is set and zeros otherwise (every element is written);
+ *   counts int32 [N][L]: tokens per level (all rows are equal without cu_seqlens; the reference
+ *   keeps a single [L] row).  A sequence whose length is not a multiple of 64 is treated as
+ *   completed by null tokens (k = v = 0, beta = 0, g = 0).
+ */
+int lampa_hgdn_final_state(const lampa_gdn_desc* d, const void* k, const void* v, const void* g,
+                           const void* beta, const int64_t* cu_seqlens, void* ws, size_t ws_bytes,
+                           float* states, int32_t* counts, int32_t* status, void* stream);
+/*
+ * One decode step of the hierarchical rule on a Fenwick state, in place.
+ * Replaces: hattention_step -> step_state / step_output (models/hattention/kernel.py:570-633,
+ * recurrent.py:134-166, HState.cascade_weak / insert / dot: recurrent.py:42-100), reached through
+ * chunk_h_gated_delta_rule(initial_state=..., output_final_state=True) with T = 1
+ * (gated_delta_rule_apis.py:102-127).
+ *   d->T must be 1; q,k [B,H,K]; v,o [B,H,V]; g,beta [B,H]; lam [B,H,L];
+ *   states fp32 [B][H][K][V][L] and counts int32 [L] (one row for the whole batch) are updated:
+ *   full levels cascade upward (capacity 2^l), every level is multiplied by
+ *   e^g (I - beta k k^T), level 0 becomes beta k v^T, counts[0] += 1;
+ *   o = q^T sum_l lam_l S_l.  As in lampa_hgdn_fwd q and k are l2-normalised when
+ *   d->use_l2norm and the result does not depend on d->scale.  A cascade that would leave the
+ *   last level sets LAMPA_ERR_LEVELS in the status word and changes nothing.
+ */
+int lampa_hgdn_step(const lampa_gdn_desc* d, const void* q, const void* k, const void* v,
+                    const void* g, const void* beta, const void* lam, float* states,
+                    int32_t* counts, void* o, int32_t* status, void* stream);
+/*
  * E2LSH projection and integer bucket ids.
  * Replaces: E2LSH.forward (models/model_utils/hash_utils.py:359-371; copies in
  * models/baselines/hmamba.py:275-285, full_mamba2.py:128-141) — the float projection — and adds

@@ -2,13 +2,14 @@
 chunkwise gated-delta-rule forward, behind the reference's own Python entry points."""
 from ._lib import LampaError, check_status  # noqa: F401
 from .gated_delta import (  # noqa: F401
-    HStruct, HType, chunk_gated_delta_rule, chunk_h_gated_delta_rule, hattention_kernel, num_levels_required)
+    HState, HStruct, HType, chunk_gated_delta_rule, chunk_h_gated_delta_rule, hattention_kernel,
+    hattention_prefill, hattention_step, num_levels_required)
 from .lsh import (  # noqa: F401
     E2LSH, LSHOrdering, batched_index_select, invert_permutation, lsh_bucket_sort, lsh_hash, lsh_mapping,
     permute_rows, segmented_sort, sort_to_buckets, unsort_from_buckets)
 
 __all__ = [
-    "LampaError", "check_status", "HStruct", "HType", "chunk_gated_delta_rule", "chunk_h_gated_delta_rule",
+    "LampaError", "check_status", "HState", "HStruct", "HType", "hattention_prefill", "hattention_step", "chunk_gated_delta_rule", "chunk_h_gated_delta_rule",
     "hattention_kernel", "num_levels_required", "E2LSH", "LSHOrdering", "batched_index_select",
     "invert_permutation", "lsh_bucket_sort", "lsh_hash", "lsh_mapping", "permute_rows", "segmented_sort",
     "sort_to_buckets", "unsort_from_buckets",

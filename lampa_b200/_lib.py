@@ -35,7 +35,7 @@ class GdnDesc(ctypes.Structure):
 
 _lib: Optional[ctypes.CDLL] = None
 EXPORTS = ["lampa_version", "lampa_error_string", "lampa_gdn_workspace_bytes", "lampa_gdn_workspace_layout",
-           "lampa_gdn_fwd", "lampa_hgdn_fwd", "lampa_lsh_hash", "lampa_segsort_workspace_bytes",
+           "lampa_gdn_fwd", "lampa_hgdn_fwd", "lampa_hgdn_final_state", "lampa_hgdn_step", "lampa_lsh_hash", "lampa_segsort_workspace_bytes",
            "lampa_segsort_stable", "lampa_permute_rows", "lampa_invert_perm", "lampa_segsort_stable_static",
            "lampa_profile_enable",
            "lampa_profile_read"]
@@ -56,6 +56,8 @@ def lib() -> ctypes.CDLL:
         L.lampa_gdn_workspace_layout.argtypes = [ctypes.POINTER(GdnDesc), ctypes.POINTER(sz)]
         L.lampa_gdn_fwd.argtypes = [ctypes.POINTER(GdnDesc)] + [vp] * 10 + [sz, vp, vp]
         L.lampa_hgdn_fwd.argtypes = [ctypes.POINTER(GdnDesc)] + [vp] * 9 + [sz, vp, vp]
+        L.lampa_hgdn_final_state.argtypes = [ctypes.POINTER(GdnDesc)] + [vp] * 6 + [sz, vp, vp, vp, vp]
+        L.lampa_hgdn_step.argtypes = [ctypes.POINTER(GdnDesc)] + [vp] * 11
         L.lampa_lsh_hash.argtypes = [vp, i64, i64, vp, vp, ctypes.c_float, i64, i32, i32, i32, vp, vp, vp, vp]
         L.lampa_segsort_workspace_bytes.argtypes = [i64, ctypes.POINTER(sz)]
         L.lampa_segsort_stable.argtypes = [vp, i32, i64, vp, i32, vp, vp, vp, sz, vp, vp]

@@ -113,6 +113,18 @@ __device__ __forceinline__ void store_out2(void* o, int dt, size_t idx, float x,
 }
 
 int launch_out_hier_umma(const GdnArgs& a, cudaStream_t st);
+template <int KD, int VD> int launch_final_high(const GdnArgs& a, float* states, cudaStream_t st);
+template <int KD, int VD> int launch_final_low(const GdnArgs& a, float* states, int32_t* counts, cudaStream_t st);
+
+// One decode step of the hierarchical rule on a Fenwick state (gdn_state.cu).
+struct StepArgs {
+    const void* q; const void* k; const void* v; const void* g; const void* beta; const void* lam;
+    float* states; int32_t* counts; void* o;
+    int qkv_dt, gb_dt, lam_dt;
+    int B, H, L, use_l2norm;
+    int32_t* status;
+};
+template <int KD, int VD> int launch_hgdn_step(const StepArgs& s, cudaStream_t st);
 
 __host__ __device__ inline int ceil_log2_int(int x) {   // smallest e with 2^e >= x (x >= 1)
     int e = 0;

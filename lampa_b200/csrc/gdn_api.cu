@@ -67,6 +67,25 @@ int make_layout(const lampa_gdn_desc* d, bool hier, Layout& l) {
     return LAMPA_OK;
 }
 
+void fill_args(const lampa_gdn_desc* d, bool hier, const Layout& l, char* base, const int64_t* cu,
+               int32_t* status, GdnArgs& a) {
+    a.q = a.k = a.v = a.g = a.beta = a.lam = nullptr; a.h0 = nullptr; a.ht = nullptr; a.o = nullptr;
+    a.qkv_dt = d->qkv_dtype; a.gb_dt = d->gb_dtype; a.lam_dt = d->lam_dtype;
+    a.H = d->H; a.L = hier ? d->L : 0; a.LC = l.LC;
+    a.use_l2norm = d->use_l2norm; a.scale = d->scale;
+    a.fixed_T = cu ? 0 : d->T;
+    a.fixed_cps = cu ? 0 : (d->T + CHUNK - 1) / CHUNK;
+    a.nseq = l.nseq; a.nc_max = l.nc_max; a.nb_max = l.nb_max; a.nhigh_max = l.nhigh_max;
+    a.tok_off = (int64_t*)(base + l.off_tok);
+    a.chunk_off = (int32_t*)(base + l.off_chunk);
+    a.block_off = (int32_t*)(base + l.off_block);
+    a.rec = base + l.off_rec; a.rec_bytes = l.rec_bytes;
+    a.blk = base + l.off_blk;
+    a.entry = (float*)(base + l.off_entry);
+    a.status = status;
+    { const char* e = getenv("LAMPA_B200_NO_UMMA"); a.use_umma = (e && e[0] == '1') ? 0 : 1; }
+}
+
 int run(const lampa_gdn_desc* d, bool hier, const void* q, const void* k, const void* v, const void* g,
         const void* beta, const void* lam, const float* h0, const int64_t* cu, void* o, float* ht,
         void* ws, size_t ws_bytes, int32_t* status, void* stream) {
@@ -83,29 +102,18 @@ int run(const lampa_gdn_desc* d, bool hier, const void* q, const void* k, const 
     cudaStream_t st = (cudaStream_t)stream;
     char* base = (char*)ws;
 
+    GdnArgs a;
+    fill_args(d, hier, l, base, cu, status, a);
+    a.q = q; a.k = k; a.v = v; a.g = g; a.beta = beta; a.lam = lam; a.h0 = h0; a.ht = ht; a.o = o;
+
     PlanArgs p;
     p.cu = cu; p.nseq = l.nseq; p.B = d->B; p.T = d->T; p.L = d->L; p.hier = hier ? 1 : 0;
-    p.tok_off = (int64_t*)(base + l.off_tok);
-    p.chunk_off = (int32_t*)(base + l.off_chunk);
-    p.block_off = (int32_t*)(base + l.off_block);
+    p.tok_off = (int64_t*)a.tok_off;
+    p.chunk_off = (int32_t*)a.chunk_off;
+    p.block_off = (int32_t*)a.block_off;
     p.status = status;
     rc = launch_plan(p, st);
     if (rc != LAMPA_OK) return rc;
-
-    GdnArgs a;
-    a.q = q; a.k = k; a.v = v; a.g = g; a.beta = beta; a.lam = lam; a.h0 = h0; a.ht = ht; a.o = o;
-    a.qkv_dt = d->qkv_dtype; a.gb_dt = d->gb_dtype; a.lam_dt = d->lam_dtype;
-    a.H = d->H; a.L = hier ? d->L : 0; a.LC = l.LC;
-    a.use_l2norm = d->use_l2norm; a.scale = d->scale;
-    a.fixed_T = cu ? 0 : d->T;
-    a.fixed_cps = cu ? 0 : (d->T + CHUNK - 1) / CHUNK;
-    a.nseq = l.nseq; a.nc_max = l.nc_max; a.nb_max = l.nb_max; a.nhigh_max = l.nhigh_max;
-    a.tok_off = p.tok_off; a.chunk_off = p.chunk_off; a.block_off = p.block_off;
-    a.rec = base + l.off_rec; a.rec_bytes = l.rec_bytes;
-    a.blk = base + l.off_blk;
-    a.entry = (float*)(base + l.off_entry);
-    a.status = status;
-    { const char* e = getenv("LAMPA_B200_NO_UMMA"); a.use_umma = (e && e[0] == '1') ? 0 : 1; }
 
 #define LAMPA_DISPATCH(KD, VD)                                         \
     do {                                                               \
@@ -173,4 +181,52 @@ extern "C" int lampa_hgdn_fwd(const lampa_gdn_desc* d, const void* q, const void
                               const void* g, const void* beta, const void* lam, const int64_t* cu_seqlens,
                               void* o, void* ws, size_t ws_bytes, int32_t* status, void* stream) {
     return run(d, true, q, k, v, g, beta, lam, nullptr, cu_seqlens, o, nullptr, ws, ws_bytes, status, stream);
+}
+
+extern "C" int lampa_hgdn_final_state(const lampa_gdn_desc* d, const void* k, const void* v, const void* g,
+                                      const void* beta, const int64_t* cu_seqlens, void* ws, size_t ws_bytes,
+                                      float* states, int32_t* counts, int32_t* status, void* stream) {
+    Layout l;
+    int rc = make_layout(d, true, l);
+    if (rc != LAMPA_OK) return rc;
+    if (d->L < ELL0) return LAMPA_ERR_LEVELS;
+    if ((int64_t)d->B * d->T == 0) return LAMPA_OK;
+    if (!k || !v || !g || !beta || !ws || !states || !counts) return LAMPA_ERR_ARG;
+    if (d->nseq > 0 && !cu_seqlens) return LAMPA_ERR_ARG;
+    if (ws_bytes < l.total || ((uintptr_t)ws & 1023)) return LAMPA_ERR_WORKSPACE;
+    cudaStream_t st = (cudaStream_t)stream;
+    GdnArgs a;
+    fill_args(d, true, l, (char*)ws, cu_seqlens, status, a);
+    a.k = k; a.v = v; a.g = g; a.beta = beta;
+#define LAMPA_DISPATCH(KD, VD)                                           \
+    do {                                                                 \
+        rc = launch_final_low<KD, VD>(a, states, counts, st);            \
+        if (rc != LAMPA_OK) return rc;                                   \
+        return launch_final_high<KD, VD>(a, states, st);                 \
+    } while (0)
+    if (d->K == 64) LAMPA_DISPATCH(64, 64);
+    if (d->K == 32) LAMPA_DISPATCH(32, 32);
+    LAMPA_DISPATCH(16, 32);
+#undef LAMPA_DISPATCH
+}
+
+extern "C" int lampa_hgdn_step(const lampa_gdn_desc* d, const void* q, const void* k, const void* v,
+                               const void* g, const void* beta, const void* lam, float* states,
+                               int32_t* counts, void* o, int32_t* status, void* stream) {
+    if (!d || d->B <= 0 || d->H <= 0 || d->T != 1) return LAMPA_ERR_ARG;
+    if (!dims_supported(d->K, d->V)) return LAMPA_ERR_UNSUPPORTED;
+    if (d->L < 1 || d->L > 40) return LAMPA_ERR_ARG;
+    for (int dt : {d->qkv_dtype, d->gb_dtype, d->lam_dtype})
+        if (dt != LAMPA_BF16 && dt != LAMPA_F16 && dt != LAMPA_F32) return LAMPA_ERR_ARG;
+    if (!q || !k || !v || !g || !beta || !lam || !states || !counts || !o) return LAMPA_ERR_ARG;
+    StepArgs s;
+    s.q = q; s.k = k; s.v = v; s.g = g; s.beta = beta; s.lam = lam;
+    s.states = states; s.counts = counts; s.o = o;
+    s.qkv_dt = d->qkv_dtype; s.gb_dt = d->gb_dtype; s.lam_dt = d->lam_dtype;
+    s.B = d->B; s.H = d->H; s.L = d->L; s.use_l2norm = d->use_l2norm;
+    s.status = status;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (d->K == 64) return launch_hgdn_step<64, 64>(s, st);
+    if (d->K == 32) return launch_hgdn_step<32, 32>(s, st);
+    return launch_hgdn_step<16, 32>(s, st);
 }

@@ -306,6 +306,88 @@ __global__ void __launch_bounds__(VD * 2) gdn_level_kernel(GdnArgs a) {
 }
 
 // -------------------------------------------------------------------------------------------------
+// final state, hierarchical rule, chunk levels.  After a sequence of NT chunks the Fenwick state
+// holds chunk level l (lambda index 7 + l) exactly when bit l of NT - 1 is set: the first half of
+// the level's current period, carried through every chunk up to the last one without the closing
+// reset (the reference's hattention_prefill keeps the same thing, models/hattention/kernel.py:
+// 377-470 and chunkwise_hgdn.py:738-739).  One CTA per (sequence, head, level) re-runs at most one
+// block of chunks over the records the forward left in the workspace: levels inside a block start
+// from zero at the period's first chunk, cross-block levels start from the entry state the level
+// pass stored for the last block.  states is [N][H][K][V][L] fp32; unoccupied levels are zeroed.
+// -------------------------------------------------------------------------------------------------
+template <int KD, int VD>
+__global__ void __launch_bounds__(VD * 2) hgdn_final_high_kernel(GdnArgs a, float* states) {
+    using R = Rec<KD, VD>;
+    constexpr int NST = 3;
+    extern __shared__ __align__(1024) unsigned char smem[];
+    const int seq = blockIdx.x, h = blockIdx.y, lev = blockIdx.z, H = a.H;
+    const int nch = a.chunk_off[seq + 1] - a.chunk_off[seq];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    const int row0 = warp * 16;
+    const int n = nch - 1;
+    const bool live = nch > 0 && lev < 30 && ((n >> lev) & 1);
+
+    float C[KD / 8][4];
+    zero_state<KD>(C);
+    if (live) {
+        int c_first, half_end;
+        if (lev < BLOCK_LOG) {
+            c_first = n & ~((2 << lev) - 1);
+            half_end = c_first + (1 << lev);
+        } else {
+            c_first = (n >> BLOCK_LOG) << BLOCK_LOG;
+            half_end = c_first;
+            const int gb = a.block_off[seq] + (n >> BLOCK_LOG);
+            const float* e = a.entry + (((size_t)gb * a.nhigh_max + (lev - BLOCK_LOG)) * H + h) * R::STATE_FLOATS;
+            load_slab_f32<KD>(C, e, KD, row0, lane);
+        }
+        Pipe<NST> pipe;
+        pipe.bar = reinterpret_cast<uint64_t*>(smem);
+        pipe.stage = smem + 1024;
+        pipe.stage_bytes = R::PRE_BYTES;
+        pipe.src = a.rec + ((size_t)(a.chunk_off[seq] + c_first) * H + h) * a.rec_bytes;
+        pipe.src_stride = (size_t)H * a.rec_bytes;
+        pipe.copy_bytes = R::PRE_BYTES;
+        pipe.nsteps = n - c_first + 1;
+        pipe.dead = false;
+        pipe.status = a.status;
+        pipe.start();
+        for (int i = 0; i < pipe.nsteps; ++i) {
+            const unsigned char* st = pipe.acquire(i);
+            const __nv_bfloat16* sM = reinterpret_cast<const __nv_bfloat16*>(st + R::M_OFF);
+            const __nv_bfloat16* sBt = reinterpret_cast<const __nv_bfloat16*>(st + R::BT_OFF);
+            // the state enters the tensor core as bf16 hi + bf16 lo (two products), so that re-rounding
+            // it at every chunk does not accumulate in the state handed to the caller
+            uint32_t sp[KD / 16][4], sl[KD / 16][4];
+            pack_state<KD>(C, sp);
+#pragma unroll
+            for (int kk = 0; kk < KD / 16; ++kk)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float2 hi = unpack_bf16x2(sp[kk][e]);
+                    const int nt = 2 * kk + (e >> 1), c0 = (e & 1) * 2;
+                    sl[kk][e] = pack_bf16x2(C[nt][c0] - hi.x, C[nt][c0 + 1] - hi.y);
+                }
+            if (c_first + i < half_end) load_slab_bf16<KD>(C, sBt, row0, lane);
+            else zero_state<KD>(C);
+            if (i > 0 || lev >= BLOCK_LOG) {
+                state_times_mt<KD, Tile<KD>>(C, sp, sM, lane);
+                state_times_mt<KD, Tile<KD>>(C, sl, sM, lane);
+            }
+        }
+    }
+    float* dst = states + ((size_t)seq * H + h) * KD * VD * a.L + ELL0 + lev;
+#pragma unroll
+    for (int nt = 0; nt < KD / 8; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int kk = nt * 8 + 2 * t + (e & 1), vv = row0 + g + (e >> 1) * 8;
+            dst[((size_t)kk * VD + vv) * a.L] = C[nt][e];
+        }
+}
+
+// -------------------------------------------------------------------------------------------------
 // output, plain rule:  O_n = O_local + Q~ S_n ;  S_{n+1} = M S_n + B
 // -------------------------------------------------------------------------------------------------
 template <int KD, int VD>
@@ -613,6 +695,22 @@ int launch_scan_hier(const GdnArgs& a, cudaStream_t st) {
     if (ng == 2) return launch_out_hier<KD, VD, 2>(a, st);
     return launch_out_hier<KD, VD, 3>(a, st);
 }
+
+template <int KD, int VD>
+int launch_final_high(const GdnArgs& a, float* states, cudaStream_t st) {
+    using R = Rec<KD, VD>;
+    if (a.L <= ELL0) return LAMPA_OK;
+    const int smem = 1024 + 3 * R::PRE_BYTES;
+    LAMPA_TRY(set_smem(hgdn_final_high_kernel<KD, VD>, smem));
+    ProfScope prof("hgdn_final_high", st);
+    hgdn_final_high_kernel<KD, VD><<<dim3(a.nseq, a.H, a.L - ELL0), VD * 2, smem, st>>>(a, states);
+    LAMPA_LAUNCHED();
+    return LAMPA_OK;
+}
+
+template int launch_final_high<64, 64>(const GdnArgs&, float*, cudaStream_t);
+template int launch_final_high<32, 32>(const GdnArgs&, float*, cudaStream_t);
+template int launch_final_high<16, 32>(const GdnArgs&, float*, cudaStream_t);
 
 template int launch_scan_plain<64, 64>(const GdnArgs&, cudaStream_t);
 template int launch_scan_plain<32, 32>(const GdnArgs&, cudaStream_t);

@@ -4,6 +4,7 @@ Same names, argument meaning and error behaviour as the reference entry points:
   chunk_gated_delta_rule    models/hattention/gated_delta_rule_ori.py:235-357
   chunk_h_gated_delta_rule  models/hattention/gated_delta_rule_apis.py:20-134
   hattention_kernel         models/hattention/kernel.py:338-374
+  hattention_prefill / hattention_step / HState   kernel.py:470-633, recurrent.py:9-131
 Forward only (no autograd graph is recorded).  Everything runs in the CUDA library on
 the current torch stream; there is no PyTorch or CPU fallback.
 """
@@ -152,8 +153,41 @@ def chunk_gated_delta_rule(
     return o, ht
 
 
+class HState:
+    """Fenwick state of the hierarchical rule (models/hattention/recurrent.py:9-131): `states`
+    [B,H,K,V,L] and `counts` [L] int32 (tokens held per level).  Always fp32 on the device; the
+    cascade / insert / dot methods of the reference live in the library's step kernel."""
+
+    def __init__(self, base: int, htype, hstruct, shape, dtype: torch.dtype, device) -> None:
+        if getattr(htype, "name", htype) != "WEAK" or base != 2:
+            raise NotImplementedError
+        if dtype != torch.float32:
+            raise NotImplementedError("states are kept in fp32")
+        self.base = base
+        self.htype = htype
+        self.hstruct = hstruct
+        self.shape = tuple(shape)
+        self.dtype = dtype
+        self.device = torch.device(device)
+        self.max_num_levels = self.shape[-1]
+        self.states = torch.zeros(self.shape, dtype=dtype, device=device)
+        self.counts = torch.zeros(self.max_num_levels, dtype=torch.int32, device=device)
+
+    def reset_states(self) -> None:
+        self.states.zero_()
+
+    def to(self, dtype: Optional[torch.dtype] = None, device=None) -> "HState":
+        new = HState.__new__(HState)
+        new.__dict__.update(self.__dict__)
+        new.dtype = self.dtype if dtype is None else dtype
+        new.device = self.device if device is None else torch.device(device)
+        new.states = self.states.to(dtype=new.dtype, device=new.device)
+        new.counts = self.counts.to(dtype=torch.int32, device=new.device)
+        return new
+
+
 @torch.no_grad()
-def _hgdn(q, k, v, g, beta, lam, cu_seqlens, use_l2norm):
+def _hgdn(q, k, v, g, beta, lam, cu_seqlens, use_l2norm, want_state: bool = False):
     dev, q, k, v, g, beta, lam, cu = _prep_inputs(q, k, v, g, beta, lam, cu_seqlens)
     B, T, H, K = q.shape
     V = v.shape[-1]
@@ -169,9 +203,69 @@ def _hgdn(q, k, v, g, beta, lam, cu_seqlens, use_l2norm):
                                 L.ptr(lam), L.ptr(cu), L.ptr(o), L.ptr(ws), ws.numel(), L.ptr(st),
                                 L.stream_ptr(dev))
     L.check(rc, "lampa_hgdn_fwd")
+    states = counts = None
+    if want_state:
+        N = B if cu is None else len(cu) - 1
+        Lv = lam.shape[-1]
+        states = torch.empty(N, H, K, V, Lv, dtype=torch.float32, device=dev)
+        counts = torch.empty(N, Lv, dtype=torch.int32, device=dev)
+        rc = L.lib().lampa_hgdn_final_state(ctypes.byref(desc), L.ptr(k), L.ptr(v), L.ptr(g), L.ptr(beta),
+                                            L.ptr(cu), L.ptr(ws), ws.numel(), L.ptr(states), L.ptr(counts),
+                                            L.ptr(st), L.stream_ptr(dev))
+        L.check(rc, "lampa_hgdn_final_state")
+    if L.debug_checks():
+        L.check_status(dev)
+    return (o, states, counts) if want_state else o
+
+
+@torch.no_grad()
+def _hgdn_step(hstate: HState, q, k, v, g, beta, lam, use_l2norm: bool = True) -> torch.Tensor:
+    """One token per batch row: q,k [B,H,K]; v [B,H,V]; g,beta [B,H]; lam [B,H,L] (as given to
+    the kernel, i.e. not divided by scale).  Updates hstate in place, returns o [B,H,V]."""
+    dev = L.require_cuda(q, k, v, g, beta, lam, hstate.states, hstate.counts)
+    B, H, K = q.shape
+    V = v.shape[-1]
+    Lv = lam.shape[-1]
+    if tuple(hstate.states.shape) != (B, H, K, V, Lv) or hstate.states.dtype != torch.float32:
+        raise ValueError(f"state must be fp32 [{B},{H},{K},{V},{Lv}]")
+    if not hstate.states.is_contiguous():
+        hstate.states = hstate.states.contiguous()
+    q, k, v, g, lam = (x.contiguous() for x in (q, k, v, g, lam))
+    beta = beta.to(g.dtype).contiguous()
+    desc = L.GdnDesc(B=B, T=1, H=H, K=K, V=V, L=Lv, nseq=0, qkv_dtype=L.dtype_code(q.dtype),
+                     gb_dtype=L.dtype_code(g.dtype), lam_dtype=L.dtype_code(lam.dtype),
+                     use_l2norm=int(bool(use_l2norm)), scale=1.0)
+    o = torch.empty(B, H, V, dtype=q.dtype, device=dev)
+    st = L.status_word(dev)
+    rc = L.lib().lampa_hgdn_step(ctypes.byref(desc), L.ptr(q), L.ptr(k), L.ptr(v), L.ptr(g), L.ptr(beta),
+                                 L.ptr(lam), L.ptr(hstate.states), L.ptr(hstate.counts), L.ptr(o),
+                                 L.ptr(st), L.stream_ptr(dev))
+    L.check(rc, "lampa_hgdn_step")
     if L.debug_checks():
         L.check_status(dev)
     return o
+
+
+@torch.no_grad()
+def _hgdn_prefill(q, k, v, g, beta, lam, use_l2norm: bool = True):
+    """(o, HState) after all T tokens: whole chunks through the chunkwise kernels, the remaining
+    T mod 64 tokens through the step kernel — the split hattention_prefill makes
+    (models/hattention/kernel.py:470-560)."""
+    B, T, H, K = q.shape
+    V, Lv = v.shape[-1], lam.shape[-1]
+    dev = L.require_cuda(q, k, v, g, beta, lam)
+    T0 = T - T % CHUNK
+    hstate = HState(2, HType.WEAK, HStruct.GDELTA, (B, H, K, V, Lv), torch.float32, dev)
+    o = torch.empty(B, T, H, V, dtype=q.dtype, device=dev)
+    if T0 > 0:
+        o0, states, counts = _hgdn(q[:, :T0], k[:, :T0], v[:, :T0], g[:, :T0], beta[:, :T0], lam[:, :T0],
+                                   None, use_l2norm, want_state=True)
+        o[:, :T0] = o0
+        hstate.states = states
+        hstate.counts = counts[0].contiguous()
+    for t in range(T0, T):
+        o[:, t] = _hgdn_step(hstate, q[:, t], k[:, t], v[:, t], g[:, t], beta[:, t], lam[:, t], use_l2norm)
+    return o, hstate
 
 
 def chunk_h_gated_delta_rule(
@@ -182,7 +276,7 @@ def chunk_h_gated_delta_rule(
     l: torch.Tensor,
     beta: torch.Tensor,
     scale: float = None,
-    initial_state=None,
+    initial_state: Optional[HState] = None,
     output_final_state: bool = False,
     cu_seqlens: Optional[torch.LongTensor] = None,
     head_first: bool = False,
@@ -192,16 +286,58 @@ def chunk_h_gated_delta_rule(
 
     l: [B,T,H,L] level weights.  The reference divides l by `scale` and multiplies the
     normalised q by it (gated_delta_rule_apis.py:68-70, kernel.py:109-111); the two cancel, so
-    the kernel takes l as given and the result does not depend on `scale`.
-    Beyond the reference: `cu_seqlens` and T not a multiple of 64 are accepted.
-    `output_final_state=True` (the HState prefill/step branches, kernel.py:377-633) is not
-    implemented yet.
+    the kernels take l as given and the result does not depend on `scale`.
+    The three branches of the reference (gated_delta_rule_apis.py:72-129):
+      output_final_state=False                  -> (o, None)
+      output_final_state=True, no initial_state -> (o, HState) after all T tokens (prefill)
+      output_final_state=True, initial_state    -> T must be 1: one decode step on the state
+                                                   (updated in place and returned)
+    Beyond the reference: `cu_seqlens` and T not a multiple of 64 are accepted by the first branch.
     """
     _common_checks(q, k, v, beta, head_first, cu_seqlens, None)
     assert use_qk_l2norm_in_kernel is True
-    if output_final_state or initial_state is not None:
-        raise NotImplementedError("hierarchical final/initial state (HState) is not implemented")
-    return _hgdn(q, k, v, g, beta, l, cu_seqlens, True), None
+    if output_final_state is False:
+        if initial_state is not None:
+            raise NotImplementedError
+        return _hgdn(q, k, v, g, beta, l, cu_seqlens, True), None
+    if cu_seqlens is not None:
+        raise NotImplementedError("final state of packed sequences is not exposed at this level")
+    if initial_state is None:
+        return _hgdn_prefill(q, k, v, g, beta, l, True)
+    if not all([q.ndim == 4, q.shape[1] == 1, k.ndim == 4, k.shape[1] == 1, v.ndim == 4, v.shape[1] == 1,
+                beta.ndim == 3, beta.shape[1] == 1, g.ndim == 3, g.shape[1] == 1,
+                l.ndim == 4, l.shape[1] == 1]):
+        raise ValueError
+    o = _hgdn_step(initial_state, q[:, 0], k[:, 0], v[:, 0], g[:, 0], beta[:, 0], l[:, 0], True)
+    return o.unsqueeze(1), initial_state
+
+
+def hattention_prefill(q, k, v, b, g, l, scale, head_first, level_base, htype, hstruct,
+                       chunk_size: Optional[int] = None, use_qk_l2norm_in_kernel: bool = False):
+    """hattention_prefill of models/hattention/kernel.py:470-560 for GDELTA / WEAK / base 2:
+    returns (o, HState).  `l` is the weight the reference kernel sees (already divided by scale)."""
+    if getattr(hstruct, "name", hstruct) != "GDELTA" or getattr(htype, "name", htype) != "WEAK" or level_base != 2:
+        raise NotImplementedError
+    if head_first or (chunk_size is not None and chunk_size != CHUNK):
+        raise NotImplementedError
+    if not use_qk_l2norm_in_kernel or scale is None or b is None:
+        raise NotImplementedError
+    return _hgdn_prefill(q, k, v, g, b, l * scale, True)
+
+
+def hattention_step(hstate: HState, q, k, v, b, g, l, scale, level_base, htype, hstruct,
+                    use_qk_l2norm_in_kernel: bool = False):
+    """hattention_step of models/hattention/kernel.py:570-633: q,k [B,H,K]; v [B,H,V]; b,g [B,H];
+    l [B,H,L].  Returns (o [B,H,V], hstate) with hstate updated in place."""
+    if not all([q.ndim == 3, k.ndim == 3, v.ndim == 3, b.ndim == 2 if b is not None else True,
+                g.ndim == 2, l.ndim == 3, q.dtype == k.dtype, q.dtype == v.dtype,
+                hstate.base == level_base]):
+        raise TypeError
+    if getattr(hstruct, "name", hstruct) != "GDELTA" or getattr(htype, "name", htype) != "WEAK" or level_base != 2:
+        raise NotImplementedError
+    if not use_qk_l2norm_in_kernel or scale is None or b is None:
+        raise NotImplementedError
+    return _hgdn_step(hstate, q, k, v, g, b, l * scale, True), hstate
 
 
 def hattention_kernel(
