@@ -222,6 +222,41 @@ int lampa_invert_perm(const int64_t* perm, const int64_t* seg_offsets, int32_t n
                       int64_t* inv, void* stream);
 
 /*
+ * Per-row range of the LSH projections: mn/mx/range [rows] fp32 (any may be NULL) over the n
+ * values of each row of a and, when b is given, of b as well; range = max - min.
+ * Replaces: the four max/min reductions of lsh_mapping / lsh_mapping1
+ * (models/model_utils/hash_utils.py:333-355, copy in models/baselines/hmamba.py:253-272), whose
+ * `hash_shift` is the region stride of the geo shift.
+ */
+int lampa_row_range(const float* a, const float* b, int32_t rows, int64_t n, float* mn, float* mx,
+                    float* range, void* stream);
+/*
+ * Quantile regions of one coordinate.  rank int64 [n]: position of each hit in the ascending
+ * order of the coordinate (the inverse of the reference's argsort, lampa_invert_perm of a
+ * lampa_segsort_stable result); num_regions fp32 [rows] (fractional region counts per
+ * (round, head) row).  out fp32 [rows][n] = floor(rank / ceil(n / num_regions[r])) + 1.
+ * Replaces: quantile_partition (models/model_utils/hash_utils.py:14-27) as called by
+ * prepare_input (models/hattention/modeling_gated_deltaproduct.py:1214-1219, models/rwkv/RWKV.py:61-66).
+ */
+int lampa_quantile_regions(const int64_t* rank, const float* num_regions, int32_t rows, int64_t n,
+                           float* out, void* stream);
+/*
+ * Region shift and shifted sort keys, fp32 [rows][n]:
+ *   shift = (reg_phi * hash_shift[r]) * (ceil(regions_eta[r]) + 1) + reg_eta * hash_shift[r]
+ *   out   = shift                          when proj is NULL   (get_geo_shift)
+ *   out   = (i < raw_size ? proj : +inf) + shift   otherwise   (the keys HEPT sorts)
+ * every product and sum rounded separately, in this order.  The regions come either from
+ * reg_eta / reg_phi (fp32 [rows][n], lampa_quantile_regions output) or, when those are NULL,
+ * straight from rank_eta / rank_phi (int64 [n]) and regions_phi, without materialising them.
+ * Replaces: get_geo_shift and the `hashed[..., raw_size:] = inf; hashed + shifts` statements of
+ * HEPTAttention.forward (models/attention/hept.py:78-88, 127-136; copy in
+ * models/baselines/hmamba.py:76-90).
+ */
+int lampa_geo_keys(const float* proj, const float* reg_eta, const float* reg_phi,
+                   const int64_t* rank_eta, const int64_t* rank_phi, const float* regions_eta,
+                   const float* regions_phi, const float* hash_shift, int32_t rows, int64_t n,
+                   int64_t raw_size, float* out, void* stream);
+/*
  * Per-kernel timing for benchmarks (no counterpart in the reference, which has no timing code).
  * lampa_profile_enable(1) makes every later launch of this library record a pair of CUDA events
  * on its stream; lampa_profile_enable(0) stops and clears.  lampa_profile_read synchronises on

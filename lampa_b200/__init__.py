@@ -4,6 +4,8 @@ from ._lib import LampaError, check_status  # noqa: F401
 from .gated_delta import (  # noqa: F401
     HState, HStruct, HType, chunk_gated_delta_rule, chunk_h_gated_delta_rule, hattention_kernel,
     hattention_prefill, hattention_step, num_levels_required)
+from .geo import (  # noqa: F401
+    get_geo_shift, get_regions, hept_positions, pad_to_multiple, quantile_partition, region_inputs, row_range)
 from .lsh import (  # noqa: F401
     E2LSH, LSHOrdering, batched_index_select, invert_permutation, lsh_bucket_sort, lsh_hash, lsh_mapping,
     permute_rows, segmented_sort, sort_to_buckets, unsort_from_buckets)
@@ -12,5 +14,6 @@ __all__ = [
     "LampaError", "check_status", "HState", "HStruct", "HType", "hattention_prefill", "hattention_step", "chunk_gated_delta_rule", "chunk_h_gated_delta_rule",
     "hattention_kernel", "num_levels_required", "E2LSH", "LSHOrdering", "batched_index_select",
     "invert_permutation", "lsh_bucket_sort", "lsh_hash", "lsh_mapping", "permute_rows", "segmented_sort",
-    "sort_to_buckets", "unsort_from_buckets",
+    "sort_to_buckets", "unsort_from_buckets", "get_geo_shift", "get_regions", "hept_positions", "pad_to_multiple",
+    "quantile_partition", "region_inputs", "row_range",
 ]

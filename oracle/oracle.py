@@ -187,3 +187,61 @@ def lsh_ordering(coords, alpha) -> np.ndarray:
     norm = np.sqrt((coords.astype(np.float32) ** 2).sum(-1, dtype=np.float32)).astype(np.float32)
     norm_idx = segsort(norm)
     return segsort(key, init=norm_idx)
+
+
+# ---- region (geo) shift of the LSH keys: numpy fp32, one rounding per elementwise op ------------
+
+def quantile_regions(sorted_idx, num_regions) -> np.ndarray:
+    """quantile_partition (models/model_utils/hash_utils.py:14-27): sorted_idx [N] is the argsort
+    of one coordinate, num_regions [R] fp32.  Returns fp32 [R, N]:
+    floor(rank / ceil(N / R_r)) + 1 with rank = inverse permutation of sorted_idx."""
+    sorted_idx = np.asarray(sorted_idx, np.int64)
+    n = sorted_idx.shape[0]
+    rank = np.empty(n, np.int64)
+    rank[sorted_idx] = np.arange(n, dtype=np.int64)
+    rs = np.ceil(np.float32(n) / np.asarray(num_regions, np.float32).reshape(-1))     # [R]
+    return (np.floor_divide(rank[None, :].astype(np.float32), rs[:, None]) + np.float32(1)).astype(np.float32)
+
+
+def geo_shift(regions_eta, hash_shift, reg_eta, reg_phi) -> np.ndarray:
+    """get_geo_shift (models/attention/hept.py:78-88) for one of its two identical halves:
+    (reg_phi * range) * (ceil(R_eta) + 1) + reg_eta * range, fp32 [R, N]."""
+    hs = np.asarray(hash_shift, np.float32).reshape(-1, 1)
+    stride = (np.ceil(np.asarray(regions_eta, np.float32)).reshape(-1, 1) + np.float32(1)).astype(np.float32)
+    phi = (np.asarray(reg_phi, np.float32) * hs).astype(np.float32) * stride
+    eta = (np.asarray(reg_eta, np.float32) * hs).astype(np.float32)
+    return (phi.astype(np.float32) + eta).astype(np.float32)
+
+
+def row_range(a, b=None) -> np.ndarray:
+    """hash_shift of lsh_mapping (hash_utils.py:333-340): max - min over the last axis of a
+    (and b), fp32 [R]."""
+    a = np.asarray(a, np.float32).reshape(-1, a.shape[-1])
+    mx, mn = a.max(-1), a.min(-1)
+    if b is not None:
+        b = np.asarray(b, np.float32).reshape(-1, b.shape[-1])
+        mx, mn = np.maximum(mx, b.max(-1)), np.minimum(mn, b.min(-1))
+    return (mx - mn).astype(np.float32)
+
+
+def geo_keys(proj, shift, raw_size: int) -> np.ndarray:
+    """Shifted sort keys (hept.py:130-136): padded hits get +inf before the shift is added."""
+    k = np.array(proj, np.float32).reshape(shift.shape)
+    k[:, raw_size:] = np.inf
+    return (k + shift).astype(np.float32)
+
+
+def e2lsh_proj(vecs, alpha) -> np.ndarray:
+    """E2LSH.forward (hash_utils.py:366-371): vecs [heads, N, dim], alpha [heads, dim, rounds]
+    -> fp32 [rounds, heads, N], accumulated in the frozen order of oracle_lsh_ids."""
+    vecs = _f32(vecs)
+    alpha = _f32(alpha)
+    heads, N, dim = vecs.shape
+    rounds = alpha.shape[-1]
+    out = np.empty((rounds, heads, N), np.float32)
+    for h in range(heads):
+        acc = vecs[h, :, 0:1] * alpha[h, 0][None, :]
+        for d in range(1, dim):
+            acc = (acc + (vecs[h, :, d:d + 1] * alpha[h, d][None, :]).astype(np.float32)).astype(np.float32)
+        out[:, h, :] = acc.T
+    return out

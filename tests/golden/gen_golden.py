@@ -9,7 +9,9 @@ It executes the reference's pure-PyTorch CPU statements of the path
 models/hattention/base.py::hattention_materialized_dplr helpers,
 models/baselines/hmamba.py::LSHOrdering / E2LSH / lsh_mapping,
 models/model_utils/hash_utils.py::invert_permutation / batched_index_select,
-models/attention/hept.py::sort_to_buckets / unsort_from_buckets) on seeded
+models/attention/hept.py::sort_to_buckets / unsort_from_buckets / get_geo_shift,
+models/model_utils/hash_utils.py::pad_to_multiple / get_regions / quantile_partition /
+E2LSH / lsh_mapping) on seeded
 inputs and stores inputs + outputs as small .npz files.  Nothing from the
 reference is copied; only numbers it produced are stored.
 """
@@ -69,12 +71,68 @@ def gdn_inputs(seed, T, H, K, V, L=None, g_shift=2.0):
     return q, k, v, beta, g, lam
 
 
+def gen_geo(ref: str):
+    """Region shift of the HEPT keys: the statements of prepare_input
+    (models/hattention/modeling_gated_deltaproduct.py:1210-1222) and of HEPTAttention.forward
+    up to the positions (models/attention/hept.py:118-138), run with the reference's functions."""
+    einops = __import__("einops")
+    hu = load_defs(os.path.join(ref, "models", "model_utils", "hash_utils.py"),
+                   {"pad_to_multiple", "get_regions", "quantile_partition", "E2LSH", "lsh_mapping", "uniform"},
+                   extra={"rearrange": einops.rearrange, "F": torch.nn.functional})
+    hp = load_defs(os.path.join(ref, "models", "attention", "hept.py"), {"get_geo_shift"},
+                   extra={"rearrange": einops.rearrange, "List": list})
+    rearrange = einops.rearrange
+    raw, block, heads, rounds, dim, num_regions = 1090, 100, 4, 3, 8, 40
+    gen = torch.Generator().manual_seed(4242)
+    eta = torch.randn(raw, generator=gen) * 1.5
+    phi = (torch.rand(raw, generator=gen) * 2 - 1) * np.pi
+    coords_raw = torch.stack([eta, phi], -1)
+    q_raw = torch.randn(heads, raw, dim, generator=gen)
+    k_raw = torch.randn(heads, raw, dim, generator=gen)
+    torch.manual_seed(11)
+    regions = hu["get_regions"](num_regions, rounds, heads)              # [c, a, h]
+    e2lsh = hu["E2LSH"](n_hashes=rounds, n_heads=heads, dim=dim)
+    with torch.no_grad():
+        coords = hu["pad_to_multiple"](coords_raw, block, dims=0, value=float("inf"))
+        sorted_eta = torch.argsort(coords[..., 0], dim=-1)
+        sorted_phi = torch.argsort(coords[..., 1], dim=-1)
+        regions_h = rearrange(regions, "c a h -> a (c h)")
+        reg_eta = hu["quantile_partition"](sorted_eta, regions_h[0][:, None])
+        reg_phi = hu["quantile_partition"](sorted_phi, regions_h[1][:, None])
+        n = coords.shape[0]
+        q_hat = torch.zeros(heads, n, dim); q_hat[:, :raw] = q_raw
+        k_hat = torch.zeros(heads, n, dim); k_hat[:, :raw] = k_raw
+        qh, kh, hs = hu["lsh_mapping"](e2lsh, q_hat, k_hat)
+        hs = rearrange(hs, "c h d -> (c h) d")
+        qh[..., raw:] = float("inf")
+        kh[..., raw:] = float("inf")
+        q_shift, k_shift = hp["get_geo_shift"](regions_h, hs, [reg_eta, reg_phi], rounds)
+        q_keys = qh + q_shift
+        k_keys = kh + k_shift
+        q_pos = q_keys.argsort(dim=-1)
+        k_pos = k_keys.argsort(dim=-1)
+    np.savez_compressed(
+        os.path.join(HERE, "geo_shift_N1090_R12.npz"),
+        coords=coords_raw.numpy(), q_hat=q_hat.numpy(), k_hat=k_hat.numpy(), regions=regions.numpy(),
+        alpha=e2lsh.alpha.detach().numpy(), beta=e2lsh.beta.detach().numpy(),
+        raw_size=np.int64(raw), block_size=np.int64(block),
+        sorted_eta=sorted_eta.numpy(), sorted_phi=sorted_phi.numpy(),
+        reg_eta=reg_eta.numpy(), reg_phi=reg_phi.numpy(), hash_shift=hs.numpy(),
+        q_hashed=qh.numpy(), k_hashed=kh.numpy(), q_shift=q_shift.numpy(), k_shift=k_shift.numpy(),
+        q_keys=q_keys.numpy(), k_keys=k_keys.numpy(), q_pos=q_pos.numpy(), k_pos=k_pos.numpy())
+    print("geo ok", tuple(reg_eta.shape), tuple(q_pos.shape), float(hs.max()))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--only", default="", help="'geo': write only the region-shift fixture")
     args = ap.parse_args()
     ref = args.reference
     torch.set_num_threads(8)
+    gen_geo(ref)
+    if args.only == "geo":
+        return
     base, recurrent = load_hattention(ref)
 
     # ---- hierarchical + plain gated delta, reference token recurrence -------------

@@ -109,3 +109,19 @@ def _rank_main(rank, world, port, lens):
 def test_two_rank_plan_and_gather_over_gloo():
     lens = [700, 60, 1500, 333, 64, 900, 5]
     mp.spawn(_rank_main, args=(2, _free_port(), lens), nprocs=2, join=True)
+
+
+def test_get_regions_matches_reference_draws(golden_dir):
+    """Seeded region counts equal the reference's get_regions (fixture written by gen_golden.py)."""
+    import numpy as np
+    import torch
+    from lampa_b200.geo import get_regions, pad_to_multiple
+    z = np.load(os.path.join(golden_dir, "geo_shift_N1090_R12.npz"))
+    torch.manual_seed(11)
+    r = get_regions(40, 3, 4)
+    assert tuple(r.shape) == (3, 2, 4)
+    np.testing.assert_array_equal(r.numpy(), z["regions"])
+    x = torch.arange(10.0).view(5, 2)
+    p = pad_to_multiple(x, 4, dims=0, value=float("inf"))
+    assert tuple(p.shape) == (8, 2) and torch.isinf(p[5:]).all() and torch.equal(p[:5], x)
+    assert pad_to_multiple(x, 5, dims=0) is x

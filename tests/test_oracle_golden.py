@@ -112,3 +112,34 @@ def test_integer_ids_and_stable_sort_properties():
     perm_s = oracle.segsort(row, seg)
     for a, b in zip(seg[:-1], seg[1:]):
         np.testing.assert_array_equal(perm_s[a:b], np.argsort(row[a:b], kind="stable"))
+
+
+def test_geo_shift_against_reference_fixture(golden_dir):
+    """quantile_partition / get_geo_shift / lsh_mapping of the reference (tests/golden/gen_golden.py)."""
+    z = np.load(os.path.join(golden_dir, "geo_shift_N1090_R12.npz"))
+    regions = z["regions"]                                     # [c, a, h]
+    regions_h = regions.transpose(1, 0, 2).reshape(2, -1)      # "c a h -> a (c h)"
+    re = oracle.quantile_regions(z["sorted_eta"], regions_h[0])
+    rp = oracle.quantile_regions(z["sorted_phi"], regions_h[1])
+    np.testing.assert_array_equal(re, z["reg_eta"])
+    np.testing.assert_array_equal(rp, z["reg_phi"])
+    raw = int(z["raw_size"])
+    qh = z["q_hashed"].copy(); kh = z["k_hashed"].copy()
+    qh[..., raw:] = 0.0; kh[..., raw:] = 0.0                   # padded rows project to 0 before the +inf
+    np.testing.assert_array_equal(oracle.row_range(qh, kh), z["hash_shift"].reshape(-1))
+    shift = oracle.geo_shift(regions_h[0], z["hash_shift"], re, rp)
+    np.testing.assert_array_equal(shift, z["q_shift"].reshape(shift.shape))
+    np.testing.assert_array_equal(shift, z["k_shift"].reshape(shift.shape))
+    keys = oracle.geo_keys(qh, shift, raw)
+    np.testing.assert_array_equal(keys, z["q_keys"].reshape(keys.shape))
+    # projections: same numbers as the reference's bmm up to summation order
+    proj = oracle.e2lsh_proj(z["q_hat"], z["alpha"])
+    np.testing.assert_allclose(proj[..., :raw], z["q_hashed"][..., :raw], rtol=1e-5, atol=1e-5)
+    # stable sort of the reference keys reproduces the reference positions on the real hits
+    # (equal keys may come out in either order from the reference's non-stable argsort)
+    kq = z["q_keys"].reshape(-1, keys.shape[-1])
+    pos = np.stack([oracle.segsort(r) for r in kq])
+    ref_pos = z["q_pos"].reshape(pos.shape)
+    differ = pos[:, :raw] != ref_pos[:, :raw]
+    assert differ.mean() < 1e-3
+    np.testing.assert_array_equal(np.take_along_axis(kq, pos, 1)[:, :raw], np.take_along_axis(kq, ref_pos, 1)[:, :raw])
