@@ -126,32 +126,79 @@ __device__ __forceinline__ void zero_acc(float (&acc)[N][4]) {
 
 // -------------------------------------------------------------------------------------------------
 // Solve kernel: one warp per (chunk, head) computes A0 = tril(diag(beta) K K^T, -1) on tensor
-// cores and X = (I + A0)^-1 by an fp32 right-looking substitution (once x_j is final every later
-// row takes x_i -= A0[i][j] x_j, all independent).  Lane c owns columns c and c + 32; the second
-// is zero above row 32, so it only joins for j >= 32 and re-uses the A0 values already loaded for
-// column c: the substitution is bound by shared-memory wavefronts (one broadcast load per FMA
-// group), and this halves them.  It is its own kernel because it needs 18.7 KB of shared memory and
-// ~130 registers for 32 threads, so 12 of these CTAs share an SM and hide each other's 63-step
-// dependency chain.  Awb = X diag(beta) goes, as bf16 [64][72], into the record's O_local slot
-// (consumed and then overwritten by the preparation kernel).
+// cores and X = (I + A0)^-1 blockwise, as the reference's solve_tril does
+// (models/hattention/solve_tril.py:221-276): the four 16x16 diagonal blocks by fp32 forward
+// substitution (lane = one column of one block, two blocks at a time), then the off-diagonal
+// blocks by products on the tensor cores,
+//     X_ba = -X_bb A_ba X_aa      first inside the two 32x32 halves, then for the 32x32 corner,
+// everything in place in one fp32 [64][68] tile that first holds A0.  The products keep fp32
+// accuracy by splitting each operand into bf16 hi + bf16 lo and issuing hi*hi + lo*hi + hi*lo
+// (the reference asks for IEEE fp32 dots there).  It is its own kernel because 17.7 KB of shared
+// memory per warp lets 12 of these CTAs share an SM.  Awb = X diag(beta) goes, as bf16 [64][72],
+// into the record's O_local slot (consumed and then overwritten by the preparation kernel).
 // -------------------------------------------------------------------------------------------------
 template <int KD>
 struct SolveSmem {
     static constexpr int KP = KD + 8, CP = CHUNK + 8;
+    static constexpr int PA = CHUNK + 4;               // fp32 pitch: 68 floats, B-fragment loads hit 32 banks
     static constexpr int K = 0;                        // bf16 [64][KP], dead once K K^T is in registers
-    static constexpr int AT = 0;                       // fp32 [64][72]: A0 transposed (aliases K)
-    static constexpr int BETA = AT + CHUNK * CP * 4;
+    static constexpr int A = 0;                        // fp32 [64][PA]: A0, then X in place (aliases K)
+    static constexpr int BETA = A + CHUNK * PA * 4;
     static constexpr int BYTES = BETA + CHUNK * 4;
+    static_assert(CHUNK * KP * 2 <= CHUNK * PA * 4, "K must fit under the fp32 tile");
 };
+
+__device__ __forceinline__ void split2(float x, float y, uint32_t& hi, uint32_t& lo) {
+    hi = pack_bf16x2(x, y);
+    const float2 h = unpack_bf16x2(hi);
+    lo = pack_bf16x2(x - h.x, y - h.y);
+}
+// A fragment (rows r0.., columns c0.. of an fp32 tile in shared memory), split into hi and lo
+__device__ __forceinline__ void load_a_f32(const float* s, int pitch, int r0, int c0, int lane,
+                                           uint32_t (&hi)[4], uint32_t (&lo)[4]) {
+    const int g = lane >> 2, t = lane & 3;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        const float2 v = *reinterpret_cast<const float2*>(s + (r0 + g + (q & 1) * 8) * pitch + c0 + 2 * t + (q >> 1) * 8);
+        split2(v.x, v.y, hi[q], lo[q]);
+    }
+}
+// B fragment of the 16 x 8 block B[k][n] = s[(k0 + k) * pitch + n0 + n]
+__device__ __forceinline__ void load_b_f32(const float* s, int pitch, int k0, int n0, int lane,
+                                           uint32_t (&hi)[2], uint32_t (&lo)[2]) {
+    const int g = lane >> 2, t = lane & 3;
+#pragma unroll
+    for (int q = 0; q < 2; ++q)
+        split2(s[(k0 + 2 * t + 8 * q) * pitch + n0 + g], s[(k0 + 2 * t + 1 + 8 * q) * pitch + n0 + g], hi[q], lo[q]);
+}
+__device__ __forceinline__ void mma3(float (&c)[4], const uint32_t (&ah)[4], const uint32_t (&al)[4],
+                                     const uint32_t (&bh)[2], const uint32_t (&bl)[2]) {
+    mma16816(c, ah, bh[0], bh[1]);
+    mma16816(c, al, bh[0], bh[1]);
+    mma16816(c, ah, bl[0], bl[1]);
+}
+// two adjacent accumulator tiles (16 x 16) as the A fragment of the next product
+__device__ __forceinline__ void acc_to_a(const float (&c0)[4], const float (&c1)[4], uint32_t (&hi)[4], uint32_t (&lo)[4]) {
+    split2(c0[0], c0[1], hi[0], lo[0]);
+    split2(c0[2], c0[3], hi[1], lo[1]);
+    split2(c1[0], c1[1], hi[2], lo[2]);
+    split2(c1[2], c1[3], hi[3], lo[3]);
+}
+// s[r0 + ..][c0 + 8 nt + ..] = -acc
+__device__ __forceinline__ void store_neg_tile(float* s, int pitch, int r0, int c0, int lane, const float (&c)[4]) {
+    const int g = lane >> 2, t = lane & 3;
+    *reinterpret_cast<float2*>(s + (r0 + g) * pitch + c0 + 2 * t) = make_float2(-c[0], -c[1]);
+    *reinterpret_cast<float2*>(s + (r0 + g + 8) * pitch + c0 + 2 * t) = make_float2(-c[2], -c[3]);
+}
 
 template <int KD, int VD>
 __global__ void __launch_bounds__(32) gdn_solve_kernel(GdnArgs a) {
     using S = SolveSmem<KD>;
     using R = Rec<KD, VD>;
-    constexpr int KP = S::KP, CP = S::CP;
+    constexpr int KP = S::KP, CP = S::CP, PA = S::PA;
     extern __shared__ __align__(128) unsigned char smem[];
     __nv_bfloat16* sK = reinterpret_cast<__nv_bfloat16*>(smem + S::K);
-    float* sAT = reinterpret_cast<float*>(smem + S::AT);
+    float* sA = reinterpret_cast<float*>(smem + S::A);
     float* sBeta = reinterpret_cast<float*>(smem + S::BETA);
     const int h = blockIdx.x, c = blockIdx.y, H = a.H;
     ChunkLoc loc;
@@ -186,58 +233,159 @@ __global__ void __launch_bounds__(32) gdn_solve_kernel(GdnArgs a) {
         sBeta[row] = bv;
     }
     __syncwarp();
-    // A0^T[j][i] = beta_i (k_i . k_j) for i > j.  All lower tiles are accumulated first: the fp32
-    // matrix then takes over the storage of K (18.4 KB per CTA instead of 27.6 KB: 12 CTAs per SM).
-    float acc0[2][4], acc1[4][4], acc2[6][4], acc3[8][4];
-    zero_acc<2>(acc0); zero_acc<4>(acc1); zero_acc<6>(acc2); zero_acc<8>(acc3);
-    warp_gemm<2, KD, false, false>(acc0, sK, KP, 0, sK, KP, 0, lane);
-    warp_gemm<4, KD, false, false>(acc1, sK, KP, 16, sK, KP, 0, lane);
-    warp_gemm<6, KD, false, false>(acc2, sK, KP, 32, sK, KP, 0, lane);
-    warp_gemm<8, KD, false, false>(acc3, sK, KP, 48, sK, KP, 0, lane);
-    const float bi[8] = {sBeta[gq], sBeta[gq + 8], sBeta[16 + gq], sBeta[24 + gq],
-                         sBeta[32 + gq], sBeta[40 + gq], sBeta[48 + gq], sBeta[56 + gq]};
-    __syncwarp();
+    // A0[i][j] = beta_i (k_i . k_j) for i > j.  All lower tiles are accumulated first: the fp32
+    // tile then takes over the storage of K.
+    {
+        float acc0[2][4], acc1[4][4], acc2[6][4], acc3[8][4];
+        zero_acc<2>(acc0); zero_acc<4>(acc1); zero_acc<6>(acc2); zero_acc<8>(acc3);
+        warp_gemm<2, KD, false, false>(acc0, sK, KP, 0, sK, KP, 0, lane);
+        warp_gemm<4, KD, false, false>(acc1, sK, KP, 16, sK, KP, 0, lane);
+        warp_gemm<6, KD, false, false>(acc2, sK, KP, 32, sK, KP, 0, lane);
+        warp_gemm<8, KD, false, false>(acc3, sK, KP, 48, sK, KP, 0, lane);
+        const float bi[8] = {sBeta[gq], sBeta[gq + 8], sBeta[16 + gq], sBeta[24 + gq],
+                             sBeta[32 + gq], sBeta[40 + gq], sBeta[48 + gq], sBeta[56 + gq]};
+        __syncwarp();
 #define LAMPA_PUT_A0(ACC, NT, M0)                                                              \
-    _Pragma("unroll") for (int nt = 0; nt < NT; ++nt) {                                        \
-        _Pragma("unroll") for (int e = 0; e < 4; ++e) {                                        \
-            const int i = M0 + gq + (e >> 1) * 8, j = nt * 8 + 2 * tq + (e & 1);               \
-            sAT[j * CP + i] = (i > j) ? bi[M0 / 8 + (e >> 1)] * ACC[nt][e] : 0.f;              \
-        }                                                                                      \
-    }
-    LAMPA_PUT_A0(acc0, 2, 0)
-    LAMPA_PUT_A0(acc1, 4, 16)
-    LAMPA_PUT_A0(acc2, 6, 32)
-    LAMPA_PUT_A0(acc3, 8, 48)
+        _Pragma("unroll") for (int nt = 0; nt < NT; ++nt) {                                    \
+            _Pragma("unroll") for (int hh = 0; hh < 2; ++hh) {                                 \
+                const int i = M0 + gq + hh * 8, j = nt * 8 + 2 * tq;                           \
+                const float bb = bi[M0 / 8 + hh];                                              \
+                *reinterpret_cast<float2*>(sA + i * PA + j) =                                  \
+                    make_float2(i > j ? bb * ACC[nt][2 * hh] : 0.f, i > j + 1 ? bb * ACC[nt][2 * hh + 1] : 0.f); \
+            }                                                                                  \
+        }
+        LAMPA_PUT_A0(acc0, 2, 0)
+        LAMPA_PUT_A0(acc1, 4, 16)
+        LAMPA_PUT_A0(acc2, 6, 32)
+        LAMPA_PUT_A0(acc3, 8, 48)
 #undef LAMPA_PUT_A0
-    __syncwarp();
-    float r[CHUNK], s2[CHUNK / 2];
+        // blocks above the diagonal stay zero in X
 #pragma unroll
-    for (int i = 0; i < CHUNK; ++i) r[i] = (i == lane) ? 1.f : 0.f;
+        for (int bi2 = 0; bi2 < 3; ++bi2)
 #pragma unroll
-    for (int i = 0; i < CHUNK / 2; ++i) s2[i] = (i == lane) ? 1.f : 0.f;
+            for (int bj = bi2 + 1; bj < 4; ++bj)
 #pragma unroll
-    for (int j = 0; j < CHUNK - 1; ++j) {
-        const float rj = r[j];
-        const float sj = (j >= CHUNK / 2) ? s2[j >= CHUNK / 2 ? j - CHUNK / 2 : 0] : 0.f;
-#pragma unroll
-        for (int i4 = ((j + 1) / 4) * 4; i4 < CHUNK; i4 += 4) {
-            const float4 av = *reinterpret_cast<const float4*>(sAT + j * CP + i4);
-            const float ae[4] = {av.x, av.y, av.z, av.w};
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                if (i4 + e > j) {
-                    r[i4 + e] -= ae[e] * rj;
-                    if (j >= CHUNK / 2) s2[i4 + e - CHUNK / 2 >= 0 ? i4 + e - CHUNK / 2 : 0] -= ae[e] * sj;
+                for (int q = 0; q < 2; ++q) {
+                    const int e = lane + 32 * q;                  // 64 float4 per 16 x 16 block
+                    *reinterpret_cast<float4*>(sA + (16 * bi2 + (e >> 2)) * PA + 16 * bj + (e & 3) * 4) =
+                        make_float4(0.f, 0.f, 0.f, 0.f);
                 }
+    }
+    __syncwarp();
+    // ---- diagonal blocks: X_dd = (I + A_dd)^-1, lane = (block of the pair, column) ----
+#pragma unroll
+    for (int pass = 0; pass < 2; ++pass) {
+        const int base = 16 * (2 * pass + (lane >> 4)), cc = lane & 15;
+        float x[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            float sum = (i == cc) ? 1.f : 0.f;
+#pragma unroll
+            for (int q = 0; q < (i + 3) / 4; ++q) {
+                const float4 av = *reinterpret_cast<const float4*>(sA + (base + i) * PA + base + 4 * q);
+                const float ae[4] = {av.x, av.y, av.z, av.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                    if (4 * q + e < i) sum -= ae[e] * x[4 * q + e];
+            }
+            x[i] = sum;
+        }
+        __syncwarp();
+#pragma unroll
+        for (int i = 0; i < 16; ++i) sA[(base + i) * PA + base + cc] = x[i];
+    }
+    __syncwarp();
+    // ---- inside each 32 x 32 half: X_ba = -(X_bb A_ba) X_aa with a = 2p, b = 2p + 1 ----
+#pragma unroll
+    for (int p = 0; p < 2; ++p) {
+        const int ra = 32 * p, rb = 32 * p + 16;
+        float q0[2][4];
+        zero_acc<2>(q0);
+        {
+            uint32_t ah[4], al[4];
+            load_a_f32(sA, PA, rb, rb, lane, ah, al);
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt) {
+                uint32_t bh[2], bl[2];
+                load_b_f32(sA, PA, rb, ra + 8 * nt, lane, bh, bl);
+                mma3(q0[nt], ah, al, bh, bl);
             }
         }
-    }
-    __nv_bfloat16* gA = reinterpret_cast<__nv_bfloat16*>(a.rec + ((size_t)c * H + h) * a.rec_bytes + R::OL_OFF);
-    const float b0 = sBeta[lane], b1 = sBeta[lane + 32];
+        float xo[2][4];
+        zero_acc<2>(xo);
+        {
+            uint32_t ah[4], al[4];
+            acc_to_a(q0[0], q0[1], ah, al);
 #pragma unroll
-    for (int i = 0; i < CHUNK; ++i) {
-        gA[i * CP + lane] = __float2bfloat16_rn(r[i] * b0);
-        gA[i * CP + lane + 32] = __float2bfloat16_rn(i >= CHUNK / 2 ? s2[i >= CHUNK / 2 ? i - CHUNK / 2 : 0] * b1 : 0.f);
+            for (int nt = 0; nt < 2; ++nt) {
+                uint32_t bh[2], bl[2];
+                load_b_f32(sA, PA, ra, ra + 8 * nt, lane, bh, bl);
+                mma3(xo[nt], ah, al, bh, bl);
+            }
+        }
+        __syncwarp();
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) store_neg_tile(sA, PA, rb, ra + 8 * nt, lane, xo[nt]);
+    }
+    __syncwarp();
+    // ---- the 32 x 32 corner: X_ba = -(X_b A_ba) X_a with a = rows/cols 0..31, b = 32..63 ----
+    {
+        float qc[2][4][4];
+        zero_acc<4>(qc[0]); zero_acc<4>(qc[1]);
+#pragma unroll
+        for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+            for (int ks = 0; ks <= mt; ++ks) {                    // X_b is block lower-triangular
+                uint32_t ah[4], al[4];
+                load_a_f32(sA, PA, 32 + 16 * mt, 32 + 16 * ks, lane, ah, al);
+#pragma unroll
+                for (int nt = 0; nt < 4; ++nt) {
+                    uint32_t bh[2], bl[2];
+                    load_b_f32(sA, PA, 32 + 16 * ks, 8 * nt, lane, bh, bl);
+                    mma3(qc[mt][nt], ah, al, bh, bl);
+                }
+            }
+        float xc[2][4][4];
+        zero_acc<4>(xc[0]); zero_acc<4>(xc[1]);
+#pragma unroll
+        for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+            for (int ks = 0; ks < 2; ++ks) {
+                uint32_t ah[4], al[4];
+                acc_to_a(qc[mt][2 * ks], qc[mt][2 * ks + 1], ah, al);
+#pragma unroll
+                for (int nt = 0; nt < 2 + 2 * ks; ++nt) {          // X_a rows 0..15 are [X_00 | 0]
+                    uint32_t bh[2], bl[2];
+                    load_b_f32(sA, PA, 16 * ks, 8 * nt, lane, bh, bl);
+                    mma3(xc[mt][nt], ah, al, bh, bl);
+                }
+            }
+        __syncwarp();
+#pragma unroll
+        for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+            for (int nt = 0; nt < 4; ++nt) store_neg_tile(sA, PA, 32 + 16 * mt, 8 * nt, lane, xc[mt][nt]);
+    }
+    __syncwarp();
+    // ---- Awb = X diag(beta), bf16, 16 bytes per lane and store ----
+    __nv_bfloat16* gA = reinterpret_cast<__nv_bfloat16*>(a.rec + ((size_t)c * H + h) * a.rec_bytes + R::OL_OFF);
+    {
+        const int ch = lane & 7;
+        float bj[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) bj[e] = sBeta[8 * ch + e];
+#pragma unroll
+        for (int it = 0; it < 16; ++it) {
+            const int row = it * 4 + (lane >> 3);
+            const float4 v0 = *reinterpret_cast<const float4*>(sA + row * PA + 8 * ch);
+            const float4 v1 = *reinterpret_cast<const float4*>(sA + row * PA + 8 * ch + 4);
+            uint4 u;
+            u.x = pack_bf16x2(v0.x * bj[0], v0.y * bj[1]);
+            u.y = pack_bf16x2(v0.z * bj[2], v0.w * bj[3]);
+            u.z = pack_bf16x2(v1.x * bj[4], v1.y * bj[5]);
+            u.w = pack_bf16x2(v1.z * bj[6], v1.w * bj[7]);
+            *reinterpret_cast<uint4*>(gA + row * CP + 8 * ch) = u;
+        }
     }
 }
 
