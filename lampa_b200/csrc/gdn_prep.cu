@@ -40,12 +40,14 @@ int launch_plan(const PlanArgs& p, cudaStream_t st) {
 template <int KD, int VD>
 struct PrepSmem {
     static constexpr int KP = KD + 8, VP = VD + 8, CP = CHUNK + 8;
+    static constexpr int PA = CHUNK + 4;                         // fp32 pitch of the inverse's working tile (over AW and UH)
     static constexpr int Q = 0;                                  // bf16 [64][KP]   q (normalised); later W (rows are warp-private)
     static constexpr int K = Q + CHUNK * KP * 2;                 // bf16 [64][KP]   k (normalised)
     static constexpr int V = K + CHUNK * KP * 2;                 // bf16 [64][VP]   v
     static constexpr int AW = V + CHUNK * VP * 2;                // bf16 [64][CP]   Awb = (I + A0)^-1 diag(beta)
     static constexpr int UH = AW + CHUNK * CP * 2;               // bf16 [64][VP]   diag(e^{Glast-G}) U
-    static constexpr int G = UH + CHUNK * VP * 2;                // fp32 [64] G, [64] beta, [64] e^G, [64] e^{Glast-G}
+    static constexpr int AFTER_UH = UH + CHUNK * VP * 2, AFTER_SA = AW + CHUNK * PA * 4;   // the fp32 tile covers AW and UH
+    static constexpr int G = AFTER_UH > AFTER_SA ? AFTER_UH : AFTER_SA;   // fp32 [64] G, [64] beta, [64] e^G, [64] e^{Glast-G}
     static constexpr int LAM = G + 4 * CHUNK * 4;                // fp32 [64][L+1]
     static int bytes(int L) { return LAM + CHUNK * (L + 1) * 4; }
 };
@@ -125,29 +127,9 @@ __device__ __forceinline__ void zero_acc(float (&acc)[N][4]) {
 }
 
 // -------------------------------------------------------------------------------------------------
-// Solve kernel: one warp per (chunk, head) computes A0 = tril(diag(beta) K K^T, -1) on tensor
-// cores and X = (I + A0)^-1 blockwise, as the reference's solve_tril does
-// (models/hattention/solve_tril.py:221-276): the four 16x16 diagonal blocks by fp32 forward
-// substitution (lane = one column of one block, two blocks at a time), then the off-diagonal
-// blocks by products on the tensor cores,
-//     X_ba = -X_bb A_ba X_aa      first inside the two 32x32 halves, then for the 32x32 corner,
-// everything in place in one fp32 [64][68] tile that first holds A0.  The products keep fp32
-// accuracy by splitting each operand into bf16 hi + bf16 lo and issuing hi*hi + lo*hi + hi*lo
-// (the reference asks for IEEE fp32 dots there).  It is its own kernel because 17.7 KB of shared
-// memory per warp lets 12 of these CTAs share an SM.  Awb = X diag(beta) goes, as bf16 [64][72],
-// into the record's O_local slot (consumed and then overwritten by the preparation kernel).
+// Split-bf16 fragments for products that must keep fp32 accuracy (the blockwise triangular inverse):
+// operands live as fp32 in shared memory and enter the tensor core as bf16 hi + bf16 lo.
 // -------------------------------------------------------------------------------------------------
-template <int KD>
-struct SolveSmem {
-    static constexpr int KP = KD + 8, CP = CHUNK + 8;
-    static constexpr int PA = CHUNK + 4;               // fp32 pitch: 68 floats, B-fragment loads hit 32 banks
-    static constexpr int K = 0;                        // bf16 [64][KP], dead once K K^T is in registers
-    static constexpr int A = 0;                        // fp32 [64][PA]: A0, then X in place (aliases K)
-    static constexpr int BETA = A + CHUNK * PA * 4;
-    static constexpr int BYTES = BETA + CHUNK * 4;
-    static_assert(CHUNK * KP * 2 <= CHUNK * PA * 4, "K must fit under the fp32 tile");
-};
-
 __device__ __forceinline__ void split2(float x, float y, uint32_t& hi, uint32_t& lo) {
     hi = pack_bf16x2(x, y);
     const float2 h = unpack_bf16x2(hi);
@@ -189,204 +171,6 @@ __device__ __forceinline__ void store_neg_tile(float* s, int pitch, int r0, int 
     const int g = lane >> 2, t = lane & 3;
     *reinterpret_cast<float2*>(s + (r0 + g) * pitch + c0 + 2 * t) = make_float2(-c[0], -c[1]);
     *reinterpret_cast<float2*>(s + (r0 + g + 8) * pitch + c0 + 2 * t) = make_float2(-c[2], -c[3]);
-}
-
-template <int KD, int VD>
-__global__ void __launch_bounds__(32) gdn_solve_kernel(GdnArgs a) {
-    using S = SolveSmem<KD>;
-    using R = Rec<KD, VD>;
-    constexpr int KP = S::KP, CP = S::CP, PA = S::PA;
-    extern __shared__ __align__(128) unsigned char smem[];
-    __nv_bfloat16* sK = reinterpret_cast<__nv_bfloat16*>(smem + S::K);
-    float* sA = reinterpret_cast<float*>(smem + S::A);
-    float* sBeta = reinterpret_cast<float*>(smem + S::BETA);
-    const int h = blockIdx.x, c = blockIdx.y, H = a.H;
-    ChunkLoc loc;
-    if (!locate_chunk(a, c, loc)) return;
-    const int lane = threadIdx.x;
-    const int gq = lane >> 2, tq = lane & 3;
-    const int64_t t0 = loc.t0;
-    const int len = loc.len;
-#pragma unroll
-    for (int rr = 0; rr < 2; ++rr) {
-        const int row = lane + 32 * rr;
-        const bool valid = row < len;
-        const size_t tok = (size_t)(t0 + row);
-        float bv = 0.f;
-        if (valid) bv = load_as_float(a.beta, tok * H + h, a.gb_dt);
-        float x[KD / 2], y[KD / 2];
-        load_half_row<KD>(a.k, a.qkv_dt, (tok * H + h) * KD, valid, x);
-        load_half_row<KD>(a.k, a.qkv_dt, (tok * H + h) * KD + KD / 2, valid, y);
-        if (a.use_l2norm) {
-            // same summation order as the preparation kernel (half rows first), so both see the same K
-            float ss = 0.f, ss2 = 0.f;
-#pragma unroll
-            for (int i = 0; i < KD / 2; ++i) ss += x[i] * x[i];
-#pragma unroll
-            for (int i = 0; i < KD / 2; ++i) ss2 += y[i] * y[i];
-            const float rn = rsqrtf(ss + ss2 + 1e-6f);
-#pragma unroll
-            for (int i = 0; i < KD / 2; ++i) { x[i] *= rn; y[i] *= rn; }
-        }
-        store_half_row_bf16<KD / 2>(sK + row * KP, x);
-        store_half_row_bf16<KD / 2>(sK + row * KP + KD / 2, y);
-        sBeta[row] = bv;
-    }
-    __syncwarp();
-    // A0[i][j] = beta_i (k_i . k_j) for i > j.  All lower tiles are accumulated first: the fp32
-    // tile then takes over the storage of K.
-    {
-        float acc0[2][4], acc1[4][4], acc2[6][4], acc3[8][4];
-        zero_acc<2>(acc0); zero_acc<4>(acc1); zero_acc<6>(acc2); zero_acc<8>(acc3);
-        warp_gemm<2, KD, false, false>(acc0, sK, KP, 0, sK, KP, 0, lane);
-        warp_gemm<4, KD, false, false>(acc1, sK, KP, 16, sK, KP, 0, lane);
-        warp_gemm<6, KD, false, false>(acc2, sK, KP, 32, sK, KP, 0, lane);
-        warp_gemm<8, KD, false, false>(acc3, sK, KP, 48, sK, KP, 0, lane);
-        const float bi[8] = {sBeta[gq], sBeta[gq + 8], sBeta[16 + gq], sBeta[24 + gq],
-                             sBeta[32 + gq], sBeta[40 + gq], sBeta[48 + gq], sBeta[56 + gq]};
-        __syncwarp();
-#define LAMPA_PUT_A0(ACC, NT, M0)                                                              \
-        _Pragma("unroll") for (int nt = 0; nt < NT; ++nt) {                                    \
-            _Pragma("unroll") for (int hh = 0; hh < 2; ++hh) {                                 \
-                const int i = M0 + gq + hh * 8, j = nt * 8 + 2 * tq;                           \
-                const float bb = bi[M0 / 8 + hh];                                              \
-                *reinterpret_cast<float2*>(sA + i * PA + j) =                                  \
-                    make_float2(i > j ? bb * ACC[nt][2 * hh] : 0.f, i > j + 1 ? bb * ACC[nt][2 * hh + 1] : 0.f); \
-            }                                                                                  \
-        }
-        LAMPA_PUT_A0(acc0, 2, 0)
-        LAMPA_PUT_A0(acc1, 4, 16)
-        LAMPA_PUT_A0(acc2, 6, 32)
-        LAMPA_PUT_A0(acc3, 8, 48)
-#undef LAMPA_PUT_A0
-        // blocks above the diagonal stay zero in X
-#pragma unroll
-        for (int bi2 = 0; bi2 < 3; ++bi2)
-#pragma unroll
-            for (int bj = bi2 + 1; bj < 4; ++bj)
-#pragma unroll
-                for (int q = 0; q < 2; ++q) {
-                    const int e = lane + 32 * q;                  // 64 float4 per 16 x 16 block
-                    *reinterpret_cast<float4*>(sA + (16 * bi2 + (e >> 2)) * PA + 16 * bj + (e & 3) * 4) =
-                        make_float4(0.f, 0.f, 0.f, 0.f);
-                }
-    }
-    __syncwarp();
-    // ---- diagonal blocks: X_dd = (I + A_dd)^-1, lane = (block of the pair, column) ----
-#pragma unroll
-    for (int pass = 0; pass < 2; ++pass) {
-        const int base = 16 * (2 * pass + (lane >> 4)), cc = lane & 15;
-        float x[16];
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-            float sum = (i == cc) ? 1.f : 0.f;
-#pragma unroll
-            for (int q = 0; q < (i + 3) / 4; ++q) {
-                const float4 av = *reinterpret_cast<const float4*>(sA + (base + i) * PA + base + 4 * q);
-                const float ae[4] = {av.x, av.y, av.z, av.w};
-#pragma unroll
-                for (int e = 0; e < 4; ++e)
-                    if (4 * q + e < i) sum -= ae[e] * x[4 * q + e];
-            }
-            x[i] = sum;
-        }
-        __syncwarp();
-#pragma unroll
-        for (int i = 0; i < 16; ++i) sA[(base + i) * PA + base + cc] = x[i];
-    }
-    __syncwarp();
-    // ---- inside each 32 x 32 half: X_ba = -(X_bb A_ba) X_aa with a = 2p, b = 2p + 1 ----
-#pragma unroll
-    for (int p = 0; p < 2; ++p) {
-        const int ra = 32 * p, rb = 32 * p + 16;
-        float q0[2][4];
-        zero_acc<2>(q0);
-        {
-            uint32_t ah[4], al[4];
-            load_a_f32(sA, PA, rb, rb, lane, ah, al);
-#pragma unroll
-            for (int nt = 0; nt < 2; ++nt) {
-                uint32_t bh[2], bl[2];
-                load_b_f32(sA, PA, rb, ra + 8 * nt, lane, bh, bl);
-                mma3(q0[nt], ah, al, bh, bl);
-            }
-        }
-        float xo[2][4];
-        zero_acc<2>(xo);
-        {
-            uint32_t ah[4], al[4];
-            acc_to_a(q0[0], q0[1], ah, al);
-#pragma unroll
-            for (int nt = 0; nt < 2; ++nt) {
-                uint32_t bh[2], bl[2];
-                load_b_f32(sA, PA, ra, ra + 8 * nt, lane, bh, bl);
-                mma3(xo[nt], ah, al, bh, bl);
-            }
-        }
-        __syncwarp();
-#pragma unroll
-        for (int nt = 0; nt < 2; ++nt) store_neg_tile(sA, PA, rb, ra + 8 * nt, lane, xo[nt]);
-    }
-    __syncwarp();
-    // ---- the 32 x 32 corner: X_ba = -(X_b A_ba) X_a with a = rows/cols 0..31, b = 32..63 ----
-    {
-        float qc[2][4][4];
-        zero_acc<4>(qc[0]); zero_acc<4>(qc[1]);
-#pragma unroll
-        for (int mt = 0; mt < 2; ++mt)
-#pragma unroll
-            for (int ks = 0; ks <= mt; ++ks) {                    // X_b is block lower-triangular
-                uint32_t ah[4], al[4];
-                load_a_f32(sA, PA, 32 + 16 * mt, 32 + 16 * ks, lane, ah, al);
-#pragma unroll
-                for (int nt = 0; nt < 4; ++nt) {
-                    uint32_t bh[2], bl[2];
-                    load_b_f32(sA, PA, 32 + 16 * ks, 8 * nt, lane, bh, bl);
-                    mma3(qc[mt][nt], ah, al, bh, bl);
-                }
-            }
-        float xc[2][4][4];
-        zero_acc<4>(xc[0]); zero_acc<4>(xc[1]);
-#pragma unroll
-        for (int mt = 0; mt < 2; ++mt)
-#pragma unroll
-            for (int ks = 0; ks < 2; ++ks) {
-                uint32_t ah[4], al[4];
-                acc_to_a(qc[mt][2 * ks], qc[mt][2 * ks + 1], ah, al);
-#pragma unroll
-                for (int nt = 0; nt < 2 + 2 * ks; ++nt) {          // X_a rows 0..15 are [X_00 | 0]
-                    uint32_t bh[2], bl[2];
-                    load_b_f32(sA, PA, 16 * ks, 8 * nt, lane, bh, bl);
-                    mma3(xc[mt][nt], ah, al, bh, bl);
-                }
-            }
-        __syncwarp();
-#pragma unroll
-        for (int mt = 0; mt < 2; ++mt)
-#pragma unroll
-            for (int nt = 0; nt < 4; ++nt) store_neg_tile(sA, PA, 32 + 16 * mt, 8 * nt, lane, xc[mt][nt]);
-    }
-    __syncwarp();
-    // ---- Awb = X diag(beta), bf16, 16 bytes per lane and store ----
-    __nv_bfloat16* gA = reinterpret_cast<__nv_bfloat16*>(a.rec + ((size_t)c * H + h) * a.rec_bytes + R::OL_OFF);
-    {
-        const int ch = lane & 7;
-        float bj[8];
-#pragma unroll
-        for (int e = 0; e < 8; ++e) bj[e] = sBeta[8 * ch + e];
-#pragma unroll
-        for (int it = 0; it < 16; ++it) {
-            const int row = it * 4 + (lane >> 3);
-            const float4 v0 = *reinterpret_cast<const float4*>(sA + row * PA + 8 * ch);
-            const float4 v1 = *reinterpret_cast<const float4*>(sA + row * PA + 8 * ch + 4);
-            uint4 u;
-            u.x = pack_bf16x2(v0.x * bj[0], v0.y * bj[1]);
-            u.y = pack_bf16x2(v0.z * bj[2], v0.w * bj[3]);
-            u.z = pack_bf16x2(v1.x * bj[4], v1.y * bj[5]);
-            u.w = pack_bf16x2(v1.z * bj[6], v1.w * bj[7]);
-            *reinterpret_cast<uint4*>(gA + row * CP + 8 * ch) = u;
-        }
-    }
 }
 
 // With beta folded into the columns of the inverse (Awb = (I + A0)^-1 diag(beta), Aub = Awb .* E):
@@ -449,15 +233,6 @@ __global__ void __launch_bounds__(128, 4) gdn_prep_kernel(GdnArgs a) {
             issue_half_row<KD>(a.q, (tok * H + h) * KD + half * (KD / 2), valid, rq);
             issue_half_row<KD>(a.k, (tok * H + h) * KD + half * (KD / 2), valid, rk);
             issue_half_row<VD>(a.v, (tok * H + h) * VD + half * (VD / 2), valid, rv);
-        }
-        uint4 raw_aw[5];   // Awb tile written by the solve kernel into the record's O_local slot
-        {
-            const uint4* ga = reinterpret_cast<const uint4*>(a.rec + ((size_t)c * H + h) * a.rec_bytes + R::OL_OFF);
-#pragma unroll
-            for (int i = 0; i < 5; ++i) {
-                const int idx = tid + 128 * i;
-                raw_aw[i] = (idx < CHUNK * CP / 8) ? __ldg(ga + idx) : make_uint4(0u, 0u, 0u, 0u);
-            }
         }
         float gv = 0.f, bv = 0.f;
         if (tid < len) {   // len <= 64: threads 0..len-1 carry g and beta of token tid
@@ -522,11 +297,6 @@ __global__ void __launch_bounds__(128, 4) gdn_prep_kernel(GdnArgs a) {
         if (two_byte) convert_half_row<VD>(rv, a.qkv_dt, y);
         else load_half_row<VD>(a.v, a.qkv_dt, (tok * H + h) * VD + half * (VD / 2), valid, y);
         store_half_row_bf16<VD / 2>(sV + r * VP + half * (VD / 2), y);
-#pragma unroll
-        for (int i = 0; i < 5; ++i) {
-            const int idx = tid + 128 * i;
-            if (idx < CHUNK * CP / 8) reinterpret_cast<uint4*>(sAw)[idx] = raw_aw[i];
-        }
 
         if (tid < CHUNK) {
             float cs = gv;
@@ -559,6 +329,133 @@ __global__ void __launch_bounds__(128, 4) gdn_prep_kernel(GdnArgs a) {
     }
 
     const int m0 = warp * 16;
+    // ---- stage 1: Awb = (I + A0)^-1 diag(beta), A0 = tril(diag(beta) K K^T, -1) ---------------------
+    // Blockwise, as the reference's solve_tril does (models/hattention/solve_tril.py:221-276): warp w
+    // forms rows 16w.. of A0 on the tensor cores and inverts its own 16x16 diagonal block by fp32
+    // forward substitution (lane = column); the off-diagonal blocks follow as X_ba = -(X_bb A_ba) X_aa,
+    // first inside the two 32x32 halves, then for the 32x32 corner, in place in one fp32 [64][68] tile
+    // that lies over the Awb and U^ buffers (both written later).  These products keep fp32 accuracy
+    // by splitting each operand into bf16 hi + lo and issuing hi*hi + lo*hi + hi*lo (the reference
+    // asks for IEEE fp32 dots there).
+    {
+        constexpr int PA = S::PA;
+        float* sA = reinterpret_cast<float*>(smem + S::AW);
+        {
+            float acc[8][4];
+            zero_acc<8>(acc);
+            warp_gemm<8, KD, false, false>(acc, sK, KP, m0, sK, KP, 0, lane, KD, m0 + 16);
+#pragma unroll
+            for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+                for (int hh = 0; hh < 2; ++hh) {
+                    const int i = m0 + gq + hh * 8, j = nt * 8 + 2 * tq;
+                    const float bb = sBeta[i];
+                    *reinterpret_cast<float2*>(sA + i * PA + j) =
+                        make_float2(i > j ? bb * acc[nt][2 * hh] : 0.f, i > j + 1 ? bb * acc[nt][2 * hh + 1] : 0.f);
+                }
+        }
+        __syncwarp();
+        {
+            const int cc = lane & 15;
+            float x[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                float sum = (i == cc) ? 1.f : 0.f;
+#pragma unroll
+                for (int q = 0; q < (i + 3) / 4; ++q) {
+                    const float4 av = *reinterpret_cast<const float4*>(sA + (m0 + i) * PA + m0 + 4 * q);
+                    const float ae[4] = {av.x, av.y, av.z, av.w};
+#pragma unroll
+                    for (int e = 0; e < 4; ++e)
+                        if (4 * q + e < i) sum -= ae[e] * x[4 * q + e];
+                }
+                x[i] = sum;
+            }
+            __syncwarp();
+            if (lane < 16) {
+#pragma unroll
+                for (int i = 0; i < 16; ++i) sA[(m0 + i) * PA + m0 + cc] = x[i];
+            }
+        }
+        __syncthreads();
+        if (warp & 1) {   // X_ba of the pair (a, b) = (warp - 1, warp)
+            const int ra = m0 - 16, rb = m0;
+            float q0[2][4], xo[2][4];
+            zero_acc<2>(q0);
+            zero_acc<2>(xo);
+            uint32_t ah[4], al[4];
+            load_a_f32(sA, PA, rb, rb, lane, ah, al);
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt) {
+                uint32_t bh[2], bl[2];
+                load_b_f32(sA, PA, rb, ra + 8 * nt, lane, bh, bl);
+                mma3(q0[nt], ah, al, bh, bl);
+            }
+            acc_to_a(q0[0], q0[1], ah, al);
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt) {
+                uint32_t bh[2], bl[2];
+                load_b_f32(sA, PA, ra, ra + 8 * nt, lane, bh, bl);
+                mma3(xo[nt], ah, al, bh, bl);
+            }
+            __syncwarp();
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt) store_neg_tile(sA, PA, rb, ra + 8 * nt, lane, xo[nt]);
+        }
+        __syncthreads();
+        {   // the 32x32 corner: warp = (row tile mt, column half nh)
+            const int mt = warp >> 1, nh = warp & 1;
+            float qc[4][4], xc[2][4];
+            zero_acc<4>(qc);
+            zero_acc<2>(xc);
+#pragma unroll
+            for (int ks = 0; ks < 2; ++ks)
+                if (ks <= mt) {                                   // X_b is block lower-triangular
+                    uint32_t ah[4], al[4];
+                    load_a_f32(sA, PA, 32 + 16 * mt, 32 + 16 * ks, lane, ah, al);
+#pragma unroll
+                    for (int nt = 0; nt < 4; ++nt) {
+                        uint32_t bh[2], bl[2];
+                        load_b_f32(sA, PA, 32 + 16 * ks, 8 * nt, lane, bh, bl);
+                        mma3(qc[nt], ah, al, bh, bl);
+                    }
+                }
+#pragma unroll
+            for (int ks = 0; ks < 2; ++ks) {
+                uint32_t ah[4], al[4];
+                acc_to_a(qc[2 * ks], qc[2 * ks + 1], ah, al);
+#pragma unroll
+                for (int n = 0; n < 2; ++n) {
+                    const int nt = 2 * nh + n;
+                    if (nt < 2 + 2 * ks) {                        // X_a rows 0..15 are [X_00 | 0]
+                        uint32_t bh[2], bl[2];
+                        load_b_f32(sA, PA, 16 * ks, 8 * nt, lane, bh, bl);
+                        mma3(xc[n], ah, al, bh, bl);
+                    }
+                }
+            }
+            __syncthreads();                                      // every warp has read A_ba
+#pragma unroll
+            for (int n = 0; n < 2; ++n) store_neg_tile(sA, PA, 32 + 16 * mt, 8 * (2 * nh + n), lane, xc[n]);
+        }
+        __syncthreads();
+        {   // Awb = X diag(beta) as bf16, written over the front of the fp32 tile
+            const int r = tid >> 1, half = tid & 1;
+            uint32_t w[16];
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+                const float4 v = *reinterpret_cast<const float4*>(sA + r * PA + half * 32 + 4 * q);
+                const float4 b = *reinterpret_cast<const float4*>(sBeta + half * 32 + 4 * q);
+                w[2 * q] = pack_bf16x2(v.x * b.x, v.y * b.y);
+                w[2 * q + 1] = pack_bf16x2(v.z * b.z, v.w * b.w);
+            }
+            __syncthreads();
+#pragma unroll
+            for (int q = 0; q < 4; ++q)
+                reinterpret_cast<uint4*>(sAw + r * CP + half * 32)[q] = make_uint4(w[4 * q], w[4 * q + 1], w[4 * q + 2], w[4 * q + 3]);
+        }
+        __syncthreads();
+    }
     PREP_TICK(1);
     const float osc = HIER ? 1.f : a.scale;
     // ---- per-warp part (rows m0..m0+15 of everything; nothing leaves the warp) --------------------
@@ -737,11 +634,6 @@ int launch_prep(const GdnArgs& a, bool hier, cudaStream_t st) {
     const int smem = S::bytes(hier ? a.L : 0);
     dim3 grid(a.H, a.nc_max);
     cudaError_t e;
-    {
-        ProfScope prof_s("gdn_solve", st);
-        gdn_solve_kernel<KD, VD><<<grid, 32, SolveSmem<KD>::BYTES, st>>>(a);
-        if (cudaGetLastError() != cudaSuccess) return LAMPA_ERR_CUDA;
-    }
     ProfScope prof(hier ? "gdn_prep_hier" : "gdn_prep_plain", st);
     if (hier) {
         e = cudaFuncSetAttribute(gdn_prep_kernel<KD, VD, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
