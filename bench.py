@@ -300,7 +300,6 @@ def run_ours(args):
             "gdn_prep_hier": ("tensor", H * n_chunks * (7 * 524288 + 2 * 174763)),
             "gdn_out_hier": ("tensor", H * n_chunks * (n_lev * 2.5 * 524288)),
             "gdn_out_hier_umma": ("tensor", H * n_chunks * (n_lev * 2.5 * 524288)),
-            "gdn_solve": ("hbm", H * n_chunks * (64 * 64 * 2 + 64 * 72 * 2 + 64 * 4)),   # reads k, beta; writes Awb
             "gdn_compose": ("tensor", H * n_chunks * 2 * 2 * 64 ** 3),
             "gdn_level_hier": ("tensor", H * (n_chunks // 32) * 5 * 2 * 64 ** 3),
             "lsh_hash": ("hbm", N_HITS * 120),
@@ -310,8 +309,8 @@ def run_ours(args):
         }
         # DRAM bytes (read + write) per launch on the default workload, from the committed ncu capture
         # profiles/kernels_bench_60k_hier.md
-        ncu_traffic = {"gdn_prep_hier": 639.4e6, "gdn_out_hier": 435.2e6, "gdn_out_hier_umma": 435.2e6, "gdn_solve": 104.6e6, "gdn_compose": 145.4e6,
-                       "gdn_level_hier": 6.6e6, "segsort": 5.8e6, "lsh_hash": 5.8e6, "permute_rows": 6.3e6}
+        ncu_traffic = {"gdn_prep_hier": 494.0e6, "gdn_out_hier_umma": 413.6e6, "gdn_compose": 192.7e6,
+                       "gdn_level_hier": 6.6e6, "segsort": 5.8e6, "lsh_hash": 5.8e6, "permute_rows": 43.3e6}
         bound, units = alg.get(dom, ("hbm", 0))
         dur_s = per_kernel[dom]["ms_per_launch"] * 1e-3
         if bound == "tensor":
