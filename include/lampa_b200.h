@@ -257,6 +257,54 @@ int lampa_geo_keys(const float* proj, const float* reg_eta, const float* reg_phi
                    const float* regions_phi, const float* hash_shift, int32_t rows, int64_t n,
                    int64_t raw_size, float* out, void* stream);
 /*
+ * Short causal depthwise convolution with optional SiLU on a projection, token-major.
+ * Replaces: ShortConvolution.forward's prefill path -> causal_conv1d_fwd (+ the final-state copies)
+ * (models/hattention/short_convolution.py:595-680, 39-112, 256-291, 484-525).
+ *   x, y, residual (or NULL): [B, T, D] of `dtype`; weight [D, W] and bias [D] (or NULL) of `w_dtype`;
+ *   W <= 8; D a multiple of 8 (4 for fp32); cu_seqlens int64 [nseq+1] on the device with B == 1, or
+ *   NULL / nseq = 0;  y[t, d] = act(bias[d] + sum_i weight[d, i] x[t - (W-1) + i, d]) + residual, taps
+ *   before the start of the token's sequence read as zero, accumulated in fp32 oldest tap first.
+ *   final_state (or NULL): [N, D, W] of `dtype`, slot w = x[eos - W + w, d]; slots before the
+ *   sequence start are zeroed when zero_fill != 0 (the reference's packed path) and left as they
+ *   are otherwise (its in-place update of an existing cache).
+ */
+int lampa_short_conv_fwd(const void* x, const void* weight, const void* bias, const void* residual,
+                         const int64_t* cu_seqlens, int32_t nseq, int64_t B, int64_t T, int32_t D,
+                         int32_t W, int32_t dtype, int32_t w_dtype, int32_t silu, void* y,
+                         void* final_state, int32_t zero_fill, void* stream);
+/*
+ * Decode step of the same convolution: cache [N, D, W] moves one slot left and takes x [N, D] in
+ * its last slot (in place); y = act(bias + sum_w cache[n, d, w] weight[d, w]) + residual.
+ * Replaces: ShortConvolution.step -> causal_conv1d_update (short_convolution.py:682-717, 203-253, 357-389).
+ */
+int lampa_short_conv_step(const void* x, void* cache, const void* weight, const void* bias,
+                          const void* residual, int64_t N, int32_t D, int32_t W, int32_t dtype,
+                          int32_t w_dtype, int32_t silu, void* y, void* stream);
+/*
+ * Gate inputs of the hierarchical gated-delta layer from its projections:
+ *   g [n_tok, H] fp32 = -exp(A_log[h]) softplus(a + dt_bias[h]);  beta [n_tok, H] = sigmoid(b);
+ *   lam [n_tok, H, L] = softplus(Lw[h,l] dl) (lambda_mode 0, "positive"), exp(-exp(Lw) softplus(dl))
+ *   (1, "bounded") or Lw dl (2, default); each times mask[n_tok] (fp32 0/1) when mask is given.
+ *   a, b [n_tok, H] and dl [n_tok, H, L] of `in_dtype`; A_log, dt_bias [H], Lw [H, L] fp32.
+ *   Any of g / beta / lam may be NULL to skip it.
+ * Replaces: models/hattention/modeling_h_gated_deltanet.py:429-450 and compute_lambda (151-166).
+ */
+int lampa_gate_inputs(const void* a, const void* b, const void* dl, const float* A_log,
+                      const float* dt_bias, const float* Lw, const float* mask, int64_t n_tok,
+                      int32_t H, int32_t L, int32_t in_dtype, int32_t beta_dtype, int32_t lam_dtype,
+                      int32_t lambda_mode, float* g, void* beta, void* lam, void* stream);
+/*
+ * Gated RMS norm over rows of D (the mixer's output norm, one row per token and head):
+ *   y = x / sqrt(mean(x^2) + eps) * weight * g * sigmoid(g)     (sigmoid_only: ... * sigmoid(g))
+ *   x, g, y [rows, D] of `dtype`, weight [D] of `w_dtype` or NULL; D a multiple of 8 (4 for fp32),
+ *   at most 1024 (512 for fp32).
+ * Replaces: FusedRMSNormGated.forward -> rms_norm_gated -> layer_norm_gated_fwd_kernel
+ * (models/hattention/fused_norm.py:1003-1064, 858-880, 40-112) without residual / prenorm.
+ */
+int lampa_rmsnorm_gate(const void* x, const void* g, const void* weight, int64_t rows, int32_t D,
+                       int32_t dtype, int32_t w_dtype, float eps, int32_t sigmoid_only, void* y,
+                       void* stream);
+/*
  * Per-kernel timing for benchmarks (no counterpart in the reference, which has no timing code).
  * lampa_profile_enable(1) makes every later launch of this library record a pair of CUDA events
  * on its stream; lampa_profile_enable(0) stops and clears.  lampa_profile_read synchronises on

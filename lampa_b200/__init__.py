@@ -6,6 +6,8 @@ from .gated_delta import (  # noqa: F401
     hattention_prefill, hattention_step, num_levels_required)
 from .geo import (  # noqa: F401
     get_geo_shift, get_regions, hept_positions, pad_to_multiple, quantile_partition, region_inputs, row_range)
+from .layer import (  # noqa: F401
+    FusedRMSNormGated, ShortConvolution, compute_lambda, gate_inputs, rms_norm_gated)
 from .lsh import (  # noqa: F401
     E2LSH, LSHOrdering, batched_index_select, invert_permutation, lsh_bucket_sort, lsh_hash, lsh_mapping,
     permute_rows, segmented_sort, sort_to_buckets, unsort_from_buckets)
@@ -15,5 +17,6 @@ __all__ = [
     "hattention_kernel", "num_levels_required", "E2LSH", "LSHOrdering", "batched_index_select",
     "invert_permutation", "lsh_bucket_sort", "lsh_hash", "lsh_mapping", "permute_rows", "segmented_sort",
     "sort_to_buckets", "unsort_from_buckets", "get_geo_shift", "get_regions", "hept_positions", "pad_to_multiple",
-    "quantile_partition", "region_inputs", "row_range",
+    "quantile_partition", "region_inputs", "row_range", "FusedRMSNormGated", "ShortConvolution", "compute_lambda",
+    "gate_inputs", "rms_norm_gated",
 ]

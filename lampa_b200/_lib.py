@@ -37,6 +37,7 @@ _lib: Optional[ctypes.CDLL] = None
 EXPORTS = ["lampa_version", "lampa_error_string", "lampa_gdn_workspace_bytes", "lampa_gdn_workspace_layout",
            "lampa_gdn_fwd", "lampa_hgdn_fwd", "lampa_hgdn_final_state", "lampa_hgdn_step", "lampa_lsh_hash", "lampa_segsort_workspace_bytes",
            "lampa_segsort_stable", "lampa_permute_rows", "lampa_invert_perm", "lampa_segsort_stable_static",
+           "lampa_short_conv_fwd", "lampa_short_conv_step", "lampa_gate_inputs", "lampa_rmsnorm_gate",
            "lampa_row_range", "lampa_quantile_regions", "lampa_geo_keys",
            "lampa_profile_enable",
            "lampa_profile_read"]
@@ -68,6 +69,10 @@ def lib() -> ctypes.CDLL:
         L.lampa_row_range.argtypes = [vp, vp, i32, i64, vp, vp, vp, vp]
         L.lampa_quantile_regions.argtypes = [vp, vp, i32, i64, vp, vp]
         L.lampa_geo_keys.argtypes = [vp] * 8 + [i32, i64, i64, vp, vp]
+        L.lampa_short_conv_fwd.argtypes = [vp, vp, vp, vp, vp, i32, i64, i64, i32, i32, i32, i32, i32, vp, vp, i32, vp]
+        L.lampa_short_conv_step.argtypes = [vp, vp, vp, vp, vp, i64, i32, i32, i32, i32, i32, vp, vp]
+        L.lampa_gate_inputs.argtypes = [vp] * 7 + [i64, i32, i32, i32, i32, i32, i32, vp, vp, vp, vp]
+        L.lampa_rmsnorm_gate.argtypes = [vp, vp, vp, i64, i32, i32, i32, ctypes.c_float, i32, vp, vp]
         L.lampa_profile_enable.argtypes = [ctypes.c_int]
         L.lampa_profile_read.argtypes = [ctypes.c_char_p, sz, ctypes.POINTER(ctypes.c_float),
                                          ctypes.POINTER(i32), i32, ctypes.POINTER(i32)]

@@ -245,3 +245,95 @@ def e2lsh_proj(vecs, alpha) -> np.ndarray:
             acc = (acc + (vecs[h, :, d:d + 1] * alpha[h, d][None, :]).astype(np.float32)).astype(np.float32)
         out[:, h, :] = acc.T
     return out
+
+
+# ---- producers / consumers of the op inside one layer (numpy fp32) ------------------------------
+
+def _softplus(x):
+    x = np.asarray(x, np.float32)
+    return np.where(x > 20, x, np.log1p(np.exp(np.minimum(x, 20)))).astype(np.float32)
+
+
+def _sigmoid(x):
+    return (1.0 / (1.0 + np.exp(-np.asarray(x, np.float32)))).astype(np.float32)
+
+
+def gate_inputs(a, b, dl, A_log, dt_bias, Lw, mode="positive"):
+    """g, beta, lambda of the hierarchical layer (models/hattention/modeling_h_gated_deltanet.py:
+    429-437, compute_lambda 151-166).  a, b [..., H]; dl [..., H, L]."""
+    g = (-np.exp(np.asarray(A_log, np.float32)) * _softplus(np.asarray(a, np.float32) + np.asarray(dt_bias, np.float32))).astype(np.float32)
+    beta = _sigmoid(b)
+    Lw = np.asarray(Lw, np.float32)
+    dl = np.asarray(dl, np.float32)
+    if mode == "positive":
+        lam = _softplus(Lw * dl)
+    elif mode == "bounded":
+        lam = np.exp(-np.exp(Lw) * _softplus(dl)).astype(np.float32)
+    else:
+        lam = (Lw * dl).astype(np.float32)
+    return g, beta, lam
+
+
+def short_conv(x, w, bias=None, residual=None, cu=None, silu=True):
+    """Causal depthwise convolution of ShortConvolution (models/hattention/short_convolution.py:
+    39-112): x [B, T, D], w [D, W]; y[t] = act(bias + sum_i w[:, i] x[t - (W-1) + i]) + residual,
+    taps before the sequence start are zero.  cu: sequence offsets over the flattened tokens (B = 1)."""
+    x = np.asarray(x, np.float32)
+    w = np.asarray(w, np.float32)
+    B, T, D = x.shape
+    W = w.shape[1]
+    y = np.zeros_like(x)
+    bounds = [(bi, 0, T) for bi in range(B)] if cu is None else [(0, int(s), int(e)) for s, e in zip(cu[:-1], cu[1:])]
+    for bi, s, e in bounds:
+        seg = x[bi, s:e]
+        acc = np.zeros_like(seg)
+        for i in range(W):
+            sh = W - 1 - i
+            if sh < seg.shape[0]:
+                acc[sh:] += seg[:seg.shape[0] - sh] * w[:, i]
+        y[bi, s:e] = acc
+    if bias is not None:
+        y = y + np.asarray(bias, np.float32)
+    if silu:
+        y = y * _sigmoid(y)
+    if residual is not None:
+        y = y + np.asarray(residual, np.float32)
+    return y.astype(np.float32)
+
+
+def short_conv_state(x, W, cu=None):
+    """Last W tokens of each sequence as [N, D, W], zero where the sequence is shorter
+    (short_convolution.py:484-502, 617-626)."""
+    x = np.asarray(x, np.float32)
+    B, T, D = x.shape
+    bounds = [(bi, 0, T) for bi in range(B)] if cu is None else [(0, int(s), int(e)) for s, e in zip(cu[:-1], cu[1:])]
+    out = np.zeros((len(bounds), D, W), np.float32)
+    for n, (bi, s, e) in enumerate(bounds):
+        m = min(W, e - s)
+        if m > 0:
+            out[n, :, W - m:] = x[bi, e - m:e].T
+    return out
+
+
+def short_conv_step(x, cache, w, bias=None, silu=True):
+    """Decode step (short_convolution.py:203-253): returns (y [N, D], new cache [N, D, W])."""
+    cache = np.roll(np.asarray(cache, np.float32), -1, axis=-1)
+    cache[:, :, -1] = np.asarray(x, np.float32)
+    y = (cache * np.asarray(w, np.float32)).sum(-1)
+    if bias is not None:
+        y = y + np.asarray(bias, np.float32)
+    if silu:
+        y = y * _sigmoid(y)
+    return y.astype(np.float32), cache
+
+
+def rmsnorm_gate(x, g, w=None, eps=1e-5, sigmoid_only=False):
+    """Gated RMS norm of the layer output (models/hattention/fused_norm.py:40-112)."""
+    x = np.asarray(x, np.float32)
+    g = np.asarray(g, np.float32)
+    rstd = 1.0 / np.sqrt((x * x).mean(-1, keepdims=True) + np.float32(eps))
+    y = x * rstd
+    if w is not None:
+        y = y * np.asarray(w, np.float32)
+    y = y * _sigmoid(g) if sigmoid_only else y * g * _sigmoid(g)
+    return y.astype(np.float32)

@@ -11,7 +11,7 @@ models/baselines/hmamba.py::LSHOrdering / E2LSH / lsh_mapping,
 models/model_utils/hash_utils.py::invert_permutation / batched_index_select,
 models/attention/hept.py::sort_to_buckets / unsort_from_buckets / get_geo_shift,
 models/model_utils/hash_utils.py::pad_to_multiple / get_regions / quantile_partition /
-E2LSH / lsh_mapping) on seeded
+E2LSH / lsh_mapping, and the layer statements listed in gen_layer) on seeded
 inputs and stores inputs + outputs as small .npz files.  Nothing from the
 reference is copied; only numbers it produced are stored.
 """
@@ -123,15 +123,86 @@ def gen_geo(ref: str):
     print("geo ok", tuple(reg_eta.shape), tuple(q_pos.shape), float(hs.max()))
 
 
+def gen_layer(ref: str):
+    """Producers / consumers of the op inside one HGatedDeltaNet layer, from the reference's own
+    pure-PyTorch statements: compute_lambda (models/hattention/modeling_h_gated_deltanet.py:151-166),
+    the g / beta expressions of HGatedDeltaNet.forward (429-430, restated here since they are
+    inline), ShortConvolution's parameters and its documented equivalent
+    `_conv_forward(x, weight, bias)[..., :T]` + SiLU (models/hattention/short_convolution.py:528-573,
+    650-654), the cache statements (617-626, 700-703), and rms_norm_ref followed by the swish gate of
+    the fused kernel (models/hattention/fused_norm.py:1306-1327, 99-107)."""
+    import warnings
+    from typing import Optional, Tuple
+    import torch.nn.functional as F
+    einops = __import__("einops")
+    hd = os.path.join(ref, "models", "hattention")
+    ml = load_defs(os.path.join(hd, "modeling_h_gated_deltanet.py"), {"compute_lambda"},
+                   extra={"warnings": warnings, "click": __import__("click"), "Optional": Optional})
+    sc = load_defs(os.path.join(hd, "short_convolution.py"), {"ShortConvolution"},
+                   extra={"warnings": warnings, "Optional": Optional, "Tuple": Tuple, "rearrange": einops.rearrange,
+                          "causal_conv1d_fn": None, "causal_conv1d_update_cuda": None})
+    fn = load_defs(os.path.join(hd, "fused_norm.py"), {"rms_norm_ref"}, extra={"F": F})
+    gen = torch.Generator().manual_seed(777)
+    B, T, H, Lv, D, W, Dv = 2, 70, 3, 9, 48, 4, 32
+    a = torch.randn(B, T, H, generator=gen)
+    b = torch.randn(B, T, H, generator=gen)
+    dl = torch.randn(B, T, H, Lv, generator=gen) * 2
+    A_log = torch.log(torch.empty(H).uniform_(0, 16, generator=gen))
+    dt_bias = torch.randn(H, generator=gen)
+    Lp = 1 + 0.3 * torch.randn(H, Lv, generator=gen)
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore")
+        lam = {m: ml["compute_lambda"](Lp[None, None], dl, m) for m in ("positive", "bounded", None)}
+    g = -A_log.float().exp() * F.softplus(a.float() + dt_bias)
+    beta = b.sigmoid()
+    torch.manual_seed(3)
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore")
+        conv = sc["ShortConvolution"](hidden_size=D, kernel_size=W, bias=True, activation="silu", use_fast_conv1d=False)
+    x = torch.randn(B, T, D, generator=gen)
+    res = torch.randn(B, T, D, generator=gen)
+    with torch.no_grad():
+        y = F.silu(conv._conv_forward(x.transpose(1, 2), conv.weight, conv.bias)[..., :T]).transpose(1, 2) + res
+        cache = torch.zeros(B, D, W)
+        cache[:, :, -min(W, T):].copy_(x[..., -min(W, T):, :].transpose(1, 2))
+        # packed: two sequences of 31 and 39 tokens taken from batch row 0
+        cu = [0, 31, 70]
+        yv = torch.cat([F.silu(conv._conv_forward(x[0:1, s:e].transpose(1, 2), conv.weight, conv.bias)[..., :e - s]).transpose(1, 2)
+                        for s, e in zip(cu[:-1], cu[1:])], 1)
+        # decode step on the cache: roll, insert, weighted sum
+        xs = torch.randn(B, 1, D, generator=gen)
+        c2 = cache.roll(shifts=-1, dims=-1)
+        c2[:, :, -1] = xs[:, 0]
+        ys = F.silu(torch.sum(c2 * conv.weight[:, 0], dim=-1) + conv.bias)[:, None]
+        xo = torch.randn(B, T, H, Dv, generator=gen)
+        go = torch.randn(B, T, H, Dv, generator=gen)
+        wn = 1 + 0.2 * torch.randn(Dv, generator=gen)
+        yn = fn["rms_norm_ref"](xo, wn, None, eps=1e-5, upcast=True)
+        yn = yn * go * torch.sigmoid(go)
+    np.savez_compressed(
+        os.path.join(HERE, "layer_ops.npz"),
+        a=a.numpy(), b=b.numpy(), dl=dl.numpy(), A_log=A_log.numpy(), dt_bias=dt_bias.numpy(), L=Lp.numpy(),
+        g=g.numpy(), beta=beta.numpy(), lam_positive=lam["positive"].numpy(), lam_bounded=lam["bounded"].numpy(),
+        lam_default=lam[None].numpy(),
+        conv_w=conv.weight.detach().numpy(), conv_b=conv.bias.detach().numpy(), x=x.numpy(), res=res.numpy(),
+        y=y.numpy(), cache=cache.numpy(), cu=np.array(cu, np.int64), y_packed=yv.numpy(),
+        x_step=xs.numpy(), y_step=ys.numpy(), cache_step=c2.numpy(),
+        norm_x=xo.numpy(), norm_g=go.numpy(), norm_w=wn.numpy(), norm_y=yn.numpy())
+    print("layer ok", tuple(y.shape), float(y.abs().max()), float(yn.abs().max()))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", default="/root/reference")
-    ap.add_argument("--only", default="", help="'geo': write only the region-shift fixture")
+    ap.add_argument("--only", default="", help="'geo' / 'layer': write only that fixture")
     args = ap.parse_args()
     ref = args.reference
     torch.set_num_threads(8)
-    gen_geo(ref)
-    if args.only == "geo":
+    if args.only in ("", "geo"):
+        gen_geo(ref)
+    if args.only in ("", "layer"):
+        gen_layer(ref)
+    if args.only:
         return
     base, recurrent = load_hattention(ref)
 

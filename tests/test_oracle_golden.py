@@ -143,3 +143,23 @@ def test_geo_shift_against_reference_fixture(golden_dir):
     differ = pos[:, :raw] != ref_pos[:, :raw]
     assert differ.mean() < 1e-3
     np.testing.assert_array_equal(np.take_along_axis(kq, pos, 1)[:, :raw], np.take_along_axis(kq, ref_pos, 1)[:, :raw])
+
+
+def test_layer_ops_against_reference_fixture(golden_dir):
+    """compute_lambda, the g/beta expressions, ShortConvolution and the gated RMS norm of the
+    reference (tests/golden/gen_golden.py::gen_layer)."""
+    z = np.load(os.path.join(golden_dir, "layer_ops.npz"))
+    for mode, key in (("positive", "lam_positive"), ("bounded", "lam_bounded"), (None, "lam_default")):
+        g, beta, lam = oracle.gate_inputs(z["a"], z["b"], z["dl"], z["A_log"], z["dt_bias"], z["L"], mode)
+        np.testing.assert_allclose(lam, z[key], rtol=2e-6, atol=1e-6)
+    np.testing.assert_allclose(g, z["g"], rtol=2e-6, atol=1e-6)
+    np.testing.assert_allclose(beta, z["beta"], rtol=2e-6, atol=1e-6)
+    w = z["conv_w"][:, 0]
+    np.testing.assert_allclose(oracle.short_conv(z["x"], w, z["conv_b"], z["res"]), z["y"], rtol=1e-5, atol=1e-5)
+    np.testing.assert_allclose(oracle.short_conv(z["x"][:1], w, z["conv_b"], cu=z["cu"]), z["y_packed"], rtol=1e-5, atol=1e-5)
+    np.testing.assert_array_equal(oracle.short_conv_state(z["x"], 4), z["cache"])
+    ys, cs = oracle.short_conv_step(z["x_step"][:, 0], z["cache"], w, z["conv_b"])
+    np.testing.assert_allclose(ys, z["y_step"][:, 0], rtol=1e-5, atol=1e-5)
+    np.testing.assert_array_equal(cs, z["cache_step"])
+    np.testing.assert_allclose(oracle.rmsnorm_gate(z["norm_x"], z["norm_g"], z["norm_w"], 1e-5), z["norm_y"],
+                               rtol=1e-5, atol=1e-5)
