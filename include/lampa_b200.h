@@ -261,7 +261,7 @@ int lampa_geo_keys(const float* proj, const float* reg_eta, const float* reg_phi
  * Replaces: ShortConvolution.forward's prefill path -> causal_conv1d_fwd (+ the final-state copies)
  * (models/hattention/short_convolution.py:595-680, 39-112, 256-291, 484-525).
  *   x, y, residual (or NULL): [B, T, D] of `dtype`; weight [D, W] and bias [D] (or NULL) of `w_dtype`;
- *   W <= 8; D a multiple of 8 (4 for fp32); cu_seqlens int64 [nseq+1] on the device with B == 1, or
+ *   W <= 8; D a multiple of 4; cu_seqlens int64 [nseq+1] on the device with B == 1, or
  *   NULL / nseq = 0;  y[t, d] = act(bias[d] + sum_i weight[d, i] x[t - (W-1) + i, d]) + residual, taps
  *   before the start of the token's sequence read as zero, accumulated in fp32 oldest tap first.
  *   final_state (or NULL): [N, D, W] of `dtype`, slot w = x[eos - W + w, d]; slots before the

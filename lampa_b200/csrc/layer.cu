@@ -55,12 +55,49 @@ __device__ __forceinline__ void store_vec(void* p, size_t elem, const float (&x)
     *reinterpret_cast<uint4*>((char*)p + elem * (DT == LAMPA_F32 ? 4 : 2)) = u;
 }
 
-__device__ __forceinline__ float sigmoidf_(float x) { return 1.f / (1.f + __expf(-x)); }
-__device__ __forceinline__ float softplusf_(float x) { return x > 20.f ? x : log1pf(__expf(x)); }   // torch's threshold
+__device__ __forceinline__ float sigmoidf_(float x) { return __fdividef(1.f, 1.f + __expf(-x)); }
+// log(1 + e^x) as max(x, 0) + log1p(e^-|x|); the log1p is the hardware log above 0.01 (absolute
+// error 2e-7) and its cubic Taylor polynomial below.  torch switches to x above 20, where the
+// two agree to fp32 rounding.
+__device__ __forceinline__ float softplusf_(float x) {
+    const float e = __expf(-fabsf(x));
+    const float l = e > 0.01f ? __logf(1.f + e) : e * (1.f - e * (0.5f - e * (1.f / 3.f)));
+    return fmaxf(x, 0.f) + l;
+}
+
+// Four channels of one token: 8 bytes of bf16 / fp16, 16 bytes of fp32.
+template <int DT> struct Raw4 { using T = uint2; };
+template <> struct Raw4<LAMPA_F32> { using T = uint4; };
+template <int DT>
+__device__ __forceinline__ typename Raw4<DT>::T ldg4(const void* p, size_t elem) {
+    return __ldg(reinterpret_cast<const typename Raw4<DT>::T*>((const char*)p + elem * (DT == LAMPA_F32 ? 4 : 2)));
+}
+__device__ __forceinline__ void unpack4(const uint4& u, float (&x)[4], int) {
+    x[0] = __uint_as_float(u.x); x[1] = __uint_as_float(u.y); x[2] = __uint_as_float(u.z); x[3] = __uint_as_float(u.w);
+}
+__device__ __forceinline__ void unpack4(const uint2& u, float (&x)[4], int dt) {
+    float2 a, b;
+    if (dt == LAMPA_BF16) { a = unpack_bf16x2(u.x); b = unpack_bf16x2(u.y); }
+    else { a = __half22float2(*reinterpret_cast<const __half2*>(&u.x)); b = __half22float2(*reinterpret_cast<const __half2*>(&u.y)); }
+    x[0] = a.x; x[1] = a.y; x[2] = b.x; x[3] = b.y;
+}
+template <int DT>
+__device__ __forceinline__ void store4(void* p, size_t elem, const float (&x)[4]) {
+    if (DT == LAMPA_F32) {
+        *reinterpret_cast<uint4*>((char*)p + elem * 4) =
+            make_uint4(__float_as_uint(x[0]), __float_as_uint(x[1]), __float_as_uint(x[2]), __float_as_uint(x[3]));
+    } else if (DT == LAMPA_BF16) {
+        *reinterpret_cast<uint2*>((char*)p + elem * 2) = make_uint2(pack_bf16x2(x[0], x[1]), pack_bf16x2(x[2], x[3]));
+    } else {
+        const __half2 h0 = __floats2half2_rn(x[0], x[1]), h1 = __floats2half2_rn(x[2], x[3]);
+        *reinterpret_cast<uint2*>((char*)p + elem * 2) =
+            make_uint2(*reinterpret_cast<const uint32_t*>(&h0), *reinterpret_cast<const uint32_t*>(&h1));
+    }
+}
 
 // -------------------------------------------------------------------------------------------------
 // y[t, d] = act(bias[d] + sum_i w[d, i] x[t - (W-1) + i, d]) (+ residual), taps before the start
-// of the token's sequence read as zero.  Thread = 16 bytes of channels x CONV_TOKENS consecutive
+// of the token's sequence read as zero.  Thread = 4 channels x CONV_TOKENS consecutive
 // tokens; the W-1 earlier rows are re-read once per run (from L2), everything else is read once.
 // -------------------------------------------------------------------------------------------------
 struct ConvArgs {
@@ -72,16 +109,17 @@ struct ConvArgs {
     int D, W, silu, w_dt;
 };
 
-template <int DT, int MW>   // MW: compile-time bound on the number of taps (sizes the register window)
+template <int DT, int MW, bool EXACT>   // MW: compile-time bound on the number of taps; EXACT: W == MW, known to the compiler
 __global__ void __launch_bounds__(128) short_conv_fwd_kernel(ConvArgs a) {
-    constexpr int NV = Vec16<DT>::N;
+    constexpr int NV = 4;
+    using RawT = typename Raw4<DT>::T;
     const int cg = blockIdx.y * blockDim.x + threadIdx.x;          // channel group
     if (cg * NV >= a.D) return;
     const int d0 = cg * NV;
     const int64_t t_begin = ((int64_t)blockIdx.x * blockDim.y + threadIdx.y) * CONV_TOKENS;
     if (t_begin >= a.n_tok) return;
     const int64_t t_end = min(t_begin + CONV_TOKENS, a.n_tok);
-    const int W = a.W;
+    const int W = EXACT ? MW : a.W;
 
     float wt[MW][NV], bs[NV];
 #pragma unroll
@@ -116,15 +154,14 @@ __global__ void __launch_bounds__(128) short_conv_fwd_kernel(ConvArgs a) {
     for (int i = 0; i < MW - 1; ++i)
         if (i < W - 1) {
             const int64_t tt = t_begin - (W - 1) + i;
-            if (tt >= bos) load_vec<DT>(a.x, (size_t)tt * a.D + d0, win[i]);
+            if (tt >= bos) unpack4(ldg4<DT>(a.x, (size_t)tt * a.D + d0), win[i], DT);
         }
     // all rows of the run are requested before the first one is used
-    uint4 raw[CONV_TOKENS];
+    RawT raw[CONV_TOKENS];
 #pragma unroll
     for (int i = 0; i < CONV_TOKENS; ++i) {
-        const int64_t t = t_begin + i;
-        raw[i] = t < t_end ? __ldg(reinterpret_cast<const uint4*>((const char*)a.x + ((size_t)t * a.D + d0) * (DT == LAMPA_F32 ? 4 : 2)))
-                           : make_uint4(0u, 0u, 0u, 0u);
+        const int64_t t = min(t_begin + i, t_end - 1);            // rows past the end re-read the last one, unused
+        raw[i] = ldg4<DT>(a.x, (size_t)t * a.D + d0);
     }
     // bit i of starts: token t_begin + i opens a sequence (its history is empty)
     uint32_t starts = 0;
@@ -152,7 +189,7 @@ __global__ void __launch_bounds__(128) short_conv_fwd_kernel(ConvArgs a) {
                 for (int j = 0; j < NV; ++j) win[i][j] = 0.f;
         }
         float cur[NV];
-        unpack_vec<DT>(raw[it], cur);
+        unpack4(raw[it], cur, DT);
         float acc[NV];
 #pragma unroll
         for (int j = 0; j < NV; ++j) acc[j] = 0.f;
@@ -177,11 +214,11 @@ __global__ void __launch_bounds__(128) short_conv_fwd_kernel(ConvArgs a) {
         }
         if (a.residual) {
             float r[NV];
-            load_vec<DT>(a.residual, (size_t)t * a.D + d0, r);
+            unpack4(ldg4<DT>(a.residual, (size_t)t * a.D + d0), r, DT);
 #pragma unroll
             for (int j = 0; j < NV; ++j) out[j] += r[j];
         }
-        store_vec<DT>(a.y, (size_t)t * a.D + d0, out);
+        store4<DT>(a.y, (size_t)t * a.D + d0, out);
         // slide: history slot i takes slot i + 1, the newest history slot takes the current token
 #pragma unroll
         for (int i = 0; i < MW - 2; ++i)
@@ -258,31 +295,71 @@ struct GateArgs {
     int64_t n_tok; int H, L, in_dt, beta_dt, lam_dt, mode;
 };
 
-__global__ void __launch_bounds__(256) gate_inputs_kernel(GateArgs p) {
-    const int64_t per_tok = (int64_t)p.H * (p.L + 1);
+__device__ __forceinline__ float lambda_of(float Lv, float dv, int mode) {
+    if (mode == 0) return softplusf_(Lv * dv);
+    if (mode == 1) return __expf(-__expf(Lv) * softplusf_(dv));
+    return Lv * dv;
+}
+
+// g and beta: one (token, head) per thread
+__global__ void __launch_bounds__(256) gate_gb_kernel(GateArgs p) {
     const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (idx >= p.n_tok * per_tok) return;
-    // the first n_tok * H threads produce g and beta, the rest one lambda each
-    const int64_t n_gb = p.n_tok * p.H;
-    if (idx < n_gb) {
-        const int h = (int)(idx % p.H);
-        const float m = p.mask ? p.mask[idx / p.H] : 1.f;
-        if (p.g) {
-            const float av = load_as_float(p.a, idx, p.in_dt);
-            p.g[idx] = -__expf(p.A_log[h]) * softplusf_(av + p.dt_bias[h]) * m;
+    if (idx >= p.n_tok * p.H) return;
+    const int h = (int)(idx % p.H);
+    const float m = p.mask ? p.mask[idx / p.H] : 1.f;
+    if (p.g) {
+        const float av = load_as_float(p.a, idx, p.in_dt);
+        p.g[idx] = -__expf(p.A_log[h]) * softplusf_(av + p.dt_bias[h]) * m;
+    }
+    if (p.beta) store_from_float(p.beta, idx, sigmoidf_(load_as_float(p.b, idx, p.in_dt)) * m, p.beta_dt);
+}
+
+// lambda: VEC consecutive (token, head, level) elements per thread, 16-byte loads when VEC == 8
+template <int VEC>
+__global__ void __launch_bounds__(256) gate_lambda_kernel(GateArgs p) {
+    const int64_t HL = (int64_t)p.H * p.L, total = p.n_tok * HL;
+    const int64_t j0 = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * VEC;
+    if (j0 >= total) return;
+    float dv[VEC];
+    if (VEC == 8) {
+        const uint4 u = __ldg(reinterpret_cast<const uint4*>((const uint16_t*)p.dl + j0));
+        const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            float2 f;
+            if (p.in_dt == LAMPA_BF16) f = unpack_bf16x2(w[q]);
+            else f = __half22float2(*reinterpret_cast<const __half2*>(&w[q]));
+            dv[2 * q] = f.x; dv[2 * q + 1] = f.y;
         }
-        if (p.beta) store_from_float(p.beta, idx, sigmoidf_(load_as_float(p.b, idx, p.in_dt)) * m, p.beta_dt);
-    } else if (p.lam) {
-        const int64_t j = idx - n_gb;
-        const int l = (int)(j % p.L);
-        const int h = (int)((j / p.L) % p.H);
-        const float m = p.mask ? p.mask[j / ((int64_t)p.L * p.H)] : 1.f;
-        const float dv = load_as_float(p.dl, j, p.in_dt), Lv = p.Lw[h * p.L + l];
-        float v;
-        if (p.mode == 0) v = softplusf_(Lv * dv);
-        else if (p.mode == 1) v = __expf(-__expf(Lv) * softplusf_(dv));
-        else v = Lv * dv;
-        store_from_float(p.lam, j, v * m, p.lam_dt);
+    } else {
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) dv[e] = j0 + e < total ? load_as_float(p.dl, j0 + e, p.in_dt) : 0.f;
+    }
+    int64_t tok = j0 / HL;
+    int r = (int)(j0 - tok * HL);                     // position inside the token's H x L block
+    float out[VEC];
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) {
+        const float m = p.mask ? p.mask[min(tok, p.n_tok - 1)] : 1.f;
+        out[e] = lambda_of(p.Lw[r], dv[e], p.mode) * m;
+        if (++r == HL) { r = 0; ++tok; }
+    }
+    if (VEC == 8 && p.lam_dt != LAMPA_F32) {
+        uint4 u;
+        if (p.lam_dt == LAMPA_BF16) {
+            u = make_uint4(pack_bf16x2(out[0], out[1]), pack_bf16x2(out[2], out[3]), pack_bf16x2(out[4], out[5]), pack_bf16x2(out[6], out[7]));
+        } else {
+            __half2 hh[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) hh[q] = __floats2half2_rn(out[2 * q], out[2 * q + 1]);
+            u = make_uint4(*reinterpret_cast<uint32_t*>(&hh[0]), *reinterpret_cast<uint32_t*>(&hh[1]),
+                           *reinterpret_cast<uint32_t*>(&hh[2]), *reinterpret_cast<uint32_t*>(&hh[3]));
+        }
+        *reinterpret_cast<uint4*>((uint16_t*)p.lam + j0) = u;
+    } else {
+#pragma unroll
+        for (int e = 0; e < VEC; ++e)
+            if (j0 + e < total) store_from_float(p.lam, j0 + e, out[e], p.lam_dt);
     }
 }
 
@@ -290,43 +367,71 @@ __global__ void __launch_bounds__(256) gate_inputs_kernel(GateArgs p) {
 // Gated RMS norm over rows of D: y = x rsqrt(mean(x^2) + eps) w * gate, gate = g sigmoid(g)
 // (swish / silu) or sigmoid(g).  One warp per row, 16 bytes per lane and step.
 // -------------------------------------------------------------------------------------------------
-template <int DT>
+// A row is spread over LPR = min(32, D/16 bytes) lanes (rounded up to a power of two), so a warp
+// holds 32/LPR rows at a time; VPL vectors per lane cover rows wider than 32 vectors.  Each lane
+// keeps RPI = 4/VPL rows in flight: all their x and g vectors are requested before the first use.
+template <int DT, int VPL>
 __global__ void __launch_bounds__(256)
-rmsnorm_gate_kernel(const void* x, const void* g, const void* w, int w_dt, int64_t rows, int D, float eps,
+rmsnorm_gate_kernel(const void* x, const void* g, const void* w, int w_dt, int64_t rows, int D, int lpr, float eps,
                     int sigmoid_only, void* y) {
     constexpr int NV = Vec16<DT>::N;
-    constexpr int MAXV = 4;                                // D <= 32 lanes * 4 * NV
-    const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    if (row >= rows) return;
+    constexpr int RPI = 4 / VPL;
+    constexpr int EB = DT == LAMPA_F32 ? 4 : 2;
     const int lane = threadIdx.x & 31;
-    float xv[MAXV][NV];
-    float ss = 0.f;
+    const int rpw = 32 / lpr;                              // rows per warp and step
+    const int sub = lane / lpr, l = lane - sub * lpr;
+    const int nvec = D / NV;
+    float wv[VPL][NV];
 #pragma unroll
-    for (int it = 0; it < MAXV; ++it) {
-        const int c0 = (it * 32 + lane) * NV;
-        if (c0 < D) {
-            load_vec<DT>(x, (size_t)row * D + c0, xv[it]);
+    for (int v = 0; v < VPL; ++v)
 #pragma unroll
-            for (int j = 0; j < NV; ++j) ss += xv[it][j] * xv[it][j];
+        for (int j = 0; j < NV; ++j) {
+            const int c = (l + lpr * v) * NV + j;
+            wv[v][j] = (w && c < D) ? load_as_float(w, c, w_dt) : 1.f;
         }
-    }
+    const int64_t warp_id = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int64_t n_warps = (int64_t)gridDim.x * (blockDim.x >> 5);
+    const int64_t rows_per_iter = (int64_t)rpw * RPI;
+    for (int64_t base = warp_id * rows_per_iter; base < rows; base += n_warps * rows_per_iter) {
+        uint4 rx[RPI][VPL], rg[RPI][VPL];
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-    const float rstd = 1.f / sqrtf(ss / (float)D + eps);
+        for (int r = 0; r < RPI; ++r) {
+            const int64_t row = base + (int64_t)r * rpw + sub;
 #pragma unroll
-    for (int it = 0; it < MAXV; ++it) {
-        const int c0 = (it * 32 + lane) * NV;
-        if (c0 < D) {
-            float gv[NV], out[NV];
-            load_vec<DT>(g, (size_t)row * D + c0, gv);
-#pragma unroll
-            for (int j = 0; j < NV; ++j) {
-                const float wv = w ? load_as_float(w, c0 + j, w_dt) : 1.f;
-                const float yv = xv[it][j] * rstd * wv;
-                const float s = sigmoidf_(gv[j]);
-                out[j] = sigmoid_only ? yv * s : yv * gv[j] * s;
+            for (int v = 0; v < VPL; ++v) {
+                const int vi = l + lpr * v;
+                const bool ok = row < rows && vi < nvec;
+                const size_t off = ((size_t)row * D + (size_t)vi * NV) * EB;
+                rx[r][v] = ok ? __ldg(reinterpret_cast<const uint4*>((const char*)x + off)) : make_uint4(0u, 0u, 0u, 0u);
+                rg[r][v] = ok ? __ldg(reinterpret_cast<const uint4*>((const char*)g + off)) : make_uint4(0u, 0u, 0u, 0u);
             }
-            store_vec<DT>(y, (size_t)row * D + c0, out);
+        }
+#pragma unroll
+        for (int r = 0; r < RPI; ++r) {
+            const int64_t row = base + (int64_t)r * rpw + sub;
+            float xv[VPL][NV];
+            float ss = 0.f;
+#pragma unroll
+            for (int v = 0; v < VPL; ++v) {
+                unpack_vec<DT>(rx[r][v], xv[v]);
+#pragma unroll
+                for (int j = 0; j < NV; ++j) ss += xv[v][j] * xv[v][j];
+            }
+            for (int o = lpr >> 1; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+            const float rstd = 1.f / sqrtf(ss / (float)D + eps);
+#pragma unroll
+            for (int v = 0; v < VPL; ++v) {
+                const int vi = l + lpr * v;
+                float gv[NV], out[NV];
+                unpack_vec<DT>(rg[r][v], gv);
+#pragma unroll
+                for (int j = 0; j < NV; ++j) {
+                    const float yv = xv[v][j] * rstd * wv[v][j];
+                    const float sg = sigmoidf_(gv[j]);
+                    out[j] = sigmoid_only ? yv * sg : yv * gv[j] * sg;
+                }
+                if (row < rows && vi < nvec) store_vec<DT>(y, (size_t)row * D + (size_t)vi * NV, out);
+            }
         }
     }
 }
@@ -343,11 +448,11 @@ extern "C" int lampa_short_conv_fwd(const void* x, const void* weight, const voi
                                     void* final_state, int32_t zero_fill, void* stream) {
     if (B <= 0 || T < 0 || D <= 0 || W < 1 || W > CONV_MAX_W || !dt_ok(dtype) || !dt_ok(w_dtype)) return LAMPA_ERR_ARG;
     if (nseq < 0 || (nseq > 0 && (B != 1 || !cu_seqlens))) return LAMPA_ERR_ARG;
-    const int nv = dtype == LAMPA_F32 ? 4 : 8;
+    const int nv = 4;
     if (D % nv != 0) return LAMPA_ERR_UNSUPPORTED;
     if (B * T == 0) return LAMPA_OK;
     if (!x || !weight || !y) return LAMPA_ERR_ARG;
-    if (((uintptr_t)x | (uintptr_t)y | (uintptr_t)residual) & 15) return LAMPA_ERR_ARG;
+    if (((uintptr_t)x | (uintptr_t)y | (uintptr_t)residual) & (dtype == LAMPA_F32 ? 15 : 7)) return LAMPA_ERR_ARG;
     cudaStream_t st = (cudaStream_t)stream;
     ConvArgs a;
     a.x = x; a.w = weight; a.bias = bias; a.residual = residual; a.cu = cu_seqlens; a.y = y;
@@ -359,8 +464,10 @@ extern "C" int lampa_short_conv_fwd(const void* x, const void* weight, const voi
         ProfScope prof("short_conv_fwd", st);
 #define LAMPA_CONV(DT)                                                                    \
         do {                                                                              \
-            if (W <= 4) short_conv_fwd_kernel<DT, 4><<<grid, block, 0, st>>>(a);          \
-            else short_conv_fwd_kernel<DT, CONV_MAX_W><<<grid, block, 0, st>>>(a);        \
+            if (W == 4) short_conv_fwd_kernel<DT, 4, true><<<grid, block, 0, st>>>(a);            \
+            else if (W == 2) short_conv_fwd_kernel<DT, 2, true><<<grid, block, 0, st>>>(a);       \
+            else if (W == 8) short_conv_fwd_kernel<DT, 8, true><<<grid, block, 0, st>>>(a);       \
+            else short_conv_fwd_kernel<DT, CONV_MAX_W, false><<<grid, block, 0, st>>>(a);         \
         } while (0)
         if (dtype == LAMPA_BF16) LAMPA_CONV(LAMPA_BF16);
         else if (dtype == LAMPA_F16) LAMPA_CONV(LAMPA_F16);
@@ -403,10 +510,21 @@ extern "C" int lampa_gate_inputs(const void* a, const void* b, const void* dl, c
     p.g = g; p.beta = beta; p.lam = lam;
     p.n_tok = n_tok; p.H = H; p.L = lam ? L : 0; p.in_dt = in_dtype; p.beta_dt = beta_dtype; p.lam_dt = lam_dtype;
     p.mode = lambda_mode;
-    const int64_t tot = n_tok * H * (p.L + 1);
-    ProfScope prof("gate_inputs", (cudaStream_t)stream);
-    gate_inputs_kernel<<<(unsigned)((tot + 255) / 256), 256, 0, (cudaStream_t)stream>>>(p);
-    return cudaGetLastError() == cudaSuccess ? LAMPA_OK : LAMPA_ERR_CUDA;
+    cudaStream_t st = (cudaStream_t)stream;
+    ProfScope prof("gate_inputs", st);
+    if (g || beta) {
+        const int64_t tot = n_tok * H;
+        gate_gb_kernel<<<(unsigned)((tot + 255) / 256), 256, 0, st>>>(p);
+        if (cudaGetLastError() != cudaSuccess) return LAMPA_ERR_CUDA;
+    }
+    if (lam) {
+        const int64_t tot = n_tok * H * L;
+        const bool vec = in_dtype != LAMPA_F32 && tot % 8 == 0 && (((uintptr_t)dl | (uintptr_t)lam) & 15) == 0;
+        if (vec) gate_lambda_kernel<8><<<(unsigned)((tot / 8 + 255) / 256), 256, 0, st>>>(p);
+        else gate_lambda_kernel<1><<<(unsigned)((tot + 255) / 256), 256, 0, st>>>(p);
+        if (cudaGetLastError() != cudaSuccess) return LAMPA_ERR_CUDA;
+    }
+    return LAMPA_OK;
 }
 
 extern "C" int lampa_rmsnorm_gate(const void* x, const void* g, const void* weight, int64_t rows, int32_t D,
@@ -418,10 +536,22 @@ extern "C" int lampa_rmsnorm_gate(const void* x, const void* g, const void* weig
     if (rows == 0) return LAMPA_OK;
     if (!x || !g || !y || (((uintptr_t)x | (uintptr_t)g | (uintptr_t)y) & 15)) return LAMPA_ERR_ARG;
     cudaStream_t st = (cudaStream_t)stream;
-    const unsigned grid = (unsigned)((rows + 7) / 8);
+    const int nvec = D / nv;
+    int lpr = 1;
+    while (lpr < nvec && lpr < 32) lpr <<= 1;
+    const int vpl = (nvec + lpr - 1) / lpr;                       // 1 .. 4
+    const int64_t rows_per_block = (int64_t)8 * (32 / lpr) * (4 / (vpl == 3 ? 4 : vpl));
+    const unsigned grid = (unsigned)std::min<int64_t>((rows + rows_per_block - 1) / rows_per_block, 148 * 16);
     ProfScope prof("rmsnorm_gate", st);
-    if (dtype == LAMPA_BF16) rmsnorm_gate_kernel<LAMPA_BF16><<<grid, 256, 0, st>>>(x, g, weight, w_dtype, rows, D, eps, sigmoid_only, y);
-    else if (dtype == LAMPA_F16) rmsnorm_gate_kernel<LAMPA_F16><<<grid, 256, 0, st>>>(x, g, weight, w_dtype, rows, D, eps, sigmoid_only, y);
-    else rmsnorm_gate_kernel<LAMPA_F32><<<grid, 256, 0, st>>>(x, g, weight, w_dtype, rows, D, eps, sigmoid_only, y);
+#define LAMPA_NORM(DT)                                                                                                   \
+    do {                                                                                                                 \
+        if (vpl == 1) rmsnorm_gate_kernel<DT, 1><<<grid, 256, 0, st>>>(x, g, weight, w_dtype, rows, D, lpr, eps, sigmoid_only, y); \
+        else if (vpl == 2) rmsnorm_gate_kernel<DT, 2><<<grid, 256, 0, st>>>(x, g, weight, w_dtype, rows, D, lpr, eps, sigmoid_only, y); \
+        else rmsnorm_gate_kernel<DT, 4><<<grid, 256, 0, st>>>(x, g, weight, w_dtype, rows, D, lpr, eps, sigmoid_only, y); \
+    } while (0)
+    if (dtype == LAMPA_BF16) LAMPA_NORM(LAMPA_BF16);
+    else if (dtype == LAMPA_F16) LAMPA_NORM(LAMPA_F16);
+    else LAMPA_NORM(LAMPA_F32);
+#undef LAMPA_NORM
     return cudaGetLastError() == cudaSuccess ? LAMPA_OK : LAMPA_ERR_CUDA;
 }
