@@ -1,8 +1,8 @@
 // Hierarchical output pass on the 5th-generation tensor cores (tcgen05.mma, accumulators in TMEM)
 // for K = V = 64.
 //
-// Per (block of 32 chunks, head) one CTA of 4 warps keeps every level state the block touches as
-// rows of bf16 A operands in shared memory: slot s holds S_l^T (64 rows v x 64 columns k), two slots
+// Per (block of 32 chunks, head) one CTA keeps every level state the block touches as rows of
+// bf16 A operands in tensor memory: slot s holds S_l^T (64 rows v x 64 columns k), two slots
 // per 128-row operand ("pair").  Slots 0..4 are the chunk levels that live inside the block,
 // the following ones the cross-block levels this block reads (seeded from the level pass).
 // A chunk is one record {M | Q~ | B^T | O_local | lambda}; its first 16 KB, the M and Q~ tiles back to
@@ -10,14 +10,18 @@
 //     D[128 x 128] = [S_a^T ; S_b^T] (128 x 64)  x  [M ; Q~]^T (64 x 128),
 // yields both the advanced states (columns 0..63: S^T M^T) and the levels' contributions to the
 // output (columns 64..127: S^T Q~^T = (Q~ S)^T).  The epilogue, one thread per TMEM lane (= state
-// row), scales the contribution by lambda and accumulates it over the pairs, adds B^T where the
-// level is collecting, clears it at the end of its period, and writes the bf16 row back into the A
-// operand for the next chunk.  Warp-specialised: 16 epilogue warps (two warpgroups advance the states,
-// 32 columns each; two read them and also transpose and store the output) and one control warp whose
-// first lane streams the records in (bulk async copies, three stages) and issues the MMAs.  A pair's
-// MMA for the next chunk is issued as soon as that pair's epilogue has handed its operand back
-// (mbarriers only, no block-wide barrier on the state path), so the tensor core runs ahead of the
-// epilogues.  MMA completion is tracked by tcgen05.commit on one mbarrier per pair; every wait is bounded.
+// row) and quarter of the columns, adds B^T where the level is collecting, clears it at the end of
+// its period and writes the bf16 row back into the A operand for the next chunk; then it scales
+// the level's contribution to its 16 tokens by lambda and accumulates it over the pairs.
+// Warp-specialised: 16 epilogue warps (warp = 32 rows x 16 state columns x 16 tokens; together they
+// also transpose the chunk's output through shared memory and store it with O_local added) and one
+// control warp whose first lane streams the records in (bulk async copies, three stages) and issues
+// the MMAs.  A pair's MMA for the next chunk is issued as soon as every warp has handed that pair's
+// operand back and the accumulator buffer it will overwrite has been read (two mbarriers per pair,
+// no block-wide barrier on the state path).  MMA completion is tracked by tcgen05.commit on one
+// mbarrier per pair; every wait is bounded.  Measured alternatives that were slower: letting the
+// accumulator buffers alternate along the issue order (the next chunk's first MMA then overlaps the
+// last epilogue: +18 us), and issuing a pair's two TMEM loads together (+50 us, spills at 96 registers).
 #include "gdn.cuh"
 #include "profile.cuh"
 
@@ -27,7 +31,7 @@ namespace {
 
 constexpr int UKD = 64, UVD = 64;
 constexpr int UNP = 5;                       // pairs of slots: 5 in-block levels + up to 5 cross-block levels
-constexpr int UEPI_WARPS = 16;               // 4 warpgroups: two advance the states (32 columns each), two read them
+constexpr int UEPI_WARPS = 16;               // 4 warpgroups, each covering 16 state columns and 16 tokens of all 128 rows
 constexpr int UTHREADS = (UEPI_WARPS + 1) * 32;   // plus one control warp
 constexpr int UNST = 3;                      // record stages
 using UR = Rec<UKD, UVD>;
@@ -71,28 +75,23 @@ __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence:
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }
 
-// 32 consecutive fp32 columns of this thread's TMEM lane
-__device__ __forceinline__ void tmem_ld32(float (&x)[32], uint32_t taddr) {
+// 16 consecutive fp32 columns of this thread's TMEM lane
+__device__ __forceinline__ void tmem_ld16(float (&x)[16], uint32_t taddr) {
     uint32_t* r = reinterpret_cast<uint32_t*>(x);
-#define LAMPA_LD16(o)                                                                                                     \
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];\n" \
-                 : "=r"(r[o + 0]), "=r"(r[o + 1]), "=r"(r[o + 2]), "=r"(r[o + 3]), "=r"(r[o + 4]), "=r"(r[o + 5]),          \
-                   "=r"(r[o + 6]), "=r"(r[o + 7]), "=r"(r[o + 8]), "=r"(r[o + 9]), "=r"(r[o + 10]), "=r"(r[o + 11]),       \
-                   "=r"(r[o + 12]), "=r"(r[o + 13]), "=r"(r[o + 14]), "=r"(r[o + 15])                                     \
-                 : "r"(taddr + o));
-    LAMPA_LD16(0) LAMPA_LD16(16)
-#undef LAMPA_LD16
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                 : "r"(taddr));
     asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
 }
 
-// write 32 floats as 16 columns of packed bf16 pairs of this thread's TMEM lane (half a row of an A operand)
-__device__ __forceinline__ void tmem_st_bf16x32(uint32_t taddr, const float (&x)[32]) {
-    uint32_t w[16];
+// write 16 floats as 8 columns of packed bf16 pairs of this thread's TMEM lane (a quarter row of an A operand)
+__device__ __forceinline__ void tmem_st_bf16x16(uint32_t taddr, const float (&x)[16]) {
+    uint32_t w[8];
 #pragma unroll
-    for (int c = 0; c < 16; ++c) w[c] = pack_bf16x2(x[2 * c], x[2 * c + 1]);
-    asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};\n"
-                 :: "r"(taddr), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7]),
-                    "r"(w[8]), "r"(w[9]), "r"(w[10]), "r"(w[11]), "r"(w[12]), "r"(w[13]), "r"(w[14]), "r"(w[15]) : "memory");
+    for (int c = 0; c < 8; ++c) w[c] = pack_bf16x2(x[2 * c], x[2 * c + 1]);
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};\n"
+                 :: "r"(taddr), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7]) : "memory");
     asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
 }
 
@@ -106,6 +105,7 @@ __global__ void __launch_bounds__(UTHREADS, 1) gdn_out_hier_umma_kernel(GdnArgs 
     uint64_t* sfree = full + UNST;                                      // stage consumed           (16 warps)
     uint64_t* mdone = sfree + UNST;                                     // pair's MMA complete      (commit)
     uint64_t* aready = mdone + UNP;                                     // pair's operand rewritten (16 warps)
+    uint64_t* dfree = aready + UNP;                                     // pair's accumulator read  (16 warps)
     uint32_t* tslot = reinterpret_cast<uint32_t*>(smem + SM_BAR + 256);
     float* sOT = reinterpret_cast<float*>(smem + SM_OT);
 
@@ -120,10 +120,10 @@ __global__ void __launch_bounds__(UTHREADS, 1) gdn_out_hier_umma_kernel(GdnArgs 
     const int nsteps = min(BLOCK_CHUNKS, nch - b * BLOCK_CHUNKS);
     const int64_t tok0 = a.tok_off[seq] + (int64_t)b * BLOCK_CHUNKS * CHUNK, tok_end = a.tok_off[seq + 1];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int wg = warp >> 2;                          // 0,1: advance columns 32*wg..; 2,3: read tokens 32*(wg-2)..; 4: control
+    const int wg = warp >> 2;                          // 0..3: state columns / tokens 16*wg .. 16*wg+15; 4: control
     const int row = (warp & 3) * 32 + lane;            // TMEM lane = row of the pair's A operand
     const int u = row >> 6, v = row & 63;              // which slot of the pair, which state row
-    const int half = wg & 1;
+    const int part = wg & 3;
     const int lam_bytes = a.LC * CHUNK * 4;
     const int stage_bytes = ustage_bytes(a.LC);
     unsigned char* stage0 = smem + SM_STAGE;
@@ -142,7 +142,7 @@ __global__ void __launch_bounds__(UTHREADS, 1) gdn_out_hier_umma_kernel(GdnArgs 
 #pragma unroll
         for (int s = 0; s < UNST; ++s) { mbar_init(full + s, 1); mbar_init(sfree + s, UEPI_WARPS); }
 #pragma unroll
-        for (int p = 0; p < UNP; ++p) { mbar_init(mdone + p, 1); mbar_init(aready + p, UEPI_WARPS); }
+        for (int p = 0; p < UNP; ++p) { mbar_init(mdone + p, 1); mbar_init(aready + p, UEPI_WARPS); mbar_init(dfree + p, UEPI_WARPS); }
         fence_mbar_init();
     }
     if (warp == 0) {
@@ -156,23 +156,23 @@ __global__ void __launch_bounds__(UTHREADS, 1) gdn_out_hier_umma_kernel(GdnArgs 
     const uint32_t taddr = *tslot;
     const uint32_t tlane = taddr + ((uint32_t)((warp & 3) * 32) << 16);
     // initial states: zero for the in-block levels, the block's entry state for the cross-block ones
-    if (wg < 2) {
+    if (wg < 4) {
         for (int p = 0; p < npairs; ++p) {
             const int s = 2 * p + u;
-            float x[32];
+            float x[16];
 #pragma unroll
-            for (int i = 0; i < 32; ++i) x[i] = 0.f;
+            for (int i = 0; i < 16; ++i) x[i] = 0.f;
             if (s >= BLOCK_LOG && s < nslots) {
                 const int lh = (live_pack >> (4 * (s - BLOCK_LOG))) & 15;
                 const float4* e = reinterpret_cast<const float4*>(
-                    a.entry + (((size_t)gb * a.nhigh_max + lh) * H + h) * UR::STATE_FLOATS + (size_t)v * UKD + 32 * half);
+                    a.entry + (((size_t)gb * a.nhigh_max + lh) * H + h) * UR::STATE_FLOATS + (size_t)v * UKD + 16 * part);
 #pragma unroll
-                for (int i = 0; i < 8; ++i) {
+                for (int i = 0; i < 4; ++i) {
                     const float4 f = e[i];
                     x[4 * i] = f.x; x[4 * i + 1] = f.y; x[4 * i + 2] = f.z; x[4 * i + 3] = f.w;
                 }
             }
-            tmem_st_bf16x32(tlane + TM_A + 32 * p + 16 * half, x);
+            tmem_st_bf16x16(tlane + TM_A + 32 * p + 8 * part, x);
         }
     }
     tc_fence_before();
@@ -197,12 +197,12 @@ __global__ void __launch_bounds__(UTHREADS, 1) gdn_out_hier_umma_kernel(GdnArgs 
                 for (int p = 0; p < npairs; ++p) {
                     // the pair's operand rewritten by the previous chunk ...
                     if (i > 0) mbar_wait(aready + p, (uint32_t)((i - 1) & 1), dead, a.status, 400 + p);
-                    // ... and the accumulator buffer (p & 1) drained by the pair that used it last
+                    // ... and the accumulator buffer (p & 1) read out by the pair that used it last
                     if (p >= 2) {
-                        mbar_wait(aready + (p - 2), (uint32_t)(i & 1), dead, a.status, 410 + p);
+                        mbar_wait(dfree + (p - 2), (uint32_t)(i & 1), dead, a.status, 410 + p);
                     } else if (i > 0) {
                         const int q = ((npairs - 1) & 1) == p ? npairs - 1 : npairs - 2;
-                        if (q > p) mbar_wait(aready + q, (uint32_t)((i - 1) & 1), dead, a.status, 420 + p);
+                        mbar_wait(dfree + max(q, p), (uint32_t)((i - 1) & 1), dead, a.status, 420 + p);
                     }
                     tc_fence_after();
                     const uint32_t b_base = smem_u32(st + UR::M_OFF);
@@ -219,20 +219,21 @@ __global__ void __launch_bounds__(UTHREADS, 1) gdn_out_hier_umma_kernel(GdnArgs 
             }
         }
     } else {
-        // ---- epilogue warps ---------------------------------------------------------------------------
+        // ---- epilogue warps: every warp advances 16 state columns and reads 16 tokens of its 32 rows ----
         for (int i = 0; i < nsteps; ++i) {
             const unsigned char* st = stage0 + (size_t)(i % UNST) * stage_bytes;
             const float* sLam = reinterpret_cast<const float*>(st + STAGE_TILES);
             const unsigned char* sBt = st + UR::BT_OFF;
             const int n = b * BLOCK_CHUNKS + i;
-            const int otid = tid - 256;                       // output thread index of the read warpgroups
-            const int64_t t_out = tok0 + (int64_t)i * CHUNK + (otid >> 2);
             const float* sOl = reinterpret_cast<const float*>(st + UR::OL_OFF);
             mbar_wait(full + (i % UNST), (uint32_t)((i / UNST) & 1), dead, a.status, 250 + i);
+            // this row's 16 columns of B^T, shared by every level that collects in this chunk
+            const uint4 bq0 = *reinterpret_cast<const uint4*>(sBt + v * 128 + (((2 * part) ^ (v & 7)) << 4));
+            const uint4 bq1 = *reinterpret_cast<const uint4*>(sBt + v * 128 + (((2 * part + 1) ^ (v & 7)) << 4));
 
-            float oacc[32];
+            float oacc[16];
 #pragma unroll
-            for (int j = 0; j < 32; ++j) oacc[j] = 0.f;
+            for (int j = 0; j < 16; ++j) oacc[j] = 0.f;
 
             for (int p = 0; p < npairs; ++p) {
                 mbar_wait(mdone + p, (uint32_t)(i & 1), dead, a.status, 300 + p);
@@ -253,85 +254,80 @@ __global__ void __launch_bounds__(UTHREADS, 1) gdn_out_hier_umma_kernel(GdnArgs 
                 }
                 if (lam_row >= a.LC) do_read = false;      // only reachable when the level check already failed
                 const uint32_t tcol = tlane + (uint32_t)(TM_D + (p & 1) * 128);
-                if (wg >= 2) {
-                    if (do_read) {
-                        float y[32];
-                        tmem_ld32(y, tcol + 64 + 32 * half);
-                        const float4* lr = reinterpret_cast<const float4*>(sLam + lam_row * CHUNK + 32 * half);
-#pragma unroll
-                        for (int j = 0; j < 8; ++j) {
-                            const float4 l4 = lr[j];
-                            oacc[4 * j] += l4.x * y[4 * j]; oacc[4 * j + 1] += l4.y * y[4 * j + 1];
-                            oacc[4 * j + 2] += l4.z * y[4 * j + 2]; oacc[4 * j + 3] += l4.w * y[4 * j + 3];
-                        }
-                    }
-                } else if (active && i + 1 < nsteps) {
-                    float x[32];
+                // state path first: the next chunk's MMA of this pair waits for it
+                if (active && i + 1 < nsteps) {
+                    float x[16];
                     if (clear) {
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) x[j] = 0.f;
+                        for (int j = 0; j < 16; ++j) x[j] = 0.f;
                     } else {
-                        tmem_ld32(x, tcol + 32 * half);
+                        tmem_ld16(x, tcol + 16 * part);
                         if (add_b) {
+                            const uint32_t bw[8] = {bq0.x, bq0.y, bq0.z, bq0.w, bq1.x, bq1.y, bq1.z, bq1.w};
 #pragma unroll
-                            for (int c = 0; c < 4; ++c) {
-                                const uint4 q4 = *reinterpret_cast<const uint4*>(sBt + v * 128 + (((4 * half + c) ^ (v & 7)) << 4));
-                                const float2 f0 = unpack_bf16x2(q4.x), f1 = unpack_bf16x2(q4.y), f2 = unpack_bf16x2(q4.z), f3 = unpack_bf16x2(q4.w);
-                                x[8 * c] += f0.x; x[8 * c + 1] += f0.y; x[8 * c + 2] += f1.x; x[8 * c + 3] += f1.y;
-                                x[8 * c + 4] += f2.x; x[8 * c + 5] += f2.y; x[8 * c + 6] += f3.x; x[8 * c + 7] += f3.y;
+                            for (int c = 0; c < 8; ++c) {
+                                const float2 f = unpack_bf16x2(bw[c]);
+                                x[2 * c] += f.x; x[2 * c + 1] += f.y;
                             }
                         }
                     }
-                    tmem_st_bf16x32(tlane + TM_A + 32 * p + 16 * half, x);
+                    tmem_st_bf16x16(tlane + TM_A + 32 * p + 8 * part, x);
                 }
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(aready + p);
-            }
-            if (wg < 2) {
+                // read path: lambda-weighted contribution of this level to 16 tokens
+                if (do_read) {
+                    float y[16];
+                    tmem_ld16(y, tcol + 64 + 16 * part);
+                    const float4* lr = reinterpret_cast<const float4*>(sLam + lam_row * CHUNK + 16 * part);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const float4 l4 = lr[j];
+                        oacc[4 * j] += l4.x * y[4 * j]; oacc[4 * j + 1] += l4.y * y[4 * j + 1];
+                        oacc[4 * j + 2] += l4.z * y[4 * j + 2]; oacc[4 * j + 3] += l4.w * y[4 * j + 3];
+                    }
+                }
+                tc_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(sfree + (i % UNST));
+                if (lane == 0) mbar_arrive(dfree + p);
             }
-            if (wg >= 2) {
-                // output (read warpgroups only): sum the two halves of the pairs, add O_local, transpose
-                asm volatile("bar.sync 1, 256;\n" ::: "memory");       // previous chunk's transpose buffer fully read
+            // output: sum the two rows (levels) of the pairs through shared memory, add O_local, store
+            asm volatile("bar.sync 1, 512;\n" ::: "memory");       // previous chunk's transpose buffer fully read
 #pragma unroll
-                for (int j = 0; j < 32; ++j) sOT[(u * 64 + 32 * half + j) * 64 + v] = oacc[j];
-                asm volatile("bar.sync 1, 256;\n" ::: "memory");
+            for (int j = 0; j < 16; ++j) sOT[(u * 64 + 16 * part + j) * 64 + v] = oacc[j];
+            asm volatile("bar.sync 1, 512;\n" ::: "memory");
+            {
+                const int tok = tid >> 3, col = (tid & 7) * 8;
+                const int64_t t_out = tok0 + (int64_t)i * CHUNK + tok;
                 if (t_out < tok_end) {
-                    const int tok = otid >> 2, col = (otid & 3) * 16;
                     const size_t idx = ((size_t)t_out * H + h) * UVD + col;
-                    float r[16];
+                    float r[8];
 #pragma unroll
-                    for (int q = 0; q < 4; ++q) {
+                    for (int q = 0; q < 2; ++q) {
                         const float4 p0 = *reinterpret_cast<const float4*>(sOT + (0 * 64 + tok) * 64 + col + 4 * q);
                         const float4 q0 = *reinterpret_cast<const float4*>(sOT + (1 * 64 + tok) * 64 + col + 4 * q);
-                        r[4 * q] = p0.x + q0.x; r[4 * q + 1] = p0.y + q0.y; r[4 * q + 2] = p0.z + q0.z; r[4 * q + 3] = p0.w + q0.w;
-                    }
-#pragma unroll
-                    for (int q = 0; q < 4; ++q) {
                         const float4 o4 = *reinterpret_cast<const float4*>(sOl + tok * UR::OP + col + 4 * q);
-                        r[4 * q] += o4.x; r[4 * q + 1] += o4.y; r[4 * q + 2] += o4.z; r[4 * q + 3] += o4.w;
+                        r[4 * q] = p0.x + q0.x + o4.x; r[4 * q + 1] = p0.y + q0.y + o4.y;
+                        r[4 * q + 2] = p0.z + q0.z + o4.z; r[4 * q + 3] = p0.w + q0.w + o4.w;
                     }
                     if (a.qkv_dt == LAMPA_F32) {
                         float4* o4 = reinterpret_cast<float4*>((float*)a.o + idx);
-#pragma unroll
-                        for (int q = 0; q < 4; ++q) o4[q] = make_float4(r[4 * q], r[4 * q + 1], r[4 * q + 2], r[4 * q + 3]);
+                        o4[0] = make_float4(r[0], r[1], r[2], r[3]);
+                        o4[1] = make_float4(r[4], r[5], r[6], r[7]);
                     } else {
-                        uint32_t w[8];
+                        uint32_t w[4];
 #pragma unroll
-                        for (int q = 0; q < 8; ++q) {
+                        for (int q = 0; q < 4; ++q) {
                             if (a.qkv_dt == LAMPA_BF16) w[q] = pack_bf16x2(r[2 * q], r[2 * q + 1]);
                             else { const __half2 hh = __floats2half2_rn(r[2 * q], r[2 * q + 1]); w[q] = *reinterpret_cast<const uint32_t*>(&hh); }
                         }
-                        uint4* o4 = reinterpret_cast<uint4*>((uint16_t*)a.o + idx);
-                        o4[0] = make_uint4(w[0], w[1], w[2], w[3]);
-                        o4[1] = make_uint4(w[4], w[5], w[6], w[7]);
+                        *reinterpret_cast<uint4*>((uint16_t*)a.o + idx) = make_uint4(w[0], w[1], w[2], w[3]);
                     }
                 }
-                __syncwarp();
-                if (lane == 0) mbar_arrive(sfree + (i % UNST));   // O_local of this stage has been read
             }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(sfree + (i % UNST));   // B^T, lambda and O_local of this stage have been read
         }
     }
     tc_fence_before();
