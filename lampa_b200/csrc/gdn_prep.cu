@@ -596,12 +596,16 @@ __global__ void __launch_bounds__(128, 4) gdn_prep_kernel(GdnArgs a) {
     PREP_TICK(5);
 
     // ---- stage 4: M[a][b] = e^{G_last} (delta_ab - sum_tok K[tok][a] W[tok][b]);  B^T = U^^T K -----
+    // Both tiles are assembled in the record's layout in shared memory (over Awb and V, which are
+    // dead by now) and leave as two bulk copies instead of 4-byte stores from every lane.
+    __nv_bfloat16* stM = reinterpret_cast<__nv_bfloat16*>(smem + S::AW);
+    __nv_bfloat16* stB = reinterpret_cast<__nv_bfloat16*>(smem + S::V);
+    static_assert(R::M_BYTES <= CHUNK * CP * 2 && R::BT_BYTES <= CHUNK * VP * 2, "staging tiles must fit");
     if (m0 < KD) {
         float acc[KD / 8][4];
         zero_acc<KD / 8>(acc);
         warp_gemm<KD / 8, CHUNK, true, true>(acc, sK, KP, m0, sW, KP, 0, lane, CHUNK, KD);
         const float egl = sEG[CHUNK - 1];
-        __nv_bfloat16* gM = reinterpret_cast<__nv_bfloat16*>(rec + R::M_OFF);
 #pragma unroll
         for (int nt = 0; nt < KD / 8; ++nt)
 #pragma unroll
@@ -609,21 +613,28 @@ __global__ void __launch_bounds__(128, 4) gdn_prep_kernel(GdnArgs a) {
                 const int i = m0 + gq + hh * 8, j = nt * 8 + 2 * tq;
                 const float m_0 = egl * (((i == j) ? 1.f : 0.f) - acc[nt][2 * hh]);
                 const float m_1 = egl * (((i == j + 1) ? 1.f : 0.f) - acc[nt][2 * hh + 1]);
-                *reinterpret_cast<uint32_t*>(gM + R::T::off(i, j)) = pack_bf16x2(m_0, m_1);
+                *reinterpret_cast<uint32_t*>(stM + R::T::off(i, j)) = pack_bf16x2(m_0, m_1);
             }
     }
     if (m0 < VD) {
         float acc[KD / 8][4];
         zero_acc<KD / 8>(acc);
         warp_gemm<KD / 8, CHUNK, true, true>(acc, sUh, VP, m0, sK, KP, 0, lane, CHUNK, KD);
-        __nv_bfloat16* gB = reinterpret_cast<__nv_bfloat16*>(rec + R::BT_OFF);
 #pragma unroll
         for (int nt = 0; nt < KD / 8; ++nt)
 #pragma unroll
             for (int hh = 0; hh < 2; ++hh) {
                 const int i = m0 + gq + hh * 8, j = nt * 8 + 2 * tq;
-                *reinterpret_cast<uint32_t*>(gB + R::T::off(i, j)) = pack_bf16x2(acc[nt][2 * hh], acc[nt][2 * hh + 1]);
+                *reinterpret_cast<uint32_t*>(stB + R::T::off(i, j)) = pack_bf16x2(acc[nt][2 * hh], acc[nt][2 * hh + 1]);
             }
+    }
+    fence_async_shared();
+    __syncthreads();
+    if (tid == 0) {
+        bulk_s2g(rec + R::M_OFF, stM, R::M_BYTES);
+        bulk_s2g(rec + R::BT_OFF, stB, R::BT_BYTES);
+        bulk_commit();
+        bulk_wait_read();
     }
     PREP_TICK(6);
 }
