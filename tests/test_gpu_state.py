@@ -199,3 +199,46 @@ def test_step_reports_a_full_hierarchy(lb):
         assert torch.equal(before, hs.states)
     finally:
         os.environ["LAMPA_B200_CHECK"] = "1"
+
+
+def test_final_state_of_packed_sequences_through_the_c_abi(lb):
+    """lampa_hgdn_final_state with cu_seqlens: one Fenwick state and one counts row per sequence
+    (the Python op does not expose this; the C entry point does)."""
+    import ctypes
+    from lampa_b200 import _lib as L, synth
+    H, K, V = 2, 64, 64
+    lens = [2112, 64, 0, 4160, 640]
+    cu = np.concatenate([[0], np.cumsum(lens)]).astype(np.int64)
+    T = int(cu[-1])
+    Lv = lb.num_levels_required(max(lens)) + 1
+    inp = synth.gdn_inputs(41, T, H, K, V, L=Lv, g_shift=-3.0)
+    d = _cuda(inp)
+    cud = torch.from_numpy(cu).cuda()
+    N = len(lens)
+    desc = L.GdnDesc(B=1, T=T, H=H, K=K, V=V, L=Lv, nseq=N, qkv_dtype=L.LAMPA_BF16, gb_dtype=L.LAMPA_F32,
+                     lam_dtype=L.LAMPA_F32, use_l2norm=1, scale=1.0)
+    nbytes = ctypes.c_size_t(0)
+    L.check(L.lib().lampa_gdn_workspace_bytes(ctypes.byref(desc), ctypes.byref(nbytes)), "workspace")
+    buf = torch.empty(nbytes.value + 1024, dtype=torch.uint8, device="cuda:0")
+    ws = buf[(-buf.data_ptr()) % 1024:][: nbytes.value]
+    o = torch.empty(1, T, H, V, dtype=torch.bfloat16, device="cuda:0")
+    st = L.status_word(torch.device("cuda:0"))
+    stream = L.stream_ptr(torch.device("cuda:0"))
+    L.check(L.lib().lampa_hgdn_fwd(ctypes.byref(desc), L.ptr(d["q"]), L.ptr(d["k"]), L.ptr(d["v"]), L.ptr(d["g"]),
+                                   L.ptr(d["beta"]), L.ptr(d["lam"]), L.ptr(cud), L.ptr(o), L.ptr(ws), ws.numel(),
+                                   L.ptr(st), stream), "lampa_hgdn_fwd")
+    states = torch.full((N, H, K, V, Lv), float("nan"), device="cuda:0")
+    counts = torch.full((N, Lv), -1, dtype=torch.int32, device="cuda:0")
+    L.check(L.lib().lampa_hgdn_final_state(ctypes.byref(desc), L.ptr(d["k"]), L.ptr(d["v"]), L.ptr(d["g"]),
+                                           L.ptr(d["beta"]), L.ptr(cud), L.ptr(ws), ws.numel(), L.ptr(states),
+                                           L.ptr(counts), L.ptr(st), stream), "lampa_hgdn_final_state")
+    L.check_status(torch.device("cuda:0"))
+    for n, (s, e) in enumerate(zip(cu[:-1], cu[1:])):
+        got_s, got_c = to_np(states[n]), to_np(counts[n])
+        if e == s:
+            assert not got_s.any() and not got_c.any()
+            continue
+        sub = {k: x[:, s:e] for k, x in inp.items()}
+        _, sref, cref = _ref(sub)
+        np.testing.assert_array_equal(got_c, cref)
+        _close_states(got_s, sref, f"sequence {n}")
