@@ -66,14 +66,18 @@ lsh_hash_kernel(const float* __restrict__ x, int64_t row_stride, int64_t head_st
 }
 
 // -------------------------------------------------------------------------------------------------
-// Segmented stable LSD radix sort.  One thread-block cluster (up to 8 CTAs, sized at launch so that
-// all clusters are resident at once) per segment: each CTA owns a contiguous slice of the segment
-// in its current order, digit histograms are exchanged through distributed shared memory, and the
-// passes are separated by the hardware cluster barrier (no flag spinning anywhere).  Keys are
-// reduced to (key - min) first, so only ceil(bits(range)/8) passes run: two for the ~15-bit bucket
-// ids of this workload.  Inside a pass a CTA walks its slice in tiles of 4096 keys; a warp takes
-// 128 consecutive keys as four rounds of 32, ranking each round with match_any on top of a
-// per-warp digit histogram, so the order (round, lane) is the key order and the sort is stable.
+// Segmented stable LSD radix sort.  One thread-block cluster (up to 8 CTAs) per segment: each CTA
+// owns a contiguous slice of the segment in its current order, digit histograms are exchanged
+// through distributed shared memory, and the passes are separated by the hardware cluster barrier
+// (no flag spinning anywhere).  The cluster size is the largest one for which the occupancy
+// calculator reports all clusters resident at once: a cluster lives inside one GPC, and a size that
+// merely divides the SM count left a third of the clusters waiting for a second wave (103 us
+// against 57 us for the 24 x 60 000 keys of the benchmark).  Keys are reduced to (key - min) first,
+// so only ceil(bits(range)/8) passes run: two for the ~15-bit bucket ids of this workload.  A CTA
+// keeps its slice of the current pass in shared memory when it fits (filled by the histogram sweep,
+// read back by the scatter) and walks it in tiles of 4096 keys; a warp takes 128 consecutive keys
+// as four rounds of 32, ranking each round with ballots on top of a per-warp digit histogram, so
+// the order (round, lane) is the key order and the sort is stable.
 // -------------------------------------------------------------------------------------------------
 constexpr int SORT_THREADS = 1024;
 constexpr int SORT_MAX_CL = 8;
@@ -93,7 +97,7 @@ __global__ void __launch_bounds__(SORT_THREADS, 1)
 segsort_kernel(const void* __restrict__ keys, int key_type, int64_t n_total,
                const int64_t* __restrict__ seg, int nseg, const int64_t* __restrict__ init,
                int64_t* __restrict__ perm, uint32_t* kbuf0, uint32_t* kbuf1, uint32_t* ibuf0,
-               uint32_t* ibuf1) {
+               uint32_t* ibuf1, int cache_cap) {
     cg::cluster_group cluster = cg::this_cluster();
     const int rank = (int)cluster.block_rank();
     const int ncl = (int)cluster.num_blocks();
@@ -117,15 +121,41 @@ segsort_kernel(const void* __restrict__ keys, int key_type, int64_t n_total,
     extern __shared__ uint32_t sort_dyn[];         // [SORT_TILE] keys, [SORT_TILE] indices of the tile, grouped by digit
     uint32_t* skey = sort_dyn;
     uint32_t* sidx = sort_dyn + SORT_TILE;
+    // the CTA's slice (keys and indices of the current pass) stays in shared memory when it fits:
+    // the histogram sweep fills it and the scatter reads it back instead of going to L2 again
+    uint32_t* ckey = sort_dyn + 2 * SORT_TILE;
+    uint32_t* cidx = ckey + cache_cap;
+    const bool cached = (hi - lo) <= (int64_t)cache_cap;
 
     // ---- key range over the whole segment -------------------------------------------------------
     if (tid == 0) { red[0] = 0xFFFFFFFFu; red[1] = 0u; }
     __syncthreads();
     {
         uint32_t mn = 0xFFFFFFFFu, mx = 0u;
-        for (int64_t i = lo + tid; i < hi; i += SORT_THREADS) {
-            const uint32_t u = key_xform(keys, key_type, s0 + i);
-            mn = min(mn, u); mx = max(mx, u);
+        if (cached) {   // position i holds element init[i]; four independent loads in flight per thread
+            for (int64_t i0 = lo + tid; i0 < hi; i0 += 4 * SORT_THREADS) {
+                uint32_t ix[4], u[4];
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const int64_t i = i0 + (int64_t)q * SORT_THREADS;
+                    ix[q] = i < hi ? (init ? (uint32_t)init[s0 + i] : (uint32_t)i) : 0u;
+                }
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const int64_t i = i0 + (int64_t)q * SORT_THREADS;
+                    u[q] = i < hi ? key_xform(keys, key_type, s0 + ix[q]) : 0u;
+                }
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const int64_t i = i0 + (int64_t)q * SORT_THREADS;
+                    if (i < hi) { ckey[i - lo] = u[q]; cidx[i - lo] = ix[q]; mn = min(mn, u[q]); mx = max(mx, u[q]); }
+                }
+            }
+        } else {
+            for (int64_t i = lo + tid; i < hi; i += SORT_THREADS) {
+                const uint32_t u = key_xform(keys, key_type, s0 + i);
+                mn = min(mn, u); mx = max(mx, u);
+            }
         }
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) {
@@ -160,11 +190,35 @@ segsort_kernel(const void* __restrict__ keys, int key_type, int64_t n_total,
         // (a) digit histogram of this CTA's slice
         for (int d = tid; d < 256; d += SORT_THREADS) hist[d] = 0;
         __syncthreads();
-        for (int64_t i = lo + tid; i < hi; i += SORT_THREADS) {
-            uint32_t u;
-            if (p == 0) u = key_xform(keys, key_type, s0 + (init ? init[s0 + i] : i)) - gmn;   // position i holds element init[i]
-            else u = ksrc[s0 + i];
-            atomicAdd(&hist[(u >> shift) & 255u], 1u);
+        if (cached) {
+            for (int64_t i0 = lo + tid; i0 < hi; i0 += 4 * SORT_THREADS) {
+                uint32_t u[4], ix[4];
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const int64_t i = i0 + (int64_t)q * SORT_THREADS;
+                    u[q] = 0u; ix[q] = 0u;
+                    if (i < hi) {
+                        if (p == 0) u[q] = ckey[i - lo] - gmn;
+                        else { u[q] = ksrc[s0 + i]; ix[q] = isrc[s0 + i]; }
+                    }
+                }
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const int64_t i = i0 + (int64_t)q * SORT_THREADS;
+                    if (i < hi) {
+                        ckey[i - lo] = u[q];
+                        if (p > 0) cidx[i - lo] = ix[q];
+                        atomicAdd(&hist[(u[q] >> shift) & 255u], 1u);
+                    }
+                }
+            }
+        } else {
+            for (int64_t i = lo + tid; i < hi; i += SORT_THREADS) {
+                uint32_t u;
+                if (p == 0) u = key_xform(keys, key_type, s0 + (init ? init[s0 + i] : i)) - gmn;   // position i holds element init[i]
+                else u = ksrc[s0 + i];
+                atomicAdd(&hist[(u >> shift) & 255u], 1u);
+            }
         }
         __syncthreads();
         cluster.sync();
@@ -201,7 +255,10 @@ segsort_kernel(const void* __restrict__ keys, int key_type, int64_t n_total,
                 const int64_t i = t0 + warp * (32 * SORT_ITEMS) + it * 32 + lane;
                 u[it] = 0; idx[it] = 0;
                 if (i < hi) {
-                    if (p == 0) {
+                    if (cached) {
+                        u[it] = ckey[i - lo];
+                        idx[it] = cidx[i - lo];
+                    } else if (p == 0) {
                         idx[it] = init ? (uint32_t)init[s0 + i] : (uint32_t)i;
                         u[it] = key_xform(keys, key_type, s0 + idx[it]) - gmn;
                     } else {
@@ -296,13 +353,12 @@ segsort_kernel(const void* __restrict__ keys, int key_type, int64_t n_total,
             __syncthreads();
             if (tid < 256) dbase[tid] += tile_tot[tid];
         }
-        __threadfence();
-        cluster.sync();   // scattered keys visible to the whole cluster; histograms free again
+        cluster.sync();   // release/acquire at cluster scope: scattered keys visible to the peers; histograms free again
     }
     cluster.sync();       // no CTA leaves while a peer may still read its shared memory
 }
 
-// Cluster size for nseg segments: as large as possible (<= 8) while all clusters fit the GPU at once.
+// Upper bound of the cluster size for nseg segments: SMs / segments, at most 8 (the launcher lowers it until all fit).
 static int sort_cluster_size(int nseg) {
     int dev = 0, sms = 148;
     if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
@@ -315,23 +371,36 @@ static int sort_cluster_size(int nseg) {
 static int launch_segsort(const void* keys, int key_type, int64_t n_total, const int64_t* seg, int nseg,
                           const int64_t* init, int64_t* perm, uint32_t* k0, uint32_t* k1, uint32_t* i0,
                           uint32_t* i1, cudaStream_t st) {
-    const int cl = sort_cluster_size(nseg);
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)nseg * cl, 1, 1);
-    cfg.blockDim = dim3(SORT_THREADS, 1, 1);
-    cfg.dynamicSmemBytes = 2 * SORT_TILE * sizeof(uint32_t);
-    cfg.stream = st;
-    if (cudaFuncSetAttribute(segsort_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)cfg.dynamicSmemBytes) != cudaSuccess)
+    if (cudaFuncSetAttribute(segsort_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(2 * SORT_TILE + 2 * 12288) * 4) != cudaSuccess)
         return LAMPA_ERR_CUDA;
+    // Cluster size: the largest one for which every segment's cluster is resident at the same time.
+    // A cluster has to fit inside one GPC, so the SM count alone does not tell (148 SMs hold 24
+    // clusters of 6 only if every GPC has 18 usable SMs): ask the occupancy calculator.
+    cudaLaunchConfig_t cfg = {};
     cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = cl;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    int cl = sort_cluster_size(nseg), cache_cap = 0;
+    for (;; --cl) {
+        // slice cache: the slice of an equal split, or twice the average slice when the segments are ragged
+        // (larger slices simply read from global memory), rounded up to 1 K keys, at most 12 K (96 KB)
+        const int64_t avg = (n_total / (nseg > 0 ? nseg : 1) + cl - 1) / cl + 1;
+        const int64_t want = seg ? 2 * avg : avg;
+        cache_cap = (int)std::min<int64_t>(12288, (want + 1023) / 1024 * 1024);
+        cfg.gridDim = dim3((unsigned)nseg * cl, 1, 1);
+        cfg.blockDim = dim3(SORT_THREADS, 1, 1);
+        cfg.dynamicSmemBytes = (2 * SORT_TILE + 2 * (size_t)cache_cap) * sizeof(uint32_t);
+        cfg.stream = st;
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = cl;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        if (cl == 1) break;
+        int resident = 0;
+        if (cudaOccupancyMaxActiveClusters(&resident, segsort_kernel, &cfg) == cudaSuccess && resident >= nseg) break;
+    }
     const cudaError_t e = cudaLaunchKernelEx(&cfg, segsort_kernel, keys, key_type, n_total, seg, nseg, init, perm,
-                                             k0, k1, i0, i1);
+                                             k0, k1, i0, i1, cache_cap);
     return e == cudaSuccess ? LAMPA_OK : LAMPA_ERR_CUDA;
 }
 
