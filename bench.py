@@ -387,6 +387,50 @@ def run_plain(args):
         "kernels": {n: {"ms_per_launch": r["ms"] / r["launches"]} for n, r in prof.items()}}), flush=True)
 
 
+def run_layer(args):
+    """The layer's elementwise producers / consumers at the benchmark shape (not the headline metric): short
+    convolution on a [T, H*K] projection, gate inputs (g, beta, lambda) and the gated RMS norm of the output.
+    Each is timed alone with CUDA events, L2 flushed between launches; GB/s over the algorithmic bytes."""
+    from lampa_b200 import _lib as L
+    from lampa_b200.layer import ShortConvolution, gate_inputs, rms_norm_gated
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    T, Lv, dt = 61440, 17, torch.bfloat16
+    gen = torch.Generator().manual_seed(20259)
+    rnd = lambda *shape: torch.randn(*shape, generator=gen).to(dt).to(dev)
+    x = rnd(1, T, H * K)
+    conv = ShortConvolution(H * K, 4).to(dev).to(dt)
+    a, b, dl = rnd(1, T, H), rnd(1, T, H), rnd(1, T, H * Lv)
+    A_log, dtb, Lp = torch.zeros(H, device=dev), torch.zeros(H, device=dev), torch.ones(H, Lv, device=dev)
+    o, g, w = rnd(1, T, H, V), rnd(1, T, H, V), torch.ones(V, device=dev).to(dt)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    ops = {
+        "short_conv_fwd": (lambda: conv(x), 2 * x.numel() * 2),
+        "gate_inputs": (lambda: gate_inputs(a, b, dl, A_log, dtb, Lp, "positive"),
+                        a.numel() * (2 + 2 + 4 + 2) + dl.numel() * (2 + 2)),
+        "rmsnorm_gate": (lambda: rms_norm_gated(o, g, w, None, "swish", eps=1e-5), 3 * o.numel() * 2),
+    }
+    out = {}
+    for name, (fn, nbytes) in ops.items():
+        for _ in range(max(args.warmup, 3)):
+            fn()
+        L.profile_enable(True)
+        for _ in range(args.steps):
+            flush.zero_()
+            fn()
+        torch.cuda.synchronize()
+        prof = L.profile_read()
+        L.profile_enable(False)
+        ms = prof[name]["ms"] / prof[name]["launches"]
+        out[name] = {"us_per_launch": ms * 1e3, "algorithmic_bytes": nbytes, "gbs": nbytes / (ms * 1e-3) / 1e9,
+                     "frac_of_measured_hbm": nbytes / (ms * 1e-3) / 1e9 / peaks()["hbm_gbs"]}
+    print(json.dumps({"metric": "GB/s, layer producers/consumers", "unit": "GB/s", "n_gpus": 1, "steps": args.steps,
+                      "dtype": "bf16", "data": "synthetic",
+                      "config": {"workload": f"ShortConvolution [T={T}, D={H * K}, W=4] + gate inputs (H={H}, L={Lv}) + "
+                                             f"FusedRMSNormGated [{T * H} rows of {V}], L2 flushed between launches"},
+                      "kernels": out}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -397,14 +441,17 @@ def main():
     ap.add_argument("--cpu-sample", type=int, default=0, help="hits in the CPU baseline pass (default: all)")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer (end-to-end) leg")
     ap.add_argument("--hits", type=int, default=N_HITS, help="hits of the event (default: the 60k-hit workload)")
-    ap.add_argument("--workload", default="event", choices=["event", "plain"],
+    ap.add_argument("--workload", default="event", choices=["event", "plain", "layer"],
                     help="event: the headline LSH + hierarchical step; plain: configuration 1 "
-                         "(chunk_gated_delta_rule, T=65536, H=8, K=V=64, initial and final state), device-resident only")
+                         "(chunk_gated_delta_rule, T=65536, H=8, K=V=64, initial and final state), device-resident only; "
+                         "layer: the elementwise kernels around the op (short convolution, gate inputs, gated norm)")
     args = ap.parse_args()
     if args.hits != N_HITS:
         set_event_size(args.hits)
     if args.workload == "plain":
         run_plain(args)
+    elif args.workload == "layer":
+        run_layer(args)
     elif args.impl == "reference":
         run_reference(args)
     else:
