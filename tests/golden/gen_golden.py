@@ -193,7 +193,7 @@ def gen_layer(ref: str):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="path of the reference checkout")
     ap.add_argument("--only", default="", help="'geo' / 'layer': write only that fixture")
     args = ap.parse_args()
     ref = args.reference
