@@ -99,7 +99,15 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" :: "r"(smem_u32(bar)) : "memory");
 }
 
-__global__ void __launch_bounds__(UTHREADS, 1) gdn_out_hier_umma_kernel(GdnArgs a) {
+// Launch order of the (block, head) units.  A unit's time grows with the number of level pairs it
+// carries (3 to 5, from the set bits of its block index), and 240 units on 148 SMs leave the second
+// round partly empty: handing the long units out first lets the short ones fill the tail.
+struct UnitOrder {
+    int nbs;                    // blocks per sequence when all sequences are equally long and nbs <= 64, else 0
+    unsigned char order[64];    // block indices, most level pairs first
+};
+
+__global__ void __launch_bounds__(UTHREADS, 1) gdn_out_hier_umma_kernel(GdnArgs a, UnitOrder uo) {
     extern __shared__ __align__(1024) unsigned char smem[];
     uint64_t* full = reinterpret_cast<uint64_t*>(smem + SM_BAR);      // record landed            (tx count)
     uint64_t* sfree = full + UNST;                                      // stage consumed           (16 warps)
@@ -109,7 +117,16 @@ __global__ void __launch_bounds__(UTHREADS, 1) gdn_out_hier_umma_kernel(GdnArgs 
     uint32_t* tslot = reinterpret_cast<uint32_t*>(smem + SM_BAR + 256);
     float* sOT = reinterpret_cast<float*>(smem + SM_OT);
 
-    const int gb = blockIdx.x, h = blockIdx.y, H = a.H;
+    const int H = a.H;
+    int gb, h;
+    if (uo.nbs > 0) {
+        const int per_rank = H * a.nseq, r = blockIdx.x / per_rank, rem = blockIdx.x - r * per_rank;
+        h = rem % H;
+        gb = (rem / H) * uo.nbs + uo.order[r];
+    } else {
+        gb = blockIdx.x % a.nb_max;
+        h = blockIdx.x / a.nb_max;
+    }
     if (gb >= a.block_off[a.nseq]) return;
     const int seq = find_seq(a.block_off, a.nseq, gb);
     const int b = gb - a.block_off[seq];
@@ -342,8 +359,21 @@ int launch_out_hier_umma(const GdnArgs& a, cudaStream_t st) {
     if (smem > 227 * 1024 || a.nhigh_max > UNP) return LAMPA_ERR_UNSUPPORTED;
     if (cudaFuncSetAttribute(gdn_out_hier_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
         return LAMPA_ERR_CUDA;
+    UnitOrder uo;
+    uo.nbs = 0;
+    if (a.fixed_T > 0 && a.nseq > 0 && a.nb_max % a.nseq == 0 && a.nb_max / a.nseq <= 64) {
+        uo.nbs = a.nb_max / a.nseq;
+        int n = 0;
+        for (int pairs = UNP; pairs >= 0; --pairs)        // stable: block order kept inside a class
+            for (int b = 0; b < uo.nbs; ++b) {
+                int live = 0;
+                for (int lh = 0; lh < a.nhigh_max; ++lh) live += (b >> lh) & 1;
+                if ((BLOCK_LOG + live + 1) / 2 == pairs) uo.order[n++] = (unsigned char)b;
+            }
+        if (n != uo.nbs) uo.nbs = 0;
+    }
     ProfScope prof("gdn_out_hier_umma", st);
-    gdn_out_hier_umma_kernel<<<dim3(a.nb_max, a.H), UTHREADS, smem, st>>>(a);
+    gdn_out_hier_umma_kernel<<<dim3((unsigned)a.nb_max * a.H), UTHREADS, smem, st>>>(a, uo);
     return cudaGetLastError() == cudaSuccess ? LAMPA_OK : LAMPA_ERR_CUDA;
 }
 

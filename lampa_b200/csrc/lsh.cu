@@ -3,7 +3,9 @@
 #include <cooperative_groups.h>
 
 #include <algorithm>
+#include <map>
 #include <mutex>
+#include <tuple>
 
 #include "common.cuh"
 #include "profile.cuh"
@@ -368,6 +370,23 @@ static int sort_cluster_size(int nseg) {
     return cl;
 }
 
+// cudaOccupancyMaxActiveClusters for this kernel, remembered per (device, cluster size, cache size):
+// the answer does not change and the query costs tens of microseconds of host time.
+static int clusters_resident(const cudaLaunchConfig_t& cfg, int cl, int cache_cap) {
+    static std::mutex mu;
+    static std::map<std::tuple<int, int, int>, int> memo;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    const auto key = std::make_tuple(dev, cl, cache_cap);
+    std::lock_guard<std::mutex> lk(mu);
+    const auto it = memo.find(key);
+    if (it != memo.end()) return it->second;
+    int resident = 0;
+    if (cudaOccupancyMaxActiveClusters(&resident, segsort_kernel, &cfg) != cudaSuccess) resident = 0;
+    memo[key] = resident;
+    return resident;
+}
+
 static int launch_segsort(const void* keys, int key_type, int64_t n_total, const int64_t* seg, int nseg,
                           const int64_t* init, int64_t* perm, uint32_t* k0, uint32_t* k1, uint32_t* i0,
                           uint32_t* i1, cudaStream_t st) {
@@ -396,8 +415,7 @@ static int launch_segsort(const void* keys, int key_type, int64_t n_total, const
         cfg.attrs = attr;
         cfg.numAttrs = 1;
         if (cl == 1) break;
-        int resident = 0;
-        if (cudaOccupancyMaxActiveClusters(&resident, segsort_kernel, &cfg) == cudaSuccess && resident >= nseg) break;
+        if (clusters_resident(cfg, cl, cache_cap) >= nseg) break;
     }
     const cudaError_t e = cudaLaunchKernelEx(&cfg, segsort_kernel, keys, key_type, n_total, seg, nseg, init, perm,
                                              k0, k1, i0, i1, cache_cap);
