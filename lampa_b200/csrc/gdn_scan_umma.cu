@@ -38,12 +38,12 @@ using UR = Rec<UKD, UVD>;
 
 // shared-memory map (bytes); everything that tcgen05 reads is 1024-byte aligned
 constexpr int SM_BAR = 0;                    // full[UNST], mma[UNP] mbarriers, TMEM slot
-constexpr int SM_OT = 1024;                  // fp32 [2][64 tokens][64 v]: output transpose / pair-half sum
+constexpr int SM_OT = 1024;                  // two buffers (chunk parity) of fp32 [2][64 tokens][64 v]: output transpose / pair-half sum
 // TMEM columns (512 allocated): the states as bf16 A operands, 32 columns per pair, then two
 // 128-column accumulator buffers used by the pairs in turn
 constexpr int TM_A = 0;
 constexpr int TM_D = 192;
-constexpr int SM_STAGE = SM_OT + 2 * 64 * 64 * 4;
+constexpr int SM_STAGE = SM_OT + 2 * 2 * 64 * 64 * 4;
 constexpr int STAGE_TILES = UR::LAM_OFF;     // M | Q~ | B^T | O_local, then the lambda rows: the whole record
 __host__ __device__ constexpr int ustage_bytes(int LC) { return (STAGE_TILES + LC * CHUNK * 4 + 1023) / 1024 * 1024; }
 
@@ -309,10 +309,13 @@ __global__ void __launch_bounds__(UTHREADS, 1) gdn_out_hier_umma_kernel(GdnArgs 
                 __syncwarp();
                 if (lane == 0) mbar_arrive(dfree + p);
             }
-            // output: sum the two rows (levels) of the pairs through shared memory, add O_local, store
-            asm volatile("bar.sync 1, 512;\n" ::: "memory");       // previous chunk's transpose buffer fully read
+            // output: sum the two rows (levels) of the pairs through shared memory, add O_local, store.
+            // The transpose buffer alternates with the chunk, so one barrier per chunk is enough: a warp
+            // that runs ahead writes the other buffer, and it cannot get two chunks ahead of a warp that
+            // is still reading without passing the barrier in between.
+            float* sOTc = sOT + (i & 1) * (2 * 64 * 64);
 #pragma unroll
-            for (int j = 0; j < 16; ++j) sOT[(u * 64 + 16 * part + j) * 64 + v] = oacc[j];
+            for (int j = 0; j < 16; ++j) sOTc[(u * 64 + 16 * part + j) * 64 + v] = oacc[j];
             asm volatile("bar.sync 1, 512;\n" ::: "memory");
             {
                 const int tok = tid >> 3, col = (tid & 7) * 8;
@@ -322,8 +325,8 @@ __global__ void __launch_bounds__(UTHREADS, 1) gdn_out_hier_umma_kernel(GdnArgs 
                     float r[8];
 #pragma unroll
                     for (int q = 0; q < 2; ++q) {
-                        const float4 p0 = *reinterpret_cast<const float4*>(sOT + (0 * 64 + tok) * 64 + col + 4 * q);
-                        const float4 q0 = *reinterpret_cast<const float4*>(sOT + (1 * 64 + tok) * 64 + col + 4 * q);
+                        const float4 p0 = *reinterpret_cast<const float4*>(sOTc + (0 * 64 + tok) * 64 + col + 4 * q);
+                        const float4 q0 = *reinterpret_cast<const float4*>(sOTc + (1 * 64 + tok) * 64 + col + 4 * q);
                         const float4 o4 = *reinterpret_cast<const float4*>(sOl + tok * UR::OP + col + 4 * q);
                         r[4 * q] = p0.x + q0.x + o4.x; r[4 * q + 1] = p0.y + q0.y + o4.y;
                         r[4 * q + 2] = p0.z + q0.z + o4.z; r[4 * q + 3] = p0.w + q0.w + o4.w;
