@@ -21,7 +21,11 @@
 // no block-wide barrier on the state path).  MMA completion is tracked by tcgen05.commit on one
 // mbarrier per pair; every wait is bounded.  Measured alternatives that were slower: letting the
 // accumulator buffers alternate along the issue order (the next chunk's first MMA then overlaps the
-// last epilogue: +18 us), and issuing a pair's two TMEM loads together (+50 us, spills at 96 registers).
+// last epilogue: +18 us), three accumulator buffers for units of at most four pairs (+18 us), and issuing a
+// pair's two TMEM loads together (+50 us, spills at 96 registers).  In-kernel counters of one epilogue warp
+// (four pairs): 5.8 k cycles per chunk = record wait 0.5 k, waiting for MMAs 1.8 k, state update 1.5 k,
+// read-out 0.7 k, transpose + output 1.3 k.  More run-ahead for the tensor core never helped: an MMA in
+// flight and the epilogue's tcgen05.ld/st appear to take turns on tensor memory.
 #include "gdn.cuh"
 #include "profile.cuh"
 
