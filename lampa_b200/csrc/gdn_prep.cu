@@ -120,6 +120,22 @@ __device__ __forceinline__ void store_half_row_bf16(__nv_bfloat16* dst, const fl
     }
 }
 
+// Half of a token's lambda row (levels half, half + 2, ...) into shared memory: NIT loads in flight, then NIT stores.
+template <int NIT>
+__device__ __forceinline__ void stage_lambda(const void* lam, int dt, size_t base, int L, int half, bool valid, float* dst) {
+    float lv[NIT];
+#pragma unroll
+    for (int i = 0; i < NIT; ++i) {
+        const int l = half + 2 * i;
+        lv[i] = (valid && l < L) ? load_as_float(lam, base + l, dt) : 0.f;
+    }
+#pragma unroll
+    for (int i = 0; i < NIT; ++i) {
+        const int l = half + 2 * i;
+        if (l < L) dst[l] = lv[i];
+    }
+}
+
 template <int N>
 __device__ __forceinline__ void zero_acc(float (&acc)[N][4]) {
 #pragma unroll
@@ -239,18 +255,11 @@ __global__ void __launch_bounds__(128, 4) gdn_prep_kernel(GdnArgs a) {
             gv = load_as_float(a.g, (size_t)(t0 + tid) * H + h, a.gb_dt);
             bv = load_as_float(a.beta, (size_t)(t0 + tid) * H + h, a.gb_dt);
         }
-        if (HIER) {   // all of the row's loads in flight before the first store (L <= 40)
-            float lv[20];
-#pragma unroll
-            for (int i = 0; i < 20; ++i) {
-                const int l = half + 2 * i;
-                lv[i] = (valid && l < a.L) ? load_as_float(a.lam, (tok * H + h) * a.L + l, a.lam_dt) : 0.f;
-            }
-#pragma unroll
-            for (int i = 0; i < 20; ++i) {
-                const int l = half + 2 * i;
-                if (l < a.L) sLam[r * LP + l] = lv[i];
-            }
+        if (HIER) {   // all of the row's loads in flight before the first store; the unrolled length follows L
+            const size_t lam_base = (tok * H + h) * a.L;
+            if (a.L <= 18) stage_lambda<9>(a.lam, a.lam_dt, lam_base, a.L, half, valid, sLam + r * LP);
+            else if (a.L <= 24) stage_lambda<12>(a.lam, a.lam_dt, lam_base, a.L, half, valid, sLam + r * LP);
+            else stage_lambda<20>(a.lam, a.lam_dt, lam_base, a.L, half, valid, sLam + r * LP);
         }
         if (h == 0) {   // L2 prefetch of the token rows (all heads) of a chunk ~80 chunks ahead
             ChunkLoc l2;
