@@ -302,10 +302,15 @@ __global__ void __launch_bounds__(128, 4) gdn_prep_kernel(GdnArgs a) {
             for (int i = 0; i < KD / 2; ++i) x[i] *= rn;
         }
         store_half_row_bf16<KD / 2>(sK + r * KP + half * (KD / 2), x);
-        float y[VD / 2];
-        if (two_byte) convert_half_row<VD>(rv, a.qkv_dt, y);
-        else load_half_row<VD>(a.v, a.qkv_dt, (tok * H + h) * VD + half * (VD / 2), valid, y);
-        store_half_row_bf16<VD / 2>(sV + r * VP + half * (VD / 2), y);
+        if (a.qkv_dt == LAMPA_BF16) {   // v is used as it is: the raw 16-byte pieces go straight to shared memory
+#pragma unroll
+            for (int i = 0; i < VD / 16; ++i) reinterpret_cast<uint4*>(sV + r * VP + half * (VD / 2))[i] = rv[i];
+        } else {
+            float y[VD / 2];
+            if (two_byte) convert_half_row<VD>(rv, a.qkv_dt, y);
+            else load_half_row<VD>(a.v, a.qkv_dt, (tok * H + h) * VD + half * (VD / 2), valid, y);
+            store_half_row_bf16<VD / 2>(sV + r * VP + half * (VD / 2), y);
+        }
 
         if (tid < CHUNK) {
             float cs = gv;
