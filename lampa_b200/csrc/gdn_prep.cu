@@ -358,12 +358,13 @@ __global__ void __launch_bounds__(128, 4) gdn_prep_kernel(GdnArgs a) {
             float acc[8][4];
             zero_acc<8>(acc);
             warp_gemm<8, KD, false, false>(acc, sK, KP, m0, sK, KP, 0, lane, KD, m0 + 16);
+            const float b2[2] = {sBeta[m0 + gq], sBeta[m0 + gq + 8]};   // read before the stores below: they may alias for the compiler
 #pragma unroll
             for (int nt = 0; nt < 8; ++nt)
 #pragma unroll
                 for (int hh = 0; hh < 2; ++hh) {
                     const int i = m0 + gq + hh * 8, j = nt * 8 + 2 * tq;
-                    const float bb = sBeta[i];
+                    const float bb = b2[hh];
                     *reinterpret_cast<float2*>(sA + i * PA + j) =
                         make_float2(i > j ? bb * acc[nt][2 * hh] : 0.f, i > j + 1 ? bb * acc[nt][2 * hh + 1] : 0.f);
                 }
@@ -522,18 +523,34 @@ __global__ void __launch_bounds__(128, 4) gdn_prep_kernel(GdnArgs a) {
         }
         // Pm = R .* E .* lambda, as A fragments;  O_local = s Pm V
         {
+            // level(i, j) = bit_length(i ^ j).  Off the diagonal 8x8 tile it depends on the tile only
+            // (3 + bit_length(i/8 ^ j/8)): one lambda per (row, tile) serves both of the thread's columns.
+            const float gi2[2] = {sG[m0 + gq], sG[m0 + gq + 8]};
 #pragma unroll
-            for (int nt = 0; nt < 8; ++nt)
+            for (int nt = 0; nt < 8; ++nt) {
+                const float2 gj = *reinterpret_cast<const float2*>(sG + nt * 8 + 2 * tq);
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const int i = m0 + gq + (e >> 1) * 8, j = nt * 8 + 2 * tq + (e & 1);
-                    float p = 0.f;
-                    if (i >= j && nt * 8 < m0 + 16) {
-                        p = racc[nt][e] * __expf(sG[i] - sG[j]);
-                        if (HIER) p *= sLam[i * LP + (32 - __clz(i ^ j))];
+                for (int hh = 0; hh < 2; ++hh) {
+                    const int i = m0 + gq + hh * 8, j = nt * 8 + 2 * tq;
+                    const int it = (m0 >> 3) + hh;                     // the row's 8x8 tile index (warp-uniform)
+                    float p0 = 0.f, p1 = 0.f;
+                    if (nt <= it) {
+                        if (i >= j) p0 = racc[nt][2 * hh] * __expf(gi2[hh] - gj.x);
+                        if (i >= j + 1) p1 = racc[nt][2 * hh + 1] * __expf(gi2[hh] - gj.y);
+                        if (HIER) {
+                            if (nt < it) {
+                                const float lt = sLam[i * LP + 3 + (32 - __clz(it ^ nt))];
+                                p0 *= lt; p1 *= lt;
+                            } else {
+                                p0 *= sLam[i * LP + (32 - __clz(i ^ j))];
+                                p1 *= sLam[i * LP + (32 - __clz(i ^ (j + 1)))];
+                            }
+                        }
                     }
-                    racc[nt][e] = p;
+                    racc[nt][2 * hh] = p0;
+                    racc[nt][2 * hh + 1] = p1;
                 }
+            }
 #pragma unroll
             for (int kk = 0; kk < 4; ++kk) {
                 ra[kk][0] = pack_bf16x2(racc[2 * kk][0], racc[2 * kk][1]);
