@@ -482,10 +482,12 @@ __global__ void __launch_bounds__(128, 4) gdn_prep_kernel(GdnArgs a) {
         warp_gemm<8, KD, false, false>(racc, sQ, KP, m0, sK, KP, 0, lane, KD, m0 + 16);
 #pragma unroll
         for (int nt = 0; nt < 8; ++nt)
+            if (nt >= (m0 >> 3)) {       // only the warp's two diagonal 8-column tiles can hold i < j
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const int i = m0 + gq + (e >> 1) * 8, j = nt * 8 + 2 * tq + (e & 1);
-                if (i < j) racc[nt][e] = 0.f;
+                for (int e = 0; e < 4; ++e) {
+                    const int i = m0 + gq + (e >> 1) * 8, j = nt * 8 + 2 * tq + (e & 1);
+                    if (i < j) racc[nt][e] = 0.f;
+                }
             }
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk) {
@@ -510,12 +512,13 @@ __global__ void __launch_bounds__(128, 4) gdn_prep_kernel(GdnArgs a) {
             zero_acc<KD / 8>(acc);
             warp_gemm_ra<KD / 8, 4, true>(acc, ra, sK, KP, 0, lane, m0 + 16, KD);
             __nv_bfloat16* gQ = reinterpret_cast<__nv_bfloat16*>(rec + R::QT_OFF);
+            const float fq[2] = {osc * sEG[m0 + gq], osc * sEG[m0 + gq + 8]};
 #pragma unroll
             for (int nt = 0; nt < KD / 8; ++nt)
 #pragma unroll
                 for (int hh = 0; hh < 2; ++hh) {
                     const int i = m0 + gq + hh * 8, j = nt * 8 + 2 * tq;
-                    const float f = osc * sEG[i];
+                    const float f = fq[hh];
                     const float2 qv = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(sQ + i * KP + j));
                     *reinterpret_cast<uint32_t*>(gQ + R::T::off(i, j)) =
                         pack_bf16x2(f * (qv.x - acc[nt][2 * hh]), f * (qv.y - acc[nt][2 * hh + 1]));
@@ -576,6 +579,7 @@ __global__ void __launch_bounds__(128, 4) gdn_prep_kernel(GdnArgs a) {
             float acc[VD / 8][4];
             zero_acc<VD / 8>(acc);
             const float g_lo = sG[m0 + gq], g_hi = sG[m0 + gq + 8];
+            const float fu[2] = {sEGl[m0 + gq], sEGl[m0 + gq + 8]};   // read before the stores to U^ below
 #pragma unroll
             for (int kk = 0; kk < 4; ++kk) {
                 if (kk * 16 < m0 + 16) {
@@ -584,11 +588,17 @@ __global__ void __launch_bounds__(128, 4) gdn_prep_kernel(GdnArgs a) {
 #pragma unroll
                     for (int x = 0; x < 4; ++x) {
                         const int i = m0 + gq + (x & 1) * 8, j = kk * 16 + (x >> 1) * 8 + 2 * tq;
-                        const float gi = (x & 1) ? g_hi : g_lo;
-                        const float2 w = unpack_bf16x2(af[x]);
-                        const float u0 = (i >= j) ? w.x * __expf(gi - sG[j]) : 0.f;
-                        const float u1 = (i >= j + 1) ? w.y * __expf(gi - sG[j + 1]) : 0.f;
-                        af[x] = pack_bf16x2(u0, u1);
+                        const int it = (m0 >> 3) + (x & 1), jt = 2 * kk + (x >> 1);   // 8x8 tile of the row / of the columns
+                        if (jt > it) {
+                            af[x] = 0u;                                           // above the diagonal
+                        } else {
+                            const float gi = (x & 1) ? g_hi : g_lo;
+                            const float2 gj = *reinterpret_cast<const float2*>(sG + j);
+                            const float2 w = unpack_bf16x2(af[x]);
+                            const float u0 = (i >= j) ? w.x * __expf(gi - gj.x) : 0.f;
+                            const float u1 = (i >= j + 1) ? w.y * __expf(gi - gj.y) : 0.f;
+                            af[x] = pack_bf16x2(u0, u1);
+                        }
                     }
 #pragma unroll
                     for (int nt = 0; nt < VD / 8; nt += 2) {
@@ -604,7 +614,7 @@ __global__ void __launch_bounds__(128, 4) gdn_prep_kernel(GdnArgs a) {
 #pragma unroll
                 for (int hh = 0; hh < 2; ++hh) {
                     const int i = m0 + gq + hh * 8, j = nt * 8 + 2 * tq;
-                    const float f = sEGl[i];
+                    const float f = fu[hh];
                     *reinterpret_cast<uint32_t*>(sUh + i * VP + j) = pack_bf16x2(f * acc[nt][2 * hh], f * acc[nt][2 * hh + 1]);
                 }
         }
