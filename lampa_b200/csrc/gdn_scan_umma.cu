@@ -241,12 +241,30 @@ __global__ void __launch_bounds__(UTHREADS, 1) gdn_out_hier_umma_kernel(GdnArgs 
         }
     } else {
         // ---- epilogue warps: every warp advances 16 state columns and reads 16 tokens of its 32 rows ----
+        // per pair, the lambda row of this thread's slot, and the slots that exist and have a lambda row
+        uint32_t lam_pack = 0, slot_ok = 0;          // 5 bits per pair: the lambda row of slot 2p + u
+#pragma unroll
+        for (int p = 0; p < UNP; ++p) {
+            const int s = 2 * p + u;
+            const int row = s < BLOCK_LOG ? s : BLOCK_LOG + (int)((live_pack >> (4 * max(s - BLOCK_LOG, 0))) & 15);
+            lam_pack |= (uint32_t)(row & 31) << (5 * p);
+        }
+        for (int s = 0; s < nslots; ++s) {
+            const int row = s < BLOCK_LOG ? s : BLOCK_LOG + (int)((live_pack >> (4 * (s - BLOCK_LOG))) & 15);
+            if (row < a.LC) slot_ok |= 1u << s;      // a missing row is only reachable when the level check already failed
+        }
         for (int i = 0; i < nsteps; ++i) {
             const unsigned char* st = stage0 + (size_t)(i % UNST) * stage_bytes;
             const float* sLam = reinterpret_cast<const float*>(st + STAGE_TILES);
             const unsigned char* sBt = st + UR::BT_OFF;
             const int n = b * BLOCK_CHUNKS + i;
             const float* sOl = reinterpret_cast<const float*>(st + UR::OL_OFF);
+            // what this chunk does to each slot, as bit masks: in-block level s is read when bit s of n is
+            // set and cleared when its period of 2^(s+1) chunks ends (all of bits 0..s set); the cross-block
+            // slots are read by every chunk
+            const uint32_t low = (uint32_t)n & (BLOCK_CHUNKS - 1);
+            const uint32_t read_mask = (low | (~0u << BLOCK_LOG)) & slot_ok;
+            const uint32_t clear_mask = low & ~(low + 1u) & (BLOCK_CHUNKS - 1);      // trailing ones of n
             mbar_wait(full + (i % UNST), (uint32_t)((i / UNST) & 1), dead, a.status, 250 + i);
             // this row's 16 columns of B^T, shared by every level that collects in this chunk
             const uint4 bq0 = *reinterpret_cast<const uint4*>(sBt + v * 128 + (((2 * part) ^ (v & 7)) << 4));
@@ -261,19 +279,8 @@ __global__ void __launch_bounds__(UTHREADS, 1) gdn_out_hier_umma_kernel(GdnArgs 
                 tc_fence_after();
                 const int s = 2 * p + u;
                 const bool active = s < nslots;
-                bool do_read = false, clear = false, add_b = false;
-                int lam_row = 0;
-                if (s < BLOCK_LOG) {
-                    const int per = 2 << s, pos = n & (per - 1), bit = (n >> s) & 1;
-                    do_read = bit != 0;
-                    clear = pos == per - 1;
-                    add_b = bit == 0;
-                    lam_row = s;
-                } else if (active) {
-                    do_read = true;
-                    lam_row = BLOCK_LOG + ((live_pack >> (4 * (s - BLOCK_LOG))) & 15);
-                }
-                if (lam_row >= a.LC) do_read = false;      // only reachable when the level check already failed
+                const bool do_read = (read_mask >> s) & 1u, clear = (clear_mask >> s) & 1u, add_b = !((n >> s) & 1) && s < BLOCK_LOG;
+                const int lam_row = (int)((lam_pack >> (5 * p)) & 31u);
                 const uint32_t tcol = tlane + (uint32_t)(TM_D + (p & 1) * 128);
                 // state path first: the next chunk's MMA of this pair waits for it
                 if (active && i + 1 < nsteps) {
