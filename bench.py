@@ -374,7 +374,7 @@ def run_ours(args):
         }
         # DRAM bytes (read + write) per launch on the default workload, from the committed ncu capture
         # profiles/kernels_bench_60k_hier.md
-        ncu_traffic = {"gdn_prep_hier": 491.8e6, "gdn_out_hier_umma": 420.4e6, "gdn_compose": 192.5e6,
+        ncu_traffic = {"gdn_prep_hier": 493.3e6, "gdn_out_hier_umma": 421.4e6, "gdn_compose": 192.3e6,
                        "gdn_level_hier": 6.6e6, "segsort": 5.8e6, "lsh_hash": 5.8e6, "permute_rows": 43.3e6}
         bound, units = alg.get(dom, ("hbm", 0))
         dur_s = per_kernel[dom]["ms_per_launch"] * 1e-3
