@@ -305,6 +305,42 @@ int lampa_rmsnorm_gate(const void* x, const void* g, const void* weight, int64_t
                        int32_t dtype, int32_t w_dtype, float eps, int32_t sigmoid_only, void* y,
                        void* stream);
 /*
+ * Bucketed RBF-kernel attention of the HEPT layer, fp32.  Per (round, head) the n hits are taken in
+ * the order q_pos / k_pos (int64 [rounds][heads][n]; NULL: rows are already in order), cut into
+ * buckets of `bucket` consecutive hits (n % bucket == 0, bucket <= 128), and inside a bucket
+ *   p_ij = exp(min(0, q_i.k_j - |q_i|^2/2 - |k_j|^2/2)),  denom_i = sum_j p_ij + 1e-20,
+ *   so_i = sum_j p_ij v_j.
+ * q, k: [heads][n][dq], v: [heads][n][dv], shared by all rounds and gathered by position; with
+ * inputs_per_round != 0 they carry a leading [rounds] axis (rows pre-sorted per round).
+ * so [rounds][heads][n][dv] and denom [rounds][heads][n]: row i of a bucket is written at its
+ * sorted place (scatter == 0: the outputs of qkv_res) or at hit q_pos[i] (scatter != 0: after
+ * unsort_from_buckets with the inverse permutation).  dv <= 128; shared memory bounds dq
+ * (LAMPA_ERR_UNSUPPORTED beyond).
+ * Replaces: qkv_res (models/attention/hept.py:22-33) and, with positions, the sort_to_buckets /
+ * unsort_from_buckets calls around it in HEPTAttention.forward (hept.py:141-150).
+ */
+int lampa_bucket_rbf_attn(const float* q, const float* k, const float* v, const int64_t* q_pos,
+                          const int64_t* k_pos, int32_t rounds, int32_t heads, int64_t n, int32_t bucket,
+                          int32_t dq, int32_t dv, int32_t inputs_per_round, int32_t scatter, float* so,
+                          float* denom, void* stream);
+/*
+ * out[row][:] = (sum over rounds of so[r][row][:]) / (sum over rounds of denom[r][row]), rounds added
+ * in order.  rows = heads * n.  Replaces: `o.sum(dim=0) / logits.sum(dim=0)` (hept.py:151).
+ */
+int lampa_bucket_attn_combine(const float* so, const float* denom, int32_t rounds, int64_t rows,
+                              int32_t dv, float* out, void* stream);
+/*
+ * Inputs of the bucket attention from the layer's projections: query, key, value [n][heads][d]
+ * (token-major), coords [n][cd], scale [heads][cd] (= sqrt(2 * per-head coordinate weights));
+ * q_hat = k_hat's coordinate part = scale * coords, appended to query / key; outputs head-major
+ * q_hat, k_hat [heads][n][d + cd], v_out [heads][n][d] (may be NULL); rows >= raw_size zeroed.
+ * Replaces: the elementwise part of prep_qk and the rearrange / zero-padding statements of
+ * HEPTAttention.forward (hept.py:55-63, 121-126).
+ */
+int lampa_hept_prep_qk(const float* query, const float* key, const float* value, const float* scale,
+                       const float* coords, int64_t n, int32_t heads, int32_t d, int32_t cd,
+                       int64_t raw_size, float* q_hat, float* k_hat, float* v_out, void* stream);
+/*
  * Per-kernel timing for benchmarks (no counterpart in the reference, which has no timing code).
  * lampa_profile_enable(1) makes every later launch of this library record a pair of CUDA events
  * on its stream; lampa_profile_enable(0) stops and clears.  lampa_profile_read synchronises on

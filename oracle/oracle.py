@@ -337,3 +337,61 @@ def rmsnorm_gate(x, g, w=None, eps=1e-5, sigmoid_only=False):
         y = y * np.asarray(w, np.float32)
     y = y * _sigmoid(g) if sigmoid_only else y * g * _sigmoid(g)
     return y.astype(np.float32)
+
+
+# ---- bucketed RBF-kernel attention of the HEPT layer (numpy, float64 accumulation) --------------
+
+def qkv_res(s_query, s_key, s_value):
+    """models/attention/hept.py:22-33 on rows already in bucket order [..., bucketsz, d]:
+    p = exp(min(0, q.k - |q|^2/2 - |k|^2/2)), denom = sum_j p + 1e-20, so = p @ v.  Computed in
+    float64 from the fp32 inputs: the exponent is a difference of large terms, and the test
+    tolerance is stated against this value."""
+    q = np.asarray(s_query, np.float64)
+    k = np.asarray(s_key, np.float64)
+    v = np.asarray(s_value, np.float64)
+    qs = -0.5 * (q * q).sum(-1, keepdims=True)
+    ks = -0.5 * (k * k).sum(-1, keepdims=True)
+    d = np.einsum("...id,...jd->...ij", q, k) + qs + np.swapaxes(ks, -1, -2)
+    p = np.exp(np.minimum(d, 0.0))
+    return p.sum(-1, keepdims=True) + 1e-20, np.einsum("...ij,...jd->...id", p, v)
+
+
+def hept_prep_qk(query, key, w, coords, raw_size=None):
+    """prep_qk (hept.py:55-63) followed by the head-major rearrange and the zeroing of padded rows
+    (hept.py:121-126), fp32 with one rounding per elementwise op: returns q_hat, k_hat
+    [heads, N, d + coords_dim]."""
+    query = np.asarray(query, np.float32)
+    key = np.asarray(key, np.float32)
+    w = np.asarray(w, np.float32)
+    coords = np.asarray(coords, np.float32)
+    qw = np.exp(np.minimum(w.sum(1), np.float32(50))).sum(-1).astype(np.float32)          # [heads, r]
+    scale = np.sqrt(np.float32(2) * np.concatenate([qw[:, :1], qw], -1)).astype(np.float32)
+    r = (scale[None] * coords[:, None]).astype(np.float32)                                  # [N, heads, cd]
+    q_hat = np.concatenate([query, r], -1).transpose(1, 0, 2).copy()
+    k_hat = np.concatenate([key, r], -1).transpose(1, 0, 2).copy()
+    if raw_size is not None:
+        q_hat[:, raw_size:] = 0
+        k_hat[:, raw_size:] = 0
+    return q_hat, k_hat
+
+
+def hept_bucket_attention(q_hat, k_hat, value, q_pos, k_pos, block: int):
+    """hept.py:141-151: gather into bucket order per (round, head), qkv_res, scatter back to hit
+    order, sum the rounds, so / denom.  q_hat, k_hat [heads, N, dq], value [heads, N, dv],
+    positions [rounds, heads, N].  Returns (out [heads, N, dv], o [rounds, heads, N, dv],
+    logits [rounds, heads, N, 1]) in float64."""
+    q_hat = np.asarray(q_hat, np.float32)
+    k_hat = np.asarray(k_hat, np.float32)
+    value = np.asarray(value, np.float32)
+    C, H, N = q_pos.shape
+    o = np.zeros((C, H, N, value.shape[-1]), np.float64)
+    lg = np.zeros((C, H, N, 1), np.float64)
+    for c in range(C):
+        for h in range(H):
+            sq = q_hat[h][q_pos[c, h]].reshape(N // block, block, -1)
+            sk = k_hat[h][k_pos[c, h]].reshape(N // block, block, -1)
+            sv = value[h][k_pos[c, h]].reshape(N // block, block, -1)
+            den, so = qkv_res(sq, sk, sv)
+            o[c, h, q_pos[c, h]] = so.reshape(N, -1)
+            lg[c, h, q_pos[c, h]] = den.reshape(N, 1)
+    return o.sum(0) / lg.sum(0), o, lg

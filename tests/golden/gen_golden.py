@@ -191,15 +191,64 @@ def gen_layer(ref: str):
     print("layer ok", tuple(y.shape), float(y.abs().max()), float(yn.abs().max()))
 
 
+def gen_hept(ref: str):
+    """Bucketed attention of the HEPT layer: prep_qk, sort_to_buckets, qkv_res, unsort_from_buckets
+    and the combination over rounds (models/attention/hept.py:9-33, 55-63, 141-151), run with the
+    reference's functions on seeded inputs with random bucket orders."""
+    einops = __import__("einops")
+    hu = load_defs(os.path.join(ref, "models", "model_utils", "hash_utils.py"),
+                   {"batched_index_select", "invert_permutation"}, extra={"rearrange": einops.rearrange})
+    hp = load_defs(os.path.join(ref, "models", "attention", "hept.py"),
+                   {"sort_to_buckets", "unsort_from_buckets", "qkv_res", "prep_qk"},
+                   extra={"rearrange": einops.rearrange, "List": list,
+                          "batched_index_select": hu["batched_index_select"]})
+    rearrange = einops.rearrange
+    raw, n, block, heads, rounds, d, cd, nw = 570, 600, 100, 3, 3, 12, 6, 4
+    gen = torch.Generator().manual_seed(777)
+    query = torch.randn(n, heads, d, generator=gen) * 0.7
+    key = query + 0.4 * torch.randn(n, heads, d, generator=gen)
+    value = torch.randn(n, heads, d, generator=gen)
+    coords = torch.randn(n, cd, generator=gen) * 0.5
+    coords[raw:] = 0.0
+    w = torch.randn(heads, d, cd - 1, nw, generator=gen) * 0.3 - 0.6
+    q_pos = torch.stack([torch.stack([torch.randperm(n, generator=gen) for _ in range(heads)]) for _ in range(rounds)])
+    k_pos = torch.stack([torch.stack([torch.randperm(n, generator=gen) for _ in range(heads)]) for _ in range(rounds)])
+    with torch.no_grad():
+        q_hat, k_hat = hp["prep_qk"](query, key, w, coords)
+        q_hat = rearrange(q_hat, "n h d -> h n d").contiguous()
+        k_hat = rearrange(k_hat, "n h d -> h n d").contiguous()
+        v = rearrange(value, "n h d -> h n d").contiguous()
+        q_hat[:, raw:] = 0.0
+        k_hat[:, raw:] = 0.0
+        v[:, raw:] = 0.0
+        s_query = hp["sort_to_buckets"](q_hat, q_pos, block)
+        s_key = hp["sort_to_buckets"](k_hat, k_pos, block)
+        s_value = hp["sort_to_buckets"](v, k_pos, block)
+        denom, so = hp["qkv_res"](s_query, s_key, s_value)
+        q_rev = hu["invert_permutation"](q_pos)
+        o = hp["unsort_from_buckets"](so, q_rev)
+        logits = hp["unsort_from_buckets"](denom, q_rev)
+        out = o.sum(dim=0) / logits.sum(dim=0)
+    np.savez_compressed(
+        os.path.join(HERE, "hept_bucket_attn.npz"),
+        query=query.numpy(), key=key.numpy(), value=value.numpy(), coords=coords.numpy(), w=w.numpy(),
+        q_pos=q_pos.numpy(), k_pos=k_pos.numpy(), raw_size=np.int64(raw), block_size=np.int64(block),
+        q_hat=q_hat.numpy(), k_hat=k_hat.numpy(), v=v.numpy(), denom=denom.numpy(), so=so.numpy(),
+        o=o.numpy(), logits=logits.numpy(), out=out.numpy())
+    print("hept ok", tuple(so.shape), tuple(out.shape), float(denom.min()), float(denom.max()))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", required=True, help="path of the reference checkout")
-    ap.add_argument("--only", default="", help="'geo' / 'layer': write only that fixture")
+    ap.add_argument("--only", default="", help="'geo' / 'layer' / 'hept': write only that fixture")
     args = ap.parse_args()
     ref = args.reference
     torch.set_num_threads(8)
     if args.only in ("", "geo"):
         gen_geo(ref)
+    if args.only in ("", "hept"):
+        gen_hept(args.reference)
     if args.only in ("", "layer"):
         gen_layer(ref)
     if args.only:

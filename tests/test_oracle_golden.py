@@ -163,3 +163,24 @@ def test_layer_ops_against_reference_fixture(golden_dir):
     np.testing.assert_array_equal(cs, z["cache_step"])
     np.testing.assert_allclose(oracle.rmsnorm_gate(z["norm_x"], z["norm_g"], z["norm_w"], 1e-5), z["norm_y"],
                                rtol=1e-5, atol=1e-5)
+
+
+def test_bucket_attention_against_reference_fixture(golden_dir):
+    """The float64 restatement of the HEPT bucket attention against the reference's fp32 run."""
+    z = np.load(os.path.join(golden_dir, "hept_bucket_attn.npz"))
+    raw, block = int(z["raw_size"]), int(z["block_size"])
+    q_hat, k_hat = oracle.hept_prep_qk(z["query"], z["key"], z["w"], z["coords"], raw)
+    np.testing.assert_allclose(q_hat, z["q_hat"], rtol=2e-6, atol=1e-7)
+    np.testing.assert_allclose(k_hat, z["k_hat"], rtol=2e-6, atol=1e-7)
+    C, H, N = z["q_pos"].shape
+    sq = np.stack([np.stack([z["q_hat"][h][z["q_pos"][c, h]] for h in range(H)]) for c in range(C)])
+    sk = np.stack([np.stack([z["k_hat"][h][z["k_pos"][c, h]] for h in range(H)]) for c in range(C)])
+    sv = np.stack([np.stack([z["v"][h][z["k_pos"][c, h]] for h in range(H)]) for c in range(C)])
+    shape = (C, H, N // block, block, -1)
+    den, so = oracle.qkv_res(sq.reshape(shape), sk.reshape(shape), sv.reshape(shape))
+    np.testing.assert_allclose(den, z["denom"], rtol=2e-5)
+    np.testing.assert_allclose(so, z["so"], rtol=2e-5, atol=2e-5)
+    out, o, lg = oracle.hept_bucket_attention(z["q_hat"], z["k_hat"], z["v"], z["q_pos"], z["k_pos"], block)
+    np.testing.assert_allclose(o, z["o"], rtol=2e-5, atol=2e-5)
+    np.testing.assert_allclose(lg, z["logits"], rtol=2e-5)
+    np.testing.assert_allclose(out, z["out"], rtol=5e-5, atol=2e-5)
