@@ -310,8 +310,11 @@ int lampa_rmsnorm_gate(const void* x, const void* g, const void* weight, int64_t
  * buckets of `bucket` consecutive hits (n % bucket == 0, bucket <= 128), and inside a bucket
  *   p_ij = exp(min(0, q_i.k_j - |q_i|^2/2 - |k_j|^2/2)),  denom_i = sum_j p_ij + 1e-20,
  *   so_i = sum_j p_ij v_j.
- * q, k: [heads][n][dq], v: [heads][n][dv], shared by all rounds and gathered by position; with
- * inputs_per_round != 0 they carry a leading [rounds] axis (rows pre-sorted per round).
+ * q, k: [heads][n] rows of dq floats, ldq floats apart; v: [heads][n] rows of dv floats, ldv apart;
+ * shared by all rounds and gathered by position; with inputs_per_round != 0 they carry a leading
+ * [rounds] axis (rows pre-sorted per round).  Rows are fetched as 16-byte pieces when the base is
+ * 16-byte aligned and the pitch is a multiple of 4 and at least the width rounded up to 4; the
+ * padding columns of such rows are read and must be zero (lampa_hept_prep_qk writes them so).
  * so [rounds][heads][n][dv] and denom [rounds][heads][n]: row i of a bucket is written at its
  * sorted place (scatter == 0: the outputs of qkv_res) or at hit q_pos[i] (scatter != 0: after
  * unsort_from_buckets with the inverse permutation).  dv <= 128; shared memory bounds dq
@@ -321,8 +324,8 @@ int lampa_rmsnorm_gate(const void* x, const void* g, const void* weight, int64_t
  */
 int lampa_bucket_rbf_attn(const float* q, const float* k, const float* v, const int64_t* q_pos,
                           const int64_t* k_pos, int32_t rounds, int32_t heads, int64_t n, int32_t bucket,
-                          int32_t dq, int32_t dv, int32_t inputs_per_round, int32_t scatter, float* so,
-                          float* denom, void* stream);
+                          int32_t dq, int32_t dv, int32_t ldq, int32_t ldv, int32_t inputs_per_round,
+                          int32_t scatter, float* so, float* denom, void* stream);
 /*
  * out[row][:] = (sum over rounds of so[r][row][:]) / (sum over rounds of denom[r][row]), rounds added
  * in order.  rows = heads * n.  Replaces: `o.sum(dim=0) / logits.sum(dim=0)` (hept.py:151).
@@ -333,13 +336,15 @@ int lampa_bucket_attn_combine(const float* so, const float* denom, int32_t round
  * Inputs of the bucket attention from the layer's projections: query, key, value [n][heads][d]
  * (token-major), coords [n][cd], scale [heads][cd] (= sqrt(2 * per-head coordinate weights));
  * q_hat = k_hat's coordinate part = scale * coords, appended to query / key; outputs head-major
- * q_hat, k_hat [heads][n][d + cd], v_out [heads][n][d] (may be NULL); rows >= raw_size zeroed.
+ * q_hat, k_hat [heads][n] rows of d + cd floats, ldq >= d + cd floats apart, the padding columns
+ * zero; v_out [heads][n][d] (may be NULL); rows >= raw_size zeroed.
  * Replaces: the elementwise part of prep_qk and the rearrange / zero-padding statements of
  * HEPTAttention.forward (hept.py:55-63, 121-126).
  */
 int lampa_hept_prep_qk(const float* query, const float* key, const float* value, const float* scale,
                        const float* coords, int64_t n, int32_t heads, int32_t d, int32_t cd,
-                       int64_t raw_size, float* q_hat, float* k_hat, float* v_out, void* stream);
+                       int32_t ldq, int64_t raw_size, float* q_hat, float* k_hat, float* v_out,
+                       void* stream);
 /*
  * Per-kernel timing for benchmarks (no counterpart in the reference, which has no timing code).
  * lampa_profile_enable(1) makes every later launch of this library record a pair of CUDA events

@@ -70,9 +70,9 @@ def lib() -> ctypes.CDLL:
         L.lampa_row_range.argtypes = [vp, vp, i32, i64, vp, vp, vp, vp]
         L.lampa_quantile_regions.argtypes = [vp, vp, i32, i64, vp, vp]
         L.lampa_geo_keys.argtypes = [vp] * 8 + [i32, i64, i64, vp, vp]
-        L.lampa_bucket_rbf_attn.argtypes = [vp] * 5 + [i32, i32, i64, i32, i32, i32, i32, i32, vp, vp, vp]
+        L.lampa_bucket_rbf_attn.argtypes = [vp] * 5 + [i32, i32, i64, i32, i32, i32, i32, i32, i32, i32, vp, vp, vp]
         L.lampa_bucket_attn_combine.argtypes = [vp, vp, i32, i64, i32, vp, vp]
-        L.lampa_hept_prep_qk.argtypes = [vp] * 5 + [i64, i32, i32, i32, i64, vp, vp, vp, vp]
+        L.lampa_hept_prep_qk.argtypes = [vp] * 5 + [i64, i32, i32, i32, i32, i64, vp, vp, vp, vp]
         L.lampa_short_conv_fwd.argtypes = [vp, vp, vp, vp, vp, i32, i64, i64, i32, i32, i32, i32, i32, vp, vp, i32, vp]
         L.lampa_short_conv_step.argtypes = [vp, vp, vp, vp, vp, i64, i32, i32, i32, i32, i32, vp, vp]
         L.lampa_gate_inputs.argtypes = [vp] * 7 + [i64, i32, i32, i32, i32, i32, i32, vp, vp, vp, vp]

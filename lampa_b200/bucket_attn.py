@@ -25,6 +25,24 @@ def _f32(t: torch.Tensor) -> torch.Tensor:
     return t.contiguous()
 
 
+def _rows(t: torch.Tensor):
+    """(tensor, row pitch) of a [..., rows, width] fp32 tensor: a dense view of padded storage
+    (last stride 1, every leading axis dense over the row pitch) is passed as it is, anything
+    else is made contiguous."""
+    if t.dtype != torch.float32:
+        raise TypeError("bucket attention runs in fp32")
+    ld = t.stride(-2) if t.dim() >= 2 else t.shape[-1]
+    ok = t.stride(-1) == 1 and ld >= t.shape[-1]
+    pitch = ld
+    for ax in range(t.dim() - 2, -1, -1):
+        ok = ok and (t.stride(ax) == pitch or t.shape[ax] == 1)
+        pitch *= t.shape[ax]
+    if ok:
+        return t, ld
+    t = t.contiguous()
+    return t, t.shape[-1]
+
+
 @torch.no_grad()
 def qkv_res(s_query: torch.Tensor, s_key: torch.Tensor, s_value: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
     """s_query, s_key [..., buckets, bucketsz, dq], s_value [..., buckets, bucketsz, dv], rows already
@@ -37,7 +55,7 @@ def qkv_res(s_query: torch.Tensor, s_key: torch.Tensor, s_value: torch.Tensor) -
     n = q.numel() // dq                       # every bucket is independent: one (round, head) row of n hits
     so = torch.empty(v.shape, dtype=torch.float32, device=dev)
     denom = torch.empty(v.shape[:-1] + (1,), dtype=torch.float32, device=dev)
-    rc = L.lib().lampa_bucket_rbf_attn(L.ptr(q), L.ptr(k), L.ptr(v), None, None, 1, 1, n, bucket, dq, dv, 1, 0,
+    rc = L.lib().lampa_bucket_rbf_attn(L.ptr(q), L.ptr(k), L.ptr(v), None, None, 1, 1, n, bucket, dq, dv, dq, dv, 1, 0,
                                        L.ptr(so), L.ptr(denom), L.stream_ptr(dev))
     L.check(rc, "lampa_bucket_rbf_attn")
     return denom, so
@@ -52,7 +70,9 @@ def hept_bucket_attention(q_hat: torch.Tensor, k_hat: torch.Tensor, value: torch
     rounds are summed and so / denom returned.  return_parts: also (o [rounds, heads, N, dv],
     logits [rounds, heads, N, 1]), the tensors the reference sums."""
     dev = L.require_cuda(q_hat, k_hat, value, q_positions, k_positions)
-    q, k, v = _f32(q_hat), _f32(k_hat), _f32(value)
+    (q, ldq), (k, ldk), (v, ldv) = _rows(q_hat), _rows(k_hat), _rows(value)
+    if ldk != ldq:
+        q, k, ldq = q.contiguous(), k.contiguous(), q.shape[-1]
     heads, n, dq = q.shape
     dv = v.shape[-1]
     if k.shape != q.shape or v.shape[:2] != q.shape[:2]:
@@ -68,7 +88,7 @@ def hept_bucket_attention(q_hat: torch.Tensor, k_hat: torch.Tensor, value: torch
     denom = torch.empty(rounds, heads, n, 1, dtype=torch.float32, device=dev)
     s = L.stream_ptr(dev)
     rc = L.lib().lampa_bucket_rbf_attn(L.ptr(q), L.ptr(k), L.ptr(v), L.ptr(qp), L.ptr(kp), rounds, heads, n,
-                                       int(block_size), dq, dv, 0, 1, L.ptr(so), L.ptr(denom), s)
+                                       int(block_size), dq, dv, ldq, ldv, 0, 1, L.ptr(so), L.ptr(denom), s)
     L.check(rc, "lampa_bucket_rbf_attn")
     out = torch.empty(heads, n, dv, dtype=torch.float32, device=dev)
     L.check(L.lib().lampa_bucket_attn_combine(L.ptr(so), L.ptr(denom), rounds, heads * n, dv, L.ptr(out), s),
@@ -98,15 +118,17 @@ def prep_qk(query: torch.Tensor, key: torch.Tensor, w: torch.Tensor, coords: tor
     if tuple(scale.shape) != (heads, cd):
         raise ValueError("w must be [heads, d, coords_dim - 1, k]")
     v = None if value is None else _f32(value)
-    qh = torch.empty(heads, n, d + cd, dtype=torch.float32, device=dev)
+    ldq = (d + cd + 3) // 4 * 4                 # rows padded with zeros to whole 16-byte pieces
+    qh = torch.empty(heads, n, ldq, dtype=torch.float32, device=dev)
     kh = torch.empty_like(qh)
     vo = None if v is None else torch.empty(heads, n, v.shape[-1], dtype=torch.float32, device=dev)
     if v is not None and v.shape[-1] != d:
         raise ValueError("value must have the head dim of query")
-    rc = L.lib().lampa_hept_prep_qk(L.ptr(q), L.ptr(k), L.ptr(v), L.ptr(scale), L.ptr(c), n, heads, d, cd,
+    rc = L.lib().lampa_hept_prep_qk(L.ptr(q), L.ptr(k), L.ptr(v), L.ptr(scale), L.ptr(c), n, heads, d, cd, ldq,
                                     n if raw_size is None else int(raw_size), L.ptr(qh), L.ptr(kh), L.ptr(vo),
                                     L.stream_ptr(dev))
     L.check(rc, "lampa_hept_prep_qk")
+    qh, kh = qh[..., :d + cd], kh[..., :d + cd]      # views of the padded rows
     if head_major:
         return (qh, kh) if v is None else (qh, kh, vo)
     return qh.transpose(0, 1), kh.transpose(0, 1)

@@ -79,6 +79,10 @@ def test_fixture_from_reference(lb, golden_dir):
     _close(to_np(o), z["o"], 2e-5, "o vs reference")
     _close_rel(to_np(lg), z["logits"], 2e-5, "logits vs reference")
     _close(to_np(out), z["out"], 5e-5, "out vs reference")
+    # the same from the padded rows that prep_qk returns (16-byte gather path): identical arithmetic
+    assert q_hat.stride(1) % 4 == 0 and q_hat.stride(1) >= q_hat.shape[-1]
+    out_p = lb.hept_bucket_attention(q_hat, k_hat, v, _c(z["q_pos"]), _c(z["k_pos"]), block)
+    _close(to_np(out_p), z["out"], 5e-5, "out from padded rows vs reference")
     ref_out, ref_o, ref_lg = oracle.hept_bucket_attention(z["q_hat"], z["k_hat"], z["v"], z["q_pos"], z["k_pos"], block)
     _close(to_np(o), ref_o, 2e-5, "o vs checker")
     _close_rel(to_np(lg), ref_lg, 2e-5, "logits vs checker")

@@ -42,10 +42,11 @@ def test_host_side_argument_errors_without_a_gpu():
     assert lib.lampa_segsort_workspace_bytes(-1, ctypes.byref(n)) == -1
     assert lib.lampa_lsh_hash(None, 24, 0, None, None, 1.0, 10, 8, 3, 6, None, None, None, None) == -1
     assert lib.lampa_permute_rows(None, None, None, 1, 10, 6, 0, None, None) == -1            # row bytes not /4
-    assert lib.lampa_bucket_rbf_attn(None, None, None, None, None, 3, 8, 1000, 30, 30, 24, 0, 1, None, None, None) == -1   # n % bucket
-    assert lib.lampa_bucket_rbf_attn(None, None, None, None, None, 3, 8, 900, 300, 30, 24, 0, 1, None, None, None) == -1   # null tensors
+    assert lib.lampa_bucket_rbf_attn(None, None, None, None, None, 3, 8, 1000, 30, 30, 24, 32, 24, 0, 1, None, None, None) == -1   # n % bucket
+    assert lib.lampa_bucket_rbf_attn(None, None, None, None, None, 3, 8, 900, 300, 30, 24, 30, 24, 0, 1, None, None, None) == -1   # null tensors
+    assert lib.lampa_bucket_rbf_attn(None, None, None, None, None, 3, 8, 900, 100, 30, 24, 28, 24, 0, 1, None, None, None) == -1   # pitch < width
     assert lib.lampa_bucket_attn_combine(None, None, 0, 10, 4, None, None) == -1
-    assert lib.lampa_hept_prep_qk(None, None, None, None, None, 10, 0, 4, 2, 10, None, None, None, None) == -1
+    assert lib.lampa_hept_prep_qk(None, None, None, None, None, 10, 0, 4, 2, 8, 10, None, None, None, None) == -1
 
 
 def test_python_api_rejects_cpu_tensors_and_bad_shapes():
