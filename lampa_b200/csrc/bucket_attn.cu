@@ -9,14 +9,20 @@
 //     denom_i = sum_j p_ij + 1e-20,      so_i = sum_j p_ij v_j
 // after which the rows go back to hit order, the rounds are summed and so / denom is the output.
 //
-// One CTA per (round, head, bucket).  Keys, values and queries of the bucket are gathered into
-// shared memory once, by position (4-byte asynchronous copies); each warp then takes tiles of 8 query rows:
-// it computes its 8 x 128 slice of p in registers (thread = 8 queries x 4 keys, operands read as
-// 16-byte shared loads: 12 loads per 128 FMAs), keeps the slice in a private shared tile and
-// multiplies it with V (thread = 8 queries x 4 value columns x a share of the keys).  The CTA
-// has as many warps as finish the bucket's tiles in whole rounds (7 for buckets of 100).
-// Arithmetic is fp32 FMA: the exponent is a difference of large terms, which tensor-core input
-// types cannot carry.
+// One CTA per (round, head, bucket), CTAs ordered head by head so that the rounds of a head find its
+// rows in L2.  Keys, values and queries of the bucket are gathered into shared memory once, by
+// position, with asynchronous copies (16-byte pieces when the rows are padded to whole pieces, else
+// 4-byte pieces); each warp then takes tiles of 4 query rows: it computes its 4 x 128 slice of p in
+// registers (thread = 4 queries x 4 keys, operands read as 16-byte shared loads: 8 loads per 64
+// FMAs), keeps the slice in a private shared tile and multiplies it with V (thread = 4 queries x 4
+// value columns x a share of the keys).  The CTA has as many warps as finish the bucket's tiles in
+// whole rounds (7 for buckets of 100); three CTAs per SM at the layer's usual sizes, so that one
+// CTA's gather overlaps the others' arithmetic.  Arithmetic is fp32 FMA: the exponent is a
+// difference of large terms, which tensor-core input types cannot carry.
+// Measured (60 000 hits, 3 rounds x 8 heads, buckets of 100, 30 + 24 features): the gather is what
+// bounds the kernel - with 4-byte pieces the copy instructions alone took 17 k of a CTA's 52 k
+// cycles (in-kernel counters), with 16-byte pieces and three CTAs per SM the kernel went from
+// 1.40 ms to 0.97 ms.
 //
 // HBM traffic per (round, head, hit): the q, k, v rows once and the so row + denom once.
 #include "common.cuh"
@@ -27,7 +33,7 @@ namespace lampa {
 
 constexpr int BA_MAX_WARPS = 8;
 constexpr int BA_MAX_BUCKET = 128;      // keys per bucket = one pass of 32 lanes x 4 keys
-constexpr int BA_QROWS = 8;             // query rows per warp tile
+constexpr int BA_QROWS = 4;             // query rows per warp tile
 
 struct BucketAttnArgs {
     const float* q; const float* k; const float* v;         // [rounds?][heads][n][d]
@@ -46,7 +52,7 @@ struct BucketAttnArgs {
 
 __host__ __device__ inline int ba_pow2_at_least(int x) { int p = 1; while (p < x) p <<= 1; return p; }
 
-// shared memory (floats): sK [128][pk] | sV [128][pv] | sQ [qrows][dq4] | per warp sP [8][128]
+// shared memory (floats): sK [128][pk] | sV [128][pv] | sQ [qrows][dq4] | per warp sP [4][128]
 // | positions: 2 x [128] int64
 __host__ __device__ inline size_t ba_smem_floats(int dq4, int pk, int pv, int qrows, int warps) {
     return (size_t)BA_MAX_BUCKET * pk + (size_t)BA_MAX_BUCKET * pv + (size_t)qrows * dq4 +
@@ -68,14 +74,14 @@ __device__ __forceinline__ void cp_async_wait_all() {
     asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;\n" ::: "memory");
 }
 
-__global__ void __launch_bounds__(BA_MAX_WARPS * 32, 2) bucket_rbf_attn_kernel(BucketAttnArgs a) {
+__global__ void __launch_bounds__(BA_MAX_WARPS * 32, 3) bucket_rbf_attn_kernel(BucketAttnArgs a) {
     extern __shared__ __align__(16) float ba_smem[];
     const int dq4 = a.dq4, pk = a.pk, pv = a.pv, bucket = a.bucket;
     const int nthr = blockDim.x, nwarps = nthr >> 5;
     float* sK = ba_smem;                                            // [128][pk]
     float* sV = sK + (size_t)BA_MAX_BUCKET * pk;                    // [128][pv]
     float* sQ = sV + (size_t)BA_MAX_BUCKET * pv;                    // [qrows][dq4]
-    float* sPall = sQ + (size_t)a.qrows * dq4;                      // per warp [8][128]
+    float* sPall = sQ + (size_t)a.qrows * dq4;                      // per warp [4][128]
     int64_t* sQpos = reinterpret_cast<int64_t*>(sPall + (size_t)nwarps * BA_QROWS * BA_MAX_BUCKET);
     int64_t* sKpos = sQpos + BA_MAX_BUCKET;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -140,7 +146,7 @@ __global__ void __launch_bounds__(BA_MAX_WARPS * 32, 2) bucket_rbf_attn_kernel(B
     cp_async_wait_all();
     __syncthreads();
 
-    float* sP = sPall + (size_t)warp * BA_QROWS * BA_MAX_BUCKET;    // [8][128]
+    float* sP = sPall + (size_t)warp * BA_QROWS * BA_MAX_BUCKET;    // [4][128]
     const int nd = a.nd, dl = lane & (nd - 1), jl = lane / nd, js = 32 / nd;
     const int jc_end = (bucket + 3) >> 2;
     // this thread's keys: lane, lane + 32, lane + 64, lane + 96 (rows pk apart, pk / 4 odd: 16-byte loads of
@@ -173,7 +179,7 @@ __global__ void __launch_bounds__(BA_MAX_WARPS * 32, 2) bucket_rbf_attn_kernel(B
 #pragma unroll
         for (int r = 0; r < BA_QROWS; ++r) qn[r] *= -0.5f;
 
-        // p = exp(min(0, q.k - |q|^2/2 - |k|^2/2)) for 8 queries x 4 keys
+        // p = exp(min(0, q.k - |q|^2/2 - |k|^2/2)) for 4 queries x 4 keys
         float acc[BA_QROWS][4];
 #pragma unroll
         for (int r = 0; r < BA_QROWS; ++r) { acc[r][0] = acc[r][1] = acc[r][2] = acc[r][3] = 0.f; }
@@ -210,7 +216,7 @@ __global__ void __launch_bounds__(BA_MAX_WARPS * 32, 2) bucket_rbf_attn_kernel(B
             for (int r = 0; r < BA_QROWS; ++r) rowsum[r] += __shfl_xor_sync(0xffffffffu, rowsum[r], o);
         __syncwarp();
 
-        // so = p . V for 8 queries x value columns 4*dl .. 4*dl+3, keys shared out over the js lane groups
+        // so = p . V for 4 queries x value columns 4*dl .. 4*dl+3, keys shared out over the js lane groups
         float o[BA_QROWS][4];
 #pragma unroll
         for (int r = 0; r < BA_QROWS; ++r) { o[r][0] = o[r][1] = o[r][2] = o[r][3] = 0.f; }
@@ -326,7 +332,7 @@ extern "C" int lampa_bucket_rbf_attn(const float* q, const float* k, const float
     a.vec_qk = ldq % 4 == 0 && ldq >= a.dq4 && al16(q) && al16(k);
     a.vec_v = ldv % 4 == 0 && ldv >= ((dv + 3) & ~3) && al16(v);
     a.vec_store = (dv % 4 == 0) && (reinterpret_cast<uintptr_t>(so) % 16 == 0);
-    // whole tiles of 8 query rows, spread over as few warps as finish in the same number of rounds
+    // whole tiles of 4 query rows, spread over as few warps as finish in the same number of rounds
     const int tiles = (bucket + BA_QROWS - 1) / BA_QROWS;
     const int tile_rounds = (tiles + BA_MAX_WARPS - 1) / BA_MAX_WARPS;
     const int warps = (tiles + tile_rounds - 1) / tile_rounds;
