@@ -499,6 +499,57 @@ def run_layer(args):
                       "kernels": out}), flush=True)
 
 
+def run_hept(args):
+    """The HEPT bucket attention at the 60k-hit event shape (not the headline metric): 3 rounds x 8 heads,
+    buckets of 100 hits, 24 value features and 24 + 6 query / key features, random bucket orders; the fused
+    gather + attention + scatter kernel and the combination over rounds, timed with CUDA events, L2 flushed
+    between launches.  TFLOP/s over the useful fp32 work (bucket^2 x (dq + dv) x 2 per bucket), GB/s over the
+    algorithmic bytes (q, k, v rows and positions read once, so and denom written once per round, head, hit)."""
+    from lampa_b200 import _lib as L
+    from lampa_b200.bucket_attn import hept_bucket_attention
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    n, heads, rounds, bucket, dq, dv = N_HITS, 8, 3, 100, 30, 24
+    gen = torch.Generator().manual_seed(20261)
+    ldq = (dq + 3) // 4 * 4
+    q = torch.zeros(heads, n, ldq)
+    k = torch.zeros(heads, n, ldq)
+    q[..., :dq] = torch.randn(heads, n, dq, generator=gen) * (2.0 / dq ** 0.5)
+    k[..., :dq] = q[..., :dq] + torch.randn(heads, n, dq, generator=gen) / dq ** 0.5
+    v = torch.randn(heads, n, dv, generator=gen)
+    pos = lambda: torch.stack([torch.stack([torch.randperm(n, generator=gen) for _ in range(heads)])
+                               for _ in range(rounds)])
+    qp, kp = pos().to(dev), pos().to(dev)
+    q, k, v = q.to(dev)[..., :dq], k.to(dev)[..., :dq], v.to(dev)       # rows padded to whole 16-byte pieces
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    for _ in range(max(args.warmup, 3)):
+        hept_bucket_attention(q, k, v, qp, kp, bucket)
+    L.profile_enable(True)
+    for _ in range(args.steps):
+        flush.zero_()
+        hept_bucket_attention(q, k, v, qp, kp, bucket)
+    torch.cuda.synchronize()
+    prof = L.profile_read()
+    L.profile_enable(False)
+    units = rounds * heads * n
+    flops = units * bucket * (dq + dv) * 2
+    nbytes = {"bucket_rbf_attn": units * (2 * dq * 4 + dv * 4 + 16 + dv * 4 + 4),
+              "bucket_attn_combine": units * (dv * 4 + 4) + heads * n * dv * 4}
+    out = {}
+    for name in ("bucket_rbf_attn", "bucket_attn_combine"):
+        ms = prof[name]["ms"] / prof[name]["launches"]
+        out[name] = {"us_per_launch": ms * 1e3, "algorithmic_bytes": nbytes[name],
+                     "gbs": nbytes[name] / (ms * 1e-3) / 1e9}
+    ms = out["bucket_rbf_attn"]["us_per_launch"] * 1e-3
+    out["bucket_rbf_attn"]["fp32_tflops"] = flops / (ms * 1e-3) / 1e12
+    total_ms = sum(o["us_per_launch"] for o in out.values()) * 1e-3
+    print(json.dumps({"metric": "hits/sec, HEPT bucket attention", "value": n / (total_ms * 1e-3), "unit": "hits/s",
+                      "n_gpus": 1, "steps": args.steps, "dtype": "f32", "data": "synthetic",
+                      "config": {"workload": f"bucket attention N={n} rounds={rounds} heads={heads} bucket={bucket} "
+                                             f"dq={dq} dv={dv}, random bucket orders, L2 flushed between launches"},
+                      "kernels": out}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -513,15 +564,18 @@ def main():
                                                             "one captured CUDA graph per stream")
     ap.add_argument("--streams", type=int, default=3,
                     help="independent events kept in flight in the device-resident leg (1: strictly back to back)")
-    ap.add_argument("--workload", default="event", choices=["event", "plain", "layer"],
+    ap.add_argument("--workload", default="event", choices=["event", "plain", "layer", "hept"],
                     help="event: the headline LSH + hierarchical step; plain: configuration 1 "
                          "(chunk_gated_delta_rule, T=65536, H=8, K=V=64, initial and final state), device-resident only; "
-                         "layer: the elementwise kernels around the op (short convolution, gate inputs, gated norm)")
+                         "layer: the elementwise kernels around the op (short convolution, gate inputs, gated norm); "
+                         "hept: the bucket attention of the HEPT layer at the event shape")
     args = ap.parse_args()
     if args.hits != N_HITS:
         set_event_size(args.hits)
     if args.workload == "plain":
         run_plain(args)
+    elif args.workload == "hept":
+        run_hept(args)
     elif args.workload == "layer":
         run_layer(args)
     elif args.impl == "reference":
