@@ -37,7 +37,11 @@ def lsh_hash(x: torch.Tensor, alpha: torch.Tensor, beta: torch.Tensor, w: float 
     dim = d if dim is None else dim
     if dim != d:
         raise ValueError("alpha's middle dimension must equal dim")
-    x = x.to(torch.float32).contiguous()
+    # head-major rows that sit in padded storage (last stride 1, heads dense over the row pitch) are read in place
+    in_place = (per_head_rows and x.dim() == 3 and x.dtype == torch.float32 and x.stride(2) == 1
+                and x.stride(1) >= x.shape[2] and x.stride(0) == x.stride(1) * x.shape[1])
+    if not in_place:
+        x = x.to(torch.float32).contiguous()
     alpha = alpha.detach().to(torch.float32).contiguous()
     beta = beta.detach().to(torch.float32).reshape(-1).contiguous()
     if beta.numel() != rounds:
@@ -45,7 +49,7 @@ def lsh_hash(x: torch.Tensor, alpha: torch.Tensor, beta: torch.Tensor, w: float 
     if per_head_rows:
         if x.dim() != 3 or x.shape[0] != heads or x.shape[2] != dim:
             raise ValueError("x must be [heads, N, dim]")
-        N, row_stride, head_stride = x.shape[1], dim, x.shape[1] * dim
+        N, row_stride, head_stride = x.shape[1], x.stride(1), x.stride(0)
     else:
         if x.dim() != 2 or x.shape[1] < dim:
             raise ValueError("x must be [N, row >= dim]")

@@ -146,6 +146,41 @@ def test_identical_points_and_far_points(lb):
     np.testing.assert_allclose(got, vv, rtol=1e-6)
 
 
+def test_attention_core_end_to_end(lb):
+    """The layer's forward between the projections and the output projection: input preparation, region
+    shift, bucket orders and attention in one call, against the checker run on the positions the call
+    itself produced (the positions have their own parity tests)."""
+    raw, block, heads, rounds, d, cd, nw = 1130, 100, 4, 3, 24, 6, 5
+    gen = torch.Generator().manual_seed(99)
+    coords_raw = torch.randn(raw, cd, generator=gen)
+    coords_raw[:, 1] = (torch.rand(raw, generator=gen) * 2 - 1) * 3.14159
+    w = torch.randn(heads, d, cd - 1, nw, generator=gen) * 0.3 - 0.8
+    torch.manual_seed(5)
+    regions = lb.get_regions(40, rounds, heads)
+    e2lsh = lb.E2LSH(n_hashes=rounds, n_heads=heads, dim=d + cd).cuda()
+    inp = lb.region_inputs(coords_raw.cuda(), regions, block)
+    n = inp["coords"].shape[0]
+    assert n == 1200
+    query = lb.pad_to_multiple(torch.randn(raw, heads, d, generator=gen) * 0.6, block, dims=0).cuda()
+    key = lb.pad_to_multiple(torch.randn(raw, heads, d, generator=gen) * 0.6, block, dims=0).cuda()
+    value = lb.pad_to_multiple(torch.randn(raw, heads, d, generator=gen), block, dims=0).cuda()
+    out = lb.hept_attention_core(e2lsh, query, key, value, w.cuda(), inp["coords"], inp["regions_h"], inp["ranks"],
+                                 raw, block)
+    assert tuple(out.shape) == (heads, n, d)
+    q_hat, k_hat, v = lb.prep_qk(query, key, w.cuda(), inp["coords"], value=value, raw_size=raw, head_major=True)
+    oq, ok = oracle.hept_prep_qk(to_np(query), to_np(key), w.numpy(), to_np(inp["coords"]), raw)
+    np.testing.assert_allclose(to_np(q_hat), oq, rtol=2e-6, atol=1e-7)
+    np.testing.assert_allclose(to_np(k_hat), ok, rtol=2e-6, atol=1e-7)
+    q_pos, k_pos = lb.hept_positions(e2lsh, q_hat, k_hat, inp["regions_h"], inp["ranks"], raw)
+    # projections read in place from the padded rows equal those of a dense copy
+    q_pos_c, _ = lb.hept_positions(e2lsh, q_hat.contiguous(), k_hat.contiguous(), inp["regions_h"], inp["ranks"], raw)
+    np.testing.assert_array_equal(to_np(q_pos), to_np(q_pos_c))
+    for p in (q_pos, k_pos):
+        assert (np.sort(to_np(p), axis=-1) == np.arange(n)).all()
+    ref_out, _, _ = oracle.hept_bucket_attention(to_np(q_hat), to_np(k_hat), to_np(v), to_np(q_pos), to_np(k_pos), block)
+    _close(to_np(out)[:, :raw], ref_out[:, :raw], 5e-5, "attention core")
+
+
 def test_argument_errors(lb):
     q = torch.zeros(1, 100, 8, device="cuda")
     v = torch.zeros(1, 100, 4, device="cuda")
