@@ -33,7 +33,6 @@ namespace lampa {
 
 constexpr int BA_MAX_WARPS = 8;
 constexpr int BA_MAX_BUCKET = 128;      // keys per bucket = one pass of 32 lanes x 4 keys
-constexpr int BA_QROWS = 4;             // query rows per warp tile
 
 struct BucketAttnArgs {
     const float* q; const float* k; const float* v;         // [rounds?][heads][n][d]
@@ -54,7 +53,7 @@ __host__ __device__ inline int ba_pow2_at_least(int x) { int p = 1; while (p < x
 
 // shared memory (floats): sK [128][pk] | sV [128][pv] | sQ [qrows][dq4] | per warp sP [4][128]
 // | positions: 2 x [128] int64
-__host__ __device__ inline size_t ba_smem_floats(int dq4, int pk, int pv, int qrows, int warps) {
+__host__ __device__ inline size_t ba_smem_floats(int dq4, int pk, int pv, int qrows, int warps, int BA_QROWS) {
     return (size_t)BA_MAX_BUCKET * pk + (size_t)BA_MAX_BUCKET * pv + (size_t)qrows * dq4 +
            (size_t)warps * BA_QROWS * BA_MAX_BUCKET + 4 * BA_MAX_BUCKET;
 }
@@ -74,7 +73,11 @@ __device__ __forceinline__ void cp_async_wait_all() {
     asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;\n" ::: "memory");
 }
 
-__global__ void __launch_bounds__(BA_MAX_WARPS * 32, 3) bucket_rbf_attn_kernel(BucketAttnArgs a) {
+// BA_QROWS: query rows per warp tile.  4 (80 registers, up to three CTAs per SM) while at least two CTAs'
+// shared memory fits an SM; 8 (fewer operand loads per FMA) for wide rows, where one CTA has the SM to itself.
+// Measured at 60 000 hits, 3 x 8: dq 54 / dv 48 1.25 ms with 4 rows against 1.62 with 8; dq 102 / dv 96 3.63 against 3.40.
+template <int BA_QROWS>
+__global__ void __launch_bounds__(BA_MAX_WARPS * 32, BA_QROWS == 4 ? 3 : 2) bucket_rbf_attn_kernel(BucketAttnArgs a) {
     extern __shared__ __align__(16) float ba_smem[];
     const int dq4 = a.dq4, pk = a.pk, pv = a.pv, bucket = a.bucket;
     const int nthr = blockDim.x, nwarps = nthr >> 5;
@@ -332,19 +335,26 @@ extern "C" int lampa_bucket_rbf_attn(const float* q, const float* k, const float
     a.vec_qk = ldq % 4 == 0 && ldq >= a.dq4 && al16(q) && al16(k);
     a.vec_v = ldv % 4 == 0 && ldv >= ((dv + 3) & ~3) && al16(v);
     a.vec_store = (dv % 4 == 0) && (reinterpret_cast<uintptr_t>(so) % 16 == 0);
-    // whole tiles of 4 query rows, spread over as few warps as finish in the same number of rounds
-    const int tiles = (bucket + BA_QROWS - 1) / BA_QROWS;
-    const int tile_rounds = (tiles + BA_MAX_WARPS - 1) / BA_MAX_WARPS;
-    const int warps = (tiles + tile_rounds - 1) / tile_rounds;
-    a.qrows = tiles * BA_QROWS;
-    const size_t smem = ba_smem_floats(a.dq4, a.pk, a.pv, a.qrows, warps) * sizeof(float);
+    // whole tiles of query rows, spread over as few warps as finish in the same number of rounds
+    auto plan = [&](int qr, int& warps, size_t& smem) {
+        const int tiles = (bucket + qr - 1) / qr;
+        const int tile_rounds = (tiles + BA_MAX_WARPS - 1) / BA_MAX_WARPS;
+        warps = (tiles + tile_rounds - 1) / tile_rounds;
+        a.qrows = tiles * qr;
+        smem = ba_smem_floats(a.dq4, a.pk, a.pv, a.qrows, warps, qr) * sizeof(float);
+    };
+    int warps; size_t smem;
+    plan(4, warps, smem);
+    const bool wide = smem > 113 * 1024;                   // not even two CTAs of 4-row tiles fit an SM
+    if (wide) plan(8, warps, smem);
     if (smem > 227 * 1024) return LAMPA_ERR_UNSUPPORTED;
     const int64_t units = (int64_t)rounds * heads * (n / bucket);
     if (units > 0x7fffffffLL) return LAMPA_ERR_UNSUPPORTED;
-    if (cudaFuncSetAttribute(bucket_rbf_attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+    auto kernel = wide ? bucket_rbf_attn_kernel<8> : bucket_rbf_attn_kernel<4>;
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
         return LAMPA_ERR_CUDA;
     ProfScope prof("bucket_rbf_attn", (cudaStream_t)stream);
-    bucket_rbf_attn_kernel<<<(unsigned)units, warps * 32, smem, (cudaStream_t)stream>>>(a);
+    kernel<<<(unsigned)units, warps * 32, smem, (cudaStream_t)stream>>>(a);
     return cudaGetLastError() == cudaSuccess ? LAMPA_OK : LAMPA_ERR_CUDA;
 }
 
