@@ -543,7 +543,21 @@ def run_hept(args):
     ms = out["bucket_rbf_attn"]["us_per_launch"] * 1e-3
     out["bucket_rbf_attn"]["fp32_tflops"] = flops / (ms * 1e-3) / 1e12
     total_ms = sum(o["us_per_launch"] for o in out.values()) * 1e-3
+    # fp32 FMA bound: no measured fp32 peak is written by the driver, so the denominator is the nominal
+    # 148 SMs x 128 FMA lanes x 2 flop x the maximum SM clock reported by NVML (1965 MHz on this pool)
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(pynvml.nvmlDeviceGetHandleByIndex(dev.index or 0),
+                                                     pynvml.NVML_CLOCK_SM))
+    except Exception:
+        mhz = 1965.0
+    peak = 148 * 128 * 2 * mhz * 1e6 / 1e12
+    roof = {"kernel": "bucket_rbf_attn", "bound": "fp32-fma", "achieved": out["bucket_rbf_attn"]["fp32_tflops"],
+            "peak": peak, "unit": "TFLOP/s", "frac": out["bucket_rbf_attn"]["fp32_tflops"] / peak,
+            "peak_source": "nominal (SMs x lanes x 2 x max SM clock)", "traffic": 310.0e6 if n == 60000 else None}
     print(json.dumps({"metric": "hits/sec, HEPT bucket attention", "value": n / (total_ms * 1e-3), "unit": "hits/s",
+                      "roofline": roof,
                       "n_gpus": 1, "steps": args.steps, "dtype": "f32", "data": "synthetic",
                       "config": {"workload": f"bucket attention N={n} rounds={rounds} heads={heads} bucket={bucket} "
                                              f"dq={dq} dv={dv}, random bucket orders, L2 flushed between launches"},
