@@ -506,7 +506,7 @@ def run_hept(args):
     between launches.  TFLOP/s over the useful fp32 work (bucket^2 x (dq + dv) x 2 per bucket), GB/s over the
     algorithmic bytes (q, k, v rows and positions read once, so and denom written once per round, head, hit)."""
     from lampa_b200 import _lib as L
-    from lampa_b200.bucket_attn import hept_bucket_attention
+    from lampa_b200.bucket_attn import assume_zero_padded, hept_bucket_attention
     dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
     torch.cuda.set_device(dev)
     n, heads, rounds, bucket, dq, dv = N_HITS, 8, 3, 100, 30, 24
@@ -520,7 +520,9 @@ def run_hept(args):
     pos = lambda: torch.stack([torch.stack([torch.randperm(n, generator=gen) for _ in range(heads)])
                                for _ in range(rounds)])
     qp, kp = pos().to(dev), pos().to(dev)
-    q, k, v = q.to(dev)[..., :dq], k.to(dev)[..., :dq], v.to(dev)       # rows padded to whole 16-byte pieces
+    q, k, v = q.to(dev)[..., :dq], k.to(dev)[..., :dq], v.to(dev)       # rows padded with zeros to whole 16-byte pieces
+    assume_zero_padded(q)
+    assume_zero_padded(k)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
     for _ in range(max(args.warmup, 3)):
         hept_bucket_attention(q, k, v, qp, kp, bucket)

@@ -176,6 +176,7 @@ int lampa_segsort_workspace_bytes(int64_t n_total, size_t* bytes);
  *   keys: int32 or fp32 [n_total]; seg_offsets int64 [nseg+1] (device) or NULL for nseg equal
  *   segments of n_total/nseg keys; init: optional starting order per segment (local indices) —
  *   the result is init composed with the stable sort of keys[init], i.e. norm_idx[bk_idx].
+ *   A segment whose offsets leave [0, n_total] is not sorted and sets LAMPA_ERR_BOUNDS in `status`.
  */
 int lampa_segsort_stable(const void* keys, int32_t key_type, int64_t n_total,
                          const int64_t* seg_offsets, int32_t nseg, const int64_t* init,
@@ -195,7 +196,12 @@ int lampa_segsort_stable(const void* keys, int32_t key_type, int64_t n_total,
  *   - n_total > LAMPA_SEGSORT_STATIC_MAX_KEYS returns LAMPA_ERR_TOO_LARGE and launches nothing;
  *   - neither this call nor anything it uses calls cudaMalloc/cudaFree or an allocating routine;
  *   - the first call on a device looks up the array's address there (cudaGetSymbolAddress, with
- *     that device current) and caches it: make that first call outside any stream capture;
+ *     that device current) and caches it.  Make that first call part of start-up: outside any
+ *     stream capture, and because it may also be the call that loads this library's device code
+ *     (with the 24 MiB array) onto the GPU when the CUDA runtime loads modules lazily;
+ *   - the cached address belongs to the device's current primary context: after a
+ *     cudaDeviceReset in the host process it is stale and this entry point must not be used again
+ *     in that process;
  *   - all calls on a device share the one array and it keeps the previous call's contents; the
  *     sort never reads what it has not just written, so nothing is cleared, but two calls that
  *     overlap on the GPU (different streams, or threads without ordering) race on it: keep
@@ -211,15 +217,18 @@ int lampa_segsort_stable_static(const void* keys, int32_t key_type, int64_t n_to
  * Replaces: points.gather (hmamba.py:348-351), sort_to_buckets / unsort_from_buckets /
  * batched_index_select (models/attention/hept.py:9-19, hash_utils.py:83-93).
  *   scatter == 0: dst[s0+i] = src[s0+perm[s0+i]];  scatter != 0: dst[s0+perm[s0+i]] = src[s0+i].
- *   row_bytes must be a multiple of 4.
+ *   row_bytes must be a multiple of 4.  An index outside its segment is not followed: that row is
+ *   skipped and LAMPA_ERR_BOUNDS goes to `status` (may be NULL).
  */
 int lampa_permute_rows(const void* src, const int64_t* perm, const int64_t* seg_offsets, int32_t nseg,
-                       int64_t n_rows, int64_t row_bytes, int32_t scatter, void* dst, void* stream);
+                       int64_t n_rows, int64_t row_bytes, int32_t scatter, void* dst, int32_t* status,
+                       void* stream);
 
 /* inv[s0 + perm[s0+i]] = i.  Replaces invert_permutation (hash_utils.py:46-57) and the
- * `perm.argsort(dim=1)` used to undo the ordering (hmamba.py:451, full_mamba2.py:678). */
+ * `perm.argsort(dim=1)` used to undo the ordering (hmamba.py:451, full_mamba2.py:678).  Entries
+ * outside their segment are skipped and reported as LAMPA_ERR_BOUNDS in `status` (may be NULL). */
 int lampa_invert_perm(const int64_t* perm, const int64_t* seg_offsets, int32_t nseg, int64_t n_total,
-                      int64_t* inv, void* stream);
+                      int64_t* inv, int32_t* status, void* stream);
 
 /*
  * Per-row range of the LSH projections: mn/mx/range [rows] fp32 (any may be NULL) over the n
@@ -355,6 +364,15 @@ int lampa_hept_prep_qk(const float* query, const float* key, const float* value,
 int lampa_profile_enable(int on);
 int lampa_profile_read(char* names, size_t names_cap, float* total_ms, int32_t* launches,
                        int32_t max_kernels, int32_t* n_kernels);
+
+/*
+ * Test hook (no counterpart in the reference): number of polls after which a device-side wait of
+ * the gated-delta kernels gives up (default and maximum 2^22).  A test sets it to 0 to see the
+ * give-up path without anything hanging: the kernels then return at once, results are undefined
+ * and LAMPA_ERR_TIMEOUT is in the status word; copies and MMAs already in flight are still waited
+ * for with the full budget before a CTA exits.  Process-wide; not for concurrent use.
+ */
+int lampa_debug_set_poll_budget(int polls);
 
 #ifdef __cplusplus
 }

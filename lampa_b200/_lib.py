@@ -41,7 +41,7 @@ EXPORTS = ["lampa_version", "lampa_error_string", "lampa_gdn_workspace_bytes", "
            "lampa_row_range", "lampa_quantile_regions", "lampa_geo_keys",
            "lampa_bucket_rbf_attn", "lampa_bucket_attn_combine", "lampa_hept_prep_qk",
            "lampa_profile_enable",
-           "lampa_profile_read"]
+           "lampa_profile_read", "lampa_debug_set_poll_budget"]
 
 
 def lib() -> ctypes.CDLL:
@@ -65,8 +65,8 @@ def lib() -> ctypes.CDLL:
         L.lampa_segsort_workspace_bytes.argtypes = [i64, ctypes.POINTER(sz)]
         L.lampa_segsort_stable.argtypes = [vp, i32, i64, vp, i32, vp, vp, vp, sz, vp, vp]
         L.lampa_segsort_stable_static.argtypes = [vp, i32, i64, vp, i32, vp, vp, vp, vp]
-        L.lampa_permute_rows.argtypes = [vp, vp, vp, i32, i64, i64, i32, vp, vp]
-        L.lampa_invert_perm.argtypes = [vp, vp, i32, i64, vp, vp]
+        L.lampa_permute_rows.argtypes = [vp, vp, vp, i32, i64, i64, i32, vp, vp, vp]
+        L.lampa_invert_perm.argtypes = [vp, vp, i32, i64, vp, vp, vp]
         L.lampa_row_range.argtypes = [vp, vp, i32, i64, vp, vp, vp, vp]
         L.lampa_quantile_regions.argtypes = [vp, vp, i32, i64, vp, vp]
         L.lampa_geo_keys.argtypes = [vp] * 8 + [i32, i64, i64, vp, vp]
@@ -78,6 +78,7 @@ def lib() -> ctypes.CDLL:
         L.lampa_gate_inputs.argtypes = [vp] * 7 + [i64, i32, i32, i32, i32, i32, i32, vp, vp, vp, vp]
         L.lampa_rmsnorm_gate.argtypes = [vp, vp, vp, i64, i32, i32, i32, ctypes.c_float, i32, vp, vp]
         L.lampa_profile_enable.argtypes = [ctypes.c_int]
+        L.lampa_debug_set_poll_budget.argtypes = [ctypes.c_int]
         L.lampa_profile_read.argtypes = [ctypes.c_char_p, sz, ctypes.POINTER(ctypes.c_float),
                                          ctypes.POINTER(i32), i32, ctypes.POINTER(i32)]
         for name in EXPORTS:

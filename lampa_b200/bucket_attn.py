@@ -25,14 +25,29 @@ def _f32(t: torch.Tensor) -> torch.Tensor:
     return t.contiguous()
 
 
+_ZERO_PADDED = "_lampa_zero_padded_rows"
+
+
+def assume_zero_padded(t: torch.Tensor) -> torch.Tensor:
+    """Declare that the storage columns between this view's width and its row pitch hold zeros, so
+    that `hept_bucket_attention` may read the rows in place with 16-byte fetches."""
+    setattr(t, _ZERO_PADDED, True)
+    return t
+
+
 def _rows(t: torch.Tensor):
     """(tensor, row pitch) of a [..., rows, width] fp32 tensor: a dense view of padded storage
     (last stride 1, every leading axis dense over the row pitch) is passed as it is, anything
-    else is made contiguous."""
+    else is made contiguous.  The kernel's 16-byte row fetch reads a row up to its width rounded
+    up to 4 floats and needs those extra columns to be zero, so a view narrower than its pitch
+    is only taken in place when its width is a multiple of 4 or when `prep_qk` produced it (it
+    writes the padding as zeros and marks the tensor); a slice of wider storage that holds other
+    data is copied."""
     if t.dtype != torch.float32:
         raise TypeError("bucket attention runs in fp32")
     ld = t.stride(-2) if t.dim() >= 2 else t.shape[-1]
     ok = t.stride(-1) == 1 and ld >= t.shape[-1]
+    ok = ok and (ld == t.shape[-1] or t.shape[-1] % 4 == 0 or getattr(t, _ZERO_PADDED, False))
     pitch = ld
     for ax in range(t.dim() - 2, -1, -1):
         ok = ok and (t.stride(ax) == pitch or t.shape[ax] == 1)
@@ -129,6 +144,8 @@ def prep_qk(query: torch.Tensor, key: torch.Tensor, w: torch.Tensor, coords: tor
                                     L.stream_ptr(dev))
     L.check(rc, "lampa_hept_prep_qk")
     qh, kh = qh[..., :d + cd], kh[..., :d + cd]      # views of the padded rows
+    assume_zero_padded(qh)                           # columns d + cd .. ldq - 1 are zero: _rows may pass them in place
+    assume_zero_padded(kh)
     if head_major:
         return (qh, kh) if v is None else (qh, kh, vo)
     return qh.transpose(0, 1), kh.transpose(0, 1)

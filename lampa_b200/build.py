@@ -35,7 +35,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
     if not force and not _stale():
         return SO
     nvcc = _nvcc()
-    extra = os.environ.get("LAMPA_NVCC_EXTRA", "").split()   # e.g. -DLAMPA_PREP_TIMING for stage timing builds
+    extra = os.environ.get("LAMPA_NVCC_EXTRA", "").split()   # extra nvcc flags
     objdir = os.path.join(HERE, "build")
     os.makedirs(objdir, exist_ok=True)
 

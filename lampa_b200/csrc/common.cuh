@@ -169,14 +169,26 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
         : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
     return ok != 0;
 }
-// Bounded wait: gives up after ~2^22 polls (each poll may itself block for a while in hardware),
-// records the failure and lets the caller carry on so that no barrier is left unbalanced.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, bool& dead, int32_t* status, int where) {
+// Bounded wait: gives up after `budget` polls (each poll may itself block for a while in hardware;
+// the default budget is 2^22), records the failure and lets the caller carry on so that no barrier
+// is left unbalanced.  A thread that has given up once (`dead`) does not wait again: it runs to the
+// end of its loop, issues nothing new and drains what it has in flight with mbar_drain.
+constexpr int MBAR_POLLS = 1 << 22;
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, bool& dead, int32_t* status, int where,
+                                          int budget = MBAR_POLLS) {
     if (dead) return false;
-    for (int i = 0; i < (1 << 22); ++i)
+    for (int i = 0; i < budget; ++i)
         if (mbar_try_wait(bar, parity)) return true;
     dead = true;
     set_status(status, LAMPA_ERR_TIMEOUT, where, (int)parity);
+    return false;
+}
+// Wait for an asynchronous operation that was already started (a bulk copy into this CTA's shared
+// memory, a committed MMA group) before the CTA gives its shared / tensor memory back; always the
+// full budget, whatever made the thread give up earlier.
+__device__ __forceinline__ bool mbar_drain(uint64_t* bar, uint32_t parity) {
+    for (int i = 0; i < MBAR_POLLS; ++i)
+        if (mbar_try_wait(bar, parity)) return true;
     return false;
 }
 // global -> shared bulk copy; dst/src 16-byte aligned, bytes a multiple of 16.

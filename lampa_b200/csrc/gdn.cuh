@@ -74,7 +74,8 @@ struct GdnArgs {
     char* blk;                            // per (block, head) composites
     float* entry;                         // entry states: plain [nb][H][V][K]; hier [nb][nhigh][H][V][K]
     int32_t* status;
-    int use_umma;                         // hierarchical output pass on tcgen05 (K = V = 64)
+    int use_umma;                         // tcgen05 kernels where they exist (K = V = 64)
+    int poll_budget;                      // polls before a device wait gives up (MBAR_POLLS unless a test lowers it)
 };
 
 struct PlanArgs {

@@ -8,6 +8,8 @@ namespace {
 
 inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
+int g_poll_budget = MBAR_POLLS;   // see lampa_debug_set_poll_budget
+
 struct Layout {
     int nseq, nc_max, nb_max, nhigh_max, LC;
     size_t rec_bytes, blk_bytes, state_bytes;
@@ -83,7 +85,9 @@ void fill_args(const lampa_gdn_desc* d, bool hier, const Layout& l, char* base, 
     a.blk = base + l.off_blk;
     a.entry = (float*)(base + l.off_entry);
     a.status = status;
-    { const char* e = getenv("LAMPA_B200_NO_UMMA"); a.use_umma = (e && e[0] == '1') ? 0 : 1; }
+    static const int no_umma = [] { const char* e = getenv("LAMPA_B200_NO_UMMA"); return (e && e[0] == '1') ? 1 : 0; }();
+    a.use_umma = no_umma ? 0 : 1;
+    a.poll_budget = g_poll_budget;
 }
 
 int run(const lampa_gdn_desc* d, bool hier, const void* q, const void* k, const void* v, const void* g,
@@ -129,7 +133,13 @@ int run(const lampa_gdn_desc* d, bool hier, const void* q, const void* k, const 
 
 }  // namespace
 
-extern "C" int lampa_version(void) { return 100; }
+extern "C" int lampa_version(void) { return 200; }
+
+extern "C" int lampa_debug_set_poll_budget(int polls) {
+    if (polls < 0) return LAMPA_ERR_ARG;
+    g_poll_budget = polls > MBAR_POLLS ? MBAR_POLLS : polls;
+    return LAMPA_OK;
+}
 
 extern "C" const char* lampa_error_string(int code) {
     switch (code) {

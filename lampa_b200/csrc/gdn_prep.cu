@@ -19,7 +19,7 @@ __global__ void plan_kernel(PlanArgs p) {
         const int64_t t1 = p.cu ? p.cu[s + 1] : (int64_t)(s + 1) * p.T;
         p.tok_off[s] = t0;
         int64_t len = t1 - t0;
-        if (len < 0 || t1 > (int64_t)p.B * p.T) { set_status(p.status, LAMPA_ERR_BOUNDS, 1, s); len = 0; }
+        if (len < 0 || t0 < 0 || t1 > (int64_t)p.B * p.T) { set_status(p.status, LAMPA_ERR_BOUNDS, 1, s); len = 0; }
         const int nch = (int)((len + CHUNK - 1) / CHUNK);
         if (p.hier && nch > 0 && ELL0 + ceil_log2_int(nch) > p.L) set_status(p.status, LAMPA_ERR_LEVELS, 1, s);
         c += nch;
@@ -196,16 +196,6 @@ __device__ __forceinline__ void store_neg_tile(float* s, int pitch, int r0, int 
 //   O_local = s ((R .* E .* lambda[i][level(i,j)]) V)
 // (s = scale and lambda = 1 for the plain rule; s = 1 for the hierarchical one).  These equal
 // the definitions in gdn.cuh: every e^{G_last-G_tok} e^{G_tok} pair collapses to e^{G_last}.
-// Stage timing for tuning builds only (-DLAMPA_PREP_TIMING): thread 0 of the first 1024 CTAs of
-// head 0 stores clock64() at each stage boundary behind the status word, which the caller of such
-// a build must size as int32[4 + 2 * 8 * 1024].
-#ifdef LAMPA_PREP_TIMING
-#define PREP_TICK(slot) do { if (threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y < 1024) \
-    reinterpret_cast<long long*>(a.status + 4)[blockIdx.y * 8 + (slot)] = clock64(); } while (0)
-#else
-#define PREP_TICK(slot) do { } while (0)
-#endif
-
 template <int KD, int VD, bool HIER>
 __global__ void __launch_bounds__(128, 4) gdn_prep_kernel(GdnArgs a) {
     using S = PrepSmem<KD, VD>;
@@ -234,7 +224,6 @@ __global__ void __launch_bounds__(128, 4) gdn_prep_kernel(GdnArgs a) {
     const int64_t t0 = loc.t0;
     const int len = loc.len;
     const int LP = a.L + 1;
-    PREP_TICK(0);
 
     // ---- stage 0: loads, l2norm, cumulative decay -------------------------------------------------
     // Every global load of the chunk is issued before any of them is consumed (one DRAM round trip
@@ -471,7 +460,6 @@ __global__ void __launch_bounds__(128, 4) gdn_prep_kernel(GdnArgs a) {
         }
         __syncthreads();
     }
-    PREP_TICK(1);
     const float osc = HIER ? 1.f : a.scale;
     // ---- per-warp part (rows m0..m0+15 of everything; nothing leaves the warp) --------------------
     {
@@ -634,7 +622,6 @@ __global__ void __launch_bounds__(128, 4) gdn_prep_kernel(GdnArgs a) {
         }
     }
     __syncthreads();
-    PREP_TICK(5);
 
     // ---- stage 4: M[a][b] = e^{G_last} (delta_ab - sum_tok K[tok][a] W[tok][b]);  B^T = U^^T K -----
     // Both tiles are assembled in the record's layout in shared memory (over Awb and V, which are
@@ -677,7 +664,6 @@ __global__ void __launch_bounds__(128, 4) gdn_prep_kernel(GdnArgs a) {
         bulk_commit();
         bulk_wait_read();
     }
-    PREP_TICK(6);
 }
 
 template <int KD, int VD>

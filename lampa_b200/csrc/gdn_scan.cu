@@ -123,13 +123,17 @@ struct Pipe {
     int nsteps;
     bool dead;
     int32_t* status;
+    int budget;          // polls per wait
+    int issued, landed;  // thread 0: copies started / copies seen complete
 
     __device__ __forceinline__ void issue(int step) {
         uint64_t* b = bar + (step % NST);
         mbar_expect_tx(b, copy_bytes);
         bulk_g2s(stage + (size_t)(step % NST) * stage_bytes, src + (size_t)step * src_stride, copy_bytes, b);
+        issued = step + 1;
     }
     __device__ __forceinline__ void start() {
+        issued = landed = 0;
         if (threadIdx.x == 0) {
             for (int s = 0; s < NST; ++s) mbar_init(bar + s, 1);
             fence_mbar_init();
@@ -141,9 +145,17 @@ struct Pipe {
     // returns the stage holding step i
     __device__ __forceinline__ const unsigned char* acquire(int i) {
         __syncthreads();
-        if (threadIdx.x == 0 && i + NST - 1 < nsteps) issue(i + NST - 1);
-        mbar_wait(bar + (i % NST), (uint32_t)((i / NST) & 1), dead, status, 100 + (i & 0xffff));
+        if (threadIdx.x == 0 && !dead && i + NST - 1 < nsteps) issue(i + NST - 1);
+        if (mbar_wait(bar + (i % NST), (uint32_t)((i / NST) & 1), dead, status, 100 + (i & 0xffff), budget) && threadIdx.x == 0)
+            landed = i + 1;
         return stage + (size_t)(i % NST) * stage_bytes;
+    }
+    // Before the CTA exits: copies that were started but never seen complete (only after a wait
+    // gave up) must land first, or they would write into shared memory that is no longer ours.
+    __device__ __forceinline__ void finish() {
+        if (threadIdx.x == 0)
+            for (int s = landed; s < issued; ++s) mbar_drain(bar + (s % NST), (uint32_t)((s / NST) & 1));
+        __syncthreads();
     }
 };
 
@@ -176,6 +188,7 @@ __global__ void __launch_bounds__((KD + VD) * 2) gdn_compose_kernel(GdnArgs a) {
     pipe.nsteps = nsteps;
     pipe.dead = false;
     pipe.status = a.status;
+    pipe.budget = a.poll_budget;
     pipe.start();
 
     const bool is_s = warp < NS;
@@ -203,6 +216,7 @@ __global__ void __launch_bounds__((KD + VD) * 2) gdn_compose_kernel(GdnArgs a) {
             state_times_mt<KD, Tile<KD>>(C, sp, sM, lane);
         }
     }
+    pipe.finish();
     char* blk = a.blk + ((size_t)gb * a.H + h) * R::BLK_BYTES;
     if (is_s) {
         store_slab_f32<KD>(C, reinterpret_cast<float*>(blk + R::BLK_B_OFF), R::BP, row0, lane);
@@ -253,6 +267,7 @@ __global__ void __launch_bounds__(VD * 2) gdn_level_kernel(GdnArgs a) {
     pipe.nsteps = nblk;
     pipe.dead = false;
     pipe.status = a.status;
+    pipe.budget = a.poll_budget;
     pipe.start();
 
     float C[KD / 8][4];
@@ -295,6 +310,7 @@ __global__ void __launch_bounds__(VD * 2) gdn_level_kernel(GdnArgs a) {
             }
         }
     }
+    pipe.finish();
     if (!HIER && a.ht != nullptr) {
         float* ht = a.ht + ((size_t)seq * H + h) * KD * VD;
 #pragma unroll
@@ -352,6 +368,7 @@ __global__ void __launch_bounds__(VD * 2) hgdn_final_high_kernel(GdnArgs a, floa
         pipe.nsteps = n - c_first + 1;
         pipe.dead = false;
         pipe.status = a.status;
+        pipe.budget = a.poll_budget;
         pipe.start();
         for (int i = 0; i < pipe.nsteps; ++i) {
             const unsigned char* st = pipe.acquire(i);
@@ -376,6 +393,7 @@ __global__ void __launch_bounds__(VD * 2) hgdn_final_high_kernel(GdnArgs a, floa
                 state_times_mt<KD, Tile<KD>>(C, sl, sM, lane);
             }
         }
+        pipe.finish();
     }
     float* dst = states + ((size_t)seq * H + h) * KD * VD * a.L + ELL0 + lev;
 #pragma unroll
@@ -417,6 +435,7 @@ __global__ void __launch_bounds__(VD * 2) gdn_out_plain_kernel(GdnArgs a) {
     pipe.nsteps = nsteps;
     pipe.dead = false;
     pipe.status = a.status;
+    pipe.budget = a.poll_budget;
     pipe.start();
 
     float C[KD / 8][4];
@@ -453,6 +472,7 @@ __global__ void __launch_bounds__(VD * 2) gdn_out_plain_kernel(GdnArgs a) {
             state_times_mt<KD, Tile<KD>>(C, sp, sM, lane);
         }
     }
+    pipe.finish();
 }
 
 // -------------------------------------------------------------------------------------------------
@@ -497,6 +517,7 @@ __global__ void __launch_bounds__(NG * VD * 2, 1) gdn_out_hier_kernel(GdnArgs a)
     pipe.nsteps = nsteps;
     pipe.dead = false;
     pipe.status = a.status;
+    pipe.budget = a.poll_budget;
     float* red = reinterpret_cast<float*>(smem + 1024 + (size_t)NST * stage_bytes);   // [NG-1][NS][32 regs][32 lanes]
     pipe.start();
 
@@ -621,6 +642,7 @@ __global__ void __launch_bounds__(NG * VD * 2, 1) gdn_out_hier_kernel(GdnArgs a)
                 }
         }
     }
+    pipe.finish();
 }
 
 // ---- launchers ------------------------------------------------------------------------------------

@@ -19,13 +19,8 @@
 // the MMAs.  A pair's MMA for the next chunk is issued as soon as every warp has handed that pair's
 // operand back and the accumulator buffer it will overwrite has been read (two mbarriers per pair,
 // no block-wide barrier on the state path).  MMA completion is tracked by tcgen05.commit on one
-// mbarrier per pair; every wait is bounded.  Measured alternatives that were slower: letting the
-// accumulator buffers alternate along the issue order (the next chunk's first MMA then overlaps the
-// last epilogue: +18 us), three accumulator buffers for units of at most four pairs (+18 us), and issuing a
-// pair's two TMEM loads together (+50 us, spills at 96 registers).  In-kernel counters of one epilogue warp
-// (four pairs): 5.8 k cycles per chunk = record wait 0.5 k, waiting for MMAs 1.8 k, state update 1.5 k,
-// read-out 0.7 k, transpose + output 1.3 k.  More run-ahead for the tensor core never helped: an MMA in
-// flight and the epilogue's tcgen05.ld/st appear to take turns on tensor memory.
+// mbarrier per pair; every wait is bounded, and a CTA whose wait ran out stops issuing copies and
+// MMAs, waits for the ones in flight and only then frees its tensor memory.
 #include "gdn.cuh"
 #include "profile.cuh"
 
@@ -118,6 +113,7 @@ __global__ void __launch_bounds__(UTHREADS, 1) gdn_out_hier_umma_kernel(GdnArgs 
     uint64_t* mdone = sfree + UNST;                                     // pair's MMA complete      (commit)
     uint64_t* aready = mdone + UNP;                                     // pair's operand rewritten (16 warps)
     uint64_t* dfree = aready + UNP;                                     // pair's accumulator read  (16 warps)
+    uint64_t* drainb = dfree + UNP;                                     // every MMA issued has completed (commit at the end)
     uint32_t* tslot = reinterpret_cast<uint32_t*>(smem + SM_BAR + 256);
     float* sOT = reinterpret_cast<float*>(smem + SM_OT);
 
@@ -164,6 +160,7 @@ __global__ void __launch_bounds__(UTHREADS, 1) gdn_out_hier_umma_kernel(GdnArgs 
         for (int s = 0; s < UNST; ++s) { mbar_init(full + s, 1); mbar_init(sfree + s, UEPI_WARPS); }
 #pragma unroll
         for (int p = 0; p < UNP; ++p) { mbar_init(mdone + p, 1); mbar_init(aready + p, UEPI_WARPS); mbar_init(dfree + p, UEPI_WARPS); }
+        mbar_init(drainb, 1);
         fence_mbar_init();
     }
     if (warp == 0) {
@@ -200,31 +197,35 @@ __global__ void __launch_bounds__(UTHREADS, 1) gdn_out_hier_umma_kernel(GdnArgs 
     __syncthreads();
     tc_fence_after();
     bool dead = false;
+    const int budget = a.poll_budget;
 
     if (wg == 4) {
         // ---- control warp: one lane streams records and issues MMAs --------------------------------
         if (lane == 0) {
+            int loaded = 0, landed = 0;              // records requested / records seen in shared memory
             auto load_record = [&](int step) {
                 uint64_t* fb = full + (step % UNST);
                 unsigned char* dst = stage0 + (size_t)(step % UNST) * stage_bytes;
                 const char* src = rec0 + (size_t)step * rec_stride;
                 mbar_expect_tx(fb, (uint32_t)(STAGE_TILES + lam_bytes));
                 bulk_g2s(dst, src, (uint32_t)(STAGE_TILES + lam_bytes), fb);
+                loaded = step + 1;
             };
             for (int s = 0; s < UNST - 1 && s < nsteps; ++s) load_record(s);
-            for (int i = 0; i < nsteps; ++i) {
+            for (int i = 0; i < nsteps && !dead; ++i) {
                 const unsigned char* st = stage0 + (size_t)(i % UNST) * stage_bytes;
-                mbar_wait(full + (i % UNST), (uint32_t)((i / UNST) & 1), dead, a.status, 200 + i);
+                if (mbar_wait(full + (i % UNST), (uint32_t)((i / UNST) & 1), dead, a.status, 200 + i, budget)) landed = i + 1;
                 for (int p = 0; p < npairs; ++p) {
                     // the pair's operand rewritten by the previous chunk ...
-                    if (i > 0) mbar_wait(aready + p, (uint32_t)((i - 1) & 1), dead, a.status, 400 + p);
+                    if (i > 0) mbar_wait(aready + p, (uint32_t)((i - 1) & 1), dead, a.status, 400 + p, budget);
                     // ... and the accumulator buffer (p & 1) read out by the pair that used it last
                     if (p >= 2) {
-                        mbar_wait(dfree + (p - 2), (uint32_t)(i & 1), dead, a.status, 410 + p);
+                        mbar_wait(dfree + (p - 2), (uint32_t)(i & 1), dead, a.status, 410 + p, budget);
                     } else if (i > 0) {
                         const int q = ((npairs - 1) & 1) == p ? npairs - 1 : npairs - 2;
-                        mbar_wait(dfree + max(q, p), (uint32_t)((i - 1) & 1), dead, a.status, 420 + p);
+                        mbar_wait(dfree + max(q, p), (uint32_t)((i - 1) & 1), dead, a.status, 420 + p, budget);
                     }
+                    if (dead) break;                 // a wait ran out: nothing more is issued
                     tc_fence_after();
                     const uint32_t b_base = smem_u32(st + UR::M_OFF);
 #pragma unroll
@@ -233,11 +234,16 @@ __global__ void __launch_bounds__(UTHREADS, 1) gdn_out_hier_umma_kernel(GdnArgs 
                                     umma_desc_k128(b_base + kk * 32), UMMA_IDESC, kk > 0 ? 1u : 0u);
                     umma_commit(mdone + p);
                 }
-                if (i + UNST - 1 < nsteps) {       // refill the stage chunk i-1 used, once everyone is done with it
-                    if (i >= 1) mbar_wait(sfree + ((i - 1) % UNST), (uint32_t)(((i - 1) / UNST) & 1), dead, a.status, 500 + i);
-                    load_record(i + UNST - 1);
+                if (!dead && i + UNST - 1 < nsteps) {       // refill the stage chunk i-1 used, once everyone is done with it
+                    if (i >= 1) mbar_wait(sfree + ((i - 1) % UNST), (uint32_t)(((i - 1) / UNST) & 1), dead, a.status, 500 + i, budget);
+                    if (!dead) load_record(i + UNST - 1);
                 }
             }
+            // nothing asynchronous may outlive the CTA: records still on their way land first, and one
+            // last commit covers every MMA issued above
+            for (int s = landed; s < loaded; ++s) mbar_drain(full + (s % UNST), (uint32_t)((s / UNST) & 1));
+            umma_commit(drainb);
+            mbar_drain(drainb, 0u);
         }
     } else {
         // ---- epilogue warps: every warp advances 16 state columns and reads 16 tokens of its 32 rows ----
@@ -265,7 +271,7 @@ __global__ void __launch_bounds__(UTHREADS, 1) gdn_out_hier_umma_kernel(GdnArgs 
             const uint32_t low = (uint32_t)n & (BLOCK_CHUNKS - 1);
             const uint32_t read_mask = (low | (~0u << BLOCK_LOG)) & slot_ok;
             const uint32_t clear_mask = low & ~(low + 1u) & (BLOCK_CHUNKS - 1);      // trailing ones of n
-            mbar_wait(full + (i % UNST), (uint32_t)((i / UNST) & 1), dead, a.status, 250 + i);
+            mbar_wait(full + (i % UNST), (uint32_t)((i / UNST) & 1), dead, a.status, 250 + i, budget);
             // this row's 16 columns of B^T, shared by every level that collects in this chunk
             const uint4 bq0 = *reinterpret_cast<const uint4*>(sBt + v * 128 + (((2 * part) ^ (v & 7)) << 4));
             const uint4 bq1 = *reinterpret_cast<const uint4*>(sBt + v * 128 + (((2 * part + 1) ^ (v & 7)) << 4));
@@ -275,7 +281,7 @@ __global__ void __launch_bounds__(UTHREADS, 1) gdn_out_hier_umma_kernel(GdnArgs 
             for (int j = 0; j < 16; ++j) oacc[j] = 0.f;
 
             for (int p = 0; p < npairs; ++p) {
-                mbar_wait(mdone + p, (uint32_t)(i & 1), dead, a.status, 300 + p);
+                mbar_wait(mdone + p, (uint32_t)(i & 1), dead, a.status, 300 + p, budget);
                 tc_fence_after();
                 const int s = 2 * p + u;
                 const bool active = s < nslots;

@@ -99,7 +99,7 @@ __global__ void __launch_bounds__(SORT_THREADS, 1)
 segsort_kernel(const void* __restrict__ keys, int key_type, int64_t n_total,
                const int64_t* __restrict__ seg, int nseg, const int64_t* __restrict__ init,
                int64_t* __restrict__ perm, uint32_t* kbuf0, uint32_t* kbuf1, uint32_t* ibuf0,
-               uint32_t* ibuf1, int cache_cap) {
+               uint32_t* ibuf1, int cache_cap, int32_t* status) {
     cg::cluster_group cluster = cg::this_cluster();
     const int rank = (int)cluster.block_rank();
     const int ncl = (int)cluster.num_blocks();
@@ -109,7 +109,10 @@ segsort_kernel(const void* __restrict__ keys, int key_type, int64_t n_total,
     int64_t s0, n;
     if (seg) { s0 = seg[s]; n = seg[s + 1] - s0; }
     else { n = n_total / nseg; s0 = (int64_t)s * n; }
-    if (n < 0) n = 0;
+    if (n < 0 || s0 < 0 || s0 + n > n_total) {   // offsets that leave the key array: sort nothing, say so
+        if (tid == 0 && rank == 0) set_status(status, LAMPA_ERR_BOUNDS, 12, s);
+        n = 0;
+    }
     const int64_t per = (n + ncl - 1) / ncl;
     const int64_t lo = min((int64_t)rank * per, n), hi = min(lo + per, n);
 
@@ -389,7 +392,7 @@ static int clusters_resident(const cudaLaunchConfig_t& cfg, int cl, int cache_ca
 
 static int launch_segsort(const void* keys, int key_type, int64_t n_total, const int64_t* seg, int nseg,
                           const int64_t* init, int64_t* perm, uint32_t* k0, uint32_t* k1, uint32_t* i0,
-                          uint32_t* i1, cudaStream_t st) {
+                          uint32_t* i1, int32_t* status, cudaStream_t st) {
     if (cudaFuncSetAttribute(segsort_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(2 * SORT_TILE + 2 * 12288) * 4) != cudaSuccess)
         return LAMPA_ERR_CUDA;
     // Cluster size: the largest one for which every segment's cluster is resident at the same time.
@@ -418,7 +421,7 @@ static int launch_segsort(const void* keys, int key_type, int64_t n_total, const
         if (clusters_resident(cfg, cl, cache_cap) >= nseg) break;
     }
     const cudaError_t e = cudaLaunchKernelEx(&cfg, segsort_kernel, keys, key_type, n_total, seg, nseg, init, perm,
-                                             k0, k1, i0, i1, cache_cap);
+                                             k0, k1, i0, i1, cache_cap, status);
     return e == cudaSuccess ? LAMPA_OK : LAMPA_ERR_CUDA;
 }
 
@@ -434,19 +437,26 @@ __device__ __forceinline__ int find_seg64(const int64_t* off, int nseg, int64_t 
     return lo;
 }
 
+// An index outside its segment is not followed: the access is skipped and LAMPA_ERR_BOUNDS is
+// recorded in the status word (a permutation that came from lampa_segsort_stable never trips it).
 template <typename VEC>
 __global__ void __launch_bounds__(256)
 permute_rows_kernel(const VEC* __restrict__ src, const int64_t* __restrict__ perm,
                     const int64_t* __restrict__ seg, int nseg, int64_t n_rows, int64_t units_per_row,
-                    int scatter, VEC* __restrict__ dst) {
+                    int scatter, VEC* __restrict__ dst, int32_t* status) {
     const int64_t total = n_rows * units_per_row;
     for (int64_t u = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; u < total;
          u += (int64_t)gridDim.x * blockDim.x) {
         const int64_t row = u / units_per_row, col = u - row * units_per_row;
-        int64_t s0;
-        if (seg) s0 = seg[find_seg64(seg, nseg, row)];
-        else { const int64_t per = n_rows / nseg; s0 = (row / per) * per; }
-        const int64_t other = s0 + perm[row];
+        int64_t s0, len;
+        if (seg) { const int si = find_seg64(seg, nseg, row); s0 = seg[si]; len = seg[si + 1] - s0; }
+        else { len = n_rows / nseg; s0 = (row / len) * len; }
+        const int64_t p = perm[row];
+        if (p < 0 || p >= len || s0 < 0 || s0 + len > n_rows) {
+            if (col == 0) set_status(status, LAMPA_ERR_BOUNDS, 10, (int)row);
+            continue;
+        }
+        const int64_t other = s0 + p;
         if (scatter) dst[other * units_per_row + col] = src[u];
         else dst[u] = src[other * units_per_row + col];
     }
@@ -454,13 +464,15 @@ permute_rows_kernel(const VEC* __restrict__ src, const int64_t* __restrict__ per
 
 __global__ void __launch_bounds__(256)
 invert_perm_kernel(const int64_t* __restrict__ perm, const int64_t* __restrict__ seg, int nseg,
-                   int64_t n_total, int64_t* __restrict__ inv) {
+                   int64_t n_total, int64_t* __restrict__ inv, int32_t* status) {
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_total;
          i += (int64_t)gridDim.x * blockDim.x) {
-        int64_t s0;
-        if (seg) s0 = seg[find_seg64(seg, nseg, i)];
-        else { const int64_t per = n_total / nseg; s0 = (i / per) * per; }
-        inv[s0 + perm[i]] = i - s0;
+        int64_t s0, len;
+        if (seg) { const int si = find_seg64(seg, nseg, i); s0 = seg[si]; len = seg[si + 1] - s0; }
+        else { len = n_total / nseg; s0 = (i / len) * len; }
+        const int64_t p = perm[i];
+        if (p < 0 || p >= len || s0 < 0 || s0 + len > n_total) { set_status(status, LAMPA_ERR_BOUNDS, 11, (int)i); continue; }
+        inv[s0 + p] = i - s0;
     }
 }
 
@@ -496,7 +508,6 @@ extern "C" int lampa_segsort_workspace_bytes(int64_t n_total, size_t* bytes) {
 extern "C" int lampa_segsort_stable(const void* keys, int32_t key_type, int64_t n_total,
                                     const int64_t* seg_offsets, int32_t nseg, const int64_t* init,
                                     int64_t* perm, void* ws, size_t ws_bytes, int32_t* status, void* stream) {
-    (void)status;
     if (n_total < 0 || nseg <= 0 || (key_type != LAMPA_KEY_I32 && key_type != LAMPA_KEY_F32)) return LAMPA_ERR_ARG;
     if (n_total == 0) return LAMPA_OK;
     if (!keys || !perm || !ws) return LAMPA_ERR_ARG;
@@ -512,12 +523,12 @@ extern "C" int lampa_segsort_stable(const void* keys, int32_t key_type, int64_t 
     uint32_t* i0 = (uint32_t*)(base + 2 * stride);
     uint32_t* i1 = (uint32_t*)(base + 3 * stride);
     ProfScope prof("segsort", (cudaStream_t)stream);
-    return launch_segsort(keys, key_type, n_total, seg_offsets, nseg, init, perm, k0, k1, i0, i1, (cudaStream_t)stream);
+    return launch_segsort(keys, key_type, n_total, seg_offsets, nseg, init, perm, k0, k1, i0, i1, status, (cudaStream_t)stream);
 }
 
 extern "C" int lampa_permute_rows(const void* src, const int64_t* perm, const int64_t* seg_offsets,
                                   int32_t nseg, int64_t n_rows, int64_t row_bytes, int32_t scatter,
-                                  void* dst, void* stream) {
+                                  void* dst, int32_t* status, void* stream) {
     if (n_rows < 0 || row_bytes <= 0 || (row_bytes & 3) || nseg <= 0) return LAMPA_ERR_ARG;
     if (n_rows == 0) return LAMPA_OK;
     if (!src || !perm || !dst) return LAMPA_ERR_ARG;
@@ -529,21 +540,21 @@ extern "C" int lampa_permute_rows(const void* src, const int64_t* perm, const in
     const unsigned grid = (unsigned)std::min<int64_t>((total + 255) / 256, 148 * 32);
     ProfScope prof("permute_rows", st);
     if (v16)
-        permute_rows_kernel<uint4><<<grid, 256, 0, st>>>((const uint4*)src, perm, seg_offsets, nseg, n_rows, upr, scatter, (uint4*)dst);
+        permute_rows_kernel<uint4><<<grid, 256, 0, st>>>((const uint4*)src, perm, seg_offsets, nseg, n_rows, upr, scatter, (uint4*)dst, status);
     else
-        permute_rows_kernel<uint32_t><<<grid, 256, 0, st>>>((const uint32_t*)src, perm, seg_offsets, nseg, n_rows, upr, scatter, (uint32_t*)dst);
+        permute_rows_kernel<uint32_t><<<grid, 256, 0, st>>>((const uint32_t*)src, perm, seg_offsets, nseg, n_rows, upr, scatter, (uint32_t*)dst, status);
     return cudaGetLastError() == cudaSuccess ? LAMPA_OK : LAMPA_ERR_CUDA;
 }
 
 extern "C" int lampa_invert_perm(const int64_t* perm, const int64_t* seg_offsets, int32_t nseg,
-                                 int64_t n_total, int64_t* inv, void* stream) {
+                                 int64_t n_total, int64_t* inv, int32_t* status, void* stream) {
     if (n_total < 0 || nseg <= 0) return LAMPA_ERR_ARG;
     if (n_total == 0) return LAMPA_OK;
     if (!perm || !inv) return LAMPA_ERR_ARG;
     if (!seg_offsets && n_total % nseg != 0) return LAMPA_ERR_ARG;
     const unsigned grid = (unsigned)std::min<int64_t>((n_total + 255) / 256, 148 * 32);
     ProfScope prof("invert_perm", (cudaStream_t)stream);
-    invert_perm_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(perm, seg_offsets, nseg, n_total, inv);
+    invert_perm_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(perm, seg_offsets, nseg, n_total, inv, status);
     return cudaGetLastError() == cudaSuccess ? LAMPA_OK : LAMPA_ERR_CUDA;
 }
 
@@ -581,7 +592,6 @@ static int static_sort_scratch(void** out) {
 extern "C" int lampa_segsort_stable_static(const void* keys, int32_t key_type, int64_t n_total,
                                            const int64_t* seg_offsets, int32_t nseg, const int64_t* init,
                                            int64_t* perm, int32_t* status, void* stream) {
-    (void)status;
     if (n_total < 0 || nseg <= 0 || (key_type != LAMPA_KEY_I32 && key_type != LAMPA_KEY_F32)) return LAMPA_ERR_ARG;
     if (n_total > (int64_t)LAMPA_SEGSORT_STATIC_MAX_KEYS) return LAMPA_ERR_TOO_LARGE;
     if (n_total == 0) return LAMPA_OK;
@@ -596,5 +606,5 @@ extern "C" int lampa_segsort_stable_static(const void* keys, int32_t key_type, i
     ProfScope prof("segsort_static", (cudaStream_t)stream);
     return launch_segsort(keys, key_type, n_total, seg_offsets, nseg, init, perm, (uint32_t*)base,
                           (uint32_t*)(base + kStaticSortStride), (uint32_t*)(base + 2 * kStaticSortStride),
-                          (uint32_t*)(base + 3 * kStaticSortStride), (cudaStream_t)stream);
+                          (uint32_t*)(base + 3 * kStaticSortStride), status, (cudaStream_t)stream);
 }

@@ -5,8 +5,10 @@ Same names, argument meaning and error behaviour as the reference entry points:
   chunk_h_gated_delta_rule  models/hattention/gated_delta_rule_apis.py:20-134
   hattention_kernel         models/hattention/kernel.py:338-374
   hattention_prefill / hattention_step / HState   kernel.py:470-633, recurrent.py:9-131
-Forward only (no autograd graph is recorded).  Everything runs in the CUDA library on
-the current torch stream; there is no PyTorch or CPU fallback.
+Forward only: the ops are not differentiable, and a call whose inputs require grad while grad
+mode is on raises instead of returning a silently detached result (the reference's forward-only
+ops raise in backward: gated_delta_rule_ori.py:555-562).  Everything runs in the CUDA library
+on the current torch stream; there is no PyTorch or CPU fallback.
 """
 from __future__ import annotations
 
@@ -44,8 +46,26 @@ def num_levels_required(T: int) -> int:
     return ELL0 + (math.ceil(math.log2(nt)) if nt > 1 else 0)
 
 
+def _check_cu_seqlens(cu_seqlens, T: int, n_levels: Optional[int] = None) -> None:
+    """Host-side validation of packed offsets when they are host-resident (the reference reads
+    them on the host too, models/hattention/index.py:69-83).  Device-resident offsets are checked
+    by the kernels instead: a bad entry empties that sequence and sets LAMPA_ERR_BOUNDS /
+    LAMPA_ERR_LEVELS in the status word, which the caller reads with `check_status()` at its next
+    synchronisation point (LAMPA_B200_CHECK=1 does so after every call)."""
+    if cu_seqlens is None or cu_seqlens.is_cuda:
+        return
+    cu = cu_seqlens.tolist()
+    if len(cu) < 2 or cu[0] != 0 or cu[-1] != T or any(b < a for a, b in zip(cu[:-1], cu[1:])):
+        raise ValueError(f"cu_seqlens must rise from 0 to the number of tokens ({T}); got {cu[:4]}...{cu[-2:]}")
+    if n_levels is not None:
+        longest = max(b - a for a, b in zip(cu[:-1], cu[1:]))
+        if n_levels < num_levels_required(longest):
+            raise ValueError(f"l has {n_levels} levels, a sequence of {longest} tokens needs {num_levels_required(longest)}")
+
+
 def _common_checks(q, k, v, beta, head_first, cu_seqlens, initial_state):
     assert q.dtype == k.dtype == v.dtype
+    assert q.dtype != torch.float32, "ChunkGatedDeltaRuleFunction does not support float32. Please use bfloat16."
     assert len(beta.shape) == 3, "beta must be of shape [B, T, H] if head_first=False, or [B, H, T] otherwise."
     if head_first:
         raise DeprecationWarning(
@@ -70,6 +90,13 @@ def _common_checks(q, k, v, beta, head_first, cu_seqlens, initial_state):
                 f"The number of initial states is expected to be equal to the number of input sequences, "
                 f"i.e., {len(cu_seqlens) - 1} rather than {initial_state.shape[0]}."
             )
+
+
+def _forward_only(*tensors) -> None:
+    if torch.is_grad_enabled() and any(t is not None and t.requires_grad for t in tensors):
+        raise NotImplementedError(
+            "lampa_b200 implements the forward pass only: backward is not implemented; "
+            "call under torch.no_grad() or detach the inputs")
 
 
 def _desc(q, v, g, lam, cu_seqlens, use_l2norm, scale) -> L.GdnDesc:
@@ -105,7 +132,6 @@ def _prep_inputs(q, k, v, g, beta, lam, cu_seqlens):
     return dev, q, k, v, g, beta, lam, cu_seqlens
 
 
-@torch.no_grad()
 def chunk_gated_delta_rule(
     q: torch.Tensor,
     k: torch.Tensor,
@@ -123,12 +149,21 @@ def chunk_gated_delta_rule(
 
     q, k: [B,T,H,K]; v: [B,T,H,V]; g (log decay), beta: [B,T,H]; initial_state: [N,H,K,V];
     cu_seqlens: [N+1] with B == 1.  Returns (o [B,T,H,V] in q's dtype, final_state [N,H,K,V]
-    fp32 or None).  Unlike the reference (gated_delta_rule_ori.py:313) fp32 q/k/v are accepted;
-    they are rounded to bf16 as tensor-core operands.
+    fp32 or None).  fp32 q/k/v are rejected as in the reference (gated_delta_rule_ori.py:313):
+    the tensor-core operands are bf16, so an fp32 call could not honour fp32 accuracy.
     """
     _common_checks(q, k, v, beta, head_first, cu_seqlens, initial_state)
+    _check_cu_seqlens(cu_seqlens, q.shape[1])
+    _forward_only(q, k, v, g, beta, initial_state)
     if scale is None:
         scale = k.shape[-1] ** -0.5
+    with torch.no_grad():
+        return _gdn_plain(q, k, v, g, beta, scale, initial_state, output_final_state, cu_seqlens,
+                          use_qk_l2norm_in_kernel)
+
+
+@torch.no_grad()
+def _gdn_plain(q, k, v, g, beta, scale, initial_state, output_final_state, cu_seqlens, use_qk_l2norm_in_kernel):
     dev, q, k, v, g, beta, _, cu = _prep_inputs(q, k, v, g, beta, None, cu_seqlens)
     B, T, H, K = q.shape
     V = v.shape[-1]
@@ -158,7 +193,7 @@ class HState:
     [B,H,K,V,L] and `counts` [L] int32 (tokens held per level).  Always fp32 on the device; the
     cascade / insert / dot methods of the reference live in the library's step kernel."""
 
-    def __init__(self, base: int, htype, hstruct, shape, dtype: torch.dtype, device) -> None:
+    def __init__(self, base: int, htype, hstruct, shape, dtype: torch.dtype, device, empty: bool = False) -> None:
         if getattr(htype, "name", htype) != "WEAK" or base != 2:
             raise NotImplementedError
         if dtype != torch.float32:
@@ -170,6 +205,9 @@ class HState:
         self.dtype = dtype
         self.device = torch.device(device)
         self.max_num_levels = self.shape[-1]
+        if empty:                      # the caller attaches tensors it already has
+            self.states = self.counts = None
+            return
         self.states = torch.zeros(self.shape, dtype=dtype, device=device)
         self.counts = torch.zeros(self.max_num_levels, dtype=torch.int32, device=device)
 
@@ -188,6 +226,7 @@ class HState:
 
 @torch.no_grad()
 def _hgdn(q, k, v, g, beta, lam, cu_seqlens, use_l2norm, want_state: bool = False):
+    _check_cu_seqlens(cu_seqlens, q.shape[1], lam.shape[-1])
     dev, q, k, v, g, beta, lam, cu = _prep_inputs(q, k, v, g, beta, lam, cu_seqlens)
     B, T, H, K = q.shape
     V = v.shape[-1]
@@ -292,16 +331,27 @@ def chunk_h_gated_delta_rule(
       output_final_state=True, no initial_state -> (o, HState) after all T tokens (prefill)
       output_final_state=True, initial_state    -> T must be 1: one decode step on the state
                                                    (updated in place and returned)
-    Beyond the reference: `cu_seqlens` and T not a multiple of 64 are accepted by the first branch.
+    Beyond the reference: `cu_seqlens` and T not a multiple of 64 are accepted by the first branch,
+    and `cu_seqlens` by the second: the returned HState then holds one state per sequence
+    (`states` [N,H,K,V,L], `counts` [N,L]); a sequence whose length is not a multiple of 64 is
+    completed by null tokens (k = v = 0, beta = 0, g = 0), which its counts include.
+    Device-side problems (a wait that ran out, device-resident cu_seqlens that are malformed or
+    need more levels than l has) are reported through `check_status()`.
     """
     _common_checks(q, k, v, beta, head_first, cu_seqlens, None)
     assert use_qk_l2norm_in_kernel is True
+    _forward_only(q, k, v, g, l, beta)
     if output_final_state is False:
         if initial_state is not None:
             raise NotImplementedError
         return _hgdn(q, k, v, g, beta, l, cu_seqlens, True), None
     if cu_seqlens is not None:
-        raise NotImplementedError("final state of packed sequences is not exposed at this level")
+        if initial_state is not None:
+            raise NotImplementedError("a decode step takes one token per batch row, not packed sequences")
+        o, states, counts = _hgdn(q, k, v, g, beta, l, cu_seqlens, True, want_state=True)
+        hs = HState(2, HType.WEAK, HStruct.GDELTA, tuple(states.shape), torch.float32, states.device, empty=True)
+        hs.states, hs.counts = states, counts
+        return o, hs
     if initial_state is None:
         return _hgdn_prefill(q, k, v, g, beta, l, True)
     if not all([q.ndim == 4, q.shape[1] == 1, k.ndim == 4, k.shape[1] == 1, v.ndim == 4, v.shape[1] == 1,

@@ -123,7 +123,7 @@ def permute_rows(src: torch.Tensor, perm: torch.Tensor, seg_offsets: Optional[to
         nseg = seg_offsets.numel() - 1
     dst = torch.empty_like(src)
     rc = L.lib().lampa_permute_rows(L.ptr(src), L.ptr(perm), L.ptr(seg_offsets), nseg, rows, row_bytes,
-                                    int(scatter), L.ptr(dst), L.stream_ptr(dev))
+                                    int(scatter), L.ptr(dst), L.ptr(L.status_word(dev)), L.stream_ptr(dev))
     L.check(rc, "lampa_permute_rows")
     return dst
 
@@ -137,7 +137,8 @@ def invert_permutation(perm: torch.Tensor) -> torch.Tensor:
     n = p.shape[-1]
     inv = torch.empty_like(p)
     nseg = p.numel() // n if n else 1
-    rc = L.lib().lampa_invert_perm(L.ptr(p), None, max(nseg, 1), p.numel(), L.ptr(inv), L.stream_ptr(dev))
+    rc = L.lib().lampa_invert_perm(L.ptr(p), None, max(nseg, 1), p.numel(), L.ptr(inv), L.ptr(L.status_word(dev)),
+                                   L.stream_ptr(dev))
     L.check(rc, "lampa_invert_perm")
     return inv
 

@@ -1,0 +1,221 @@
+"""Packed, event-sharded forward of an lshgd-style tracking model built on the library's ops.
+
+Layer structure follows the reference's model shell and mixer layer:
+  LSHGatedDelta / LSHGatedDeltaProductBlock   models/hattention/modeling_gated_deltaproduct.py:1608-1792, 1136-1199
+  HGatedDeltaNet (q/k/v + short convolution, a/b/l projections, gated output norm, o_proj)
+                                              models/hattention/modeling_h_gated_deltanet.py:255-487
+  per-event ordering of the hits by an LSH key, mixer on the ordered rows, un-ordering
+                                              models/baselines/hmamba.py:428-455
+Differences that the benchmark configuration asks for: the ordering is the integer E2LSH key
+(round r: key = sum_h id[r, h] << h, stable sort per event; block b uses round b mod rounds), the
+mixer is the hierarchical rule with `cu_seqlens` (one hierarchy per event), the MLP is
+Linear-GELU-Linear, and a batch is many events packed back to back.
+
+Host side: torch (Linear, RMS norm, GELU, residuals).  Hashing, sorting, row movement, the
+short convolutions, gate inputs, the mixer and its gated norm run in the CUDA library.
+Forward only.
+"""
+from __future__ import annotations
+
+import math
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from . import sharding
+from .gated_delta import chunk_h_gated_delta_rule, num_levels_required
+from .layer import FusedRMSNormGated, ShortConvolution, gate_inputs
+from .lsh import lsh_hash, permute_rows, segmented_sort
+
+
+class HGatedDeltaNet(nn.Module):
+    """The hierarchical gated-delta mixer layer (modeling_h_gated_deltanet.py:255-487), forward only.
+
+    forward(hidden_states [1, T, hidden] , cu_seqlens) -> [1, T, hidden].  `num_levels` is the
+    number of lambda levels the l projection produces (the reference fixes MAX_NUM_LEVELS = 13
+    for T <= 4096; here it is a constructor argument so that 60k-hit events fit).
+    """
+
+    def __init__(self, hidden_size: int = 128, expand_v: float = 1, head_dim: int = 32, num_heads: int = 4,
+                 use_gate: bool = True, use_short_conv: bool = True, conv_size: int = 4, conv_bias: bool = False,
+                 norm_eps: float = 1e-5, num_levels: int = 17, layer_idx: Optional[int] = None,
+                 device=None, dtype=None):
+        super().__init__()
+        kw = dict(device=device, dtype=dtype)
+        self.hidden_size, self.head_dim, self.num_heads = hidden_size, head_dim, num_heads
+        self.head_k_dim = head_dim
+        self.head_v_dim = int(head_dim * expand_v)
+        self.key_dim = num_heads * self.head_k_dim
+        self.value_dim = num_heads * self.head_v_dim
+        self.use_gate, self.use_short_conv, self.layer_idx = use_gate, use_short_conv, layer_idx
+        self.num_levels = num_levels
+        self.q_proj = nn.Linear(hidden_size, self.key_dim, bias=False, **kw)
+        self.k_proj = nn.Linear(hidden_size, self.key_dim, bias=False, **kw)
+        self.v_proj = nn.Linear(hidden_size, self.value_dim, bias=False, **kw)
+        self.a_proj = nn.Linear(hidden_size, num_heads, bias=False, **kw)
+        self.b_proj = nn.Linear(hidden_size, num_heads, bias=False, **kw)
+        A = torch.empty(num_heads, dtype=torch.float32).uniform_(0, 16)
+        self.A_log = nn.Parameter(torch.log(A))
+        dt_min, dt_max, dt_init_floor = 0.001, 0.1, 1e-4
+        dt = torch.exp(torch.rand(num_heads) * (math.log(dt_max) - math.log(dt_min)) + math.log(dt_min))
+        dt = torch.clamp(dt, min=dt_init_floor)
+        self.dt_bias = nn.Parameter(dt + torch.log(-torch.expm1(-dt)))
+        if use_short_conv:
+            self.q_conv1d = ShortConvolution(self.key_dim, conv_size, bias=conv_bias, activation="silu", **kw)
+            self.k_conv1d = ShortConvolution(self.key_dim, conv_size, bias=conv_bias, activation="silu", **kw)
+            self.v_conv1d = ShortConvolution(self.value_dim, conv_size, bias=conv_bias, activation="silu", **kw)
+        self.g_proj = nn.Linear(hidden_size, self.value_dim, bias=False, **kw)
+        self.o_norm = FusedRMSNormGated(self.head_v_dim, eps=norm_eps, **kw)
+        self.o_proj = nn.Linear(self.value_dim, hidden_size, bias=False, **kw)
+        self.l_proj = nn.Linear(hidden_size, num_heads * num_levels, bias=False, **kw)
+        self.lambda_mode = "positive"
+        self.L = nn.Parameter(torch.ones(num_heads, num_levels))
+
+    @torch.no_grad()
+    def forward(self, hidden_states: torch.Tensor, cu_seqlens: Optional[torch.Tensor] = None) -> torch.Tensor:
+        B, T, _ = hidden_states.shape
+        H = self.num_heads
+        if self.use_short_conv:
+            q, _ = self.q_conv1d(self.q_proj(hidden_states), cu_seqlens=cu_seqlens)
+            k, _ = self.k_conv1d(self.k_proj(hidden_states), cu_seqlens=cu_seqlens)
+            v, _ = self.v_conv1d(self.v_proj(hidden_states), cu_seqlens=cu_seqlens)
+        else:
+            q, k, v = (F.silu(p(hidden_states)) for p in (self.q_proj, self.k_proj, self.v_proj))
+        q = q.view(B, T, H, self.head_k_dim)
+        k = k.view(B, T, H, self.head_k_dim)
+        v = v.view(B, T, H, self.head_v_dim)
+        g, beta, lam = gate_inputs(self.a_proj(hidden_states), self.b_proj(hidden_states),
+                                   self.l_proj(hidden_states), self.A_log, self.dt_bias, self.L, self.lambda_mode)
+        o, _ = chunk_h_gated_delta_rule(q, k, v, g, lam, beta, cu_seqlens=cu_seqlens,
+                                        use_qk_l2norm_in_kernel=True)
+        if self.use_gate:
+            gate = self.g_proj(hidden_states).view(B, T, H, self.head_v_dim)
+            o = self.o_norm(o, gate)
+        else:
+            o = self.o_norm(o, torch.ones_like(o))
+        return self.o_proj(o.reshape(B, T, self.value_dim))
+
+
+class LSHGatedDeltaBlock(nn.Module):
+    """[RMSNorm, order by the block's LSH round, mixer, un-order, residual, RMSNorm, MLP, residual]
+    (the block of modeling_gated_deltaproduct.py:1136-1199 with the ordering of hmamba.py:428-455
+    around the mixer).  The residual stream is fp32; the mixer and the MLP compute in `dtype`."""
+
+    def __init__(self, dim: int, head_dim: int, num_heads: int, layer_idx: int, num_levels: int,
+                 mlp_ratio: int = 4, eps: float = 1e-6, dtype=torch.bfloat16, device=None):
+        super().__init__()
+        self.layer_idx, self.eps, self.dtype = layer_idx, eps, dtype
+        self.attn_norm_weight = nn.Parameter(torch.ones(dim, device=device))
+        self.attn = HGatedDeltaNet(dim, 1, head_dim, num_heads, num_levels=num_levels, layer_idx=layer_idx,
+                                   norm_eps=eps, device=device, dtype=dtype)
+        self.mlp_norm_weight = nn.Parameter(torch.ones(dim, device=device))
+        self.mlp_up = nn.Linear(dim, mlp_ratio * dim, device=device, dtype=dtype)
+        self.mlp_down = nn.Linear(mlp_ratio * dim, dim, device=device, dtype=dtype)
+
+    @torch.no_grad()
+    def forward(self, x: torch.Tensor, perm: torch.Tensor, cu: torch.Tensor) -> torch.Tensor:
+        n, d = x.shape
+        h = F.rms_norm(x, (d,), self.attn_norm_weight, self.eps).to(self.dtype)
+        hs = permute_rows(h, perm, seg_offsets=cu)
+        o = self.attn(hs.view(1, n, d), cu_seqlens=cu).view(n, d)
+        x = x + permute_rows(o, perm, seg_offsets=cu, scatter=True).float()
+        h = F.rms_norm(x, (d,), self.mlp_norm_weight, self.eps).to(self.dtype)
+        return x + self.mlp_down(F.gelu(self.mlp_up(h))).float()
+
+
+class LSHGatedDelta(nn.Module):
+    """Hit features [N, in_dim] fp32 of packed events -> clustering embedding [N, out_dim] fp32.
+
+    forward(hits, cu_seqlens): `cu_seqlens` int64 [n_events + 1] gives the row range of each event;
+    the first `coord_dim` features of a row are the coordinates that are hashed.  Events never
+    interact: every sort, convolution and mixer hierarchy restarts at an event boundary, so a
+    batch can be split by event across GPUs (`forward_sharded`).
+    """
+
+    def __init__(self, in_dim: int = 24, d_model: int = 128, n_layers: int = 4, num_heads: int = 4,
+                 head_dim: int = 32, out_dim: int = 24, n_hash_rounds: int = 3, n_hash_heads: int = 8,
+                 coord_dim: int = 6, bucket_width: float = 1.0, max_hits_per_event: int = 60000,
+                 dtype=torch.bfloat16, device=None):
+        super().__init__()
+        self.coord_dim, self.bucket_width, self.rounds = coord_dim, float(bucket_width), n_hash_rounds
+        self.max_hits_per_event = max_hits_per_event
+        self.num_levels = num_levels_required(max_hits_per_event)
+        self.encoder = nn.Linear(in_dim, d_model, device=device)
+        self.blocks = nn.ModuleList([LSHGatedDeltaBlock(d_model, head_dim, num_heads, i, self.num_levels,
+                                                        dtype=dtype, device=device) for i in range(n_layers)])
+        self.head = nn.Linear(d_model, out_dim, device=device)
+        self.lsh_alpha = nn.Parameter(torch.randn(n_hash_heads, coord_dim, n_hash_rounds, device=device),
+                                      requires_grad=False)
+        self.lsh_beta = nn.Parameter(torch.rand(n_hash_rounds, device=device) * bucket_width, requires_grad=False)
+        # fixed input scaling to O(1) features (x, y, r in m; z in 3 m; phi in pi; eta in 4); the hashes see raw rows
+        scale = torch.ones(in_dim)
+        scale[:min(in_dim, 6)] = torch.tensor([1e-3, 1e-3, 1 / 3000.0, 1e-3, 1 / math.pi, 0.25])[:min(in_dim, 6)]
+        self.register_buffer("feature_scale", scale.to(device) if device is not None else scale)
+
+    @torch.no_grad()
+    def orderings(self, hits: torch.Tensor, cu: torch.Tensor) -> torch.Tensor:
+        """Stable per-event sort of every round's packed bucket key: int64 [rounds, N], indices
+        local to the event.  One hash launch and one segmented sort serve all blocks."""
+        n = hits.shape[0]
+        packed = lsh_hash(hits, self.lsh_alpha, self.lsh_beta, self.bucket_width, dim=self.coord_dim,
+                          want_ids=False, want_packed=True)["packed"]                      # [rounds, N]
+        offs = (torch.arange(self.rounds, device=hits.device, dtype=torch.int64)[:, None] * n + cu[None, :-1]).reshape(-1)
+        seg = torch.cat([offs, torch.full((1,), self.rounds * n, device=hits.device, dtype=torch.int64)])
+        return segmented_sort(packed, seg_offsets=seg).view(self.rounds, n)
+
+    @torch.no_grad()
+    def forward(self, hits: torch.Tensor, cu_seqlens: torch.Tensor) -> torch.Tensor:
+        cu = cu_seqlens.to(device=hits.device, dtype=torch.int64)
+        perms = self.orderings(hits, cu)
+        x = self.encoder(hits * self.feature_scale)
+        for b, blk in enumerate(self.blocks):
+            x = blk(x, perms[b % self.rounds], cu)
+        return self.head(x)
+
+    def check_event_sizes(self, lengths: Sequence[int]) -> None:
+        """Host check that no event needs more lambda levels than the l projection produces."""
+        longest = max((int(n) for n in lengths), default=0)
+        if num_levels_required(longest) > self.num_levels:
+            raise ValueError(f"an event of {longest} hits needs {num_levels_required(longest)} levels; "
+                             f"the model was built for {self.max_hits_per_event} hits ({self.num_levels} levels)")
+
+
+@torch.no_grad()
+def forward_sharded(model: LSHGatedDelta, hits: torch.Tensor, lengths: Sequence[int],
+                    plan: Optional[List[List[int]]] = None, group=None, rank: Optional[int] = None,
+                    gather: bool = True, gather_stream: Optional[torch.cuda.Stream] = None
+                    ) -> Tuple[torch.Tensor, Dict[str, float]]:
+    """Event-sharded forward over the ranks of a process group.
+
+    `hits` [N_total, in_dim] are the rows of ALL events in event order and `lengths` their hit
+    counts (every rank passes the same host-side `lengths`); each rank picks the events that the
+    longest-processing-time plan gives it, packs them, runs the model on them and, with `gather`,
+    all-gathers the per-event outputs into the global event order (optionally on `gather_stream`
+    so that the caller's next step can start).  Without a process group it is the plain forward.
+    Returns (output, info) with info["imbalance"] = max / mean hits per rank.
+    """
+    import torch.distributed as dist
+    lens = [int(n) for n in lengths]
+    model.check_event_sizes(lens)
+    world = dist.get_world_size(group) if dist.is_available() and dist.is_initialized() else 1
+    if world == 1:
+        cu = torch.zeros(len(lens) + 1, dtype=torch.int64)
+        cu[1:] = torch.tensor(lens, dtype=torch.int64).cumsum(0)
+        return model(hits, cu.to(hits.device)), {"imbalance": 1.0, "owned": len(lens)}
+    rank = dist.get_rank(group) if rank is None else rank
+    plan = sharding.lpt_assign(lens, world) if plan is None else plan
+    local_hits, cu = sharding.shard_events(hits, lens, plan[rank])
+    out = (model(local_hits, cu.to(hits.device)) if len(plan[rank])
+           else hits.new_zeros(0, model.head.out_features))
+    info = {"imbalance": sharding.imbalance(lens, plan), "owned": len(plan[rank])}
+    if not gather:
+        return out, info
+    if gather_stream is None:
+        return sharding.gather_event_outputs(out, lens, plan, group), info
+    gather_stream.wait_stream(torch.cuda.current_stream(hits.device))
+    with torch.cuda.stream(gather_stream):
+        out.record_stream(gather_stream)
+        full = sharding.gather_event_outputs(out, lens, plan, group)
+    return full, info

@@ -73,7 +73,7 @@ def gather_event_outputs(local: torch.Tensor, lengths: Sequence[int], plan: Sequ
     """All-gather ragged per-event outputs ([rows_owned, D] per rank) into the global event order.
 
     Pads every rank's block to the largest block so that one all_gather suffices (NCCL or gloo),
-    then scatters rows back to their events' positions.
+    then copies each event's rows to its position.  The only collective of the path.
     """
     world = dist.get_world_size(group)
     rows = [sum(int(lengths[e]) for e in o) for o in plan]
@@ -81,8 +81,12 @@ def gather_event_outputs(local: torch.Tensor, lengths: Sequence[int], plan: Sequ
     pad = max(rows)
     buf = local.new_zeros(pad, width)
     buf[: local.shape[0]] = local
-    parts = [torch.empty_like(buf) for _ in range(world)]
-    dist.all_gather(parts, buf, group=group)
+    if local.is_cuda:
+        parts = local.new_empty(world, pad, width)
+        dist.all_gather_into_tensor(parts, buf, group=group)
+    else:
+        parts = [torch.empty_like(buf) for _ in range(world)]
+        dist.all_gather(parts, buf, group=group)
     total = sum(int(n) for n in lengths)
     out = local.new_empty(total, width)
     starts = [0]
@@ -95,3 +99,12 @@ def gather_event_outputs(local: torch.Tensor, lengths: Sequence[int], plan: Sequ
             out[starts[e]: starts[e] + n] = parts[r][pos: pos + n]
             pos += n
     return out
+
+
+def shard_events(rows: torch.Tensor, lengths: Sequence[int], owned: Sequence[int]) -> Tuple[torch.Tensor, torch.Tensor]:
+    """The rows of the events a rank owns, packed back to back, and their cu_seqlens (int64, host).
+
+    `rows` holds all events in event order ([sum(lengths), D], host or device)."""
+    cu, spans = pack_events(lengths, owned)
+    local = torch.cat([rows[s:e] for s, e in spans]) if spans else rows[:0]
+    return local, cu

@@ -126,6 +126,23 @@ def test_random_cases_against_checker(lb, N, block, H, C, dq, dv):
             np.testing.assert_array_equal(to_np(lg)[c, h][qp[c, h]], to_np(den).reshape(C, H, N, 1)[c, h])
 
 
+def test_slices_of_wider_storage_are_not_read_past_their_width(lb):
+    """q_hat / k_hat given as [..., :30] slices of 32-wide rows whose last two columns hold other
+    data: the result must be that of the 30 columns alone (the 16-byte row fetch would fold the
+    extra columns into q.k and the norms if such a view were read in place)."""
+    rng = np.random.default_rng(5)
+    H, N, dq, dv, block, C = 2, 400, 30, 24, 100, 2
+    wide_q = (rng.standard_normal((H, N, 32)) * 0.4).astype(np.float32)
+    wide_k = (wide_q + rng.standard_normal((H, N, 32)) * 0.2).astype(np.float32)
+    v = rng.standard_normal((H, N, dv)).astype(np.float32)
+    qp = np.stack([np.stack([rng.permutation(N) for _ in range(H)]) for _ in range(C)]).astype(np.int64)
+    kp = np.stack([np.stack([rng.permutation(N) for _ in range(H)]) for _ in range(C)]).astype(np.int64)
+    out = lb.hept_bucket_attention(_c(wide_q)[..., :dq], _c(wide_k)[..., :dq], _c(v), _c(qp), _c(kp), block)
+    ref_out, _, _ = oracle.hept_bucket_attention(np.ascontiguousarray(wide_q[..., :dq]),
+                                                 np.ascontiguousarray(wide_k[..., :dq]), v, qp, kp, block)
+    _close(to_np(out), ref_out, 5e-5, "out (sliced rows)")
+
+
 def test_identical_points_and_far_points(lb):
     """All hits of a bucket equal: every weight is 1 (clamp at 0), so = bucket * v, denom = bucket.
     Hits far apart: off-diagonal weights underflow to 0 and each hit sees only itself."""

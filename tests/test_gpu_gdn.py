@@ -69,13 +69,16 @@ def test_plain_options_dtypes_scale_and_batch(lb):
     assert ht is None
     oref, _ = _plain_ref(inp, scale=0.3, l2=False)
     assert_close_bf16(to_np(o[0]), oref, "o (no l2norm, scale 0.3)")
-    # fp16 and fp32 inputs (rounded to bf16 operands inside); output in the input dtype
-    for dt in (torch.float16, torch.float32):
-        o2, _ = lb.chunk_gated_delta_rule(d["q"].to(dt), d["k"].to(dt), d["v"].to(dt), d["g"], d["beta"],
-                                          use_qk_l2norm_in_kernel=True)
-        assert o2.dtype == dt
-        oref2, _ = _plain_ref(inp)
-        assert_close_bf16(to_np(o2[0]), oref2, f"o ({dt})")
+    # fp16 inputs (rounded to bf16 operands inside); output in the input dtype
+    dt = torch.float16
+    o2, _ = lb.chunk_gated_delta_rule(d["q"].to(dt), d["k"].to(dt), d["v"].to(dt), d["g"], d["beta"],
+                                      use_qk_l2norm_in_kernel=True)
+    assert o2.dtype == dt
+    oref2, _ = _plain_ref(inp)
+    assert_close_bf16(to_np(o2[0]), oref2, f"o ({dt})")
+    # fp32 q / k / v are refused, as by the reference (gated_delta_rule_ori.py:313)
+    with pytest.raises(AssertionError):
+        lb.chunk_gated_delta_rule(d["q"].float(), d["k"].float(), d["v"].float(), d["g"], d["beta"])
     # bf16 g / beta
     o3, _ = lb.chunk_gated_delta_rule(d["q"], d["k"], d["v"], d["g"].bfloat16(), d["beta"].bfloat16(),
                                       use_qk_l2norm_in_kernel=True)

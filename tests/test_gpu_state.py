@@ -242,3 +242,25 @@ def test_final_state_of_packed_sequences_through_the_c_abi(lb):
         _, sref, cref = _ref(sub)
         np.testing.assert_array_equal(got_c, cref)
         _close_states(got_s, sref, f"sequence {n}")
+
+
+def test_final_state_of_packed_sequences_through_the_python_op(lb):
+    """chunk_h_gated_delta_rule(output_final_state=True, cu_seqlens=...) returns one Fenwick state
+    and one counts row per sequence."""
+    from lampa_b200 import synth
+    H, K, V = 2, 32, 32
+    lens = [1280, 64, 3200]
+    cu = torch.tensor([0] + lens).cumsum(0)
+    T = int(cu[-1])
+    Lv = lb.num_levels_required(max(lens))
+    inp = synth.gdn_inputs(43, T, H, K, V, L=Lv, g_shift=-3.0)
+    d = _cuda(inp)
+    o, hs = lb.chunk_h_gated_delta_rule(d["q"], d["k"], d["v"], d["g"], d["lam"], d["beta"], cu_seqlens=cu,
+                                        output_final_state=True, use_qk_l2norm_in_kernel=True)
+    assert isinstance(hs, lb.HState) and tuple(hs.states.shape) == (3, H, K, V, Lv) and tuple(hs.counts.shape) == (3, Lv)
+    for n, (s, e) in enumerate(zip(cu[:-1].tolist(), cu[1:].tolist())):
+        sub = {k: x[:, s:e] for k, x in inp.items()}
+        oref, sref, cref = _ref(sub)
+        assert_close_bf16(to_np(o[0, s:e]), oref, f"o of sequence {n}")
+        np.testing.assert_array_equal(to_np(hs.counts[n]), cref)
+        _close_states(to_np(hs.states[n]), sref, f"sequence {n}")

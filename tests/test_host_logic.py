@@ -41,7 +41,7 @@ def test_host_side_argument_errors_without_a_gpu():
     assert lay[1] % 128 == 0 and lay[7] == 10 and lay[9] == 32
     assert lib.lampa_segsort_workspace_bytes(-1, ctypes.byref(n)) == -1
     assert lib.lampa_lsh_hash(None, 24, 0, None, None, 1.0, 10, 8, 3, 6, None, None, None, None) == -1
-    assert lib.lampa_permute_rows(None, None, None, 1, 10, 6, 0, None, None) == -1            # row bytes not /4
+    assert lib.lampa_permute_rows(None, None, None, 1, 10, 6, 0, None, None, None) == -1            # row bytes not /4
     assert lib.lampa_bucket_rbf_attn(None, None, None, None, None, 3, 8, 1000, 30, 30, 24, 32, 24, 0, 1, None, None, None) == -1   # n % bucket
     assert lib.lampa_bucket_rbf_attn(None, None, None, None, None, 3, 8, 900, 300, 30, 24, 30, 24, 0, 1, None, None, None) == -1   # null tensors
     assert lib.lampa_bucket_rbf_attn(None, None, None, None, None, 3, 8, 900, 100, 30, 24, 28, 24, 0, 1, None, None, None) == -1   # pitch < width
@@ -114,6 +114,52 @@ def _rank_main(rank, world, port, lens):
 def test_two_rank_plan_and_gather_over_gloo():
     lens = [700, 60, 1500, 333, 64, 900, 5]
     mp.spawn(_rank_main, args=(2, _free_port(), lens), nprocs=2, join=True)
+
+
+class _EventMeanModel:
+    """Stand-in for the packed model on CPU ranks: every row minus its event's mean (so that a
+    wrong event boundary or a wrong gather position shows), three output columns."""
+
+    class _Head:
+        out_features = 3
+
+    head = _Head()
+
+    def check_event_sizes(self, lengths):
+        pass
+
+    def __call__(self, hits, cu):
+        out = torch.empty(hits.shape[0], 3)
+        for s, e in zip(cu[:-1].tolist(), cu[1:].tolist()):
+            out[s:e] = hits[s:e, :3] - hits[s:e, :3].mean(0, keepdim=True)
+        return out
+
+
+def _sharded_rank_main(rank, world, port, lens):
+    sys.path.insert(0, ROOT)
+    from lampa_b200.model import forward_sharded
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        gen = torch.Generator().manual_seed(5)
+        hits = torch.randn(sum(lens), 4, generator=gen)
+        model = _EventMeanModel()
+        cu = torch.tensor([0] + lens).cumsum(0)
+        want = model(hits, cu)
+        got, info = forward_sharded(model, hits, lens)
+        assert torch.equal(got, want)
+        assert info["imbalance"] >= 1.0 and info["owned"] >= 1
+        local, _ = forward_sharded(model, hits, lens, gather=False)
+        assert local.shape[0] < hits.shape[0]
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_rank_sharded_forward_over_gloo():
+    lens = [700, 60, 1500, 333, 64, 900, 5]
+    mp.spawn(_sharded_rank_main, args=(2, _free_port(), lens), nprocs=2, join=True)
 
 
 def test_get_regions_matches_reference_draws(golden_dir):
