@@ -117,7 +117,7 @@ def _workspace(desc: L.GdnDesc, dev: torch.device) -> torch.Tensor:
 
 
 def _prep_inputs(q, k, v, g, beta, lam, cu_seqlens):
-    dev = L.require_cuda(q, k, v, g, beta, lam, cu_seqlens)
+    dev = L.require_cuda(q, k, v, g, beta, lam)          # cu_seqlens may live on the host: it is copied over
     if v.shape[:3] != q.shape[:3] or k.shape != q.shape or g.shape != q.shape[:3] or beta.shape != q.shape[:3]:
         raise ValueError("q/k [B,T,H,K], v [B,T,H,V], g/beta [B,T,H] expected")
     q, k, v, g, beta = (x.contiguous() for x in (q, k, v, g, beta))

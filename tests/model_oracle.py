@@ -58,8 +58,9 @@ def forward(model, hits: torch.Tensor, cu: torch.Tensor, return_parts: bool = Fa
     cu_np = cu.numpy().astype(np.int64)
     perms = orderings(model, hits.numpy(), cu_np)
     x = F.linear(hits * model.feature_scale.cpu(), model.encoder.weight.detach().cpu(), model.encoder.bias.detach().cpu())
-    parts = []
+    parts, streams = [], []
     for b, blk in enumerate(model.blocks):
+        streams.append(x.clone())
         d = x.shape[1]
         perm = perms[b % model.rounds]
         h = _bf(F.rms_norm(x, (d,), blk.attn_norm_weight.detach().cpu(), blk.eps))
@@ -72,4 +73,5 @@ def forward(model, hits: torch.Tensor, cu: torch.Tensor, return_parts: bool = Fa
         h = _bf(F.rms_norm(x, (d,), blk.mlp_norm_weight.detach().cpu(), blk.eps))
         x = x + _linear(_bf(F.gelu(_linear(h, blk.mlp_up).float())), blk.mlp_down).float()
     y = F.linear(x, model.head.weight.detach().cpu(), model.head.bias.detach().cpu())
-    return (y, perms, parts) if return_parts else y
+    streams.append(x.clone())
+    return (y, perms, parts, streams) if return_parts else y

@@ -1,14 +1,14 @@
 """GPU parity of the hierarchical rule's Fenwick state (prefill final state and decode step),
 through the C ABI, against the CPU checker's token recurrence.
 
-Outputs: the bf16 tolerance of the forward tests (max-abs <= 2e-2 * max(1, |ref|_inf), relative
-L2 <= 1e-2).  States: per level, after rescaling by the level's largest reference value, max-abs
-<= 3e-2 and relative L2 <= 3e-2.  The wider bound is for levels carried across tens of chunks with
-almost no decay: every chunk transition multiplies the bf16-rounded state by a bf16-rounded 64x64
-matrix whose diagonal is close to 1, two independent relative errors of about 1e-3 (rms) per chunk
-that add up as sqrt(chunks) where an output, which is dominated by recent tokens, does not see them
-(measured: 2.0e-2 over 99 chunks at g ~ -0.007 per token, 1.1e-2 over 31 chunks).  Keeping
-M - e^{G_last} I instead of M in the records would remove most of it.
+Outputs: the bf16 tolerance of the forward tests (tests/util.assert_close_bf16).
+States: the whole tensor [H, K, V, L] within max-abs 2e-2 of its largest value and relative L2
+1e-2, and every level on its own within the same two figures after rescaling by
+max(level's largest value, 1e-3 of the tensor's largest value).  The floor is there because a level
+that has been carried across many chunks is attenuated far below the others (each chunk applies 64
+rank-one contractions in a 64-dimensional space; after 32 chunks nothing measurable is left in
+these inputs): below a thousandth of the tensor's scale its own relative accuracy says nothing
+about the state, and what is compared there is its absolute contribution.
 Counts are compared exactly.
 """
 import os
@@ -36,22 +36,29 @@ def _cuda(d):
     return {k: v.to("cuda:0") for k, v in d.items()}
 
 
-def _close_level(got, ref, what):
-    """One level against the checker, rescaled first: strongly decayed levels sit near 1e-30,
-    where squaring for the L2 norm would underflow."""
-    m = float(np.abs(ref).max())
+def _close_level(got, ref, what, floor):
+    """One level against the checker, rescaled first (strongly decayed levels sit near 1e-30,
+    where squaring for the L2 norm would underflow)."""
+    m = max(float(np.abs(ref).max()), floor)
     if m < 1e-35:
         assert float(np.abs(got).max()) < 1e-33, what
         return
-    mx, rl = err_stats(got.astype(np.float64) / m, ref.astype(np.float64) / m)
+    g, r = got.astype(np.float64) / m, ref.astype(np.float64) / m
+    d = g - r
+    mx = float(np.abs(d).max())
+    rl = float(np.linalg.norm(d) / max(np.linalg.norm(r), np.sqrt(r.size) * 1e-3))   # floor-sized levels: against the floor
     assert np.isfinite(got).all(), f"{what}: non-finite state"
-    assert mx <= 3e-2, f"{what}: max-abs {mx:.3e} of the level's largest value"
-    assert rl <= 3e-2, f"{what}: rel-L2 {rl:.3e}"
+    assert mx <= 2e-2, f"{what}: max-abs {mx:.3e} of the level's scale"
+    assert rl <= 1e-2, f"{what}: rel-L2 {rl:.3e}"
 
 
 def _close_states(got, ref, what):
+    top = float(np.abs(ref).max())
+    mx, rl = err_stats(got, ref)
+    print(f"[parity] {what} Fenwick states: max-abs {mx:.3e} of |ref|_inf {top:.3e}, rel-L2 {rl:.3e}")
+    assert mx <= 2e-2 * max(top, 1e-30) and rl <= 1e-2, f"{what}: whole state max-abs {mx:.3e} rel-L2 {rl:.3e}"
     for l in range(ref.shape[-1]):
-        _close_level(got[..., l], ref[..., l], f"{what} level {l}")
+        _close_level(got[..., l], ref[..., l], f"{what} level {l}", 1e-3 * top)
 
 
 def _ref(inp, T=None):
@@ -72,6 +79,7 @@ STATE_CASES = [
     (4160, 1, 64, 64, -4.0, 0),     # index 64: only the top level
     (5056, 2, 32, 32, -4.0, 0),
     (4096 + 320, 3, 16, 32, 2.0, 1),
+    (64 * 601, 1, 64, 64, -6.0, 0),  # 601 chunks (index 600 = 1001011000b), decay of ~0.0025 per token
 ]
 
 
@@ -92,8 +100,7 @@ def test_prefill_state_matches_token_recurrence(lb, T, H, K, V, gs, extra):
     for l in range(Lv):
         if cref[l] == 0:
             assert not got[..., l].any(), f"level {l} must be empty"
-        else:
-            _close_level(got[..., l], sref[..., l], f"state level {l}")
+    _close_states(got, sref, f"T={T} K={K}")
     # the plain final state is the sum over levels when every lambda is 1
     _, ht = lb.chunk_gated_delta_rule(d["q"], d["k"], d["v"], d["g"], d["beta"], output_final_state=True,
                                       use_qk_l2norm_in_kernel=True)
