@@ -9,8 +9,8 @@ from concurrent.futures import ThreadPoolExecutor
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 SO = os.path.join(HERE, "liblampa_b200.so")
-SOURCES = ["lsh.cu", "geo.cu", "layer.cu", "bucket_attn.cu", "gdn_prep.cu", "gdn_scan.cu", "gdn_scan_umma.cu", "gdn_state.cu", "gdn_api.cu", "profile.cu"]
-HEADERS = ["common.cuh", "gdn.cuh", "profile.cuh", os.path.join("..", "..", "include", "lampa_b200.h")]
+SOURCES = ["lsh.cu", "geo.cu", "layer.cu", "bucket_attn.cu", "gdn_prep.cu", "gdn_prep_umma.cu", "gdn_scan.cu", "gdn_scan_umma.cu", "gdn_state.cu", "gdn_api.cu", "profile.cu"]
+HEADERS = ["common.cuh", "gdn.cuh", "gdn_inv.cuh", "gdn_load.cuh", "umma.cuh", "profile.cuh", os.path.join("..", "..", "include", "lampa_b200.h")]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC"]
 

@@ -7,7 +7,7 @@
 //   U  = (Aw .* E) diag(beta) V                        K~ = diag(e^{G_last - G}) K
 //   M  = e^{G_last} I - K~^T W~     B = K~^T U         Q~ = diag(e^G) Q - (tril(Q K^T) .* E) W~
 // so that one chunk acts on the running state as  S <- M S + B  and reads it as  Q~ S.
-// The prep kernel writes one record {M, B^T, Q~, O_local, lambda} per (chunk, head); the scan
+// The prep kernels write one record {M, Q~, B^T, O_local, lambda} per (chunk, head); the scan
 // kernels only ever multiply by those.
 #pragma once
 #include "common.cuh"
@@ -36,7 +36,7 @@ template <int KD, int VD>
 struct Rec {
     using T = Tile<KD>;
     static constexpr int KP = KD + 8;                 // padded bf16 row pitch (block composites)
-    static constexpr int OP = VD + 8;                 // fp32 row pitch (elements) of O_local
+    static constexpr int OP = VD;                     // bf16 row pitch (elements) of O_local
     static constexpr int M_OFF = 0;
     static constexpr int M_BYTES = T::bytes(KD);      // M[k_out][k_in]
     static constexpr int QT_OFF = M_OFF + M_BYTES;    // M and Q~ are adjacent: together they are one 128-row B operand
@@ -44,7 +44,7 @@ struct Rec {
     static constexpr int BT_OFF = QT_OFF + QT_BYTES;
     static constexpr int BT_BYTES = T::bytes(VD);     // B^T[v][k]
     static constexpr int OL_OFF = BT_OFF + BT_BYTES;
-    static constexpr int OL_BYTES = CHUNK * OP * 4;   // O_local[token][v]
+    static constexpr int OL_BYTES = CHUNK * OP * 2;   // O_local[token][v], bf16 (added once, in fp32, by the output pass)
     static constexpr int LAM_OFF = OL_OFF + OL_BYTES; // lambda of chunk levels: [LC][64] fp32
     static constexpr int PRE_BYTES = OL_OFF;          // M, Q~, B^T: what the compose pass streams
     static constexpr int ALIGN = T::SWZ ? 1024 : 128; // records and shared-memory stages
@@ -114,6 +114,7 @@ __device__ __forceinline__ void store_out2(void* o, int dt, size_t idx, float x,
 }
 
 int launch_out_hier_umma(const GdnArgs& a, cudaStream_t st);
+int launch_prep_umma(const GdnArgs& a, bool hier, cudaStream_t st);   // K = V = 64, 2-byte q/k/v
 template <int KD, int VD> int launch_final_high(const GdnArgs& a, float* states, cudaStream_t st);
 template <int KD, int VD> int launch_final_low(const GdnArgs& a, float* states, int32_t* counts, cudaStream_t st);
 

@@ -125,6 +125,11 @@ int run(const lampa_gdn_desc* d, bool hier, const void* q, const void* k, const 
         if (rc != LAMPA_OK) return rc;                                 \
         return hier ? launch_scan_hier<KD, VD>(a, st) : launch_scan_plain<KD, VD>(a, st); \
     } while (0)
+    if (d->K == 64 && a.use_umma && d->qkv_dtype != LAMPA_F32) {
+        rc = launch_prep_umma(a, hier, st);
+        if (rc == LAMPA_OK) return hier ? launch_scan_hier<64, 64>(a, st) : launch_scan_plain<64, 64>(a, st);
+        if (rc != LAMPA_ERR_UNSUPPORTED) return rc;       // too many lambda levels for its shared memory: the other kernel takes it
+    }
     if (d->K == 64) LAMPA_DISPATCH(64, 64);
     if (d->K == 32) LAMPA_DISPATCH(32, 32);
     LAMPA_DISPATCH(16, 32);

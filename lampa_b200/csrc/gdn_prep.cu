@@ -4,6 +4,8 @@
 // 64x64 unit-lower-triangular inverse is an fp32 substitution on CUDA cores, as in the reference
 // (models/hattention/solve_tril.py:54-61, 175-197), because bf16 there is where parity breaks.
 #include "gdn.cuh"
+#include "gdn_inv.cuh"
+#include "gdn_load.cuh"
 #include "profile.cuh"
 
 namespace lampa {
@@ -51,143 +53,6 @@ struct PrepSmem {
     static constexpr int LAM = G + 4 * CHUNK * 4;                // fp32 [64][L+1]
     static int bytes(int L) { return LAM + CHUNK * (L + 1) * 4; }
 };
-
-// Each of the 128 threads loads half a row (D/2 elements) of a [64][D] tile as floats.
-template <int D>
-__device__ __forceinline__ void load_half_row(const void* base, int dt, size_t elem_off, bool valid, float (&x)[D / 2]) {
-    constexpr int NE = D / 2;
-    if (!valid) {
-#pragma unroll
-        for (int i = 0; i < NE; ++i) x[i] = 0.f;
-        return;
-    }
-    if (dt == LAMPA_F32) {
-        const float4* p = reinterpret_cast<const float4*>((const float*)base + elem_off);
-#pragma unroll
-        for (int i = 0; i < NE / 4; ++i) {
-            const float4 f = __ldg(p + i);
-            x[4 * i] = f.x; x[4 * i + 1] = f.y; x[4 * i + 2] = f.z; x[4 * i + 3] = f.w;
-        }
-    } else {
-        const uint4* p = reinterpret_cast<const uint4*>((const uint16_t*)base + elem_off);
-#pragma unroll
-        for (int i = 0; i < NE / 8; ++i) {
-            const uint4 u = __ldg(p + i);
-            const uint32_t w[4] = {u.x, u.y, u.z, u.w};
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                float2 f;
-                if (dt == LAMPA_BF16) f = unpack_bf16x2(w[j]);
-                else f = __half22float2(*reinterpret_cast<const __half2*>(&w[j]));
-                x[8 * i + 2 * j] = f.x; x[8 * i + 2 * j + 1] = f.y;
-            }
-        }
-    }
-}
-
-// Raw 16-byte loads of half a row of a 2-byte-element tile (issued early, converted later).
-template <int D>
-__device__ __forceinline__ void issue_half_row(const void* base, size_t elem_off, bool valid, uint4 (&u)[D / 16]) {
-    const uint4* p = reinterpret_cast<const uint4*>((const uint16_t*)base + elem_off);
-#pragma unroll
-    for (int i = 0; i < D / 16; ++i) u[i] = valid ? __ldg(p + i) : make_uint4(0u, 0u, 0u, 0u);
-}
-template <int D>
-__device__ __forceinline__ void convert_half_row(const uint4 (&u)[D / 16], int dt, float (&x)[D / 2]) {
-#pragma unroll
-    for (int i = 0; i < D / 16; ++i) {
-        const uint32_t w[4] = {u[i].x, u[i].y, u[i].z, u[i].w};
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            float2 f;
-            if (dt == LAMPA_BF16) f = unpack_bf16x2(w[j]);
-            else f = __half22float2(*reinterpret_cast<const __half2*>(&w[j]));
-            x[8 * i + 2 * j] = f.x; x[8 * i + 2 * j + 1] = f.y;
-        }
-    }
-}
-
-template <int NE>
-__device__ __forceinline__ void store_half_row_bf16(__nv_bfloat16* dst, const float (&x)[NE]) {
-#pragma unroll
-    for (int i = 0; i < NE / 8; ++i) {
-        uint4 u;
-        u.x = pack_bf16x2(x[8 * i], x[8 * i + 1]);
-        u.y = pack_bf16x2(x[8 * i + 2], x[8 * i + 3]);
-        u.z = pack_bf16x2(x[8 * i + 4], x[8 * i + 5]);
-        u.w = pack_bf16x2(x[8 * i + 6], x[8 * i + 7]);
-        reinterpret_cast<uint4*>(dst)[i] = u;
-    }
-}
-
-// Half of a token's lambda row (levels half, half + 2, ...) into shared memory: NIT loads in flight, then NIT stores.
-template <int NIT>
-__device__ __forceinline__ void stage_lambda(const void* lam, int dt, size_t base, int L, int half, bool valid, float* dst) {
-    float lv[NIT];
-#pragma unroll
-    for (int i = 0; i < NIT; ++i) {
-        const int l = half + 2 * i;
-        lv[i] = (valid && l < L) ? load_as_float(lam, base + l, dt) : 0.f;
-    }
-#pragma unroll
-    for (int i = 0; i < NIT; ++i) {
-        const int l = half + 2 * i;
-        if (l < L) dst[l] = lv[i];
-    }
-}
-
-template <int N>
-__device__ __forceinline__ void zero_acc(float (&acc)[N][4]) {
-#pragma unroll
-    for (int i = 0; i < N; ++i) { acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f; }
-}
-
-// -------------------------------------------------------------------------------------------------
-// Split-bf16 fragments for products that must keep fp32 accuracy (the blockwise triangular inverse):
-// operands live as fp32 in shared memory and enter the tensor core as bf16 hi + bf16 lo.
-// -------------------------------------------------------------------------------------------------
-__device__ __forceinline__ void split2(float x, float y, uint32_t& hi, uint32_t& lo) {
-    hi = pack_bf16x2(x, y);
-    const float2 h = unpack_bf16x2(hi);
-    lo = pack_bf16x2(x - h.x, y - h.y);
-}
-// A fragment (rows r0.., columns c0.. of an fp32 tile in shared memory), split into hi and lo
-__device__ __forceinline__ void load_a_f32(const float* s, int pitch, int r0, int c0, int lane,
-                                           uint32_t (&hi)[4], uint32_t (&lo)[4]) {
-    const int g = lane >> 2, t = lane & 3;
-#pragma unroll
-    for (int q = 0; q < 4; ++q) {
-        const float2 v = *reinterpret_cast<const float2*>(s + (r0 + g + (q & 1) * 8) * pitch + c0 + 2 * t + (q >> 1) * 8);
-        split2(v.x, v.y, hi[q], lo[q]);
-    }
-}
-// B fragment of the 16 x 8 block B[k][n] = s[(k0 + k) * pitch + n0 + n]
-__device__ __forceinline__ void load_b_f32(const float* s, int pitch, int k0, int n0, int lane,
-                                           uint32_t (&hi)[2], uint32_t (&lo)[2]) {
-    const int g = lane >> 2, t = lane & 3;
-#pragma unroll
-    for (int q = 0; q < 2; ++q)
-        split2(s[(k0 + 2 * t + 8 * q) * pitch + n0 + g], s[(k0 + 2 * t + 1 + 8 * q) * pitch + n0 + g], hi[q], lo[q]);
-}
-__device__ __forceinline__ void mma3(float (&c)[4], const uint32_t (&ah)[4], const uint32_t (&al)[4],
-                                     const uint32_t (&bh)[2], const uint32_t (&bl)[2]) {
-    mma16816(c, ah, bh[0], bh[1]);
-    mma16816(c, al, bh[0], bh[1]);
-    mma16816(c, ah, bl[0], bl[1]);
-}
-// two adjacent accumulator tiles (16 x 16) as the A fragment of the next product
-__device__ __forceinline__ void acc_to_a(const float (&c0)[4], const float (&c1)[4], uint32_t (&hi)[4], uint32_t (&lo)[4]) {
-    split2(c0[0], c0[1], hi[0], lo[0]);
-    split2(c0[2], c0[3], hi[1], lo[1]);
-    split2(c1[0], c1[1], hi[2], lo[2]);
-    split2(c1[2], c1[3], hi[3], lo[3]);
-}
-// s[r0 + ..][c0 + 8 nt + ..] = -acc
-__device__ __forceinline__ void store_neg_tile(float* s, int pitch, int r0, int c0, int lane, const float (&c)[4]) {
-    const int g = lane >> 2, t = lane & 3;
-    *reinterpret_cast<float2*>(s + (r0 + g) * pitch + c0 + 2 * t) = make_float2(-c[0], -c[1]);
-    *reinterpret_cast<float2*>(s + (r0 + g + 8) * pitch + c0 + 2 * t) = make_float2(-c[2], -c[3]);
-}
 
 // With beta folded into the columns of the inverse (Awb = (I + A0)^-1 diag(beta), Aub = Awb .* E):
 //   W  = Awb K                    M   = e^{G_last} (I - K^T W)
@@ -359,90 +224,7 @@ __global__ void __launch_bounds__(128, 4) gdn_prep_kernel(GdnArgs a) {
                 }
         }
         __syncwarp();
-        {
-            const int cc = lane & 15;
-            float x[16];
-#pragma unroll
-            for (int i = 0; i < 16; ++i) {
-                float sum = (i == cc) ? 1.f : 0.f;
-#pragma unroll
-                for (int q = 0; q < (i + 3) / 4; ++q) {
-                    const float4 av = *reinterpret_cast<const float4*>(sA + (m0 + i) * PA + m0 + 4 * q);
-                    const float ae[4] = {av.x, av.y, av.z, av.w};
-#pragma unroll
-                    for (int e = 0; e < 4; ++e)
-                        if (4 * q + e < i) sum -= ae[e] * x[4 * q + e];
-                }
-                x[i] = sum;
-            }
-            __syncwarp();
-            if (lane < 16) {
-#pragma unroll
-                for (int i = 0; i < 16; ++i) sA[(m0 + i) * PA + m0 + cc] = x[i];
-            }
-        }
-        __syncthreads();
-        if (warp & 1) {   // X_ba of the pair (a, b) = (warp - 1, warp)
-            const int ra = m0 - 16, rb = m0;
-            float q0[2][4], xo[2][4];
-            zero_acc<2>(q0);
-            zero_acc<2>(xo);
-            uint32_t ah[4], al[4];
-            load_a_f32(sA, PA, rb, rb, lane, ah, al);
-#pragma unroll
-            for (int nt = 0; nt < 2; ++nt) {
-                uint32_t bh[2], bl[2];
-                load_b_f32(sA, PA, rb, ra + 8 * nt, lane, bh, bl);
-                mma3(q0[nt], ah, al, bh, bl);
-            }
-            acc_to_a(q0[0], q0[1], ah, al);
-#pragma unroll
-            for (int nt = 0; nt < 2; ++nt) {
-                uint32_t bh[2], bl[2];
-                load_b_f32(sA, PA, ra, ra + 8 * nt, lane, bh, bl);
-                mma3(xo[nt], ah, al, bh, bl);
-            }
-            __syncwarp();
-#pragma unroll
-            for (int nt = 0; nt < 2; ++nt) store_neg_tile(sA, PA, rb, ra + 8 * nt, lane, xo[nt]);
-        }
-        __syncthreads();
-        {   // the 32x32 corner: warp = (row tile mt, column half nh)
-            const int mt = warp >> 1, nh = warp & 1;
-            float qc[4][4], xc[2][4];
-            zero_acc<4>(qc);
-            zero_acc<2>(xc);
-#pragma unroll
-            for (int ks = 0; ks < 2; ++ks)
-                if (ks <= mt) {                                   // X_b is block lower-triangular
-                    uint32_t ah[4], al[4];
-                    load_a_f32(sA, PA, 32 + 16 * mt, 32 + 16 * ks, lane, ah, al);
-#pragma unroll
-                    for (int nt = 0; nt < 4; ++nt) {
-                        uint32_t bh[2], bl[2];
-                        load_b_f32(sA, PA, 32 + 16 * ks, 8 * nt, lane, bh, bl);
-                        mma3(qc[nt], ah, al, bh, bl);
-                    }
-                }
-#pragma unroll
-            for (int ks = 0; ks < 2; ++ks) {
-                uint32_t ah[4], al[4];
-                acc_to_a(qc[2 * ks], qc[2 * ks + 1], ah, al);
-#pragma unroll
-                for (int n = 0; n < 2; ++n) {
-                    const int nt = 2 * nh + n;
-                    if (nt < 2 + 2 * ks) {                        // X_a rows 0..15 are [X_00 | 0]
-                        uint32_t bh[2], bl[2];
-                        load_b_f32(sA, PA, 16 * ks, 8 * nt, lane, bh, bl);
-                        mma3(xc[n], ah, al, bh, bl);
-                    }
-                }
-            }
-            __syncthreads();                                      // every warp has read A_ba
-#pragma unroll
-            for (int n = 0; n < 2; ++n) store_neg_tile(sA, PA, 32 + 16 * mt, 8 * (2 * nh + n), lane, xc[n]);
-        }
-        __syncthreads();
+        tril_inverse_64<PA>(sA, warp, lane);
         {   // Awb = X diag(beta) as bf16, written over the front of the fp32 tile
             const int r = tid >> 1, half = tid & 1;
             uint32_t w[16];
@@ -552,14 +334,14 @@ __global__ void __launch_bounds__(128, 4) gdn_prep_kernel(GdnArgs a) {
             float acc[VD / 8][4];
             zero_acc<VD / 8>(acc);
             warp_gemm_ra<VD / 8, 4, true>(acc, ra, sV, VP, 0, lane, m0 + 16, VD);
-            float* gO = reinterpret_cast<float*>(rec + R::OL_OFF);
+            __nv_bfloat16* gO = reinterpret_cast<__nv_bfloat16*>(rec + R::OL_OFF);
 #pragma unroll
             for (int nt = 0; nt < VD / 8; ++nt)
 #pragma unroll
                 for (int hh = 0; hh < 2; ++hh) {
                     const int i = m0 + gq + hh * 8, j = nt * 8 + 2 * tq;
-                    *reinterpret_cast<float2*>(gO + i * R::OP + j) =
-                        make_float2(osc * acc[nt][2 * hh], osc * acc[nt][2 * hh + 1]);
+                    *reinterpret_cast<uint32_t*>(gO + i * R::OP + j) =
+                        pack_bf16x2(osc * acc[nt][2 * hh], osc * acc[nt][2 * hh + 1]);
                 }
         }
         // U^ = diag(e^{Glast-G}) (Awb .* E) V: the decay is applied to the A fragments in registers

@@ -445,7 +445,7 @@ __global__ void __launch_bounds__(VD * 2) gdn_out_plain_kernel(GdnArgs a) {
         const __nv_bfloat16* sM = reinterpret_cast<const __nv_bfloat16*>(st + R::M_OFF);
         const __nv_bfloat16* sBt = reinterpret_cast<const __nv_bfloat16*>(st + R::BT_OFF);
         const __nv_bfloat16* sQt = reinterpret_cast<const __nv_bfloat16*>(st + R::QT_OFF);
-        const float* sOl = reinterpret_cast<const float*>(st + R::OL_OFF);
+        const __nv_bfloat16* sOl = reinterpret_cast<const __nv_bfloat16*>(st + R::OL_OFF);
         uint32_t sp[KD / 16][4];
         pack_state<KD>(C, sp);
         const int64_t t0 = tok0 + (int64_t)i * CHUNK;
@@ -460,7 +460,7 @@ __global__ void __launch_bounds__(VD * 2) gdn_out_plain_kernel(GdnArgs a) {
 #pragma unroll
                     for (int nt = 0; nt < 2; ++nt) {
                         const int col = row0 + nt * 8 + 2 * t;
-                        const float2 ol = *reinterpret_cast<const float2*>(sOl + r * R::OP + col);
+                        const float2 ol = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(sOl + r * R::OP + col));
                         store_out2(a.o, a.qkv_dt, ((size_t)(t0 + r) * H + h) * VD + col,
                                    ol.x + tmp[nt][2 * hh], ol.y + tmp[nt][2 * hh + 1]);
                     }
@@ -541,7 +541,7 @@ __global__ void __launch_bounds__(NG * VD * 2, 1) gdn_out_hier_kernel(GdnArgs a)
         const __nv_bfloat16* sM = reinterpret_cast<const __nv_bfloat16*>(st + R::M_OFF);
         const __nv_bfloat16* sBt = reinterpret_cast<const __nv_bfloat16*>(st + R::BT_OFF);
         const __nv_bfloat16* sQt = reinterpret_cast<const __nv_bfloat16*>(st + R::QT_OFF);
-        const float* sOl = reinterpret_cast<const float*>(st + R::OL_OFF);
+        const __nv_bfloat16* sOl = reinterpret_cast<const __nv_bfloat16*>(st + R::OL_OFF);
         const float* sLam = reinterpret_cast<const float*>(st + R::LAM_OFF);
         const int n = b * BLOCK_CHUNKS + i;
 
@@ -634,7 +634,7 @@ __global__ void __launch_bounds__(NG * VD * 2, 1) gdn_out_hier_kernel(GdnArgs a)
 #pragma unroll
                         for (int nt = 0; nt < 2; ++nt) {
                             const int col = row0 + nt * 8 + 2 * t;
-                            const float2 ol = *reinterpret_cast<const float2*>(sOl + r * R::OP + col);
+                            const float2 ol = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(sOl + r * R::OP + col));
                             store_out2(a.o, a.qkv_dt, ((size_t)(t0 + r) * H + h) * VD + col,
                                        ol.x + O[mt][nt][2 * hh], ol.y + O[mt][nt][2 * hh + 1]);
                         }

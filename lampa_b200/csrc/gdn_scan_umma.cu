@@ -23,6 +23,7 @@
 // MMAs, waits for the ones in flight and only then frees its tensor memory.
 #include "gdn.cuh"
 #include "profile.cuh"
+#include "umma.cuh"
 
 namespace lampa {
 
@@ -46,57 +47,8 @@ constexpr int SM_STAGE = SM_OT + 2 * 2 * 64 * 64 * 4;
 constexpr int STAGE_TILES = UR::LAM_OFF;     // M | Q~ | B^T | O_local, then the lambda rows: the whole record
 __host__ __device__ constexpr int ustage_bytes(int LC) { return (STAGE_TILES + LC * CHUNK * 4 + 1023) / 1024 * 1024; }
 
-__device__ __forceinline__ uint64_t umma_desc_k128(uint32_t saddr) {   // K-major, 128B swizzle, 8-row groups 1024 B apart
-    uint64_t d = 0;
-    d |= (uint64_t)((saddr >> 4) & 0x3FFF);
-    d |= (uint64_t)1 << 16;                 // leading byte offset (ignored for swizzled K-major): 16 B
-    d |= (uint64_t)(1024 >> 4) << 32;       // stride byte offset
-    d |= (uint64_t)1 << 46;                 // descriptor version
-    d |= (uint64_t)2 << 61;                 // SWIZZLE_128B
-    return d;
-}
 // instruction descriptor: D fp32, A/B bf16, both K-major, M = 128, N = 128
-constexpr uint32_t UMMA_IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
-
-__device__ __forceinline__ void umma_f16_ss(uint32_t d_tmem, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
-    asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
-                 :: "r"(d_tmem), "l"(da), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
-}
-// same with the A operand in TMEM (lane = row, packed bf16 pairs, 8 columns per k-step of 16)
-__device__ __forceinline__ void umma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t db, uint32_t idesc, uint32_t accumulate) {
-    asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n"
-                 :: "r"(d_tmem), "r"(a_tmem), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint64_t* bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" :: "r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
-__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }
-
-// 16 consecutive fp32 columns of this thread's TMEM lane
-__device__ __forceinline__ void tmem_ld16(float (&x)[16], uint32_t taddr) {
-    uint32_t* r = reinterpret_cast<uint32_t*>(x);
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];\n"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-                 : "r"(taddr));
-    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
-}
-
-// write 16 floats as 8 columns of packed bf16 pairs of this thread's TMEM lane (a quarter row of an A operand)
-__device__ __forceinline__ void tmem_st_bf16x16(uint32_t taddr, const float (&x)[16]) {
-    uint32_t w[8];
-#pragma unroll
-    for (int c = 0; c < 8; ++c) w[c] = pack_bf16x2(x[2 * c], x[2 * c + 1]);
-    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};\n"
-                 :: "r"(taddr), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7]) : "memory");
-    asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
-}
-
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" :: "r"(smem_u32(bar)) : "memory");
-}
+constexpr uint32_t UMMA_IDESC = umma_idesc(128, 128);
 
 // Launch order of the (block, head) units.  A unit's time grows with the number of level pairs it
 // carries (3 to 5, from the set bits of its block index), and 240 units on 148 SMs leave the second
@@ -164,8 +116,7 @@ __global__ void __launch_bounds__(UTHREADS, 1) gdn_out_hier_umma_kernel(GdnArgs 
         fence_mbar_init();
     }
     if (warp == 0) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" :: "r"(smem_u32(tslot)), "r"(512) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+        tmem_alloc(tslot, 512);
     }
     fence_async_smem();
     tc_fence_before();
@@ -264,7 +215,7 @@ __global__ void __launch_bounds__(UTHREADS, 1) gdn_out_hier_umma_kernel(GdnArgs 
             const float* sLam = reinterpret_cast<const float*>(st + STAGE_TILES);
             const unsigned char* sBt = st + UR::BT_OFF;
             const int n = b * BLOCK_CHUNKS + i;
-            const float* sOl = reinterpret_cast<const float*>(st + UR::OL_OFF);
+            const __nv_bfloat16* sOl = reinterpret_cast<const __nv_bfloat16*>(st + UR::OL_OFF);
             // what this chunk does to each slot, as bit masks: in-block level s is read when bit s of n is
             // set and cleared when its period of 2^(s+1) chunks ends (all of bits 0..s set); the cross-block
             // slots are read by every chunk
@@ -340,13 +291,15 @@ __global__ void __launch_bounds__(UTHREADS, 1) gdn_out_hier_umma_kernel(GdnArgs 
                 if (t_out < tok_end) {
                     const size_t idx = ((size_t)t_out * H + h) * UVD + col;
                     float r[8];
+                    const uint4 ol = *reinterpret_cast<const uint4*>(sOl + tok * UR::OP + col);      // 8 bf16 of O_local
+                    const uint32_t olw[4] = {ol.x, ol.y, ol.z, ol.w};
 #pragma unroll
                     for (int q = 0; q < 2; ++q) {
                         const float4 p0 = *reinterpret_cast<const float4*>(sOTc + (0 * 64 + tok) * 64 + col + 4 * q);
                         const float4 q0 = *reinterpret_cast<const float4*>(sOTc + (1 * 64 + tok) * 64 + col + 4 * q);
-                        const float4 o4 = *reinterpret_cast<const float4*>(sOl + tok * UR::OP + col + 4 * q);
-                        r[4 * q] = p0.x + q0.x + o4.x; r[4 * q + 1] = p0.y + q0.y + o4.y;
-                        r[4 * q + 2] = p0.z + q0.z + o4.z; r[4 * q + 3] = p0.w + q0.w + o4.w;
+                        const float2 oa = unpack_bf16x2(olw[2 * q]), ob = unpack_bf16x2(olw[2 * q + 1]);
+                        r[4 * q] = p0.x + q0.x + oa.x; r[4 * q + 1] = p0.y + q0.y + oa.y;
+                        r[4 * q + 2] = p0.z + q0.z + ob.x; r[4 * q + 3] = p0.w + q0.w + ob.y;
                     }
                     if (a.qkv_dt == LAMPA_F32) {
                         float4* o4 = reinterpret_cast<float4*>((float*)a.o + idx);
@@ -369,7 +322,7 @@ __global__ void __launch_bounds__(UTHREADS, 1) gdn_out_hier_umma_kernel(GdnArgs 
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" :: "r"(taddr), "r"(512) : "memory");
+    if (warp == 0) tmem_dealloc(taddr, 512);
 }
 
 }  // namespace
