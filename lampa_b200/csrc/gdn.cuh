@@ -76,7 +76,13 @@ struct GdnArgs {
     int32_t* status;
     int use_umma;                         // tcgen05 kernels where they exist (K = V = 64)
     int poll_budget;                      // polls before a device wait gives up (MBAR_POLLS unless a test lowers it)
+    long long* ticks; int ticks_ctas;     // stage clocks for tuning: [ticks_ctas][16] or NULL (lampa_debug_set_tick_buffer)
 };
+
+// Stage clock of a preparation CTA: thread 0 of the first `ticks_ctas` CTAs stores clock64() in its slot.
+__device__ __forceinline__ void stage_tick(const GdnArgs& a, int cta, int slot) {
+    if (a.ticks != nullptr && threadIdx.x == 0 && cta < a.ticks_ctas) a.ticks[(size_t)cta * 16 + slot] = clock64();
+}
 
 struct PlanArgs {
     const int64_t* cu; int nseq; int B; int T; int L; int hier;

@@ -9,6 +9,8 @@ namespace {
 inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
 int g_poll_budget = MBAR_POLLS;   // see lampa_debug_set_poll_budget
+long long* g_ticks = nullptr;     // see lampa_debug_set_tick_buffer
+int g_ticks_ctas = 0;
 
 struct Layout {
     int nseq, nc_max, nb_max, nhigh_max, LC;
@@ -88,6 +90,8 @@ void fill_args(const lampa_gdn_desc* d, bool hier, const Layout& l, char* base, 
     static const int no_umma = [] { const char* e = getenv("LAMPA_B200_NO_UMMA"); return (e && e[0] == '1') ? 1 : 0; }();
     a.use_umma = no_umma ? 0 : 1;
     a.poll_budget = g_poll_budget;
+    a.ticks = g_ticks;
+    a.ticks_ctas = g_ticks_ctas;
 }
 
 int run(const lampa_gdn_desc* d, bool hier, const void* q, const void* k, const void* v, const void* g,
@@ -139,6 +143,13 @@ int run(const lampa_gdn_desc* d, bool hier, const void* q, const void* k, const 
 }  // namespace
 
 extern "C" int lampa_version(void) { return 200; }
+
+extern "C" int lampa_debug_set_tick_buffer(long long* ticks, int n_ctas) {
+    if (n_ctas < 0 || (n_ctas > 0 && !ticks)) return LAMPA_ERR_ARG;
+    g_ticks = n_ctas > 0 ? ticks : nullptr;
+    g_ticks_ctas = n_ctas;
+    return LAMPA_OK;
+}
 
 extern "C" int lampa_debug_set_poll_budget(int polls) {
     if (polls < 0) return LAMPA_ERR_ARG;

@@ -93,13 +93,9 @@ __global__ void __launch_bounds__(PT, 2) gdn_prep_umma_kernel(GdnArgs a) {
     const int LP = a.L + 1;
     const int budget = a.poll_budget;
     bool dead = false;
+    const int cta = blockIdx.y * gridDim.x + blockIdx.x;
+    stage_tick(a, cta, 0);
 
-    if (tid == 0) {
-#pragma unroll
-        for (int b = 0; b < NBAR; ++b) mbar_init(bars + b, 1);
-        fence_mbar_init();
-    }
-    if (warp == 0) tmem_alloc(tslot, 256);
 
     // ---- stage 0: loads, l2norm, cumulative decay -------------------------------------------------
     // thread = (token r, head sub, half of the head's row); every global load of the chunk is issued
@@ -119,28 +115,49 @@ __global__ void __launch_bounds__(PT, 2) gdn_prep_umma_kernel(GdnArgs a) {
             gv = load_as_float(a.g, (size_t)(t0 + tk) * H + 2 * pair + sb, a.gb_dt);
             bv = load_as_float(a.beta, (size_t)(t0 + tk) * H + 2 * pair + sb, a.gb_dt);
         }
-        if (HIER) {
-            const size_t lam_base = (tok * H + h) * a.L;
-            float* dst = sLam + (sub * CHUNK + r) * LP;
-            if (a.L <= 18) stage_lambda<9>(a.lam, a.lam_dt, lam_base, a.L, half, valid, dst);
-            else if (a.L <= 24) stage_lambda<12>(a.lam, a.lam_dt, lam_base, a.L, half, valid, dst);
-            else stage_lambda<20>(a.lam, a.lam_dt, lam_base, a.L, half, valid, dst);
+        // (the loads above are in flight while the barriers and the tensor memory are set up)
+        if (tid == 0) {
+#pragma unroll
+            for (int b = 0; b < NBAR; ++b) mbar_init(bars + b, 2);   // one arrival per issuing thread (one per head)
+            fence_mbar_init();
         }
-        if (pair == 0 && tid < 128) {   // L2 prefetch of the token rows (all heads) of a chunk ~80 chunks ahead
+        if (warp == 0) tmem_alloc(tslot, 256);
+        stage_tick(a, cta, 11);
+        if (pair == 0) {   // L2 prefetch of everything a chunk ~80 chunks ahead will read (all heads)
             ChunkLoc l2;
-            const int rr = tid >> 1, hf = tid & 1;
-            if (locate_chunk(a, c + 80, l2) && rr < l2.len) {
+            if (locate_chunk(a, c + 80, l2)) {
                 const size_t row = (size_t)H * 64 * 2;
-                const char* pq = (const char*)a.q + (size_t)(l2.t0 + rr) * row;
-                const char* pk = (const char*)a.k + (size_t)(l2.t0 + rr) * row;
-                const char* pv = (const char*)a.v + (size_t)(l2.t0 + rr) * row;
-                for (size_t off = (size_t)hf * 128; off < row; off += 256) {
-                    asm volatile("prefetch.global.L2 [%0];\n" :: "l"(pq + off));
-                    asm volatile("prefetch.global.L2 [%0];\n" :: "l"(pk + off));
-                    asm volatile("prefetch.global.L2 [%0];\n" :: "l"(pv + off));
+                if (tid < 128) {
+                    const int rr = tid >> 1, hf = tid & 1;
+                    if (rr < l2.len) {
+                        const char* pq = (const char*)a.q + (size_t)(l2.t0 + rr) * row;
+                        const char* pk = (const char*)a.k + (size_t)(l2.t0 + rr) * row;
+                        const char* pv = (const char*)a.v + (size_t)(l2.t0 + rr) * row;
+                        for (size_t off = (size_t)hf * 128; off < row; off += 256) {
+                            asm volatile("prefetch.global.L2 [%0];\n" :: "l"(pq + off));
+                            asm volatile("prefetch.global.L2 [%0];\n" :: "l"(pk + off));
+                            asm volatile("prefetch.global.L2 [%0];\n" :: "l"(pv + off));
+                        }
+                    }
+                } else {
+                    const int t2 = tid - 128;
+                    const size_t gb_bytes = (size_t)l2.len * H * dtype_bytes(a.gb_dt);
+                    const char* pg = (const char*)a.g + (size_t)l2.t0 * H * dtype_bytes(a.gb_dt);
+                    const char* pb = (const char*)a.beta + (size_t)l2.t0 * H * dtype_bytes(a.gb_dt);
+                    for (size_t off = (size_t)t2 * 128; off < gb_bytes; off += 128 * 128) {
+                        asm volatile("prefetch.global.L2 [%0];\n" :: "l"(pg + off));
+                        asm volatile("prefetch.global.L2 [%0];\n" :: "l"(pb + off));
+                    }
+                    if (HIER) {
+                        const size_t lam_bytes = (size_t)l2.len * H * a.L * dtype_bytes(a.lam_dt);
+                        const char* pl = (const char*)a.lam + (size_t)l2.t0 * H * a.L * dtype_bytes(a.lam_dt);
+                        for (size_t off = (size_t)t2 * 128; off < lam_bytes; off += 128 * 128)
+                            asm volatile("prefetch.global.L2 [%0];\n" :: "l"(pl + off));
+                    }
                 }
             }
         }
+        stage_tick(a, cta, 12);
         float x[32];
         uint32_t w[16];
         convert_half_row<64>(rq, a.qkv_dt, x);
@@ -155,6 +172,7 @@ __global__ void __launch_bounds__(PT, 2) gdn_prep_umma_kernel(GdnArgs a) {
         }
         pack32(x, w);
         store_row_swz(smem + S_Q + sub * TILE, r, half * 4, w);
+        stage_tick(a, cta, 13);
         convert_half_row<64>(rk, a.qkv_dt, x);
         if (a.use_l2norm) {
             float ss = 0.f;
@@ -175,6 +193,14 @@ __global__ void __launch_bounds__(PT, 2) gdn_prep_umma_kernel(GdnArgs a) {
             pack32(x, w);
         }
         store_row_swz(smem + S_V + sub * TILE, r, half * 4, w);
+        stage_tick(a, cta, 14);
+        if (HIER) {
+            const size_t lam_base = (tok * H + h) * a.L;
+            float* dst = sLam + (sub * CHUNK + r) * LP;
+            if (a.L <= 18) stage_lambda<9>(a.lam, a.lam_dt, lam_base, a.L, half, valid, dst);
+            else if (a.L <= 24) stage_lambda<12>(a.lam, a.lam_dt, lam_base, a.L, half, valid, dst);
+            else stage_lambda<20>(a.lam, a.lam_dt, lam_base, a.L, half, valid, dst);
+        }
 
         if (tid < 128) {   // inclusive cumsum of g over the 64 tokens of head sb (two warps per head)
             float cs = gv;
@@ -190,23 +216,15 @@ __global__ void __launch_bounds__(PT, 2) gdn_prep_umma_kernel(GdnArgs a) {
             asm volatile("bar.sync 1, 128;\n" ::: "memory");
             sG(sb)[tk] = cs + carry;
         }
+        stage_tick(a, cta, 15);
     }
     __syncthreads();
+    stage_tick(a, cta, 1);
     if (tid < 128) {
         const int tk = tid & 63, sb = tid >> 6;
         const float Gi = sG(sb)[tk], Gl = sG(sb)[CHUNK - 1];
         sEG(sb)[tk] = __expf(Gi);
         sEGl(sb)[tk] = __expf(Gl - Gi);
-    }
-    if (HIER) {   // lambda of the chunk levels, transposed to [level][token] for the scan
-        for (int idx = tid; idx < 2 * a.LC * CHUNK; idx += PT) {
-            const int sub = idx / (a.LC * CHUNK), rem = idx - sub * a.LC * CHUNK;
-            const int l = rem >> 6, r = rem & 63;
-            if (2 * pair + sub < H) {
-                float* lamc = reinterpret_cast<float*>(a.rec + ((size_t)c * H + 2 * pair + sub) * a.rec_bytes + R::LAM_OFF);
-                lamc[rem] = (ELL0 + l < a.L) ? sLam[(sub * CHUNK + r) * LP + ELL0 + l] : 0.f;
-            }
-        }
     }
     fence_async_smem();
     tc_fence_before();
@@ -216,20 +234,24 @@ __global__ void __launch_bounds__(PT, 2) gdn_prep_umma_kernel(GdnArgs a) {
     const uint32_t sQ = smem_u32(smem + S_Q), sK = smem_u32(smem + S_K), sV = smem_u32(smem + S_V), sX = smem_u32(smem + S_X);
 
     // ---- products 1, 2 ------------------------------------------------------------------------------
-    if (tid == 0) {
-#pragma unroll
-        for (int sub = 0; sub < 2; ++sub)
+    const bool issuer = (tid & 127) == 0;      // thread 0 issues head 0's products, thread 128 head 1's
+    const int isub = tid >> 7;
+    if (issuer) {
+        {
+            const int sub = isub;
 #pragma unroll
             for (int kk = 0; kk < 4; ++kk)
                 umma_f16_ss(taddr + ((uint32_t)(16 * sub) << 16) + T0, umma_desc_k128(sK + sub * TILE + kk * 32),
                             umma_desc_k128(sK + sub * TILE + kk * 32), ID_KK, kk > 0);
+        }
         umma_commit(bars + B_KK);
-#pragma unroll
-        for (int sub = 0; sub < 2; ++sub)
+        {
+            const int sub = isub;
 #pragma unroll
             for (int kk = 0; kk < 4; ++kk)
                 umma_f16_ss(taddr + ((uint32_t)(16 * sub) << 16) + T1, umma_desc_k128(sQ + sub * TILE + kk * 32),
                             umma_desc_k128(sK + sub * TILE + kk * 32), ID_KK, kk > 0);
+        }
         umma_commit(bars + B_QK);
     }
     __syncwarp();
@@ -244,6 +266,7 @@ __global__ void __launch_bounds__(PT, 2) gdn_prep_umma_kernel(GdnArgs a) {
     float x[32];
     uint32_t w[16];
 
+    stage_tick(a, cta, 2);
     // A0 = tril(diag(beta) K K^T, -1) as fp32 into the inverse's tile
     mbar_wait(bars + B_KK, 0u, dead, a.status, 600, budget);
     tc_fence_after();
@@ -270,8 +293,10 @@ __global__ void __launch_bounds__(PT, 2) gdn_prep_umma_kernel(GdnArgs a) {
     tc_fence_before();
     __syncthreads();
 
+    stage_tick(a, cta, 3);
     // ---- the inverse: warp = (head, 16-row block) ----------------------------------------------------
     tril_inverse_64<PA>(reinterpret_cast<float*>(smem + S_X) + (warp >> 2) * CHUNK * PA, warp & 3, lane);
+    stage_tick(a, cta, 4);
     {   // Awb = X diag(beta) and Awb diag(e^{Gl-G}) as bf16 tiles over the front of the fp32 tiles
         const int sb = tid >> 7, r = (tid & 127) >> 1, half = tid & 1;
         const float* sA = reinterpret_cast<const float*>(smem + S_X) + sb * CHUNK * PA + r * PA + half * 32;
@@ -294,29 +319,33 @@ __global__ void __launch_bounds__(PT, 2) gdn_prep_umma_kernel(GdnArgs a) {
     fence_async_smem();
     __syncthreads();
 
+    stage_tick(a, cta, 5);
     // ---- products 3, 4, 5 ---------------------------------------------------------------------------
-    if (tid == 0 && !dead) {
+    if (issuer && !dead) {
         tc_fence_after();
-#pragma unroll
-        for (int sb = 0; sb < 2; ++sb)
+        {
+            const int sb = isub;
 #pragma unroll
             for (int kk = 0; kk < 4; ++kk)
                 umma_f16_ts(taddr + ((uint32_t)(16 * sb) << 16) + T0, taddr + ((uint32_t)(16 * sb) << 16) + TA_P + 8 * kk,
                             umma_desc_mn128(sX + sb * TILE + kk * 2048), ID_KN, kk > 0);
+        }
         umma_commit(bars + B_R);
-#pragma unroll
-        for (int sb = 0; sb < 2; ++sb)
+        {
+            const int sb = isub;
 #pragma unroll
             for (int kk = 0; kk < 4; ++kk)
                 umma_f16_ss(taddr + ((uint32_t)(16 * sb) << 16) + T1, umma_desc_k128(sX + sb * TILE + kk * 32),
                             umma_desc_mn128(sK + sb * TILE + kk * 2048), ID_KN, kk > 0);
+        }
         umma_commit(bars + B_W);
-#pragma unroll
-        for (int sb = 0; sb < 2; ++sb)
+        {
+            const int sb = isub;
 #pragma unroll
             for (int kk = 0; kk < 4; ++kk)
                 umma_f16_ss(taddr + ((uint32_t)(16 * sb) << 16) + T2, umma_desc_k128(sX + 2 * TILE + sb * TILE + kk * 32),
                             umma_desc_mn128(sV + sb * TILE + kk * 2048), ID_KN, kk > 0);
+        }
         umma_commit(bars + B_U);
     }
     __syncwarp();
@@ -336,22 +365,25 @@ __global__ void __launch_bounds__(PT, 2) gdn_prep_umma_kernel(GdnArgs a) {
     tc_fence_before();
     __syncthreads();
 
+    stage_tick(a, cta, 6);
     // ---- products 6, 7 ------------------------------------------------------------------------------
-    if (tid == 0 && !dead) {
+    if (issuer && !dead) {
         tc_fence_after();
-#pragma unroll
-        for (int sb = 0; sb < 2; ++sb)
+        {
+            const int sb = isub;
 #pragma unroll
             for (int kk = 0; kk < 4; ++kk)
                 umma_f16_ss(taddr + ((uint32_t)(16 * sb) << 16) + T1, umma_desc_mn128(sK + sb * TILE + kk * 2048),
                             umma_desc_mn128(sX + sb * TILE + kk * 2048), ID_NN, kk > 0);
+        }
         umma_commit(bars + B_M);
-#pragma unroll
-        for (int sb = 0; sb < 2; ++sb)
+        {
+            const int sb = isub;
 #pragma unroll
             for (int kk = 0; kk < 4; ++kk)
                 umma_f16_ss(taddr + ((uint32_t)(16 * sb) << 16) + T2, umma_desc_mn128(sX + 2 * TILE + sb * TILE + kk * 2048),
                             umma_desc_mn128(sK + sb * TILE + kk * 2048), ID_NN, kk > 0);
+        }
         umma_commit(bars + B_B);
     }
     __syncwarp();
@@ -397,15 +429,17 @@ __global__ void __launch_bounds__(PT, 2) gdn_prep_umma_kernel(GdnArgs a) {
     tc_fence_before();
     __syncthreads();
 
+    stage_tick(a, cta, 7);
     // ---- product 8 ----------------------------------------------------------------------------------
-    if (tid == 0 && !dead) {
+    if (issuer && !dead) {
         tc_fence_after();
-#pragma unroll
-        for (int sb = 0; sb < 2; ++sb)
+        {
+            const int sb = isub;
 #pragma unroll
             for (int kk = 0; kk < 4; ++kk)
                 umma_f16_ts(taddr + ((uint32_t)(16 * sb) << 16) + T0, taddr + ((uint32_t)(16 * sb) << 16) + TA_R + 8 * kk,
                             umma_desc_mn128(sK + sb * TILE + kk * 2048), ID_KN, kk > 0);
+        }
         umma_commit(bars + B_RK);
     }
     __syncwarp();
@@ -424,19 +458,32 @@ __global__ void __launch_bounds__(PT, 2) gdn_prep_umma_kernel(GdnArgs a) {
     tc_fence_before();
     __syncthreads();
 
+    stage_tick(a, cta, 8);
     // ---- product 9 ----------------------------------------------------------------------------------
-    if (tid == 0 && !dead) {
+    if (issuer && !dead) {
         tc_fence_after();
-#pragma unroll
-        for (int sb = 0; sb < 2; ++sb)
+        {
+            const int sb = isub;
 #pragma unroll
             for (int kk = 0; kk < 4; ++kk)
                 umma_f16_ts(taddr + ((uint32_t)(16 * sb) << 16) + T1, taddr + ((uint32_t)(16 * sb) << 16) + TA_P + 8 * kk,
                             umma_desc_mn128(sV + sb * TILE + kk * 2048), ID_KN, kk > 0);
+        }
         umma_commit(bars + B_PV);
     }
     __syncwarp();
 
+    // (while product 9 runs)
+    if (HIER) {   // lambda of the chunk levels, transposed to [level][token] for the scan
+        for (int idx = tid; idx < 2 * a.LC * CHUNK; idx += PT) {
+            const int sub = idx / (a.LC * CHUNK), rem = idx - sub * a.LC * CHUNK;
+            const int l = rem >> 6, r = rem & 63;
+            if (2 * pair + sub < H) {
+                float* lamc = reinterpret_cast<float*>(a.rec + ((size_t)c * H + 2 * pair + sub) * a.rec_bytes + R::LAM_OFF);
+                lamc[rem] = (ELL0 + l < a.L) ? sLam[(sub * CHUNK + r) * LP + ELL0 + l] : 0.f;
+            }
+        }
+    }
     // B^T -> record
     mbar_wait(bars + B_B, 0u, dead, a.status, 605, budget);
     tc_fence_after();
@@ -479,14 +526,16 @@ __global__ void __launch_bounds__(PT, 2) gdn_prep_umma_kernel(GdnArgs a) {
         for (int q = 0; q < 4; ++q) dst[q] = make_uint4(w[4 * q], w[4 * q + 1], w[4 * q + 2], w[4 * q + 3]);
     }
 
+    stage_tick(a, cta, 9);
     // nothing asynchronous may outlive the CTA: one last commit covers every product issued above
-    if (tid == 0) {
+    if (issuer) {
         umma_commit(bars + B_DRAIN);
         mbar_drain(bars + B_DRAIN, 0u);
     }
     tc_fence_before();
     __syncthreads();
     if (warp == 0) tmem_dealloc(taddr, 256);
+    stage_tick(a, cta, 10);
 }
 
 }  // namespace
