@@ -69,6 +69,7 @@ struct GdnArgs {
     int fixed_T;        // tokens per sequence when there is no cu_seqlens (0 otherwise)
     int fixed_cps;      // chunks per sequence in that case: positions follow by arithmetic, no plan loads
     int nc_max, nb_max, nhigh_max;
+    long long total_tokens;  // B * T of the call (rows of the token-major inputs)
     const int64_t* tok_off; const int32_t* chunk_off; const int32_t* block_off;
     char* rec; size_t rec_bytes;          // per (chunk, head) records
     char* blk;                            // per (block, head) composites

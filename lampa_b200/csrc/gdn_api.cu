@@ -79,6 +79,7 @@ void fill_args(const lampa_gdn_desc* d, bool hier, const Layout& l, char* base, 
     a.use_l2norm = d->use_l2norm; a.scale = d->scale;
     a.fixed_T = cu ? 0 : d->T;
     a.fixed_cps = cu ? 0 : (d->T + CHUNK - 1) / CHUNK;
+    a.total_tokens = (long long)d->B * d->T;
     a.nseq = l.nseq; a.nc_max = l.nc_max; a.nb_max = l.nb_max; a.nhigh_max = l.nhigh_max;
     a.tok_off = (int64_t*)(base + l.off_tok);
     a.chunk_off = (int32_t*)(base + l.off_chunk);

@@ -67,11 +67,11 @@ __device__ __forceinline__ void store_neg_tile(float* s, int pitch, int r0, int 
 // the off-diagonal blocks follow as X_ba = -(X_bb A_ba) X_aa, first inside the two 32x32 halves,
 // then for the 32x32 corner, in place.  Those products keep fp32 accuracy by splitting each operand
 // into bf16 hi + lo and issuing hi*hi + lo*hi + hi*lo (the reference asks for IEEE fp32 dots there).
-// Contains CTA-wide barriers: all warps of the CTA call it the same number of times.
+// Contains CTA-wide barriers: every warp of the CTA calls it; warps that own no block pass active = false.
 template <int PA>
-__device__ __forceinline__ void tril_inverse_64(float* sA, int blk, int lane) {
+__device__ __forceinline__ void tril_inverse_64(float* sA, int blk, int lane, bool active = true) {
     const int m0 = blk * 16;
-    {
+    if (active) {
         const int cc = lane & 15;
         float x[16];
 #pragma unroll
@@ -94,7 +94,7 @@ __device__ __forceinline__ void tril_inverse_64(float* sA, int blk, int lane) {
         }
     }
     __syncthreads();
-    if (blk & 1) {   // X_ba of the pair (a, b) = (warp - 1, warp)
+    if (active && (blk & 1)) {   // X_ba of the pair (a, b) = (blk - 1, blk)
         const int ra = m0 - 16, rb = m0;
         float q0[2][4], xo[2][4];
         zero_acc<2>(q0);
@@ -119,11 +119,13 @@ __device__ __forceinline__ void tril_inverse_64(float* sA, int blk, int lane) {
         for (int nt = 0; nt < 2; ++nt) store_neg_tile(sA, PA, rb, ra + 8 * nt, lane, xo[nt]);
     }
     __syncthreads();
-    {   // the 32x32 corner: warp = (row tile mt, column half nh)
-        const int mt = blk >> 1, nh = blk & 1;
-        float qc[4][4], xc[2][4];
+    // the 32x32 corner: warp = (row tile mt, column half nh)
+    const int mt = blk >> 1, nh = blk & 1;
+    float xc[2][4];
+    zero_acc<2>(xc);
+    if (active) {
+        float qc[4][4];
         zero_acc<4>(qc);
-        zero_acc<2>(xc);
 #pragma unroll
         for (int ks = 0; ks < 2; ++ks)
             if (ks <= mt) {                                   // X_b is block lower-triangular
@@ -150,7 +152,9 @@ __device__ __forceinline__ void tril_inverse_64(float* sA, int blk, int lane) {
                 }
             }
         }
-        __syncthreads();                                      // every warp has read A_ba
+    }
+    __syncthreads();                                          // every warp has read A_ba
+    if (active) {
 #pragma unroll
         for (int n = 0; n < 2; ++n) store_neg_tile(sA, PA, 32 + 16 * mt, 8 * (2 * nh + n), lane, xc[n]);
     }
