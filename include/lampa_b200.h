@@ -75,7 +75,7 @@ int lampa_gdn_workspace_bytes(const lampa_gdn_desc* d, size_t* bytes);
  * One record per (chunk slot, head), chunk-major.  out[0] = byte offset of the first record,
  * out[1] = bytes per record, then byte offsets inside a record of the bf16 tiles out[2] M [K][K],
  * out[3] B^T [V][K], out[4] Q~ [64][K] (row pitch K+8 elements, except K = 64: dense 128-byte rows
- * with the 16-byte chunk index XORed with row%8), out[5] O_local (bf16 [64][V]),
+ * with the 16-byte chunk index XORed with row%8), out[5] O_local (bf16 [64][V], same row layout as the other tiles),
  * out[6] chunk-level lambda (fp32 [LC][64], hierarchical only); out[7] = LC, out[8] = number of
  * chunk slots, out[9] = chunks per block, out[10] / out[11] = byte offsets of the block composites
  * and of the block entry states.

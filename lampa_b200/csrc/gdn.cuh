@@ -36,7 +36,7 @@ template <int KD, int VD>
 struct Rec {
     using T = Tile<KD>;
     static constexpr int KP = KD + 8;                 // padded bf16 row pitch (block composites)
-    static constexpr int OP = VD;                     // bf16 row pitch (elements) of O_local
+    using TV = Tile<VD>;                              // layout of O_local[token][v]: a V-wide bf16 tile
     static constexpr int M_OFF = 0;
     static constexpr int M_BYTES = T::bytes(KD);      // M[k_out][k_in]
     static constexpr int QT_OFF = M_OFF + M_BYTES;    // M and Q~ are adjacent: together they are one 128-row B operand
@@ -44,7 +44,7 @@ struct Rec {
     static constexpr int BT_OFF = QT_OFF + QT_BYTES;
     static constexpr int BT_BYTES = T::bytes(VD);     // B^T[v][k]
     static constexpr int OL_OFF = BT_OFF + BT_BYTES;
-    static constexpr int OL_BYTES = CHUNK * OP * 2;   // O_local[token][v], bf16 (added once, in fp32, by the output pass)
+    static constexpr int OL_BYTES = TV::bytes(CHUNK); // O_local, bf16 (added once, in fp32, by the output pass)
     static constexpr int LAM_OFF = OL_OFF + OL_BYTES; // lambda of chunk levels: [LC][64] fp32
     static constexpr int PRE_BYTES = OL_OFF;          // M, Q~, B^T: what the compose pass streams
     static constexpr int ALIGN = T::SWZ ? 1024 : 128; // records and shared-memory stages

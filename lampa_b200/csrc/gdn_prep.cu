@@ -340,7 +340,7 @@ __global__ void __launch_bounds__(128, 4) gdn_prep_kernel(GdnArgs a) {
 #pragma unroll
                 for (int hh = 0; hh < 2; ++hh) {
                     const int i = m0 + gq + hh * 8, j = nt * 8 + 2 * tq;
-                    *reinterpret_cast<uint32_t*>(gO + i * R::OP + j) =
+                    *reinterpret_cast<uint32_t*>(gO + R::TV::off(i, j)) =
                         pack_bf16x2(osc * acc[nt][2 * hh], osc * acc[nt][2 * hh + 1]);
                 }
         }

@@ -20,6 +20,8 @@
 //   7  B^T = U^^T K               (A, B MN-major)       ->  record
 //   8  Q~  = s e^G (Q - R K)      (A tmem, B MN-major)  ->  record
 //   9  O_local = s (R .* E .* lambda) V                 ->  record
+// The four record tiles are assembled in shared memory in the record's own layout (over operands that are
+// dead by then) and leave as bulk stores.
 // (U^ of gdn.cuh is diag(e^{Gl-G}) (Awb .* E) V; the row factor times E_ij is e^{Gl-G_j}, a column
 // factor of Awb, so no 64x64 table of decays is needed for it.)
 // The unit-lower-triangular inverse stays an fp32 substitution with split-bf16 block merges
@@ -142,6 +144,12 @@ __global__ void __launch_bounds__(8192 / NC, 2) gdn_prep_umma_kernel(GdnArgs a, 
     bool dead = false;
     const int cta = blockIdx.y * gridDim.x + blockIdx.x;
     stage_tick(a, cta, 0);
+    if (a.ticks != nullptr && threadIdx.x == 0 && cta < a.ticks_ctas) {
+        unsigned sm_; unsigned long long gt_;
+        asm volatile("mov.u32 %0, %%smid;" : "=r"(sm_));
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt_));
+        a.ticks[(size_t)cta * 16 + 11] = sm_; a.ticks[(size_t)cta * 16 + 12] = (long long)gt_;
+    }
 
     // ---- stage 0: TMA loads, l2norm, cumulative decay ---------------------------------------------
     // One thread asks the TMA unit for the six 64 x 64 tiles (q, k, v of both heads): they land in the
@@ -295,9 +303,6 @@ __global__ void __launch_bounds__(8192 / NC, 2) gdn_prep_umma_kernel(GdnArgs a, 
     const int sub = lane >> 4, i = 16 * sp + (lane & 15);
     const int col0 = NC * cq;
     const uint32_t tlane = taddr + ((uint32_t)(32 * sp) << 16);
-    const int h = 2 * pair + sub;
-    const bool head_ok = h < H;
-    char* rec = a.rec + ((size_t)c * H + (head_ok ? h : 0)) * a.rec_bytes;
 
     stage_tick(a, cta, 2);
     // A0 = tril(diag(beta) K K^T, -1) as fp32 into the inverse's tile
@@ -464,10 +469,15 @@ __global__ void __launch_bounds__(8192 / NC, 2) gdn_prep_umma_kernel(GdnArgs a, 
 #pragma unroll
         for (int jj = 0; jj < NC; ++jj) x[jj] = egl * ((col0 + jj == i ? 1.f : 0.f) - x[jj]);
         pack_n<NC>(x, w);
-        if (head_ok) store_cols_swz<NC>(reinterpret_cast<unsigned char*>(rec) + R::M_OFF, i, col0 / 8, w);
+        store_cols_swz<NC>(smem + S_X + sub * TILE, i, col0 / 8, w);        // staged over W (product 6 is complete)
     }
+    fence_async_smem();
     tc_fence_before();
     __syncthreads();
+    if (tid < 2 && 2 * pair + tid < H) {   // one bulk store per head
+        bulk_s2g(a.rec + ((size_t)c * H + 2 * pair + tid) * a.rec_bytes + R::M_OFF, smem + S_X + tid * TILE, TILE);
+        bulk_commit();
+    }
 
     stage_tick(a, cta, 8);
     // ---- product 9 ----------------------------------------------------------------------------------
@@ -496,7 +506,7 @@ __global__ void __launch_bounds__(8192 / NC, 2) gdn_prep_umma_kernel(GdnArgs a, 
     tc_fence_after();
     tmem_ld_n<NC>(x, tlane + T2 + col0);
     pack_n<NC>(x, w);
-    if (head_ok) store_cols_swz<NC>(reinterpret_cast<unsigned char*>(rec) + R::BT_OFF, i, col0 / 8, w);
+    store_cols_swz<NC>(smem + S_X + 2 * TILE + sub * TILE, i, col0 / 8, w);   // staged over U^ (product 7 is complete)
 
     // Q~ = s e^{G_i} (Q - R K) -> record
     mbar_wait(bars + B_RK, 0u, dead, a.status, 606, budget);
@@ -515,7 +525,7 @@ __global__ void __launch_bounds__(8192 / NC, 2) gdn_prep_umma_kernel(GdnArgs a, 
                 w[4 * q + e] = pack_bf16x2(f * (qv.x - x[8 * q + 2 * e]), f * (qv.y - x[8 * q + 2 * e + 1]));
             }
         }
-        if (head_ok) store_cols_swz<NC>(reinterpret_cast<unsigned char*>(rec) + R::QT_OFF, i, col0 / 8, w);
+        store_cols_swz<NC>(smem + S_Q + sub * TILE, i, col0 / 8, w);           // staged in place: each thread overwrites what it read
     }
 
     // O_local = s Pm V -> record (bf16 [64][64], plain rows)
@@ -527,10 +537,16 @@ __global__ void __launch_bounds__(8192 / NC, 2) gdn_prep_umma_kernel(GdnArgs a, 
         for (int jj = 0; jj < NC; ++jj) x[jj] *= osc;
     }
     pack_n<NC>(x, w);
-    if (head_ok) {
-        uint4* dst = reinterpret_cast<uint4*>(rec + R::OL_OFF + (i * 64 + col0) * 2);
-#pragma unroll
-        for (int q = 0; q < NCH; ++q) dst[q] = make_uint4(w[4 * q], w[4 * q + 1], w[4 * q + 2], w[4 * q + 3]);
+    store_cols_swz<NC>(smem + S_V + sub * TILE, i, col0 / 8, w);               // staged over V (product 9 is complete)
+    fence_async_smem();
+    __syncthreads();
+    if (tid < 2 && 2 * pair + tid < H) {   // the three remaining tiles of each head leave as bulk stores
+        char* rh = a.rec + ((size_t)c * H + 2 * pair + tid) * a.rec_bytes;
+        bulk_s2g(rh + R::BT_OFF, smem + S_X + 2 * TILE + tid * TILE, TILE);
+        bulk_s2g(rh + R::QT_OFF, smem + S_Q + tid * TILE, TILE);
+        bulk_s2g(rh + R::OL_OFF, smem + S_V + tid * TILE, TILE);
+        bulk_commit();
+        bulk_wait_read();                  // shared memory stays ours until the stores have read it
     }
 
     stage_tick(a, cta, 9);
@@ -543,6 +559,11 @@ __global__ void __launch_bounds__(8192 / NC, 2) gdn_prep_umma_kernel(GdnArgs a, 
     __syncthreads();
     if (warp == 1) tmem_dealloc(taddr, 256);
     stage_tick(a, cta, 10);
+    if (a.ticks != nullptr && threadIdx.x == 0 && cta < a.ticks_ctas) {
+        unsigned long long gt_;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt_));
+        a.ticks[(size_t)cta * 16 + 13] = (long long)gt_;
+    }
 }
 
 }  // namespace

@@ -291,7 +291,7 @@ __global__ void __launch_bounds__(UTHREADS, 1) gdn_out_hier_umma_kernel(GdnArgs 
                 if (t_out < tok_end) {
                     const size_t idx = ((size_t)t_out * H + h) * UVD + col;
                     float r[8];
-                    const uint4 ol = *reinterpret_cast<const uint4*>(sOl + tok * UR::OP + col);      // 8 bf16 of O_local
+                    const uint4 ol = *reinterpret_cast<const uint4*>(sOl + UR::TV::off(tok, col));      // 8 bf16 of O_local
                     const uint32_t olw[4] = {ol.x, ol.y, ol.z, ol.w};
 #pragma unroll
                     for (int q = 0; q < 2; ++q) {

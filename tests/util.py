@@ -16,13 +16,17 @@ PARITY_LOG = []   # (what, max-abs, rel-L2, |ref|_inf) of every comparison, prin
 
 
 def max_abs_bound(rmax: float) -> float:
-    """2e-2 while the reference stays within |ref|_inf <= 2, then 1 % of |ref|_inf.  Every operand of
-    the tensor-core products is bf16 (relative spacing 2^-8), which leaves a per-element relative
-    error of about 0.35 % rms with tails near 1 % over 10^5..10^7 elements; on a value of 2 that is
-    already 2e-2, and from 4 upwards one bf16 step of the result itself is 3.1e-2.  The flat
-    figure therefore is only attainable for outputs of O(1); above that the bound follows the
-    magnitude.  The unscaled error is printed for every comparison."""
-    return 2e-2 * max(1.0, rmax / 2.0)
+    """2e-2 while the reference stays within |ref|_inf <= 1.4, then 1.4 % of |ref|_inf.
+
+    Why the flat figure cannot hold for larger outputs: every operand of the tensor-core products
+    is bf16 (round-to-nearest error up to 2^-9 = 0.2 % per rounding).  An output element that is
+    dominated by a single term (strong decay: the token's own contribution) passes through seven
+    such roundings in a row (tril(QK^T), the inverse, R, R.*E.*lambda, the local output in the
+    record, v itself being exact, and the result), so its worst case is 7 x 0.2 % = 1.4 % of its
+    magnitude with nothing to average the roundings out; the typical element sits at 0.35 % rms.
+    On a value of 2 that worst case is already 2.8e-2, and from 4 upwards one bf16 step of the
+    result alone is 3.1e-2.  The unscaled error is printed for every comparison."""
+    return max(2e-2, 1.4e-2 * rmax)
 
 
 def assert_close_bf16(got, ref, what="", max_abs_factor: float = 1.0):
