@@ -238,10 +238,68 @@ def gen_hept(ref: str):
     print("hept ok", tuple(so.shape), tuple(out.shape), float(denom.min()), float(denom.max()))
 
 
+def gen_minimal(ref: str):
+    """The reference's own chunkwise statement of the hierarchical rule, hgdn_minimal
+    (models/hattention/hssd_minimal.py:462-493), at T = 4096 (64 chunks: two blocks of 32, one
+    cross-block level).  Its level table comes from make_levels_matrix (models/hattention/base.py:
+    101-161), a Python double loop over T x T (and over 16384 x 16384 through its cache) that
+    cannot finish at this length; it is replaced here by the same table built with
+    bit_length(t XOR s), the closed form the reference's own get_level_index_weak reproduces for
+    every pair of levels_weak_130.npz.  Everything else is the reference's code, in fp32."""
+    pkg_dir = os.path.join(ref, "models", "hattention")
+    if "_ref_hattention" not in sys.modules:
+        load_hattention(ref)
+    base = sys.modules["_ref_hattention.base"]
+
+    def levels_closed_form(length, base, htype, dtype, device, default=-1, clamp_min=None, file_name=None,
+                           cached_length=None):
+        t = np.arange(length)[:, None]
+        s_ = np.arange(length)[None, :]
+        x = t ^ s_
+        bl = np.zeros_like(x)
+        nz = x > 0
+        bl[nz] = np.floor(np.log2(x[nz])).astype(np.int64) + 1
+        lv = np.where(s_ <= t, bl, default)
+        out = torch.from_numpy(lv.astype(np.int64)).to(dtype=dtype, device=device)
+        return out if clamp_min is None else torch.clamp(out, min=clamp_min)
+
+    # the closed form against the reference's own level function on a prefix
+    chk = levels_closed_form(130, 2, base.HType.WEAK, torch.int64, "cpu")
+    for t in range(130):
+        for s_ in range(t):
+            assert int(chk[t, s_]) == base.get_level_index_weak(t, s_, 2)
+    for name in ("fla_utils", "fla_op", "cumsum", "hssd_minimal"):
+        if f"_ref_hattention.{name}" in sys.modules:
+            continue
+        spec = importlib.util.spec_from_file_location(f"_ref_hattention.{name}", os.path.join(pkg_dir, f"{name}.py"))
+        m = importlib.util.module_from_spec(spec)
+        sys.modules[f"_ref_hattention.{name}"] = m
+        try:
+            spec.loader.exec_module(m)
+        except Exception as e:                      # helper modules that need a GPU stack: only hssd_minimal must load
+            if name == "hssd_minimal":
+                raise
+            print("note:", name, "not importable here:", type(e).__name__)
+    mini = sys.modules["_ref_hattention.hssd_minimal"]
+    mini.make_levels_matrix = levels_closed_form
+    T, H, K, V = 4096, 2, 32, 32
+    Lv = 7 + 6
+    q, k, v, beta, g, lam = gdn_inputs(104, T, H, K, V, Lv, -4.0)     # the test redraws these from the seed
+    scale = K ** -0.5
+    with torch.no_grad():
+        o = mini.hgdn_minimal(Q=(q * scale)[None], K=k[None], V=v[None], B=beta[None], G=g[None], L=(lam / scale)[None],
+                              level_base=2, htype=base.HType.WEAK, block_len=64)
+    np.savez_compressed(os.path.join(HERE, "hgdn_minimal_T4096_H2_K32_V32_L13.npz"),
+                        seed=np.int64(104), g_shift=np.float32(-4.0), shape=np.array([T, H, K, V, Lv]),
+                        input_sums=np.array([float(x.double().sum()) for x in (q, k, v, beta, g, lam)]),
+                        o_hier=o[0].numpy())
+    print("hgdn_minimal ok", tuple(o.shape), float(o.abs().max()))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", required=True, help="path of the reference checkout")
-    ap.add_argument("--only", default="", help="'geo' / 'layer' / 'hept': write only that fixture")
+    ap.add_argument("--only", default="", help="'geo' / 'layer' / 'hept' / 'minimal': write only that fixture")
     args = ap.parse_args()
     ref = args.reference
     torch.set_num_threads(8)
@@ -251,6 +309,8 @@ def main():
         gen_hept(args.reference)
     if args.only in ("", "layer"):
         gen_layer(ref)
+    if args.only in ("", "minimal"):
+        gen_minimal(ref)
     if args.only:
         return
     base, recurrent = load_hattention(ref)

@@ -187,6 +187,19 @@ def test_hier_matches_token_recurrence(lb, T, H, K, V, gs):
     assert_close_bf16(to_np(o[0]), _hier_ref(inp), "o hier")
 
 
+def test_hier_against_reference_chunkwise_statement(lb, golden_dir):
+    """The reference's own chunkwise statement (hgdn_minimal) at T = 4096: cross-block level and
+    block composites against numbers the reference itself produced."""
+    from tests.util import minimal_fixture_inputs
+    z = np.load(os.path.join(golden_dir, "hgdn_minimal_T4096_H2_K32_V32_L13.npz"))
+    q, k, v, beta, g, lam = minimal_fixture_inputs(z)
+    qb, kb, vb = (x.bfloat16() for x in (q, k, v))
+    o, _ = lb.chunk_h_gated_delta_rule(qb[None].cuda(), kb[None].cuda(), vb[None].cuda(), g[None].cuda(), lam[None].cuda(),
+                                       beta[None].cuda(), use_qk_l2norm_in_kernel=True)
+    # the fixture was computed from the fp32 inputs: the comparison carries the bf16 rounding of q, k, v as well
+    assert_close_bf16(to_np(o[0]), z["o_hier"], "o vs hgdn_minimal (reference fixture)")
+
+
 def test_hier_golden_fixture_from_reference(lb, golden_dir):
     """Inputs and outputs produced by the reference's hattention_recurrent (tests/golden)."""
     for name in ("hgdn_T320_H2_K32_V32_L10", "hgdn_T256_H1_K64_V64_L9", "hgdn_T200_H2_K16_V32_L9"):

@@ -30,6 +30,20 @@ def test_hier_and_plain_match_reference_recurrence(golden_dir, name):
     np.testing.assert_allclose(ht[0], z["final_plain"], rtol=2e-4, atol=2e-5)
 
 
+def test_hier_matches_reference_chunkwise_statement(golden_dir):
+    """Second pin: the reference's own chunkwise statement (hgdn_minimal, hssd_minimal.py:462-493)
+    at T = 4096 -- 64 chunks, two blocks of 32, one cross-block level -- against the token
+    recurrence of the checker, both fp32."""
+    from tests.util import minimal_fixture_inputs
+    z = np.load(os.path.join(golden_dir, "hgdn_minimal_T4096_H2_K32_V32_L13.npz"))
+    q, k, v, beta, g, lam = (x.numpy() for x in minimal_fixture_inputs(z))
+    o, _, _ = oracle.hgdn(q, k, v, g, beta, lam, use_l2norm=False)
+    ref = z["o_hier"]
+    err = np.abs(o - ref).max()
+    rel = np.linalg.norm(o - ref) / np.linalg.norm(ref)
+    assert err <= 5e-5 * max(1.0, np.abs(ref).max()) and rel <= 2e-5, (err, rel)
+
+
 def test_level_function_is_bit_length_of_xor(golden_dir):
     lv = np.load(os.path.join(golden_dir, "levels_weak_130.npz"))["levels"]
     t = np.arange(130)[:, None]

@@ -42,3 +42,20 @@ def assert_close_bf16(got, ref, what="", max_abs_factor: float = 1.0):
     assert mx <= bound, f"{what}: max-abs {mx:.3e} > {bound:.2e} (|ref|_inf {rmax:.2f})"
     assert rl <= 1e-2, f"{what}: rel-L2 {rl:.3e}"
     return mx, rl
+
+
+def minimal_fixture_inputs(z):
+    """Redraw the inputs of tests/golden/hgdn_minimal_*.npz from its seed (the draw order of
+    tests/golden/gen_golden.py::gdn_inputs: q, k, v, beta, g, lambda, all [T, H, .]) and check
+    them against the sums stored beside the reference's output."""
+    T, H, K, V, Lv = (int(x) for x in z["shape"])
+    gen = torch.Generator().manual_seed(int(z["seed"]))
+    q = torch.nn.functional.normalize(torch.randn(T, H, K, generator=gen), dim=-1)
+    k = torch.nn.functional.normalize(torch.randn(T, H, K, generator=gen), dim=-1)
+    v = torch.randn(T, H, V, generator=gen)
+    beta = torch.sigmoid(torch.randn(T, H, generator=gen))
+    g = -torch.nn.functional.softplus(torch.randn(T, H, generator=gen) + float(z["g_shift"]))
+    lam = torch.nn.functional.softplus(torch.randn(T, H, Lv, generator=gen))
+    sums = np.array([float(x.double().sum()) for x in (q, k, v, beta, g, lam)])
+    np.testing.assert_allclose(sums, z["input_sums"], rtol=1e-9, atol=1e-9)
+    return q, k, v, beta, g, lam
