@@ -51,7 +51,14 @@ def test_host_side_argument_errors_without_a_gpu():
 
 def test_python_api_rejects_cpu_tensors_and_bad_shapes():
     import lampa_b200
-    q = torch.randn(1, 128, 2, 64)
+    q = torch.randn(1, 128, 2, 64).bfloat16()
+    with pytest.raises(AssertionError):          # fp32 q / k / v are refused, as by the reference
+        lampa_b200.chunk_gated_delta_rule(q.float(), q.float(), q.float(), torch.zeros(1, 128, 2), torch.zeros(1, 128, 2))
+    with pytest.raises(NotImplementedError):     # forward only: no silent detach
+        qg = q.clone().requires_grad_(True)
+        lampa_b200.chunk_gated_delta_rule(qg, qg, qg, torch.zeros(1, 128, 2), torch.zeros(1, 128, 2))
+    with pytest.raises(ValueError):              # host-resident cu_seqlens are validated on the host
+        lampa_b200.chunk_gated_delta_rule(q, q, q, torch.zeros(1, 128, 2), torch.zeros(1, 128, 2), cu_seqlens=torch.tensor([0, 200]))
     with pytest.raises(lampa_b200.LampaError):
         lampa_b200.chunk_gated_delta_rule(q, q, q, torch.zeros(1, 128, 2), torch.zeros(1, 128, 2))
     with pytest.raises(DeprecationWarning):
