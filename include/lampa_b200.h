@@ -314,6 +314,25 @@ int lampa_rmsnorm_gate(const void* x, const void* g, const void* weight, int64_t
                        int32_t dtype, int32_t w_dtype, float eps, int32_t sigmoid_only, void* y,
                        void* stream);
 /*
+ * Residual add + RMS norm of a block's fp32 residual stream, with the ordering layer's row
+ * permutation folded in.  For every j in [0, rows): r = s0 + perm[s0 + j'] (perm: int64 indices
+ * local to the row's segment, as lampa_segsort_stable writes them; r = j when perm is NULL);
+ *   v = res[r] + delta[delta_at_r ? r : j]   (delta NULL: v = res[r], res is left untouched)
+ *   res[r] = v                                (fp32, in place)
+ *   y[y_at_r ? r : j] = v / sqrt(mean(v^2) + eps) * weight    (y NULL: the add only)
+ * so the un-ordering of a mixer's output (delta in sorted order, delta_at_r = 0, y_at_r = 1) and the
+ * ordering of the next mixer's input (delta_at_r = 1, y_at_r = 0) cost no pass of their own.
+ * res [rows, D] fp32; delta, y [rows, D] of their dtypes; weight [D] fp32 or NULL; D a multiple of 4,
+ * at most 1024.  An index outside its segment skips the row and sets LAMPA_ERR_BOUNDS in `status`.
+ * Replaces: RMSNorm.forward(x, residual, prenorm=True) (models/hattention/fused_norm.py:1288-1330,
+ * 1413-1425, as used by the block at modeling_gated_deltaproduct.py:1169-1199) together with the
+ * gather / un-gather around the mixer (models/baselines/hmamba.py:428-455).
+ */
+int lampa_add_rmsnorm(float* res, const void* delta, int32_t delta_dtype, const int64_t* perm,
+                      const int64_t* seg_offsets, int32_t nseg, int64_t rows, int32_t D,
+                      const float* weight, float eps, int32_t delta_at_r, int32_t y_at_r, void* y,
+                      int32_t y_dtype, int32_t* status, void* stream);
+/*
  * Bucketed RBF-kernel attention of the HEPT layer, fp32.  Per (round, head) the n hits are taken in
  * the order q_pos / k_pos (int64 [rounds][heads][n]; NULL: rows are already in order), cut into
  * buckets of `bucket` consecutive hits (n % bucket == 0, bucket <= 128), and inside a bucket

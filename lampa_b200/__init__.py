@@ -8,7 +8,7 @@ from .geo import (  # noqa: F401
     get_geo_shift, get_regions, hept_positions, pad_to_multiple, quantile_partition, region_inputs, row_range)
 from .bucket_attn import hept_attention_core, hept_bucket_attention, prep_qk, qkv_res  # noqa: F401
 from .layer import (  # noqa: F401
-    FusedRMSNormGated, ShortConvolution, compute_lambda, gate_inputs, rms_norm_gated)
+    FusedRMSNormGated, ShortConvolution, add_rms_norm, compute_lambda, gate_inputs, rms_norm_gated)
 from .lsh import (  # noqa: F401
     E2LSH, LSHOrdering, batched_index_select, invert_permutation, lsh_bucket_sort, lsh_hash, lsh_mapping,
     permute_rows, segmented_sort, sort_to_buckets, unsort_from_buckets)
@@ -20,5 +20,5 @@ __all__ = [
     "sort_to_buckets", "unsort_from_buckets", "qkv_res", "prep_qk", "hept_bucket_attention", "hept_attention_core",
     "get_geo_shift", "get_regions", "hept_positions", "pad_to_multiple",
     "quantile_partition", "region_inputs", "row_range", "FusedRMSNormGated", "ShortConvolution", "compute_lambda",
-    "gate_inputs", "rms_norm_gated",
+    "gate_inputs", "rms_norm_gated", "add_rms_norm",
 ]

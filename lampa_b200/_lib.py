@@ -37,7 +37,7 @@ _lib: Optional[ctypes.CDLL] = None
 EXPORTS = ["lampa_version", "lampa_error_string", "lampa_gdn_workspace_bytes", "lampa_gdn_workspace_layout",
            "lampa_gdn_fwd", "lampa_hgdn_fwd", "lampa_hgdn_final_state", "lampa_hgdn_step", "lampa_lsh_hash", "lampa_segsort_workspace_bytes",
            "lampa_segsort_stable", "lampa_permute_rows", "lampa_invert_perm", "lampa_segsort_stable_static",
-           "lampa_short_conv_fwd", "lampa_short_conv_step", "lampa_gate_inputs", "lampa_rmsnorm_gate",
+           "lampa_short_conv_fwd", "lampa_short_conv_step", "lampa_gate_inputs", "lampa_rmsnorm_gate", "lampa_add_rmsnorm",
            "lampa_row_range", "lampa_quantile_regions", "lampa_geo_keys",
            "lampa_bucket_rbf_attn", "lampa_bucket_attn_combine", "lampa_hept_prep_qk",
            "lampa_profile_enable",
@@ -77,6 +77,7 @@ def lib() -> ctypes.CDLL:
         L.lampa_short_conv_step.argtypes = [vp, vp, vp, vp, vp, i64, i32, i32, i32, i32, i32, vp, vp]
         L.lampa_gate_inputs.argtypes = [vp] * 7 + [i64, i32, i32, i32, i32, i32, i32, vp, vp, vp, vp]
         L.lampa_rmsnorm_gate.argtypes = [vp, vp, vp, i64, i32, i32, i32, ctypes.c_float, i32, vp, vp]
+        L.lampa_add_rmsnorm.argtypes = [vp, vp, i32, vp, vp, i32, i64, i32, vp, ctypes.c_float, i32, i32, vp, i32, vp, vp]
         L.lampa_profile_enable.argtypes = [ctypes.c_int]
         L.lampa_debug_set_poll_budget.argtypes = [ctypes.c_int]
         L.lampa_debug_set_tick_buffer.argtypes = [vp, ctypes.c_int]

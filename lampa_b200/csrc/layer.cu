@@ -436,6 +436,121 @@ rmsnorm_gate_kernel(const void* x, const void* g, const void* w, int w_dt, int64
     }
 }
 
+// -------------------------------------------------------------------------------------------------
+// Residual add + RMS norm over rows of D floats, with the row permutation of the ordering layer folded
+// in.  For every j in [0, rows): r = s0 + perm[j] (the row's place in the other order; r = j
+// without a permutation), v = res[r] (+ delta[delta_at_r ? r : j]); the sum is written back to
+// res[r] when there is a delta; y[y_at_r ? r : j] = v / sqrt(mean(v^2) + eps) * weight when y is
+// given.  One warp per row, four rows in flight per warp.
+// -------------------------------------------------------------------------------------------------
+struct AddNormArgs {
+    float* res; const void* delta; int delta_dt; const int64_t* perm; const int64_t* seg; int nseg;
+    int64_t rows; int D; const float* w; float eps; int delta_at_r, y_at_r; void* y; int y_dt; int32_t* status;
+};
+
+__device__ __forceinline__ int find_seg_rows(const int64_t* off, int nseg, int64_t x) {
+    int lo = 0, hi = nseg;
+    while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (off[mid] <= x) lo = mid; else hi = mid;
+    }
+    return lo;
+}
+__device__ __forceinline__ float4 load4_as_float(const void* p, size_t i, int dt) {   // i a multiple of 4
+    if (dt == LAMPA_F32) return __ldg(reinterpret_cast<const float4*>((const float*)p + i));
+    const uint2 u = __ldg(reinterpret_cast<const uint2*>((const uint16_t*)p + i));
+    float2 a, b;
+    if (dt == LAMPA_BF16) { a = unpack_bf16x2(u.x); b = unpack_bf16x2(u.y); }
+    else { a = __half22float2(*reinterpret_cast<const __half2*>(&u.x)); b = __half22float2(*reinterpret_cast<const __half2*>(&u.y)); }
+    return make_float4(a.x, a.y, b.x, b.y);
+}
+__device__ __forceinline__ void store4_from_float(void* p, size_t i, int dt, float4 v) {
+    if (dt == LAMPA_F32) { *reinterpret_cast<float4*>((float*)p + i) = v; return; }
+    uint2 u;
+    if (dt == LAMPA_BF16) { u.x = pack_bf16x2(v.x, v.y); u.y = pack_bf16x2(v.z, v.w); }
+    else {
+        const __half2 a = __floats2half2_rn(v.x, v.y), b = __floats2half2_rn(v.z, v.w);
+        u.x = *reinterpret_cast<const uint32_t*>(&a); u.y = *reinterpret_cast<const uint32_t*>(&b);
+    }
+    *reinterpret_cast<uint2*>((uint16_t*)p + i) = u;
+}
+
+template <int VPL>   // float4 vectors per lane: D <= 128 * VPL
+__global__ void __launch_bounds__(256) add_rmsnorm_kernel(AddNormArgs p) {
+    constexpr int RPI = 4;
+    const int lane = threadIdx.x & 31;
+    const int64_t warp_id = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int64_t n_warps = (int64_t)gridDim.x * (blockDim.x >> 5);
+    const int nvec = p.D >> 2;
+    float4 wv[VPL];
+#pragma unroll
+    for (int v = 0; v < VPL; ++v) {
+        const int vi = lane + 32 * v;
+        wv[v] = (p.w && vi < nvec) ? __ldg(reinterpret_cast<const float4*>(p.w) + vi) : make_float4(1.f, 1.f, 1.f, 1.f);
+    }
+    for (int64_t base = warp_id * RPI; base < p.rows; base += n_warps * RPI) {
+        int64_t rr[RPI];
+        bool ok[RPI];
+        float4 x[RPI][VPL];
+#pragma unroll
+        for (int q = 0; q < RPI; ++q) {
+            const int64_t j = base + q;
+            ok[q] = j < p.rows;
+            rr[q] = j;
+            if (ok[q] && p.perm) {
+                int64_t s0 = 0, len = p.rows;
+                if (p.seg) { const int si = find_seg_rows(p.seg, p.nseg, j); s0 = p.seg[si]; len = p.seg[si + 1] - s0; }
+                else if (p.nseg > 1) { len = p.rows / p.nseg; s0 = (j / len) * len; }
+                const int64_t pj = p.perm[j];
+                if (pj < 0 || pj >= len || s0 < 0 || s0 + len > p.rows) {
+                    if (lane == 0) set_status(p.status, LAMPA_ERR_BOUNDS, 13, (int)j);
+                    ok[q] = false;
+                } else {
+                    rr[q] = s0 + pj;
+                }
+            }
+#pragma unroll
+            for (int v = 0; v < VPL; ++v) {
+                const int vi = lane + 32 * v;
+                x[q][v] = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (ok[q] && vi < nvec) {
+                    x[q][v] = *reinterpret_cast<const float4*>(p.res + (size_t)rr[q] * p.D + 4 * vi);
+                    if (p.delta) {
+                        const float4 d = load4_as_float(p.delta, (size_t)(p.delta_at_r ? rr[q] : base + q) * p.D + 4 * vi, p.delta_dt);
+                        x[q][v].x += d.x; x[q][v].y += d.y; x[q][v].z += d.z; x[q][v].w += d.w;
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int q = 0; q < RPI; ++q) {
+            if (!ok[q]) continue;              // warp-uniform
+            float ss = 0.f;
+#pragma unroll
+            for (int v = 0; v < VPL; ++v) {
+                const int vi = lane + 32 * v;
+                if (vi < nvec) {
+                    if (p.delta) *reinterpret_cast<float4*>(p.res + (size_t)rr[q] * p.D + 4 * vi) = x[q][v];
+                    ss += x[q][v].x * x[q][v].x + x[q][v].y * x[q][v].y + x[q][v].z * x[q][v].z + x[q][v].w * x[q][v].w;
+                }
+            }
+            if (p.y == nullptr) continue;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+            const float rstd = 1.f / sqrtf(ss / (float)p.D + p.eps);
+            const size_t yrow = (size_t)(p.y_at_r ? rr[q] : base + q) * p.D;
+#pragma unroll
+            for (int v = 0; v < VPL; ++v) {
+                const int vi = lane + 32 * v;
+                if (vi < nvec)
+                    store4_from_float(p.y, yrow + 4 * vi, p.y_dt,
+                                      make_float4(x[q][v].x * rstd * wv[v].x, x[q][v].y * rstd * wv[v].y,
+                                                  x[q][v].z * rstd * wv[v].z, x[q][v].w * rstd * wv[v].w));
+            }
+        }
+    }
+}
+
 }  // namespace lampa
 
 using namespace lampa;
@@ -553,5 +668,28 @@ extern "C" int lampa_rmsnorm_gate(const void* x, const void* g, const void* weig
     else if (dtype == LAMPA_F16) LAMPA_NORM(LAMPA_F16);
     else LAMPA_NORM(LAMPA_F32);
 #undef LAMPA_NORM
+    return cudaGetLastError() == cudaSuccess ? LAMPA_OK : LAMPA_ERR_CUDA;
+}
+
+extern "C" int lampa_add_rmsnorm(float* res, const void* delta, int32_t delta_dtype, const int64_t* perm,
+                                 const int64_t* seg_offsets, int32_t nseg, int64_t rows, int32_t D,
+                                 const float* weight, float eps, int32_t delta_at_r, int32_t y_at_r, void* y,
+                                 int32_t y_dtype, int32_t* status, void* stream) {
+    if (rows < 0 || D <= 0 || nseg <= 0) return LAMPA_ERR_ARG;
+    if (D % 4 != 0 || D > 1024) return LAMPA_ERR_UNSUPPORTED;
+    if (rows == 0) return LAMPA_OK;
+    if (!res || (!delta && !y)) return LAMPA_ERR_ARG;
+    if ((delta && !dt_ok(delta_dtype)) || (y && !dt_ok(y_dtype))) return LAMPA_ERR_ARG;
+    if (perm && !seg_offsets && rows % nseg != 0) return LAMPA_ERR_ARG;
+    if ((((uintptr_t)res | (uintptr_t)delta | (uintptr_t)y | (uintptr_t)weight) & 15)) return LAMPA_ERR_ARG;
+    AddNormArgs p{res, delta, delta_dtype, perm, seg_offsets, nseg, rows, D, weight, eps, delta_at_r, y_at_r, y, y_dtype, status};
+    cudaStream_t st = (cudaStream_t)stream;
+    const unsigned grid = (unsigned)std::min<int64_t>((rows + 31) / 32, 148 * 16);
+    const int vpl = (D / 4 + 31) / 32;
+    ProfScope prof("add_rmsnorm", st);
+    if (vpl == 1) add_rmsnorm_kernel<1><<<grid, 256, 0, st>>>(p);
+    else if (vpl == 2) add_rmsnorm_kernel<2><<<grid, 256, 0, st>>>(p);
+    else if (vpl <= 4) add_rmsnorm_kernel<4><<<grid, 256, 0, st>>>(p);
+    else add_rmsnorm_kernel<8><<<grid, 256, 0, st>>>(p);
     return cudaGetLastError() == cudaSuccess ? LAMPA_OK : LAMPA_ERR_CUDA;
 }

@@ -175,6 +175,43 @@ def rms_norm_gated(x: torch.Tensor, g: torch.Tensor, weight: Optional[torch.Tens
     return y
 
 
+@torch.no_grad()
+def add_rms_norm(res: torch.Tensor, delta: Optional[torch.Tensor], weight: Optional[torch.Tensor], eps: float = 1e-6,
+                 perm: Optional[torch.Tensor] = None, seg_offsets: Optional[torch.Tensor] = None, nseg: int = 1,
+                 delta_at_r: bool = False, y_at_r: bool = False, out_dtype: Optional[torch.dtype] = torch.bfloat16):
+    """Fused residual add + RMS norm (+ row permutation) on an fp32 residual stream `res` [rows, D],
+    in place: the `RMSNorm(x, residual, prenorm=True)` of the reference's blocks
+    (models/hattention/fused_norm.py:1288-1330, modeling_gated_deltaproduct.py:1169-1199) with the
+    ordering layer's gather / un-gather (models/baselines/hmamba.py:428-455) folded in.
+
+    For every j: r = perm[j] inside j's segment (r = j without perm);
+    res[r] += delta[r if delta_at_r else j]; y[r if y_at_r else j] = rms_norm(res[r]) * weight.
+    delta None: norm only.  out_dtype None: add only (returns None)."""
+    dev = L.require_cuda(res, delta, weight, perm)
+    if res.dtype != torch.float32 or not res.is_contiguous() or res.dim() != 2:
+        raise ValueError("res must be a contiguous fp32 [rows, D] tensor (updated in place)")
+    rows, D = res.shape
+    if delta is not None:
+        delta = delta.contiguous()
+        if tuple(delta.shape) != (rows, D):
+            raise ValueError("delta must match res")
+    if perm is not None:
+        perm = perm.to(torch.int64).contiguous().view(-1)
+        if perm.numel() != rows:
+            raise ValueError("perm must have one entry per row")
+    if seg_offsets is not None:
+        seg_offsets = seg_offsets.to(device=dev, dtype=torch.int64).contiguous()
+        nseg = seg_offsets.numel() - 1
+    w = None if weight is None else weight.detach().to(torch.float32).contiguous()
+    y = None if out_dtype is None else torch.empty(rows, D, dtype=out_dtype, device=dev)
+    rc = L.lib().lampa_add_rmsnorm(L.ptr(res), L.ptr(delta), L.dtype_code(delta.dtype) if delta is not None else 0,
+                                   L.ptr(perm), L.ptr(seg_offsets), max(int(nseg), 1), rows, D, L.ptr(w), float(eps),
+                                   int(delta_at_r), int(y_at_r), L.ptr(y), L.dtype_code(out_dtype) if y is not None else 0,
+                                   L.ptr(L.status_word(dev)), L.stream_ptr(dev))
+    L.check(rc, "lampa_add_rmsnorm")
+    return y
+
+
 class FusedRMSNormGated(nn.Module):
     """RMS norm over the last axis followed by a swish (or sigmoid) gate (fused_norm.py:1003-1064)."""
 

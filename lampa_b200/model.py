@@ -26,7 +26,7 @@ import torch.nn.functional as F
 
 from . import sharding
 from .gated_delta import chunk_h_gated_delta_rule, num_levels_required
-from .layer import FusedRMSNormGated, ShortConvolution, gate_inputs
+from .layer import FusedRMSNormGated, ShortConvolution, add_rms_norm, gate_inputs
 from .lsh import lsh_hash, permute_rows, segmented_sort
 
 
@@ -115,14 +115,31 @@ class LSHGatedDeltaBlock(nn.Module):
         self.mlp_down = nn.Linear(mlp_ratio * dim, dim, device=device, dtype=dtype)
 
     @torch.no_grad()
-    def forward(self, x: torch.Tensor, perm: torch.Tensor, cu: torch.Tensor) -> torch.Tensor:
+    def mix(self, x: torch.Tensor, hs: torch.Tensor, perm: torch.Tensor, cu: torch.Tensor,
+            next_norm_weight: Optional[torch.Tensor] = None, next_perm: Optional[torch.Tensor] = None):
+        """One block on the residual stream `x` (fp32 [n, d], updated in place).  `hs` is this block's
+        normed input already in the block's order (bf16).  Returns the next block's normed, ordered
+        input when its norm weight and permutation are given (the last residual add then also
+        applies that norm and ordering, in one pass), else None."""
         n, d = x.shape
-        h = F.rms_norm(x, (d,), self.attn_norm_weight, self.eps).to(self.dtype)
-        hs = permute_rows(h, perm, seg_offsets=cu)
         o = self.attn(hs.view(1, n, d), cu_seqlens=cu).view(n, d)
-        x = x + permute_rows(o, perm, seg_offsets=cu, scatter=True).float()
-        h = F.rms_norm(x, (d,), self.mlp_norm_weight, self.eps).to(self.dtype)
-        return x + self.mlp_down(F.gelu(self.mlp_up(h))).float()
+        # x += un-ordered mixer output; h = norm(x) in hit order for the MLP: one pass
+        h = add_rms_norm(x, o, self.mlp_norm_weight, self.eps, perm=perm, seg_offsets=cu, y_at_r=True, out_dtype=self.dtype)
+        y = self.mlp_down(F.gelu(self.mlp_up(h)))
+        if next_norm_weight is None:
+            add_rms_norm(x, y, None, self.eps, out_dtype=None)
+            return None
+        # x += MLP output; next block's input = norm(x), gathered into that block's order: one pass
+        return add_rms_norm(x, y, next_norm_weight, self.eps, perm=next_perm, seg_offsets=cu, delta_at_r=True,
+                            out_dtype=self.dtype)
+
+    @torch.no_grad()
+    def forward(self, x: torch.Tensor, perm: torch.Tensor, cu: torch.Tensor) -> torch.Tensor:
+        """The block alone: returns the new residual stream (the input is not modified)."""
+        x = x.clone()
+        hs = add_rms_norm(x, None, self.attn_norm_weight, self.eps, perm=perm, seg_offsets=cu, out_dtype=self.dtype)
+        self.mix(x, hs, perm, cu)
+        return x
 
 
 class LSHGatedDelta(nn.Module):
@@ -170,8 +187,13 @@ class LSHGatedDelta(nn.Module):
         cu = cu_seqlens.to(device=hits.device, dtype=torch.int64)
         perms = self.orderings(hits, cu)
         x = self.encoder(hits * self.feature_scale)
+        nb = len(self.blocks)
+        hs = add_rms_norm(x, None, self.blocks[0].attn_norm_weight, self.blocks[0].eps, perm=perms[0], seg_offsets=cu,
+                          out_dtype=self.blocks[0].dtype) if nb else None
         for b, blk in enumerate(self.blocks):
-            x = blk(x, perms[b % self.rounds], cu)
+            nxt = self.blocks[b + 1] if b + 1 < nb else None
+            hs = blk.mix(x, hs, perms[b % self.rounds], cu,
+                         None if nxt is None else nxt.attn_norm_weight, None if nxt is None else perms[(b + 1) % self.rounds])
         return self.head(x)
 
     def check_event_sizes(self, lengths: Sequence[int]) -> None:

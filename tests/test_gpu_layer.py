@@ -156,3 +156,45 @@ def test_layer_chain_feeds_the_mixer(lb):
     yref = oracle.rmsnorm_gate(oref, to_np(gate[0].float()), None, 1e-5)
     err = np.linalg.norm(to_np(y[0].float()) - yref) / np.linalg.norm(yref)
     assert err < 2e-2, err
+
+
+@pytest.mark.parametrize("D,dt", [(128, torch.bfloat16), (96, torch.float16), (256, torch.float32), (520, torch.bfloat16)])
+def test_add_rms_norm_with_and_without_permutation(lb, D, dt):
+    """Fused residual add + RMS norm + row permutation against the plain statements
+    (rms_norm_ref of models/hattention/fused_norm.py:1313-1330 with residual, prenorm=True)."""
+    gen = torch.Generator().manual_seed(D)
+    lens = [37, 0, 64, 211]
+    rows = sum(lens)
+    cu = torch.tensor([0] + lens).cumsum(0)
+    res = torch.randn(rows, D, generator=gen)
+    delta = torch.randn(rows, D, generator=gen).to(dt)
+    w = torch.rand(D, generator=gen) + 0.5
+    perm = torch.cat([torch.randperm(n, generator=gen) for n in lens])           # local to each segment
+    glob = torch.cat([perm[cu[i]:cu[i + 1]] + cu[i] for i in range(len(lens))])   # r for every j
+
+    def norm(v):
+        return v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + 1e-6) * w
+
+    tol = 1e-5 if dt == torch.float32 else 8e-3
+    # norm only, gathered: y[j] = norm(res[r])
+    r0 = res.clone().cuda()
+    y = lb.add_rms_norm(r0, None, w.cuda(), 1e-6, perm=perm.cuda(), seg_offsets=cu, out_dtype=dt)
+    assert torch.equal(r0.cpu(), res)
+    torch.testing.assert_close(y.float().cpu(), norm(res[glob]).to(dt).float(), rtol=tol, atol=tol)
+    # delta in the other order, result in row order: res[r] += delta[j]; y[r] = norm(res[r])
+    r1 = res.clone().cuda()
+    y = lb.add_rms_norm(r1, delta.cuda(), w.cuda(), 1e-6, perm=perm.cuda(), seg_offsets=cu, y_at_r=True, out_dtype=dt)
+    want = res.clone()
+    want[glob] += delta.float()
+    torch.testing.assert_close(r1.cpu(), want, rtol=1e-6, atol=1e-6)
+    torch.testing.assert_close(y.float().cpu(), norm(want).to(dt).float(), rtol=tol, atol=tol)
+    # delta in row order, result gathered: res[r] += delta[r]; y[j] = norm(res[r])
+    r2 = res.clone().cuda()
+    y = lb.add_rms_norm(r2, delta.cuda(), w.cuda(), 1e-6, perm=perm.cuda(), seg_offsets=cu, delta_at_r=True, out_dtype=dt)
+    want = res + delta.float()
+    torch.testing.assert_close(r2.cpu(), want, rtol=1e-6, atol=1e-6)
+    torch.testing.assert_close(y.float().cpu(), norm(want)[glob].to(dt).float(), rtol=tol, atol=tol)
+    # add only, no permutation
+    r3 = res.clone().cuda()
+    assert lb.add_rms_norm(r3, delta.cuda(), None, out_dtype=None) is None
+    torch.testing.assert_close(r3.cpu(), want, rtol=1e-6, atol=1e-6)
