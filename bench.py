@@ -485,7 +485,7 @@ def model_measure(ms_, dev, rank, world, steps, warmup, e2e=True, profile=True):
     model, cu, lengths, plan = ms_["model"], ms_["cu"], ms_["lengths"], ms_["plan"]
     hits_dev = ms_["hits_host"].to(dev)
     total_hits = int(sum(lengths))
-    side = torch.cuda.Stream(dev)
+    side = torch.cuda.Stream(dev, priority=-1)      # the gather's copies and NCCL kernels go ahead of the next step's launches
     gather_us = []
 
     def barrier():

@@ -395,8 +395,9 @@ int lampa_debug_set_poll_budget(int polls);
 /*
  * Tuning hook (no counterpart in the reference): with a device buffer of n_ctas x 16 int64, thread 0
  * of the first n_ctas CTAs of the tcgen05 preparation kernel stores clock64() at its stage boundaries
- * (slot 0 = start).  n_ctas = 0 switches it off (the default).  Process-wide; the buffer must stay
- * allocated while it is set.
+ * (slots 0..10, slot 0 = start), the SM it ran on (slot 11) and the global nanosecond timer at its start
+ * and end (slots 12, 13).  n_ctas = 0 switches it off (the default).  Process-wide; the buffer must
+ * stay allocated while it is set.
  */
 int lampa_debug_set_tick_buffer(long long* ticks, int n_ctas);
 
