@@ -397,8 +397,17 @@ def run_ours(args):
         dom = max(per_kernel, key=lambda n: per_kernel[n]["ms_per_step"])
         n_chunks = T_PAD // 64
         n_lev = max(1, (n_chunks - 1).bit_length())
-        alg = {   # algorithmic cost of one launch of each kernel on this workload
-            "gdn_prep_hier": ("tensor", H * n_chunks * (7 * 524288 + 2 * 174763)),
+        import ctypes
+        lay = (ctypes.c_size_t * 12)()
+        desc = L.GdnDesc(B=1, T=T_PAD, H=H, K=K, V=V, L=LEVELS, nseq=0, qkv_dtype=L.LAMPA_BF16, gb_dtype=L.LAMPA_F32,
+                         lam_dtype=L.LAMPA_BF16, use_l2norm=1, scale=1.0)
+        L.check(L.lib().lampa_gdn_workspace_layout(ctypes.byref(desc), lay), "lampa_gdn_workspace_layout")
+        rec_bytes = int(lay[1])    # one (chunk, head) record: four 8 KB bf16 tiles + the chunk-level lambda rows, 1024-aligned
+        in_bytes = H * (2 * K + V) * 2 + 2 * H * 4 + H * LEVELS * 2     # q, k, v bf16 + g, beta fp32 + lambda bf16 per token
+        alg = {   # cost of one launch of each kernel on this workload against the roofline that bounds it
+            # preparation: 57 flop per byte moved, far below the ridge (~250): HBM-bound.  Bytes = the inputs it must
+            # read + the records this design makes it write (its compulsory traffic; the records are intermediates)
+            "gdn_prep_hier": ("hbm", T_PAD * in_bytes + H * n_chunks * rec_bytes),
             "gdn_out_hier": ("tensor", H * n_chunks * (n_lev * 2.5 * 524288)),
             "gdn_out_hier_umma": ("tensor", H * n_chunks * (n_lev * 2.5 * 524288)),
             "gdn_compose": ("tensor", H * n_chunks * 2 * 2 * 64 ** 3),
@@ -432,6 +441,10 @@ def run_ours(args):
             "roofline": {"kernel": dom, "bound": bound, "achieved": achieved, "peak": peak, "unit": unit,
                          "frac": achieved / peak,
                          "traffic": ncu_traffic.get(dom), "peak_source": pk["source"],
+                         "note": ("bytes = inputs read (%d B/token) + records written (%d B per chunk-head); inputs alone: %.0f GB/s; "
+                                  "as dense flops (SURVEY 8d, 4.02 MFLOP per chunk-head): %.0f TFLOP/s"
+                                  % (in_bytes, rec_bytes, T_PAD * in_bytes / dur_s / 1e9,
+                                     H * n_chunks * (7 * 524288 + 2 * 174763) / dur_s / 1e12)) if dom == "gdn_prep_hier" else None,
                          "whole_step_hbm_gbs": N_HITS * 4432 / (ms / args.steps * 1e-3) / 1e9},
             "kernels": per_kernel,
             "single_stream": {"value": world * N_HITS * args.steps / (ms_single * 1e-3), "unit": "hits/s",
