@@ -17,7 +17,7 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-def _sort_both(L, keys, nseg=None, seg=None, init=None):
+def _sort_both(L, keys, nseg=None, seg=None, init=None, check_free=False):
     dev = keys.device
     lib = L.lib()
     n = keys.numel()
@@ -33,12 +33,19 @@ def _sort_both(L, keys, nseg=None, seg=None, init=None):
                                   ws.numel(), L.ptr(st), stream)
     assert rc == 0
     got = torch.full((n,), -1, dtype=torch.int64, device=dev)
+    torch.cuda.synchronize()
     before = torch.cuda.memory_allocated(dev)
+    free_before = torch.cuda.mem_get_info(dev)[0]
     rc = lib.lampa_segsort_stable_static(L.ptr(keys), kt, n, L.ptr(seg), nseg, L.ptr(init), L.ptr(got),
                                          L.ptr(st), stream)
     assert rc == 0, lib.lampa_error_string(rc)
     assert torch.cuda.memory_allocated(dev) == before      # nothing was taken from torch's allocator either
     torch.cuda.synchronize()
+    if check_free:
+        # the driver's own count of free device memory: it sees a cudaMalloc made inside the library, which
+        # torch's counter cannot.  Only meaningful once the library's module image is resident (any call
+        # after the first); device allocations come in 2 MiB granules.
+        assert free_before - torch.cuda.mem_get_info(dev)[0] < (2 << 20)
     return got, want
 
 
@@ -61,10 +68,10 @@ def test_static_sort_matches_workspace_sort_on_two_calls_in_a_row():
     seg = torch.tensor([0, 1, 1, 4097, 30000, 50000], dtype=torch.int64, device=dev)
     lens = (seg[1:] - seg[:-1]).tolist()
     init = torch.cat([torch.from_numpy(rng.permutation(n).astype(np.int64)) for n in lens]).to(dev)
-    got, want = _sort_both(L, f, seg=seg, init=init)
+    got, want = _sort_both(L, f, seg=seg, init=init, check_free=True)
     assert torch.equal(got, want)
     # and once more with the first input: same answer as before
-    got2, want2 = _sort_both(L, k1.view(-1), nseg=24)
+    got2, want2 = _sort_both(L, k1.view(-1), nseg=24, check_free=True)
     assert torch.equal(got2, want2)
     L.check_status(dev)
 
