@@ -278,13 +278,18 @@ __global__ void __launch_bounds__(UTHREADS, 1) gdn_out_hier_umma_kernel(GdnArgs 
                 if (lane == 0) mbar_arrive(dfree + p);
             }
             // output: sum the two rows (levels) of the pairs through shared memory, add O_local, store.
-            // The transpose buffer alternates with the chunk, so one barrier per chunk is enough: a warp
-            // that runs ahead writes the other buffer, and it cannot get two chunks ahead of a warp that
-            // is still reading without passing the barrier in between.
+            // Tokens 16 wg .. 16 wg + 15 of the tile are written and read by warpgroup wg alone, so the barrier is the
+            // warpgroup's own.  The buffer alternates with the chunk: a warp that runs ahead writes the other buffer, and
+            // it cannot get two chunks ahead of a warp of its group that is still reading without passing that barrier.
             float* sOTc = sOT + (i & 1) * (2 * 64 * 64);
 #pragma unroll
             for (int j = 0; j < 16; ++j) sOTc[(u * 64 + 16 * part + j) * 64 + v] = oacc[j];
-            asm volatile("bar.sync 1, 512;\n" ::: "memory");
+            switch (wg) {
+                case 0: asm volatile("bar.sync 1, 128;\n" ::: "memory"); break;
+                case 1: asm volatile("bar.sync 2, 128;\n" ::: "memory"); break;
+                case 2: asm volatile("bar.sync 3, 128;\n" ::: "memory"); break;
+                default: asm volatile("bar.sync 4, 128;\n" ::: "memory"); break;
+            }
             {
                 const int tok = tid >> 3, col = (tid & 7) * 8;
                 const int64_t t_out = tok0 + (int64_t)i * CHUNK + tok;
