@@ -393,6 +393,12 @@ int lampa_profile_read(char* names, size_t names_cap, float* total_ms, int32_t* 
  */
 int lampa_debug_set_poll_budget(int polls);
 /*
+ * Test hook (no counterpart in the reference): on = 1 routes the K = V = 64 gated-delta calls that follow to the
+ * mma.sync kernels instead of the tcgen05 ones (what LAMPA_B200_NO_UMMA=1 does for a whole process), on = 0 back;
+ * lets a test compare the two tensor-core paths on the same input.  Process-wide; not for concurrent use.
+ */
+int lampa_debug_force_mma_sync(int on);
+/*
  * Tuning hook (no counterpart in the reference): with a device buffer of n_ctas x 16 int64, thread 0
  * of the first n_ctas CTAs of the tcgen05 preparation kernel stores clock64() at its stage boundaries
  * (slots 0..10, slot 0 = start), the SM it ran on (slot 11) and the global nanosecond timer at its start

@@ -41,7 +41,8 @@ EXPORTS = ["lampa_version", "lampa_error_string", "lampa_gdn_workspace_bytes", "
            "lampa_row_range", "lampa_quantile_regions", "lampa_geo_keys",
            "lampa_bucket_rbf_attn", "lampa_bucket_attn_combine", "lampa_hept_prep_qk",
            "lampa_profile_enable",
-           "lampa_profile_read", "lampa_debug_set_poll_budget", "lampa_debug_set_tick_buffer"]
+           "lampa_profile_read", "lampa_debug_set_poll_budget", "lampa_debug_set_tick_buffer",
+           "lampa_debug_force_mma_sync"]
 
 
 def lib() -> ctypes.CDLL:
@@ -80,6 +81,7 @@ def lib() -> ctypes.CDLL:
         L.lampa_add_rmsnorm.argtypes = [vp, vp, i32, vp, vp, i32, i64, i32, vp, ctypes.c_float, i32, i32, vp, i32, vp, vp]
         L.lampa_profile_enable.argtypes = [ctypes.c_int]
         L.lampa_debug_set_poll_budget.argtypes = [ctypes.c_int]
+        L.lampa_debug_force_mma_sync.argtypes = [ctypes.c_int]
         L.lampa_debug_set_tick_buffer.argtypes = [vp, ctypes.c_int]
         L.lampa_profile_read.argtypes = [ctypes.c_char_p, sz, ctypes.POINTER(ctypes.c_float),
                                          ctypes.POINTER(i32), i32, ctypes.POINTER(i32)]

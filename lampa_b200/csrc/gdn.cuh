@@ -68,6 +68,7 @@ struct GdnArgs {
     int nseq;
     int fixed_T;        // tokens per sequence when there is no cu_seqlens (0 otherwise)
     int fixed_cps;      // chunks per sequence in that case: positions follow by arithmetic, no plan loads
+    int plan_inline;    // no cu_seqlens: the first preparation CTA writes the offset tables below (no separate launch)
     int nc_max, nb_max, nhigh_max;
     long long total_tokens;  // B * T of the call (rows of the token-major inputs)
     const int64_t* tok_off; const int32_t* chunk_off; const int32_t* block_off;
@@ -83,6 +84,17 @@ struct GdnArgs {
 // Stage clock of a preparation CTA: thread 0 of the first `ticks_ctas` CTAs stores clock64() in its slot.
 __device__ __forceinline__ void stage_tick(const GdnArgs& a, int cta, int slot) {
     if (a.ticks != nullptr && threadIdx.x == 0 && cta < a.ticks_ctas) a.ticks[(size_t)cta * 16 + slot] = clock64();
+}
+
+// Offset tables of equally long sequences, written by the first CTA of the preparation kernel for the passes that
+// follow it (the preparation kernel itself locates its chunks by arithmetic in that case).
+__device__ __forceinline__ void write_fixed_plan(const GdnArgs& a) {
+    const int bps = (a.fixed_cps + BLOCK_CHUNKS - 1) / BLOCK_CHUNKS;
+    for (int s = threadIdx.x; s <= a.nseq; s += blockDim.x) {
+        const_cast<int64_t*>(a.tok_off)[s] = (int64_t)s * a.fixed_T;
+        const_cast<int32_t*>(a.chunk_off)[s] = s * a.fixed_cps;
+        const_cast<int32_t*>(a.block_off)[s] = s * bps;
+    }
 }
 
 struct PlanArgs {
@@ -121,6 +133,7 @@ __device__ __forceinline__ void store_out2(void* o, int dt, size_t idx, float x,
 }
 
 int launch_out_hier_umma(const GdnArgs& a, cudaStream_t st);
+int launch_out_plain_umma(const GdnArgs& a, cudaStream_t st);  // K = V = 64
 int launch_prep_umma(const GdnArgs& a, bool hier, cudaStream_t st);   // K = V = 64, 2-byte q/k/v
 template <int KD, int VD> int launch_final_high(const GdnArgs& a, float* states, cudaStream_t st);
 template <int KD, int VD> int launch_final_low(const GdnArgs& a, float* states, int32_t* counts, cudaStream_t st);

@@ -9,6 +9,7 @@ namespace {
 inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
 int g_poll_budget = MBAR_POLLS;   // see lampa_debug_set_poll_budget
+int g_force_mma_sync = 0;         // see lampa_debug_force_mma_sync
 long long* g_ticks = nullptr;     // see lampa_debug_set_tick_buffer
 int g_ticks_ctas = 0;
 
@@ -79,6 +80,7 @@ void fill_args(const lampa_gdn_desc* d, bool hier, const Layout& l, char* base, 
     a.use_l2norm = d->use_l2norm; a.scale = d->scale;
     a.fixed_T = cu ? 0 : d->T;
     a.fixed_cps = cu ? 0 : (d->T + CHUNK - 1) / CHUNK;
+    a.plan_inline = 0;
     a.total_tokens = (long long)d->B * d->T;
     a.nseq = l.nseq; a.nc_max = l.nc_max; a.nb_max = l.nb_max; a.nhigh_max = l.nhigh_max;
     a.tok_off = (int64_t*)(base + l.off_tok);
@@ -89,7 +91,7 @@ void fill_args(const lampa_gdn_desc* d, bool hier, const Layout& l, char* base, 
     a.entry = (float*)(base + l.off_entry);
     a.status = status;
     static const int no_umma = [] { const char* e = getenv("LAMPA_B200_NO_UMMA"); return (e && e[0] == '1') ? 1 : 0; }();
-    a.use_umma = no_umma ? 0 : 1;
+    a.use_umma = (no_umma || g_force_mma_sync) ? 0 : 1;
     a.poll_budget = g_poll_budget;
     a.ticks = g_ticks;
     a.ticks_ctas = g_ticks_ctas;
@@ -121,8 +123,12 @@ int run(const lampa_gdn_desc* d, bool hier, const void* q, const void* k, const 
     p.chunk_off = (int32_t*)a.chunk_off;
     p.block_off = (int32_t*)a.block_off;
     p.status = status;
-    rc = launch_plan(p, st);
-    if (rc != LAMPA_OK) return rc;
+    if (cu) {
+        rc = launch_plan(p, st);
+        if (rc != LAMPA_OK) return rc;
+    } else {
+        a.plan_inline = 1;         // equally long sequences: the preparation kernel writes the tables itself
+    }
 
 #define LAMPA_DISPATCH(KD, VD)                                         \
     do {                                                               \
@@ -149,6 +155,11 @@ extern "C" int lampa_debug_set_tick_buffer(long long* ticks, int n_ctas) {
     if (n_ctas < 0 || (n_ctas > 0 && !ticks)) return LAMPA_ERR_ARG;
     g_ticks = n_ctas > 0 ? ticks : nullptr;
     g_ticks_ctas = n_ctas;
+    return LAMPA_OK;
+}
+
+extern "C" int lampa_debug_force_mma_sync(int on) {
+    g_force_mma_sync = on ? 1 : 0;
     return LAMPA_OK;
 }
 

@@ -83,6 +83,7 @@ __global__ void __launch_bounds__(128, 4) gdn_prep_kernel(GdnArgs a) {
     // whole contiguous token rows of q, k, v (one head alone touches 128 B out of every H*128 B)
     const int h = blockIdx.x, c = blockIdx.y, H = a.H;
     ChunkLoc loc;
+    if (a.plan_inline && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) write_fixed_plan(a);
     if (!locate_chunk(a, c, loc)) return;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int gq = lane >> 2, tq = lane & 3;

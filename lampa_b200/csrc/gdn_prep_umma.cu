@@ -73,7 +73,8 @@ __device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap* map, int32_t 
 }
 // tensor-memory columns (256 allocated): three 64-column accumulators and two 32-column A operands
 constexpr int T0 = 0, T1 = 64, T2 = 128, TA_P = 192, TA_R = 224;
-enum { B_KK = 0, B_QK, B_R, B_W, B_U, B_M, B_B, B_RK, B_PV, B_DRAIN, B_IN, NBAR };
+// one mbarrier per group of products issued together (commits complete in issue order, so the group's last one covers it)
+enum { B_G1 = 0, B_G2, B_G3, B_RK, B_PV, B_DRAIN, B_IN, NBAR };
 
 constexpr uint32_t ID_KK = umma_idesc(64, 64, 0, 0);   // A, B K-major
 constexpr uint32_t ID_KN = umma_idesc(64, 64, 0, 1);   // A K-major (shared or tensor memory), B MN-major
@@ -135,6 +136,7 @@ __global__ void __launch_bounds__(8192 / NC, 2) gdn_prep_umma_kernel(GdnArgs a, 
         return sLam[(sb * CHUNK + r) * (a.L + 1) + lev];
     };
     ChunkLoc loc;
+    if (a.plan_inline && blockIdx.x == 0 && blockIdx.y == 0) write_fixed_plan(a);
     if (!locate_chunk(a, c, loc)) return;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int64_t t0 = loc.t0;
@@ -291,10 +293,9 @@ __global__ void __launch_bounds__(8192 / NC, 2) gdn_prep_umma_kernel(GdnArgs a, 
         const uint64_t dK = umma_desc_k128(sK + isub * TILE), dQ = umma_desc_k128(sQ + isub * TILE);
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk) umma_f16_ss(dsub + T0, desc_adv(dK, kk * 32), desc_adv(dK, kk * 32), ID_KK, kk > 0);
-        umma_commit(bars + B_KK);
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk) umma_f16_ss(dsub + T1, desc_adv(dQ, kk * 32), desc_adv(dK, kk * 32), ID_KK, kk > 0);
-        umma_commit(bars + B_QK);
+        umma_commit(bars + B_G1);
     }
     __syncwarp();
 
@@ -306,7 +307,7 @@ __global__ void __launch_bounds__(8192 / NC, 2) gdn_prep_umma_kernel(GdnArgs a, 
 
     stage_tick(a, cta, 2);
     // A0 = tril(diag(beta) K K^T, -1) as fp32 into the inverse's tile
-    mbar_wait(bars + B_KK, 0u, dead, a.status, 600, budget);
+    mbar_wait(bars + B_G1, 0u, dead, a.status, 600, budget);
     tc_fence_after();
     tmem_ld_n<NC>(x, tlane + T0 + col0);
     {
@@ -320,8 +321,6 @@ __global__ void __launch_bounds__(8192 / NC, 2) gdn_prep_umma_kernel(GdnArgs a, 
         }
     }
     // P = tril(Q K^T) as the bf16 A operand of product 3
-    mbar_wait(bars + B_QK, 0u, dead, a.status, 601, budget);
-    tc_fence_after();
     tmem_ld_n<NC>(x, tlane + T1 + col0);
 #pragma unroll
     for (int jj = 0; jj < NC; ++jj)
@@ -366,24 +365,20 @@ __global__ void __launch_bounds__(8192 / NC, 2) gdn_prep_umma_kernel(GdnArgs a, 
         const uint64_t dKN = umma_desc_mn128(sK + isub * TILE), dVN = umma_desc_mn128(sV + isub * TILE);
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk) umma_f16_ts(dsub + T0, dsub + TA_P + 8 * kk, desc_adv(dAwbN, kk * 2048), ID_KN, kk > 0);
-        umma_commit(bars + B_R);
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk) umma_f16_ss(dsub + T1, desc_adv(dAwbK, kk * 32), desc_adv(dKN, kk * 2048), ID_KN, kk > 0);
-        umma_commit(bars + B_W);
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk) umma_f16_ss(dsub + T2, desc_adv(dAwsK, kk * 32), desc_adv(dVN, kk * 2048), ID_KN, kk > 0);
-        umma_commit(bars + B_U);
+        umma_commit(bars + B_G2);
     }
     __syncwarp();
 
     // W and U^ back to shared memory (over Awb and its scaled copy: every product that read them is complete)
-    mbar_wait(bars + B_W, 0u, dead, a.status, 602, budget);
+    mbar_wait(bars + B_G2, 0u, dead, a.status, 602, budget);
     tc_fence_after();
     tmem_ld_n<NC>(x, tlane + T1 + col0);
     pack_n<NC>(x, w);
     store_cols_swz<NC>(smem + S_X + sub * TILE, i, col0 / 8, w);
-    mbar_wait(bars + B_U, 0u, dead, a.status, 603, budget);
-    tc_fence_after();
     tmem_ld_n<NC>(x, tlane + T2 + col0);
     pack_n<NC>(x, w);
     store_cols_swz<NC>(smem + S_X + 2 * TILE + sub * TILE, i, col0 / 8, w);
@@ -399,10 +394,9 @@ __global__ void __launch_bounds__(8192 / NC, 2) gdn_prep_umma_kernel(GdnArgs a, 
         const uint64_t dUN = umma_desc_mn128(sX + 2 * TILE + isub * TILE);
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk) umma_f16_ss(dsub + T1, desc_adv(dKN, kk * 2048), desc_adv(dWN, kk * 2048), ID_NN, kk > 0);
-        umma_commit(bars + B_M);
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk) umma_f16_ss(dsub + T2, desc_adv(dUN, kk * 2048), desc_adv(dKN, kk * 2048), ID_NN, kk > 0);
-        umma_commit(bars + B_B);
+        umma_commit(bars + B_G3);
     }
     __syncwarp();
 
@@ -461,7 +455,7 @@ __global__ void __launch_bounds__(8192 / NC, 2) gdn_prep_umma_kernel(GdnArgs a, 
     __syncwarp();
 
     // M[a][b] = e^{Gl} (delta_ab - (K^T W)[a][b]) -> record
-    mbar_wait(bars + B_M, 0u, dead, a.status, 604, budget);
+    mbar_wait(bars + B_G3, 0u, dead, a.status, 604, budget);
     tc_fence_after();
     tmem_ld_n<NC>(x, tlane + T1 + col0);
     {
@@ -501,9 +495,7 @@ __global__ void __launch_bounds__(8192 / NC, 2) gdn_prep_umma_kernel(GdnArgs a, 
             }
         }
     }
-    // B^T -> record
-    mbar_wait(bars + B_B, 0u, dead, a.status, 605, budget);
-    tc_fence_after();
+    // B^T -> record (product 7 completed with product 6)
     tmem_ld_n<NC>(x, tlane + T2 + col0);
     pack_n<NC>(x, w);
     store_cols_swz<NC>(smem + S_X + 2 * TILE + sub * TILE, i, col0 / 8, w);   // staged over U^ (product 7 is complete)

@@ -676,6 +676,7 @@ int launch_scan_plain(const GdnArgs& a, cudaStream_t st) {
         gdn_level_kernel<KD, VD, false><<<dim3(a.nseq, a.H, 1), VD * 2, smem, st>>>(a);
         LAMPA_LAUNCHED();
     }
+    if (KD == 64 && VD == 64 && a.use_umma) return launch_out_plain_umma(a, st);
     {
         const int smem = 1024 + 3 * R::LAM_OFF;
         LAMPA_TRY(set_smem(gdn_out_plain_kernel<KD, VD>, smem));

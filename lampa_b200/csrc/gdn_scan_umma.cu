@@ -1,5 +1,5 @@
-// Hierarchical output pass on the 5th-generation tensor cores (tcgen05.mma, accumulators in TMEM)
-// for K = V = 64.
+// Output passes on the 5th-generation tensor cores (tcgen05.mma, accumulators in TMEM) for K = V = 64:
+// the hierarchical rule first, the plain rule (one state per head) at the end of the file.
 //
 // Per (block of 32 chunks, head) one CTA keeps every level state the block touches as rows of
 // bf16 A operands in tensor memory: slot s holds S_l^T (64 rows v x 64 columns k), two slots
@@ -330,6 +330,213 @@ __global__ void __launch_bounds__(UTHREADS, 1) gdn_out_hier_umma_kernel(GdnArgs 
     if (warp == 0) tmem_dealloc(taddr, 512);
 }
 
+
+// -------------------------------------------------------------------------------------------------
+// Plain rule, same machinery with one state per head:  O_n = O_local + Q~ S_n ;  S_{n+1} = M S_n + B.
+// One CTA per (block of 32 chunks, pair of heads).  A head's state S^T (64 rows v x 64 columns k) is the
+// bf16 A operand of an MMA with M = 64, which occupies 16 lanes of each 32-lane quarter of tensor
+// memory: the two heads interleave (head 0 in lanes 0..15 of a quarter, head 1 in lanes 16..31), so one
+// tcgen05.ld hands every thread of the 16 epilogue warps one row segment, thread = (head, state row,
+// 16 columns).  Per chunk and head ONE accumulating MMA  D[64 x 128] = S^T x [M ; Q~]^T  gives the
+// advanced state (columns 0..63) and (Q~ S)^T (columns 64..127).  The chain MMA -> + B^T -> bf16
+// operand -> next MMA is serial by nature (one state), and the pass is bound by streaming the records.
+// O_local is read straight from the record in global memory by the thread that stores the output.
+// -------------------------------------------------------------------------------------------------
+constexpr int PNST = 3;                      // record stages (two heads each)
+constexpr int PSTAGE_HEAD = UR::OL_OFF;      // M | Q~ | B^T of one head
+constexpr int PSTAGE = 2 * PSTAGE_HEAD;
+constexpr int PSM_OT = 1024;                 // two buffers (chunk parity) of fp32 [2 heads][64 tokens][64 v]
+constexpr int PSM_STAGE = PSM_OT + 2 * 2 * 64 * 64 * 4;
+constexpr int PTM_A = 0, PTM_D = 64;         // tensor-memory columns (256 allocated)
+constexpr uint32_t PMMA_IDESC = umma_idesc(64, 128);
+
+__global__ void __launch_bounds__(UTHREADS, 1) gdn_out_plain_umma_kernel(GdnArgs a) {
+    extern __shared__ __align__(1024) unsigned char smem[];
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + SM_BAR);      // records landed            (tx count)
+    uint64_t* sfree = full + PNST;                                      // stage consumed            (16 warps)
+    uint64_t* mdone = sfree + PNST;                                     // chunk's MMAs complete     (commit)
+    uint64_t* aready = mdone + 1;                                       // operands rewritten        (16 warps)
+    uint64_t* drainb = aready + 1;
+    uint32_t* tslot = reinterpret_cast<uint32_t*>(smem + SM_BAR + 256);
+    float* sOT = reinterpret_cast<float*>(smem + PSM_OT);
+
+    const int H = a.H, npair = (H + 1) / 2;
+    const int gb = blockIdx.x / npair, h0 = 2 * (blockIdx.x % npair);
+    if (gb >= a.block_off[a.nseq]) return;
+    const int nheads = min(2, H - h0);
+    const int seq = find_seq(a.block_off, a.nseq, gb);
+    const int b = gb - a.block_off[seq];
+    const int nch = a.chunk_off[seq + 1] - a.chunk_off[seq];
+    const int c0 = a.chunk_off[seq] + b * BLOCK_CHUNKS;
+    const int nsteps = min(BLOCK_CHUNKS, nch - b * BLOCK_CHUNKS);
+    const int64_t tok0 = a.tok_off[seq] + (int64_t)b * BLOCK_CHUNKS * CHUNK, tok_end = a.tok_off[seq + 1];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int sp = warp & 3, cq = (warp >> 2) & 3;     // lane quarter; 16 state columns and 16 tokens
+    const int sub = lane >> 4, v = 16 * sp + (lane & 15);   // head of the pair, state row
+    unsigned char* stage0 = smem + PSM_STAGE;
+    const char* rec0 = a.rec + ((size_t)c0 * H + h0) * a.rec_bytes;
+    const size_t rec_stride = (size_t)H * a.rec_bytes;
+
+    if (tid == 0) {
+#pragma unroll
+        for (int s = 0; s < PNST; ++s) { mbar_init(full + s, 1); mbar_init(sfree + s, UEPI_WARPS); }
+        mbar_init(mdone, 1);
+        mbar_init(aready, UEPI_WARPS);
+        mbar_init(drainb, 1);
+        fence_mbar_init();
+    }
+    if (warp == 0) tmem_alloc(tslot, 256);
+    fence_async_smem();
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t taddr = *tslot;
+    const uint32_t tlane = taddr + ((uint32_t)(32 * sp) << 16);
+    // the block's entry state
+    if (warp < UEPI_WARPS) {
+        float x[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) x[i] = 0.f;
+        if (sub < nheads) {
+            const float4* e = reinterpret_cast<const float4*>(a.entry + ((size_t)gb * H + h0 + sub) * UR::STATE_FLOATS + (size_t)v * UKD + 16 * cq);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float4 f = e[i];
+                x[4 * i] = f.x; x[4 * i + 1] = f.y; x[4 * i + 2] = f.z; x[4 * i + 3] = f.w;
+            }
+        }
+        tmem_st_bf16x16(tlane + PTM_A + 8 * cq, x);
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    bool dead = false;
+    const int budget = a.poll_budget;
+
+    if (warp == UEPI_WARPS) {
+        // ---- control warp: one lane streams records and issues MMAs --------------------------------
+        if (lane == 0) {
+            int loaded = 0, landed = 0;
+            auto load_record = [&](int step) {
+                uint64_t* fb = full + (step % PNST);
+                unsigned char* dst = stage0 + (size_t)(step % PNST) * PSTAGE;
+                const char* src = rec0 + (size_t)step * rec_stride;
+                mbar_expect_tx(fb, (uint32_t)(nheads * PSTAGE_HEAD));
+                for (int hd = 0; hd < nheads; ++hd) bulk_g2s(dst + hd * PSTAGE_HEAD, src + (size_t)hd * a.rec_bytes, (uint32_t)PSTAGE_HEAD, fb);
+                loaded = step + 1;
+            };
+            for (int s = 0; s < PNST - 1 && s < nsteps; ++s) load_record(s);
+            for (int i = 0; i < nsteps && !dead; ++i) {
+                const unsigned char* st = stage0 + (size_t)(i % PNST) * PSTAGE;
+                if (mbar_wait(full + (i % PNST), (uint32_t)((i / PNST) & 1), dead, a.status, 200 + i, budget)) landed = i + 1;
+                // the operands rewritten by the previous chunk (which also means its accumulators have been read)
+                if (i > 0) mbar_wait(aready, (uint32_t)((i - 1) & 1), dead, a.status, 400, budget);
+                if (dead) break;
+                tc_fence_after();
+                for (int hd = 0; hd < nheads; ++hd) {
+                    const uint32_t dsub = taddr + ((uint32_t)(16 * hd) << 16);
+                    const uint64_t db = umma_desc_k128(smem_u32(st + hd * PSTAGE_HEAD + UR::M_OFF));
+#pragma unroll
+                    for (int kk = 0; kk < 4; ++kk) umma_f16_ts(dsub + PTM_D, dsub + PTM_A + 8 * kk, db + 2 * kk, PMMA_IDESC, kk > 0 ? 1u : 0u);
+                }
+                umma_commit(mdone);
+                if (i + PNST - 1 < nsteps) {       // refill the stage chunk i-1 used, once everyone is done with it
+                    if (i >= 1) mbar_wait(sfree + ((i - 1) % PNST), (uint32_t)(((i - 1) / PNST) & 1), dead, a.status, 500 + i, budget);
+                    if (!dead) load_record(i + PNST - 1);
+                }
+            }
+            // nothing asynchronous may outlive the CTA: records still on their way land first, and one
+            // last commit covers every MMA issued above
+            for (int s = landed; s < loaded; ++s) mbar_drain(full + (s % PNST), (uint32_t)((s / PNST) & 1));
+            umma_commit(drainb);
+            mbar_drain(drainb, 0u);
+        }
+    } else {
+        // ---- epilogue warps: thread = (head sub, state row v, 16 state columns / 16 tokens) ----------
+        const int lt = tid & 127;                      // position in the warpgroup that shares cq
+        const int otok = 16 * cq + (lt >> 3), ocol = (lt & 7) * 8;
+        for (int i = 0; i < nsteps; ++i) {
+            const unsigned char* sBt = stage0 + (size_t)(i % PNST) * PSTAGE + sub * PSTAGE_HEAD + UR::BT_OFF;
+            // this thread's 2 x 8 values of O_local (one per head), from the records in global memory
+            const int64_t t_out = tok0 + (int64_t)i * CHUNK + otok;
+            uint4 ol[2];
+#pragma unroll
+            for (int hd = 0; hd < 2; ++hd) {
+                ol[hd] = make_uint4(0u, 0u, 0u, 0u);
+                if (hd < nheads && t_out < tok_end)
+                    ol[hd] = __ldg(reinterpret_cast<const uint4*>(rec0 + (size_t)i * rec_stride + (size_t)hd * a.rec_bytes + UR::OL_OFF) + UR::TV::off(otok, ocol) / 8);
+            }
+            mbar_wait(full + (i % PNST), (uint32_t)((i / PNST) & 1), dead, a.status, 250 + i, budget);
+            mbar_wait(mdone, (uint32_t)(i & 1), dead, a.status, 300, budget);
+            tc_fence_after();
+            float x[16], y[16];
+            tmem_ld16_issue(y, tlane + PTM_D + 64 + 16 * cq);
+            if (i + 1 < nsteps) tmem_ld16_issue(x, tlane + PTM_D + 16 * cq);
+            tmem_wait_ld();
+            if (i + 1 < nsteps) {                      // S <- M S + B as the next chunk's operand
+                tmem_loaded(x);
+                const uint4 bq0 = *reinterpret_cast<const uint4*>(sBt + v * 128 + (((2 * cq) ^ (v & 7)) << 4));
+                const uint4 bq1 = *reinterpret_cast<const uint4*>(sBt + v * 128 + (((2 * cq + 1) ^ (v & 7)) << 4));
+                const uint32_t bw[8] = {bq0.x, bq0.y, bq0.z, bq0.w, bq1.x, bq1.y, bq1.z, bq1.w};
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    const float2 f = unpack_bf16x2(bw[c]);
+                    x[2 * c] += f.x; x[2 * c + 1] += f.y;
+                }
+                tmem_st_bf16x16(tlane + PTM_A + 8 * cq, x);
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) { mbar_arrive(aready); mbar_arrive(sfree + (i % PNST)); }   // operand rewritten; B^T of this stage read
+            // output: (Q~ S)^T of this row goes through shared memory to the thread that stores the token.  Tokens
+            // 16 cq .. 16 cq + 15 are written and read by the four warps with this cq alone, so the barrier is theirs;
+            // the buffer alternates with the chunk (a warp cannot get two chunks ahead of one that is still reading
+            // without passing that barrier).
+            tmem_loaded(y);
+            float* sOTc = sOT + (i & 1) * (2 * 64 * 64);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) sOTc[(sub * 64 + 16 * cq + j) * 64 + v] = y[j];
+            switch (cq) {
+                case 0: asm volatile("bar.sync 1, 128;\n" ::: "memory"); break;
+                case 1: asm volatile("bar.sync 2, 128;\n" ::: "memory"); break;
+                case 2: asm volatile("bar.sync 3, 128;\n" ::: "memory"); break;
+                default: asm volatile("bar.sync 4, 128;\n" ::: "memory"); break;
+            }
+            if (t_out < tok_end) {
+#pragma unroll
+                for (int hd = 0; hd < 2; ++hd) {
+                    if (hd >= nheads) break;
+                    const size_t idx = ((size_t)t_out * H + h0 + hd) * UVD + ocol;
+                    const uint32_t olw[4] = {ol[hd].x, ol[hd].y, ol[hd].z, ol[hd].w};
+                    float r[8];
+#pragma unroll
+                    for (int q = 0; q < 2; ++q) {
+                        const float4 p0 = *reinterpret_cast<const float4*>(sOTc + (hd * 64 + otok) * 64 + ocol + 4 * q);
+                        const float2 oa = unpack_bf16x2(olw[2 * q]), ob = unpack_bf16x2(olw[2 * q + 1]);
+                        r[4 * q] = p0.x + oa.x; r[4 * q + 1] = p0.y + oa.y; r[4 * q + 2] = p0.z + ob.x; r[4 * q + 3] = p0.w + ob.y;
+                    }
+                    if (a.qkv_dt == LAMPA_F32) {
+                        float4* o4 = reinterpret_cast<float4*>((float*)a.o + idx);
+                        o4[0] = make_float4(r[0], r[1], r[2], r[3]);
+                        o4[1] = make_float4(r[4], r[5], r[6], r[7]);
+                    } else {
+                        uint32_t w[4];
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            if (a.qkv_dt == LAMPA_BF16) w[q] = pack_bf16x2(r[2 * q], r[2 * q + 1]);
+                            else { const __half2 hh = __floats2half2_rn(r[2 * q], r[2 * q + 1]); w[q] = *reinterpret_cast<const uint32_t*>(&hh); }
+                        }
+                        *reinterpret_cast<uint4*>((uint16_t*)a.o + idx) = make_uint4(w[0], w[1], w[2], w[3]);
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(taddr, 256);
+}
+
 }  // namespace
 
 int launch_out_hier_umma(const GdnArgs& a, cudaStream_t st) {
@@ -352,6 +559,15 @@ int launch_out_hier_umma(const GdnArgs& a, cudaStream_t st) {
     }
     ProfScope prof("gdn_out_hier_umma", st);
     gdn_out_hier_umma_kernel<<<dim3((unsigned)a.nb_max * a.H), UTHREADS, smem, st>>>(a, uo);
+    return cudaGetLastError() == cudaSuccess ? LAMPA_OK : LAMPA_ERR_CUDA;
+}
+
+int launch_out_plain_umma(const GdnArgs& a, cudaStream_t st) {
+    const int smem = PSM_STAGE + PNST * PSTAGE;
+    if (cudaFuncSetAttribute(gdn_out_plain_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+        return LAMPA_ERR_CUDA;
+    ProfScope prof("gdn_out_plain_umma", st);
+    gdn_out_plain_umma_kernel<<<dim3((unsigned)a.nb_max * ((a.H + 1) / 2)), UTHREADS, smem, st>>>(a);
     return cudaGetLastError() == cudaSuccess ? LAMPA_OK : LAMPA_ERR_CUDA;
 }
 

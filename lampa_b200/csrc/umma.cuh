@@ -55,14 +55,27 @@ __device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {  
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" :: "r"(taddr), "r"(ncols) : "memory");
 }
 
-// 16 / 32 consecutive fp32 columns of this thread's TMEM lane
-__device__ __forceinline__ void tmem_ld16(float (&x)[16], uint32_t taddr) {
+// 16 / 32 consecutive fp32 columns of this thread's TMEM lane.  The _issue form returns before the data has
+// arrived: several loads can be in flight; tmem_wait_ld() and then tmem_loaded() on each array come before the
+// first use.
+__device__ __forceinline__ void tmem_ld16_issue(float (&x)[16], uint32_t taddr) {
     uint32_t* r = reinterpret_cast<uint32_t*>(x);
     asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];\n"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
                    "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
                  : "r"(taddr));
-    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+}
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
+// Pins the registers of an issued load behind the wait that precedes this call: the compiler may not move a use
+// of x above it (the wait itself names no registers).  Emits no instruction.
+template <int N>
+__device__ __forceinline__ void tmem_loaded(float (&x)[N]) {
+#pragma unroll
+    for (int i = 0; i < N; ++i) asm volatile("" : "+f"(x[i]));
+}
+__device__ __forceinline__ void tmem_ld16(float (&x)[16], uint32_t taddr) {
+    tmem_ld16_issue(x, taddr);
+    tmem_wait_ld();
 }
 __device__ __forceinline__ void tmem_ld32(float (&x)[32], uint32_t taddr) {
     uint32_t* r = reinterpret_cast<uint32_t*>(x);

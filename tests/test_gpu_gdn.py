@@ -336,14 +336,24 @@ def test_packed_events_like_config4(lb):
     assert_close_bf16(to_np(o[0]), _hier_ref(inp, cu=cu), "o hier, packed events, K=V=64")
 
 
-def test_tensor_core_paths_agree(lb, monkeypatch):
-    """The tcgen05 output pass and the mma.sync one (selected by LAMPA_B200_NO_UMMA=1) on the same input."""
-    from lampa_b200 import synth
-    T, H = 8192 + 640, 2
+def test_tensor_core_paths_agree(lb):
+    """The tcgen05 kernels and their mma.sync twins (lampa_debug_force_mma_sync) on the same input: hierarchical
+    and plain rule, preparation and output passes."""
+    from lampa_b200 import _lib as L, synth
+    T, H = 8192 + 640, 3
     inp = _cuda(synth.gdn_inputs(31, T, H, 64, 64, L=lb.num_levels_required(T), g_shift=-4.0))
-    args = (inp["q"], inp["k"], inp["v"], inp["g"], inp["lam"], inp["beta"])
-    o_t, _ = lb.chunk_h_gated_delta_rule(*args, use_qk_l2norm_in_kernel=True)
-    monkeypatch.setenv("LAMPA_B200_NO_UMMA", "1")
-    o_m, _ = lb.chunk_h_gated_delta_rule(*args, use_qk_l2norm_in_kernel=True)
-    monkeypatch.delenv("LAMPA_B200_NO_UMMA")
-    assert_close_bf16(to_np(o_t), to_np(o_m), "tcgen05 vs mma.sync output pass")
+    h0 = torch.randn(1, H, 64, 64, device="cuda") * 0.1
+    hier = lambda: lb.chunk_h_gated_delta_rule(inp["q"], inp["k"], inp["v"], inp["g"], inp["lam"], inp["beta"],
+                                               use_qk_l2norm_in_kernel=True)[0]
+    plain = lambda: lb.chunk_gated_delta_rule(inp["q"], inp["k"], inp["v"], inp["g"], inp["beta"], initial_state=h0,
+                                              output_final_state=True, use_qk_l2norm_in_kernel=True)
+    o_t, (p_t, s_t) = hier(), plain()
+    assert L.lib().lampa_debug_force_mma_sync(1) == 0
+    try:
+        o_m, (p_m, s_m) = hier(), plain()
+    finally:
+        L.lib().lampa_debug_force_mma_sync(0)
+    assert not torch.equal(o_t, o_m)          # two different kernels did run
+    assert_close_bf16(to_np(o_t), to_np(o_m), "hier: tcgen05 vs mma.sync")
+    assert_close_bf16(to_np(p_t), to_np(p_m), "plain: tcgen05 vs mma.sync")
+    assert_close_bf16(to_np(s_t), to_np(s_m), "plain final state: tcgen05 vs mma.sync")
