@@ -411,6 +411,12 @@ __global__ void __launch_bounds__(8192 / NC, 2) gdn_prep_umma_kernel(GdnArgs a, 
         // e^{G_i - G_end(tile)}, times the column's decay to the end of its tile (both <= 1): one exponential per tile.
         const int ib = i >> 3;
         const float Gi = sG(sub)[i];
+        // the row's lambda of the seven levels a chunk can hold (bit_length(i ^ j) <= 6), read once
+        float lrow[7];
+        if (HIER) {
+#pragma unroll
+            for (int l = 0; l < 7; ++l) lrow[l] = l < a.L ? lam_at(sub, i, l) : 0.f;
+        }
 #pragma unroll
         for (int b4 = 0; b4 < NC / 8; ++b4) {
             const int jb = col0 / 8 + b4;
@@ -422,7 +428,7 @@ __global__ void __launch_bounds__(8192 / NC, 2) gdn_prep_umma_kernel(GdnArgs a, 
                 const float4 c1 = *reinterpret_cast<const float4*>(sCF(sub) + 8 * jb + 4);
                 const float cf[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
                 float rowf = __expf(Gi - sG(sub)[8 * jb + 7]);
-                if (HIER) rowf *= lam_at(sub, i, 3 + (32 - __clz(ib ^ jb)));
+                if (HIER) { const int d = ib ^ jb; rowf *= d < 2 ? lrow[4] : (d < 4 ? lrow[5] : lrow[6]); }
 #pragma unroll
                 for (int e = 0; e < 8; ++e) x[8 * b4 + e] *= rowf * cf[e];
             } else {
@@ -432,7 +438,9 @@ __global__ void __launch_bounds__(8192 / NC, 2) gdn_prep_umma_kernel(GdnArgs a, 
 #pragma unroll
                 for (int e = 0; e < 8; ++e) {
                     const int j = 8 * jb + e;
-                    const float f = (j <= i) ? __expf(Gi - gj[e]) * (HIER ? lam_at(sub, i, 32 - __clz(i ^ j)) : 1.f) : 0.f;
+                    const int d = i ^ j;          // < 8 inside the diagonal tile
+                    const float lam_ij = HIER ? (d == 0 ? lrow[0] : (d < 2 ? lrow[1] : (d < 4 ? lrow[2] : lrow[3]))) : 1.f;
+                    const float f = (j <= i) ? __expf(Gi - gj[e]) * lam_ij : 0.f;
                     x[8 * b4 + e] *= f;
                 }
             }
