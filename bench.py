@@ -645,7 +645,7 @@ def run_plain(args):
     from lampa_b200 import _lib as L, synth
     dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
     torch.cuda.set_device(dev)
-    T = 65536
+    T = 65536 if args.hits == N_HITS else args.hits        # --hits shrinks the case for a profiler capture
     d = {k: v.to(dev) for k, v in synth.gdn_inputs(20251, T, H, K, V, g_shift=2.0, h0=True).items()}
 
     def step():

@@ -32,7 +32,18 @@ namespace {
 constexpr int UKD = 64, UVD = 64;
 constexpr int UNP = 5;                       // pairs of slots: 5 in-block levels + up to 5 cross-block levels
 constexpr int UEPI_WARPS = 16;               // 4 warpgroups, each covering 16 state columns and 16 tokens of all 128 rows
-constexpr int UTHREADS = (UEPI_WARPS + 1) * 32;   // plus one control warp
+constexpr int UTHREADS = (UEPI_WARPS + 2) * 32;   // plus one control warp and one relay warp
+// An mbarrier poll costs the polling warp 200 - 300 cycles even when the phase is long complete, a hardware named
+// barrier that everybody else has already reached about 30.  So only the relay warp polls the mbarriers the epilogue
+// depends on ("record landed", "pair's MMA complete") and passes each completion on through a named barrier that the
+// sixteen epilogue warps join: ids 5 + p for the pairs, 10 for the record (ids 1..4 belong to the output transpose).
+// The relay's own waits are bounded and it arrives whether or not they ran out, so nobody can be left waiting; once
+// a wait has run out it joins the barriers synchronously (relay_pass) so that it cannot run ahead of the epilogue and
+// arrive twice in one phase.
+constexpr int UNB_PAIR = 5, UNB_REC = 10, UNB_COUNT = (UEPI_WARPS + 1) * 32;
+__device__ __forceinline__ void named_arrive(int id) { asm volatile("bar.arrive %0, %1;\n" :: "r"(id), "n"(UNB_COUNT) : "memory"); }
+__device__ __forceinline__ void named_sync(int id) { asm volatile("bar.sync %0, %1;\n" :: "r"(id), "n"(UNB_COUNT) : "memory"); }
+__device__ __forceinline__ void relay_pass(int id, bool dead) { if (dead) named_sync(id); else named_arrive(id); }
 constexpr int UNST = 3;                      // record stages
 using UR = Rec<UKD, UVD>;
 
@@ -150,7 +161,7 @@ __global__ void __launch_bounds__(UTHREADS, 1) gdn_out_hier_umma_kernel(GdnArgs 
     bool dead = false;
     const int budget = a.poll_budget;
 
-    if (wg == 4) {
+    if (warp == UEPI_WARPS) {
         // ---- control warp: one lane streams records and issues MMAs --------------------------------
         if (lane == 0) {
             int loaded = 0, landed = 0;              // records requested / records seen in shared memory
@@ -196,6 +207,16 @@ __global__ void __launch_bounds__(UTHREADS, 1) gdn_out_hier_umma_kernel(GdnArgs 
             umma_commit(drainb);
             mbar_drain(drainb, 0u);
         }
+    } else if (wg == 4) {
+        // ---- relay warp (the second warp of this group): mbarrier completions -> named barriers ----
+        for (int i = 0; i < nsteps; ++i) {
+            mbar_wait(full + (i % UNST), (uint32_t)((i / UNST) & 1), dead, a.status, 250 + i, budget);
+            relay_pass(UNB_REC, dead);
+            for (int p = 0; p < npairs; ++p) {
+                mbar_wait(mdone + p, (uint32_t)(i & 1), dead, a.status, 300 + p, budget);
+                relay_pass(UNB_PAIR + p, dead);
+            }
+        }
     } else {
         // ---- epilogue warps: every warp advances 16 state columns and reads 16 tokens of its 32 rows ----
         // per pair, the lambda row of this thread's slot, and the slots that exist and have a lambda row
@@ -222,7 +243,7 @@ __global__ void __launch_bounds__(UTHREADS, 1) gdn_out_hier_umma_kernel(GdnArgs 
             const uint32_t low = (uint32_t)n & (BLOCK_CHUNKS - 1);
             const uint32_t read_mask = (low | (~0u << BLOCK_LOG)) & slot_ok;
             const uint32_t clear_mask = low & ~(low + 1u) & (BLOCK_CHUNKS - 1);      // trailing ones of n
-            mbar_wait(full + (i % UNST), (uint32_t)((i / UNST) & 1), dead, a.status, 250 + i, budget);
+            named_sync(UNB_REC);                       // record landed
             // this row's 16 columns of B^T, shared by every level that collects in this chunk
             const uint4 bq0 = *reinterpret_cast<const uint4*>(sBt + v * 128 + (((2 * part) ^ (v & 7)) << 4));
             const uint4 bq1 = *reinterpret_cast<const uint4*>(sBt + v * 128 + (((2 * part + 1) ^ (v & 7)) << 4));
@@ -232,7 +253,7 @@ __global__ void __launch_bounds__(UTHREADS, 1) gdn_out_hier_umma_kernel(GdnArgs 
             for (int j = 0; j < 16; ++j) oacc[j] = 0.f;
 
             for (int p = 0; p < npairs; ++p) {
-                mbar_wait(mdone + p, (uint32_t)(i & 1), dead, a.status, 300 + p, budget);
+                named_sync(UNB_PAIR + p);              // pair's MMA complete
                 tc_fence_after();
                 const int s = 2 * p + u;
                 const bool active = s < nslots;
@@ -451,6 +472,16 @@ __global__ void __launch_bounds__(UTHREADS, 1) gdn_out_plain_umma_kernel(GdnArgs
             umma_commit(drainb);
             mbar_drain(drainb, 0u);
         }
+    } else if (warp == UEPI_WARPS + 1) {
+        // ---- relay warp: mbarrier completions -> named barriers ----
+        for (int i = 0; i < nsteps; ++i) {
+            // the record barrier alternates between two ids: with a single MMA per chunk nothing keeps this warp from
+            // announcing record i + 1 before every epilogue warp has picked up record i
+            mbar_wait(full + (i % PNST), (uint32_t)((i / PNST) & 1), dead, a.status, 250 + i, budget);
+            relay_pass(UNB_REC + (i & 1), dead);
+            mbar_wait(mdone, (uint32_t)(i & 1), dead, a.status, 300, budget);
+            relay_pass(UNB_PAIR, dead);
+        }
     } else {
         // ---- epilogue warps: thread = (head sub, state row v, 16 state columns / 16 tokens) ----------
         const int lt = tid & 127;                      // position in the warpgroup that shares cq
@@ -466,8 +497,8 @@ __global__ void __launch_bounds__(UTHREADS, 1) gdn_out_plain_umma_kernel(GdnArgs
                 if (hd < nheads && t_out < tok_end)
                     ol[hd] = __ldg(reinterpret_cast<const uint4*>(rec0 + (size_t)i * rec_stride + (size_t)hd * a.rec_bytes + UR::OL_OFF) + UR::TV::off(otok, ocol) / 8);
             }
-            mbar_wait(full + (i % PNST), (uint32_t)((i / PNST) & 1), dead, a.status, 250 + i, budget);
-            mbar_wait(mdone, (uint32_t)(i & 1), dead, a.status, 300, budget);
+            named_sync(UNB_REC + (i & 1));             // records landed
+            named_sync(UNB_PAIR);                      // chunk's MMAs complete
             tc_fence_after();
             float x[16], y[16];
             tmem_ld16_issue(y, tlane + PTM_D + 64 + 16 * cq);
