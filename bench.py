@@ -696,6 +696,77 @@ def run_plain(args):
         "kernels": kernels}), flush=True)
 
 
+def run_heads(args):
+    """One 60k-hit event split by HEAD over the ranks (strong scaling of a single event): rank r hashes and sorts the
+    three rounds of its heads, runs the hierarchical rule on them and the [hits, H/N, V] outputs are all-gathered over
+    NCCL on a side stream, under the next event's kernels.  Device-resident; not the headline metric."""
+    import torch.distributed as dist
+    import lampa_b200
+    from lampa_b200 import _lib as L, sharding
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    ev = make_event(20252)                                      # the same event on every rank
+    h0, h1 = sharding.head_slice(H, rank, world)
+    d = {k: ev[k][:, :, h0:h1].contiguous().to(dev) for k in ("q", "k", "v", "g", "beta", "lam")}
+    hits = ev["hits"].to(dev)
+    alpha, lsh_beta = ev["alpha"][h0:h1].contiguous().to(dev), ev["lsh_beta"].to(dev)
+    hl = h1 - h0
+    side = torch.cuda.Stream(dev, priority=-1)
+    done = torch.cuda.Event()
+
+    def step():
+        ids = lampa_b200.lsh_hash(hits, alpha, lsh_beta, 1.0)["ids"]
+        perm = lampa_b200.segmented_sort(ids, nseg=ROUNDS * hl).view(ROUNDS, hl, N_HITS)
+        order = perm[0, 0]
+        lampa_b200.permute_rows(hits, order)
+        o, _ = lampa_b200.chunk_h_gated_delta_rule(d["q"], d["k"], d["v"], d["g"], d["lam"], d["beta"],
+                                                   use_qk_l2norm_in_kernel=True)
+        out = lampa_b200.permute_rows(o[0, :N_HITS].reshape(N_HITS, hl * V), order, scatter=True)
+        if world == 1:
+            return out
+        done.record()
+        with torch.cuda.stream(side):
+            side.wait_event(done)
+            full = sharding.gather_heads(out.view(N_HITS, hl, V))
+            out.record_stream(side)
+        return full
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    torch.cuda.current_stream().wait_stream(side)
+    e1.record()
+    barrier()
+    t = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    L.check_status(dev)
+    if rank == 0:
+        print(json.dumps({
+            "metric": "hits/sec, one 60k-hit event split by head", "value": N_HITS * args.steps / (ms * 1e-3), "unit": "hits/s",
+            "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps,
+            "higher_is_better": True, "scaling": "strong", "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "sharding": f"heads: {hl} of {H} per rank, ids and sorts of those heads only; "
+                       "all_gather of [hits, H/N, V] bf16 outputs on a side stream"}}), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def run_layer(args):
     """The layer's elementwise producers / consumers at the benchmark shape (not the headline metric): short
     convolution on a [T, H*K] projection, gate inputs (g, beta, lambda) and the gated RMS norm of the output.
@@ -822,12 +893,13 @@ def main():
     ap.add_argument("--no-model", action="store_true", help="skip the configuration-4 sub-measurement of the default run")
     ap.add_argument("--streams", type=int, default=3,
                     help="independent events kept in flight in the device-resident leg (1: strictly back to back)")
-    ap.add_argument("--workload", default="event", choices=["event", "model", "plain", "layer", "hept"],
+    ap.add_argument("--workload", default="event", choices=["event", "model", "plain", "layer", "hept", "heads"],
                     help="event: the headline LSH + hierarchical step; model: configuration 4, the packed 64-event "
                          "model forward, events split over the ranks (strong scaling) with an NCCL gather; plain: configuration 1 "
                          "(chunk_gated_delta_rule, T=65536, H=8, K=V=64, initial and final state), device-resident only; "
                          "layer: the elementwise kernels around the op (short convolution, gate inputs, gated norm); "
-                         "hept: the bucket attention of the HEPT layer at the event shape")
+                         "hept: the bucket attention of the HEPT layer at the event shape; heads: one event split by head over the "
+                         "ranks, outputs all-gathered over NCCL")
     args = ap.parse_args()
     if args.hits != N_HITS:
         set_event_size(args.hits)
@@ -837,6 +909,8 @@ def main():
         run_model(args)
     elif args.workload == "hept":
         run_hept(args)
+    elif args.workload == "heads":
+        run_heads(args)
     elif args.workload == "layer":
         run_layer(args)
     elif args.impl == "reference":

@@ -108,3 +108,25 @@ def shard_events(rows: torch.Tensor, lengths: Sequence[int], owned: Sequence[int
     cu, spans = pack_events(lengths, owned)
     local = torch.cat([rows[s:e] for s, e in spans]) if spans else rows[:0]
     return local, cu
+
+
+def gather_heads(local: torch.Tensor, group: Optional[dist.ProcessGroup] = None) -> torch.Tensor:
+    """All-gather the head slices of one event into the full head dimension.
+
+    `local` is [..., H / world, V] (the heads head_slice() gave this rank, in rank order); returns [..., H, V].
+    One collective, no arithmetic: the counterpart of gather_event_outputs when a single large event is split by
+    head instead of a batch of events by event."""
+    world = dist.get_world_size(group)
+    local = local.contiguous()
+    if local.is_cuda:
+        parts = local.new_empty((world,) + tuple(local.shape))
+        dist.all_gather_into_tensor(parts, local, group=group)
+    else:
+        chunks = [torch.empty_like(local) for _ in range(world)]
+        dist.all_gather(chunks, local, group=group)
+        parts = torch.stack(chunks)
+    nd = local.dim()
+    # [world, ..., h, V] -> [..., world, h, V] -> [..., world * h, V]
+    perm = list(range(1, nd - 1)) + [0, nd - 1, nd]
+    out = parts.permute(*perm)
+    return out.reshape(tuple(local.shape[:-2]) + (world * local.shape[-2], local.shape[-1]))

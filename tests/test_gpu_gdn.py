@@ -357,3 +357,19 @@ def test_tensor_core_paths_agree(lb):
     assert_close_bf16(to_np(o_t), to_np(o_m), "hier: tcgen05 vs mma.sync")
     assert_close_bf16(to_np(p_t), to_np(p_m), "plain: tcgen05 vs mma.sync")
     assert_close_bf16(to_np(s_t), to_np(s_m), "plain final state: tcgen05 vs mma.sync")
+
+
+def test_head_slices_reproduce_the_full_call(lb):
+    """Splitting one event by head (what a rank of a head-sharded job computes) gives the same rows as the full call."""
+    from lampa_b200 import synth
+    T, H = 4096 + 200, 4
+    inp = _cuda(synth.gdn_inputs(77, T, H, 64, 64, L=lb.num_levels_required(T), g_shift=-4.0))
+    full, _ = lb.chunk_h_gated_delta_rule(inp["q"], inp["k"], inp["v"], inp["g"], inp["lam"], inp["beta"],
+                                          use_qk_l2norm_in_kernel=True)
+    parts = []
+    for h0, h1 in ((0, 1), (1, 4)):           # uneven on purpose: a lone head and an odd group
+        sl = {k: inp[k][:, :, h0:h1].contiguous() for k in ("q", "k", "v", "g", "beta", "lam")}
+        o, _ = lb.chunk_h_gated_delta_rule(sl["q"], sl["k"], sl["v"], sl["g"], sl["lam"], sl["beta"],
+                                           use_qk_l2norm_in_kernel=True)
+        parts.append(o)
+    assert torch.equal(torch.cat(parts, dim=2), full)

@@ -123,6 +123,31 @@ def test_two_rank_plan_and_gather_over_gloo():
     mp.spawn(_rank_main, args=(2, _free_port(), lens), nprocs=2, join=True)
 
 
+def _head_rank_main(rank, world, port):
+    sys.path.insert(0, ROOT)
+    from lampa_b200 import sharding
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        B, T, H, V = 1, 37, 6, 5
+        full = torch.arange(B * T * H * V, dtype=torch.float32).view(B, T, H, V)
+        h0, h1 = sharding.head_slice(H, rank, world)
+        assert (h0, h1) == (rank * H // world, (rank + 1) * H // world)
+        got = sharding.gather_heads(full[:, :, h0:h1])        # a strided view: gather_heads makes it dense
+        assert torch.equal(got, full)
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_rank_head_split_and_gather_over_gloo():
+    mp.spawn(_head_rank_main, args=(2, _free_port()), nprocs=2, join=True)
+    from lampa_b200 import sharding
+    with pytest.raises(ValueError):
+        sharding.head_slice(8, 0, 3)
+
+
 class _EventMeanModel:
     """Stand-in for the packed model on CPU ranks: every row minus its event's mean (so that a
     wrong event boundary or a wrong gather position shows), three output columns."""
