@@ -153,10 +153,15 @@ def chunk_gated_delta_rule(
     the tensor-core operands are bf16, so an fp32 call could not honour fp32 accuracy.
     """
     _common_checks(q, k, v, beta, head_first, cu_seqlens, initial_state)
-    _check_cu_seqlens(cu_seqlens, q.shape[1])
     _forward_only(q, k, v, g, beta, initial_state)
     if scale is None:
         scale = k.shape[-1] ** -0.5
+    if torch.compiler.is_compiling():          # one opaque node in the traced graph (see torch_ops.py)
+        from . import torch_ops  # noqa: F401
+        o, ht = torch.ops.lampa_b200.gdn_fwd(q, k, v, g, beta, float(scale), initial_state, cu_seqlens,
+                                             bool(use_qk_l2norm_in_kernel))
+        return o, (ht if output_final_state else None)
+    _check_cu_seqlens(cu_seqlens, q.shape[1])
     with torch.no_grad():
         return _gdn_plain(q, k, v, g, beta, scale, initial_state, output_final_state, cu_seqlens,
                           use_qk_l2norm_in_kernel)
@@ -344,6 +349,9 @@ def chunk_h_gated_delta_rule(
     if output_final_state is False:
         if initial_state is not None:
             raise NotImplementedError
+        if torch.compiler.is_compiling():      # one opaque node in the traced graph (see torch_ops.py)
+            from . import torch_ops  # noqa: F401
+            return torch.ops.lampa_b200.hgdn_fwd(q, k, v, g, beta, l, cu_seqlens, True), None
         return _hgdn(q, k, v, g, beta, l, cu_seqlens, True), None
     if cu_seqlens is not None:
         if initial_state is not None:

@@ -373,3 +373,27 @@ def test_head_slices_reproduce_the_full_call(lb):
                                            use_qk_l2norm_in_kernel=True)
         parts.append(o)
     assert torch.equal(torch.cat(parts, dim=2), full)
+
+
+def test_traced_calls_become_one_dispatcher_node(lb):
+    """Under torch.compile the two forwards are single opaque nodes (torch.ops.lampa_b200.*): the whole function
+    traces without a graph break and gives the eager result."""
+    from lampa_b200 import synth
+    T, H = 1024 + 100, 2
+    inp = _cuda(synth.gdn_inputs(5, T, H, 64, 64, L=lb.num_levels_required(T), g_shift=-4.0))
+
+    def plain(q, k, v, g, b):
+        o, s = lb.chunk_gated_delta_rule(q, k, v, g, b, output_final_state=True, use_qk_l2norm_in_kernel=True)
+        return o.float() * 2 + 1, s
+
+    def hier(q, k, v, g, lam, b):
+        return lb.chunk_h_gated_delta_rule(q, k, v, g, lam, b, use_qk_l2norm_in_kernel=True)[0].float() - 1
+
+    pa = (inp["q"], inp["k"], inp["v"], inp["g"], inp["beta"])
+    ha = (inp["q"], inp["k"], inp["v"], inp["g"], inp["lam"], inp["beta"])
+    with torch.no_grad():
+        want_p, want_h = plain(*pa), hier(*ha)
+        got_p = torch.compile(plain, backend="aot_eager", fullgraph=True)(*pa)
+        got_h = torch.compile(hier, backend="aot_eager", fullgraph=True)(*ha)
+    assert torch.equal(got_p[0], want_p[0]) and torch.equal(got_p[1], want_p[1])
+    assert torch.equal(got_h, want_h)

@@ -208,3 +208,19 @@ def test_get_regions_matches_reference_draws(golden_dir):
     p = pad_to_multiple(x, 4, dims=0, value=float("inf"))
     assert tuple(p.shape) == (8, 2) and torch.isinf(p[5:]).all() and torch.equal(p[:5], x)
     assert pad_to_multiple(x, 5, dims=0) is x
+
+
+def test_dispatcher_entries_have_shape_functions():
+    """torch.ops.lampa_b200.{gdn_fwd, hgdn_fwd}: the shape functions answer for meta tensors (what a tracer sees)."""
+    from lampa_b200 import torch_ops  # noqa: F401
+    B, T, H, K, V, Lv = 1, 300, 3, 64, 64, 10
+    m = lambda *s, dt=torch.bfloat16: torch.empty(*s, dtype=dt, device="meta")
+    q, k, v = m(B, T, H, K), m(B, T, H, K), m(B, T, H, V)
+    g, beta = m(B, T, H, dt=torch.float32), m(B, T, H, dt=torch.float32)
+    o, ht = torch.ops.lampa_b200.gdn_fwd(q, k, v, g, beta, 0.125, None, None, True)
+    assert o.shape == (B, T, H, V) and o.dtype == torch.bfloat16 and ht.shape == (B, H, K, V) and ht.dtype == torch.float32
+    cu = torch.empty(5, dtype=torch.int64, device="meta")
+    o, ht = torch.ops.lampa_b200.gdn_fwd(q, k, v, g, beta, 0.125, None, cu, True)
+    assert ht.shape == (4, H, K, V)
+    o = torch.ops.lampa_b200.hgdn_fwd(q, k, v, g, beta, m(B, T, H, Lv), None, True)
+    assert o.shape == (B, T, H, V) and o.dtype == torch.bfloat16
