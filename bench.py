@@ -640,13 +640,20 @@ def run_model(args):
 
 
 def run_plain(args):
-    """Configuration 1 on one GPU: timing of the plain chunkwise rule (not the headline metric)."""
+    """Configurations 1 and 0 on one GPU: timing of the plain chunkwise rule (not the headline metric).
+    plain: T = 65536, H = 8, random initial state; config0: T = 6144, H = 4, zero initial state, with the CPU
+    restatement of the token recurrence timed beside it on the same inputs."""
     import lampa_b200
     from lampa_b200 import _lib as L, synth
     dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
     torch.cuda.set_device(dev)
-    T = 65536 if args.hits == DEFAULT_N_HITS else args.hits        # --hits shrinks the case for a profiler capture
-    d = {k: v.to(dev) for k, v in synth.gdn_inputs(20251, T, H, K, V, g_shift=2.0, h0=True).items()}
+    cfg0 = args.workload == "config0"
+    T = (6144 if cfg0 else 65536) if args.hits == DEFAULT_N_HITS else args.hits   # --hits shrinks the case for a profiler capture
+    nh = 4 if cfg0 else H                                  # heads
+    host = synth.gdn_inputs(20250 if cfg0 else 20251, T, nh, K, V, g_shift=2.0, h0=True)
+    if cfg0:
+        host["h0"].zero_()
+    d = {k: v.to(dev) for k, v in host.items()}
 
     def step():
         return lampa_b200.chunk_gated_delta_rule(d["q"], d["k"], d["v"], d["g"], d["beta"], initial_state=d["h0"],
@@ -673,10 +680,10 @@ def run_plain(args):
     pk = peaks()
     n_ch = (T + 63) // 64
     rec = 4 * 8192                                        # M, Q~, B^T, O_local: bf16 [64][64] each
-    alg = {"gdn_prep_plain": T * (H * (2 * K + V) * 2 + 2 * H * 4) + H * n_ch * rec,
-           "gdn_compose": H * n_ch * 3 * 8192,
-           "gdn_out_plain_umma": H * n_ch * rec + T * H * V * 2,
-           "gdn_out_plain": H * n_ch * rec + T * H * V * 2}
+    alg = {"gdn_prep_plain": T * (nh * (2 * K + V) * 2 + 2 * nh * 4) + nh * n_ch * rec,
+           "gdn_compose": nh * n_ch * 3 * 8192,
+           "gdn_out_plain_umma": nh * n_ch * rec + T * nh * V * 2,
+           "gdn_out_plain": nh * n_ch * rec + T * nh * V * 2}
     kernels = {}
     for n, r in prof.items():
         per = r["ms"] / r["launches"]
@@ -685,13 +692,28 @@ def run_plain(args):
             kernels[n]["hbm_gbs"] = alg[n] / (per * 1e-3) / 1e9
             kernels[n]["hbm_frac"] = kernels[n]["hbm_gbs"] / pk["hbm_gbs"]
     dom = max(kernels, key=lambda n: kernels[n]["ms_per_launch"])
+    cpu_line = None
+    if cfg0 and not args.no_cpu:
+        from oracle import oracle
+        cores = os.cpu_count() or 1
+        oracle.set_threads(cores)
+        a = [host[k][0].float().numpy() for k in ("q", "k", "v", "g", "beta")]
+        oracle.gdn_plain(*a, h0=host["h0"].numpy(), use_l2norm=True)                  # warm-up
+        t0 = time.perf_counter()
+        oracle.gdn_plain(*a, h0=host["h0"].numpy(), use_l2norm=True)
+        sec = time.perf_counter() - t0
+        cpu_line = {"value": T / sec, "unit": "tokens/s", "cores": min(cores, nh), "kind": "port",
+                    "sample": f"one pass over all {T} tokens ({sec * 1e3:.0f} ms); C restatement of the reference's token "
+                              "recurrence, OpenMP over heads"}
     print(json.dumps({
         "roofline": {"kernel": dom, "bound": "hbm", "achieved": kernels[dom].get("hbm_gbs"), "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": kernels[dom].get("hbm_frac"), "traffic": None, "peak_source": pk["source"]},
         "metric": "tokens/sec, plain chunkwise gated-delta fwd", "value": T * args.steps / (ms * 1e-3), "unit": "tokens/s",
         "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps,
         "higher_is_better": True, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": f"config 1: chunk_gated_delta_rule T={T} H=8 K=V=64 bf16, h0 + final state"},
+        "config": {"workload": f"config {0 if cfg0 else 1}: chunk_gated_delta_rule T={T} H={nh} K=V=64 bf16, "
+                               f"{'zero' if cfg0 else 'random'} initial state + final state"},
+        "cpu_baseline": cpu_line,
         "hbm_gbs_algorithmic": T * 4160 / (ms / args.steps * 1e-3) / 1e9,
         "kernels": kernels}), flush=True)
 
@@ -893,17 +915,18 @@ def main():
     ap.add_argument("--no-model", action="store_true", help="skip the configuration-4 sub-measurement of the default run")
     ap.add_argument("--streams", type=int, default=3,
                     help="independent events kept in flight in the device-resident leg (1: strictly back to back)")
-    ap.add_argument("--workload", default="event", choices=["event", "model", "plain", "layer", "hept", "heads"],
+    ap.add_argument("--workload", default="event", choices=["event", "model", "plain", "config0", "layer", "hept", "heads"],
                     help="event: the headline LSH + hierarchical step; model: configuration 4, the packed 64-event "
                          "model forward, events split over the ranks (strong scaling) with an NCCL gather; plain: configuration 1 "
                          "(chunk_gated_delta_rule, T=65536, H=8, K=V=64, initial and final state), device-resident only; "
+                         "config0: configuration 0's shape (T=6144, H=4) on the same op, with the CPU restatement beside it; "
                          "layer: the elementwise kernels around the op (short convolution, gate inputs, gated norm); "
                          "hept: the bucket attention of the HEPT layer at the event shape; heads: one event split by head over the "
                          "ranks, outputs all-gathered over NCCL")
     args = ap.parse_args()
     if args.hits != N_HITS:
         set_event_size(args.hits)
-    if args.workload == "plain":
+    if args.workload in ("plain", "config0"):
         run_plain(args)
     elif args.workload == "model" and args.impl != "reference":
         run_model(args)

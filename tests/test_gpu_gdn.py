@@ -338,25 +338,33 @@ def test_packed_events_like_config4(lb):
 
 def test_tensor_core_paths_agree(lb):
     """The tcgen05 kernels and their mma.sync twins (lampa_debug_force_mma_sync) on the same input: hierarchical
-    and plain rule, preparation and output passes."""
+    and plain rule, preparation and output passes, fixed-length and packed input, an odd number of heads."""
     from lampa_b200 import _lib as L, synth
     T, H = 8192 + 640, 3
     inp = _cuda(synth.gdn_inputs(31, T, H, 64, 64, L=lb.num_levels_required(T), g_shift=-4.0))
     h0 = torch.randn(1, H, 64, 64, device="cuda") * 0.1
+    cu = torch.tensor([0, 700, 764, 5000, T], dtype=torch.int64)
+    h0p = torch.randn(4, H, 64, 64, device="cuda") * 0.1
     hier = lambda: lb.chunk_h_gated_delta_rule(inp["q"], inp["k"], inp["v"], inp["g"], inp["lam"], inp["beta"],
                                                use_qk_l2norm_in_kernel=True)[0]
     plain = lambda: lb.chunk_gated_delta_rule(inp["q"], inp["k"], inp["v"], inp["g"], inp["beta"], initial_state=h0,
                                               output_final_state=True, use_qk_l2norm_in_kernel=True)
-    o_t, (p_t, s_t) = hier(), plain()
-    assert L.lib().lampa_debug_force_mma_sync(1) == 0
+    packed = lambda: lb.chunk_gated_delta_rule(inp["q"], inp["k"], inp["v"], inp["g"], inp["beta"], initial_state=h0p,
+                                               output_final_state=True, cu_seqlens=cu, use_qk_l2norm_in_kernel=True)
+    res = {}
     try:
-        o_m, (p_m, s_m) = hier(), plain()
+        for mode in (0, 1):                      # 0: the tcgen05 kernels; 1: their mma.sync twins
+            assert L.lib().lampa_debug_force_mma_sync(mode) == 0
+            res[mode] = (hier(), plain(), packed())
     finally:
         L.lib().lampa_debug_force_mma_sync(0)
-    assert not torch.equal(o_t, o_m)          # two different kernels did run
+    (o_t, (p_t, s_t), (q_t, r_t)), (o_m, (p_m, s_m), (q_m, r_m)) = res[0], res[1]
+    assert not torch.equal(o_t, o_m) and not torch.equal(p_t, p_m)          # different kernels did run
     assert_close_bf16(to_np(o_t), to_np(o_m), "hier: tcgen05 vs mma.sync")
     assert_close_bf16(to_np(p_t), to_np(p_m), "plain: tcgen05 vs mma.sync")
     assert_close_bf16(to_np(s_t), to_np(s_m), "plain final state: tcgen05 vs mma.sync")
+    assert_close_bf16(to_np(q_t), to_np(q_m), "plain, packed: tcgen05 vs mma.sync")
+    assert_close_bf16(to_np(r_t), to_np(r_m), "plain, packed, final states: tcgen05 vs mma.sync")
 
 
 def test_head_slices_reproduce_the_full_call(lb):
