@@ -442,7 +442,7 @@ def run_ours(args):
                          "frac": achieved / peak,
                          "traffic": ncu_traffic.get(dom), "peak_source": pk["source"],
                          "note": ("bytes = inputs read (%d B/token) + records written (%d B per chunk-head); inputs alone: %.0f GB/s; "
-                                  "as dense flops (SURVEY 8d, 4.02 MFLOP per chunk-head): %.0f TFLOP/s"
+                                  "as dense flops (nine 64^3 products + the blockwise inverse = 4.02 MFLOP per chunk-head): %.0f TFLOP/s"
                                   % (in_bytes, rec_bytes, T_PAD * in_bytes / dur_s / 1e9,
                                      H * n_chunks * (7 * 524288 + 2 * 174763) / dur_s / 1e12)) if dom == "gdn_prep_hier" else None,
                          "whole_step_hbm_gbs": N_HITS * 4432 / (ms / args.steps * 1e-3) / 1e9},
