@@ -190,9 +190,10 @@ def run_ours(args):
         perm = lampa_b200.segmented_sort(ids, nseg=ROUNDS * HEADS).view(ROUNDS, HEADS, N_HITS)
         order = perm[0, 0]
         lampa_b200.permute_rows(t["hits"], order)
+        # the output rows go straight to their hits' positions: the un-ordering is folded into the output pass's store
         o, _ = lampa_b200.chunk_h_gated_delta_rule(t["q"], t["k"], t["v"], t["g"], t["lam"], t["beta"],
-                                                   use_qk_l2norm_in_kernel=True)
-        out = lampa_b200.permute_rows(o[0, :N_HITS].reshape(N_HITS, H * V), order, scatter=True)
+                                                   use_qk_l2norm_in_kernel=True, out_perm=order)
+        out = o[0, :N_HITS].reshape(N_HITS, H * V)
         return out, order
 
     def barrier():
@@ -415,7 +416,7 @@ def run_ours(args):
             "gdn_level_hier": ("tensor", H * (n_chunks // 32) * 5 * 2 * 64 ** 3),
             "lsh_hash": ("hbm", N_HITS * 120),
             "segsort": ("hbm", N_HITS * ROUNDS * HEADS * 68),
-            "permute_rows": ("hbm", N_HITS * (16 + 2 * (96 + H * V * 2)) / 2),
+            "permute_rows": ("hbm", N_HITS * (8 + 2 * 96)),
         }
         ncu_traffic = profile_traffic() if N_HITS == 60000 else {}
         bound, units = alg.get(dom, ("hbm", 0))
@@ -747,8 +748,8 @@ def run_heads(args):
         order = perm[0, 0]
         lampa_b200.permute_rows(hits, order)
         o, _ = lampa_b200.chunk_h_gated_delta_rule(d["q"], d["k"], d["v"], d["g"], d["lam"], d["beta"],
-                                                   use_qk_l2norm_in_kernel=True)
-        out = lampa_b200.permute_rows(o[0, :N_HITS].reshape(N_HITS, hl * V), order, scatter=True)
+                                                   use_qk_l2norm_in_kernel=True, out_perm=order)
+        out = o[0, :N_HITS].reshape(N_HITS, hl * V)
         if world == 1:
             return out
         done.record()
@@ -913,7 +914,7 @@ def main():
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel from Python instead of replaying "
                                                             "one captured CUDA graph per stream")
     ap.add_argument("--no-model", action="store_true", help="skip the configuration-4 sub-measurement of the default run")
-    ap.add_argument("--streams", type=int, default=3,
+    ap.add_argument("--streams", type=int, default=4,
                     help="independent events kept in flight in the device-resident leg (1: strictly back to back)")
     ap.add_argument("--workload", default="event", choices=["event", "model", "plain", "config0", "layer", "hept", "heads"],
                     help="event: the headline LSH + hierarchical step; model: configuration 4, the packed 64-event "

@@ -111,6 +111,18 @@ int lampa_gdn_fwd(const lampa_gdn_desc* d, const void* q, const void* k, const v
 int lampa_hgdn_fwd(const lampa_gdn_desc* d, const void* q, const void* k, const void* v,
                    const void* g, const void* beta, const void* lam, const int64_t* cu_seqlens,
                    void* o, void* ws, size_t ws_bytes, int32_t* status, void* stream);
+/*
+ * The same forward with the un-ordering of a sorted event folded into the output store.
+ * Replaces: the mixer call followed by the gather with the inverse permutation that puts the rows of a sorted event
+ * back in hit order (models/baselines/hmamba.py:451-455), without the second pass over o.
+ *   Row t of the result is written to o[out_perm[t]] for t < out_perm_rows and to o[t] beyond
+ *   (the padding tokens after an event); out_perm must be a permutation of 0 .. out_perm_rows-1 for o to be fully
+ *   written.  An index outside [0, B*T) is skipped and reported as LAMPA_ERR_BOUNDS in the status word.
+ */
+int lampa_hgdn_fwd_scatter(const lampa_gdn_desc* d, const void* q, const void* k, const void* v,
+                           const void* g, const void* beta, const void* lam, const int64_t* cu_seqlens,
+                           const int64_t* out_perm, int64_t out_perm_rows, void* o, void* ws,
+                           size_t ws_bytes, int32_t* status, void* stream);
 
 /*
  * Fenwick state left by a hierarchical forward: call after lampa_hgdn_fwd with the same

@@ -35,7 +35,7 @@ class GdnDesc(ctypes.Structure):
 
 _lib: Optional[ctypes.CDLL] = None
 EXPORTS = ["lampa_version", "lampa_error_string", "lampa_gdn_workspace_bytes", "lampa_gdn_workspace_layout",
-           "lampa_gdn_fwd", "lampa_hgdn_fwd", "lampa_hgdn_final_state", "lampa_hgdn_step", "lampa_lsh_hash", "lampa_segsort_workspace_bytes",
+           "lampa_gdn_fwd", "lampa_hgdn_fwd", "lampa_hgdn_fwd_scatter", "lampa_hgdn_final_state", "lampa_hgdn_step", "lampa_lsh_hash", "lampa_segsort_workspace_bytes",
            "lampa_segsort_stable", "lampa_permute_rows", "lampa_invert_perm", "lampa_segsort_stable_static",
            "lampa_short_conv_fwd", "lampa_short_conv_step", "lampa_gate_inputs", "lampa_rmsnorm_gate", "lampa_add_rmsnorm",
            "lampa_row_range", "lampa_quantile_regions", "lampa_geo_keys",
@@ -60,6 +60,7 @@ def lib() -> ctypes.CDLL:
         L.lampa_gdn_workspace_layout.argtypes = [ctypes.POINTER(GdnDesc), ctypes.POINTER(sz)]
         L.lampa_gdn_fwd.argtypes = [ctypes.POINTER(GdnDesc)] + [vp] * 10 + [sz, vp, vp]
         L.lampa_hgdn_fwd.argtypes = [ctypes.POINTER(GdnDesc)] + [vp] * 9 + [sz, vp, vp]
+        L.lampa_hgdn_fwd_scatter.argtypes = [ctypes.POINTER(GdnDesc)] + [vp] * 8 + [i64, vp, vp, sz, vp, vp]
         L.lampa_hgdn_final_state.argtypes = [ctypes.POINTER(GdnDesc)] + [vp] * 6 + [sz, vp, vp, vp, vp]
         L.lampa_hgdn_step.argtypes = [ctypes.POINTER(GdnDesc)] + [vp] * 11
         L.lampa_lsh_hash.argtypes = [vp, i64, i64, vp, vp, ctypes.c_float, i64, i32, i32, i32, vp, vp, vp, vp]

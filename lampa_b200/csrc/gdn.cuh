@@ -61,6 +61,7 @@ struct Rec {
 struct GdnArgs {
     const void* q; const void* k; const void* v; const void* g; const void* beta; const void* lam;
     const float* h0; float* ht; void* o;
+    const int64_t* out_perm; long long out_perm_rows;   // optional scatter of the output rows (lampa_hgdn_fwd_scatter)
     int qkv_dt, gb_dt, lam_dt;
     int H, L, LC;
     int use_l2norm;
@@ -123,6 +124,19 @@ __device__ __forceinline__ bool locate_chunk(const GdnArgs& a, int c, ChunkLoc& 
     loc.t0 = a.tok_off[loc.seq] + (int64_t)(c - a.chunk_off[loc.seq]) * CHUNK;
     loc.len = (int)min((int64_t)CHUNK, a.tok_off[loc.seq + 1] - loc.t0);
     return true;
+}
+
+// Row of o that token t of the call is written to: its own, or out_perm[t] for the first out_perm_rows tokens
+// when the caller asked for the output to be scattered (the un-ordering of a sorted event folded into the store).
+// -1 (after reporting LAMPA_ERR_BOUNDS) for an index outside the output: that row is not written.
+__device__ __forceinline__ int64_t out_row(const GdnArgs& a, int64_t t) {
+    if (t >= a.out_perm_rows) return t;
+    const int64_t r = a.out_perm[t];
+    if (r < 0 || r >= a.total_tokens) {
+        set_status(a.status, LAMPA_ERR_BOUNDS, 30, (int)t);
+        return -1;
+    }
+    return r;
 }
 
 // Two output values (adjacent state columns) of one token, converted to the output type.

@@ -75,6 +75,7 @@ int make_layout(const lampa_gdn_desc* d, bool hier, Layout& l) {
 void fill_args(const lampa_gdn_desc* d, bool hier, const Layout& l, char* base, const int64_t* cu,
                int32_t* status, GdnArgs& a) {
     a.q = a.k = a.v = a.g = a.beta = a.lam = nullptr; a.h0 = nullptr; a.ht = nullptr; a.o = nullptr;
+    a.out_perm = nullptr; a.out_perm_rows = 0;
     a.qkv_dt = d->qkv_dtype; a.gb_dt = d->gb_dtype; a.lam_dt = d->lam_dtype;
     a.H = d->H; a.L = hier ? d->L : 0; a.LC = l.LC;
     a.use_l2norm = d->use_l2norm; a.scale = d->scale;
@@ -99,7 +100,8 @@ void fill_args(const lampa_gdn_desc* d, bool hier, const Layout& l, char* base, 
 
 int run(const lampa_gdn_desc* d, bool hier, const void* q, const void* k, const void* v, const void* g,
         const void* beta, const void* lam, const float* h0, const int64_t* cu, void* o, float* ht,
-        void* ws, size_t ws_bytes, int32_t* status, void* stream) {
+        void* ws, size_t ws_bytes, int32_t* status, void* stream, const int64_t* out_perm = nullptr,
+        int64_t out_perm_rows = 0) {
     Layout l;
     int rc = make_layout(d, hier, l);
     if (rc != LAMPA_OK) return rc;
@@ -116,6 +118,7 @@ int run(const lampa_gdn_desc* d, bool hier, const void* q, const void* k, const 
     GdnArgs a;
     fill_args(d, hier, l, base, cu, status, a);
     a.q = q; a.k = k; a.v = v; a.g = g; a.beta = beta; a.lam = lam; a.h0 = h0; a.ht = ht; a.o = o;
+    a.out_perm = out_perm; a.out_perm_rows = out_perm ? out_perm_rows : 0;
 
     PlanArgs p;
     p.cu = cu; p.nseq = l.nseq; p.B = d->B; p.T = d->T; p.L = d->L; p.hier = hier ? 1 : 0;
@@ -219,6 +222,15 @@ extern "C" int lampa_hgdn_fwd(const lampa_gdn_desc* d, const void* q, const void
                               const void* g, const void* beta, const void* lam, const int64_t* cu_seqlens,
                               void* o, void* ws, size_t ws_bytes, int32_t* status, void* stream) {
     return run(d, true, q, k, v, g, beta, lam, nullptr, cu_seqlens, o, nullptr, ws, ws_bytes, status, stream);
+}
+
+extern "C" int lampa_hgdn_fwd_scatter(const lampa_gdn_desc* d, const void* q, const void* k, const void* v,
+                                      const void* g, const void* beta, const void* lam, const int64_t* cu_seqlens,
+                                      const int64_t* out_perm, int64_t out_perm_rows, void* o, void* ws,
+                                      size_t ws_bytes, int32_t* status, void* stream) {
+    if (!d || out_perm_rows < 0 || out_perm_rows > (int64_t)d->B * d->T || (out_perm_rows > 0 && !out_perm)) return LAMPA_ERR_ARG;
+    return run(d, true, q, k, v, g, beta, lam, nullptr, cu_seqlens, o, nullptr, ws, ws_bytes, status, stream,
+               out_perm, out_perm_rows);
 }
 
 extern "C" int lampa_hgdn_final_state(const lampa_gdn_desc* d, const void* k, const void* v, const void* g,

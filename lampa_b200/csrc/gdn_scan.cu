@@ -456,12 +456,13 @@ __global__ void __launch_bounds__(VD * 2) gdn_out_plain_kernel(GdnArgs a) {
 #pragma unroll
             for (int hh = 0; hh < 2; ++hh) {
                 const int r = mt * 16 + g + hh * 8;
-                if (t0 + r < tok_end) {
+                const int64_t orow = t0 + r < tok_end ? out_row(a, t0 + r) : -1;
+                if (orow >= 0) {
 #pragma unroll
                     for (int nt = 0; nt < 2; ++nt) {
                         const int col = row0 + nt * 8 + 2 * t;
                         const float2 ol = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(sOl + R::TV::off(r, col)));
-                        store_out2(a.o, a.qkv_dt, ((size_t)(t0 + r) * H + h) * VD + col,
+                        store_out2(a.o, a.qkv_dt, ((size_t)orow * H + h) * VD + col,
                                    ol.x + tmp[nt][2 * hh], ol.y + tmp[nt][2 * hh + 1]);
                     }
                 }
@@ -630,12 +631,13 @@ __global__ void __launch_bounds__(NG * VD * 2, 1) gdn_out_hier_kernel(GdnArgs a)
 #pragma unroll
                 for (int hh = 0; hh < 2; ++hh) {
                     const int r = mt * 16 + g + hh * 8;
-                    if (t0 + r < tok_end) {
+                    const int64_t orow = t0 + r < tok_end ? out_row(a, t0 + r) : -1;
+                    if (orow >= 0) {
 #pragma unroll
                         for (int nt = 0; nt < 2; ++nt) {
                             const int col = row0 + nt * 8 + 2 * t;
                             const float2 ol = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(sOl + R::TV::off(r, col)));
-                            store_out2(a.o, a.qkv_dt, ((size_t)(t0 + r) * H + h) * VD + col,
+                            store_out2(a.o, a.qkv_dt, ((size_t)orow * H + h) * VD + col,
                                        ol.x + O[mt][nt][2 * hh], ol.y + O[mt][nt][2 * hh + 1]);
                         }
                     }

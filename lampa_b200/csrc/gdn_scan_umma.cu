@@ -314,8 +314,9 @@ __global__ void __launch_bounds__(UTHREADS, 1) gdn_out_hier_umma_kernel(GdnArgs 
             {
                 const int tok = tid >> 3, col = (tid & 7) * 8;
                 const int64_t t_out = tok0 + (int64_t)i * CHUNK + tok;
-                if (t_out < tok_end) {
-                    const size_t idx = ((size_t)t_out * H + h) * UVD + col;
+                const int64_t orow = t_out < tok_end ? out_row(a, t_out) : -1;
+                if (orow >= 0) {
+                    const size_t idx = ((size_t)orow * H + h) * UVD + col;
                     float r[8];
                     const uint4 ol = *reinterpret_cast<const uint4*>(sOl + UR::TV::off(tok, col));      // 8 bf16 of O_local
                     const uint32_t olw[4] = {ol.x, ol.y, ol.z, ol.w};
@@ -533,11 +534,12 @@ __global__ void __launch_bounds__(UTHREADS, 1) gdn_out_plain_umma_kernel(GdnArgs
                 case 2: asm volatile("bar.sync 3, 128;\n" ::: "memory"); break;
                 default: asm volatile("bar.sync 4, 128;\n" ::: "memory"); break;
             }
-            if (t_out < tok_end) {
+            const int64_t orow = t_out < tok_end ? out_row(a, t_out) : -1;
+            if (orow >= 0) {
 #pragma unroll
                 for (int hd = 0; hd < 2; ++hd) {
                     if (hd >= nheads) break;
-                    const size_t idx = ((size_t)t_out * H + h0 + hd) * UVD + ocol;
+                    const size_t idx = ((size_t)orow * H + h0 + hd) * UVD + ocol;
                     const uint32_t olw[4] = {ol[hd].x, ol[hd].y, ol[hd].z, ol[hd].w};
                     float r[8];
 #pragma unroll

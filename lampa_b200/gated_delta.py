@@ -230,7 +230,7 @@ class HState:
 
 
 @torch.no_grad()
-def _hgdn(q, k, v, g, beta, lam, cu_seqlens, use_l2norm, want_state: bool = False):
+def _hgdn(q, k, v, g, beta, lam, cu_seqlens, use_l2norm, want_state: bool = False, out_perm=None):
     _check_cu_seqlens(cu_seqlens, q.shape[1], lam.shape[-1])
     dev, q, k, v, g, beta, lam, cu = _prep_inputs(q, k, v, g, beta, lam, cu_seqlens)
     B, T, H, K = q.shape
@@ -243,9 +243,17 @@ def _hgdn(q, k, v, g, beta, lam, cu_seqlens, use_l2norm, want_state: bool = Fals
     o = torch.empty(B, T, H, V, dtype=q.dtype, device=dev)
     ws = _workspace(desc, dev)
     st = L.status_word(dev)
-    rc = L.lib().lampa_hgdn_fwd(ctypes.byref(desc), L.ptr(q), L.ptr(k), L.ptr(v), L.ptr(g), L.ptr(beta),
-                                L.ptr(lam), L.ptr(cu), L.ptr(o), L.ptr(ws), ws.numel(), L.ptr(st),
-                                L.stream_ptr(dev))
+    if out_perm is None:
+        rc = L.lib().lampa_hgdn_fwd(ctypes.byref(desc), L.ptr(q), L.ptr(k), L.ptr(v), L.ptr(g), L.ptr(beta),
+                                    L.ptr(lam), L.ptr(cu), L.ptr(o), L.ptr(ws), ws.numel(), L.ptr(st),
+                                    L.stream_ptr(dev))
+    else:
+        L.require_cuda(out_perm)
+        if out_perm.dtype != torch.int64 or out_perm.dim() != 1 or not out_perm.is_contiguous() or out_perm.numel() > B * T:
+            raise ValueError("out_perm must be a contiguous int64 vector of at most B*T row indices")
+        rc = L.lib().lampa_hgdn_fwd_scatter(ctypes.byref(desc), L.ptr(q), L.ptr(k), L.ptr(v), L.ptr(g), L.ptr(beta),
+                                            L.ptr(lam), L.ptr(cu), L.ptr(out_perm), out_perm.numel(), L.ptr(o),
+                                            L.ptr(ws), ws.numel(), L.ptr(st), L.stream_ptr(dev))
     L.check(rc, "lampa_hgdn_fwd")
     states = counts = None
     if want_state:
@@ -325,6 +333,7 @@ def chunk_h_gated_delta_rule(
     cu_seqlens: Optional[torch.LongTensor] = None,
     head_first: bool = False,
     use_qk_l2norm_in_kernel: bool = False,
+    out_perm: Optional[torch.LongTensor] = None,
 ):
     """Hierarchical (Fenwick-level) chunkwise gated-delta-rule forward.
 
@@ -340,6 +349,9 @@ def chunk_h_gated_delta_rule(
     and `cu_seqlens` by the second: the returned HState then holds one state per sequence
     (`states` [N,H,K,V,L], `counts` [N,L]); a sequence whose length is not a multiple of 64 is
     completed by null tokens (k = v = 0, beta = 0, g = 0), which its counts include.
+    `out_perm` (int64 [n <= B*T], first branch only) folds the un-ordering of a sorted event into the output store:
+    row t of the result lands in o.view(B*T, H, V)[out_perm[t]] for t < n (hmamba.py:451-455 gathers with the inverse
+    permutation in a second pass); rows from n on stay where they are.
     Device-side problems (a wait that ran out, device-resident cu_seqlens that are malformed or
     need more levels than l has) are reported through `check_status()`.
     """
@@ -349,10 +361,10 @@ def chunk_h_gated_delta_rule(
     if output_final_state is False:
         if initial_state is not None:
             raise NotImplementedError
-        if torch.compiler.is_compiling():      # one opaque node in the traced graph (see torch_ops.py)
+        if torch.compiler.is_compiling() and out_perm is None:      # one opaque node in the traced graph (see torch_ops.py)
             from . import torch_ops  # noqa: F401
             return torch.ops.lampa_b200.hgdn_fwd(q, k, v, g, beta, l, cu_seqlens, True), None
-        return _hgdn(q, k, v, g, beta, l, cu_seqlens, True), None
+        return _hgdn(q, k, v, g, beta, l, cu_seqlens, True, out_perm=out_perm), None
     if cu_seqlens is not None:
         if initial_state is not None:
             raise NotImplementedError("a decode step takes one token per batch row, not packed sequences")

@@ -405,3 +405,34 @@ def test_traced_calls_become_one_dispatcher_node(lb):
         got_h = torch.compile(hier, backend="aot_eager", fullgraph=True)(*ha)
     assert torch.equal(got_p[0], want_p[0]) and torch.equal(got_p[1], want_p[1])
     assert torch.equal(got_h, want_h)
+
+
+@pytest.mark.parametrize("K,V,force_mma", [(64, 64, False), (64, 64, True), (32, 32, False)])
+def test_output_scatter_equals_a_separate_row_scatter(lb, K, V, force_mma, monkeypatch):
+    """out_perm folds the un-ordering into the output store: same bits as the plain call followed by a row scatter."""
+    from lampa_b200 import _lib as L, synth
+    T, n, H = 2048 + 128, 2100, 3                      # the last 76 tokens are padding and stay where they are
+    inp = _cuda(synth.gdn_inputs(9, T, H, K, V, L=lb.num_levels_required(T), g_shift=-4.0))
+    args = (inp["q"], inp["k"], inp["v"], inp["g"], inp["lam"], inp["beta"])
+    perm = torch.randperm(n, generator=torch.Generator().manual_seed(3)).cuda()
+    bad = perm.clone()
+    bad[5] = T + 7
+    L.lib().lampa_debug_force_mma_sync(int(force_mma))
+    try:
+        plain, _ = lb.chunk_h_gated_delta_rule(*args, use_qk_l2norm_in_kernel=True)
+        fused, _ = lb.chunk_h_gated_delta_rule(*args, use_qk_l2norm_in_kernel=True, out_perm=perm)
+        monkeypatch.setenv("LAMPA_B200_CHECK", "0")    # the status word is read below, not inside the call
+        out, _ = lb.chunk_h_gated_delta_rule(*args, use_qk_l2norm_in_kernel=True, out_perm=bad)
+    finally:
+        L.lib().lampa_debug_force_mma_sync(0)
+    want = plain.clone()
+    want[0, :n] = lb.permute_rows(plain[0, :n].reshape(n, H * V), perm, scatter=True).view(n, H, V)
+    assert torch.equal(fused, want)
+    # an index outside the output is skipped and reported, nothing else is disturbed
+    torch.cuda.synchronize()
+    with pytest.raises(lb.LampaError):
+        lb.check_status(out.device)
+    lb.check_status(out.device)                        # reading the status clears it
+    keep = torch.ones(n, dtype=torch.bool, device="cuda")
+    keep[5] = False
+    assert torch.equal(out[0, perm[keep]], want[0, perm[keep]])
