@@ -128,15 +128,24 @@ __device__ __forceinline__ bool locate_chunk(const GdnArgs& a, int c, ChunkLoc& 
 
 // Row of o that token t of the call is written to: its own, or out_perm[t] for the first out_perm_rows tokens
 // when the caller asked for the output to be scattered (the un-ordering of a sorted event folded into the store).
-// -1 (after reporting LAMPA_ERR_BOUNDS) for an index outside the output: that row is not written.
+// -1 for an index outside the output: that row is not written (the preparation kernel has reported it, see
+// check_out_perm; the output passes stay free of the reporting code).
+// SCAT is a compile-time flag so that the common, unscattered store keeps its plain address arithmetic: the output
+// passes test a.out_perm_rows once per chunk and run one of two copies of their store code.
+template <bool SCAT>
 __device__ __forceinline__ int64_t out_row(const GdnArgs& a, int64_t t) {
-    if (t >= a.out_perm_rows) return t;
+    if (!SCAT || t >= a.out_perm_rows) return t;
     const int64_t r = a.out_perm[t];
-    if (r < 0 || r >= a.total_tokens) {
+    return (unsigned long long)r < (unsigned long long)a.total_tokens ? r : -1;
+}
+struct ScatterOn { static constexpr bool value = true; };
+struct ScatterOff { static constexpr bool value = false; };
+// The scatter indices of one chunk's tokens, checked by the first 64 threads of one preparation CTA per chunk.
+__device__ __forceinline__ void check_out_perm(const GdnArgs& a, int64_t t0, int len) {
+    const int64_t t = t0 + threadIdx.x;
+    if (a.out_perm_rows > 0 && (int)threadIdx.x < len && t < a.out_perm_rows &&
+        (unsigned long long)a.out_perm[t] >= (unsigned long long)a.total_tokens)
         set_status(a.status, LAMPA_ERR_BOUNDS, 30, (int)t);
-        return -1;
-    }
-    return r;
 }
 
 // Two output values (adjacent state columns) of one token, converted to the output type.

@@ -90,6 +90,7 @@ __global__ void __launch_bounds__(128, 4) gdn_prep_kernel(GdnArgs a) {
     const int64_t t0 = loc.t0;
     const int len = loc.len;
     const int LP = a.L + 1;
+    if (h == 0) check_out_perm(a, t0, len);
 
     // ---- stage 0: loads, l2norm, cumulative decay -------------------------------------------------
     // Every global load of the chunk is issued before any of them is consumed (one DRAM round trip

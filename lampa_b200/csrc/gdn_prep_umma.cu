@@ -141,6 +141,7 @@ __global__ void __launch_bounds__(8192 / NC, 2) gdn_prep_umma_kernel(GdnArgs a, 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int64_t t0 = loc.t0;
     const int len = loc.len;
+    if (blockIdx.x == 0) check_out_perm(a, t0, len);
     const int LP = a.L + 1;
     const int budget = a.poll_budget;
     bool dead = false;

@@ -449,25 +449,28 @@ __global__ void __launch_bounds__(VD * 2) gdn_out_plain_kernel(GdnArgs a) {
         uint32_t sp[KD / 16][4];
         pack_state<KD>(C, sp);
         const int64_t t0 = tok0 + (int64_t)i * CHUNK;
+        auto emit = [&](auto scat) {
 #pragma unroll
-        for (int mt = 0; mt < 4; ++mt) {
-            float tmp[2][4];
-            read_tile<KD>(tmp, sp, sQt, mt, lane);
+            for (int mt = 0; mt < 4; ++mt) {
+                float tmp[2][4];
+                read_tile<KD>(tmp, sp, sQt, mt, lane);
 #pragma unroll
-            for (int hh = 0; hh < 2; ++hh) {
-                const int r = mt * 16 + g + hh * 8;
-                const int64_t orow = t0 + r < tok_end ? out_row(a, t0 + r) : -1;
-                if (orow >= 0) {
+                for (int hh = 0; hh < 2; ++hh) {
+                    const int r = mt * 16 + g + hh * 8;
+                    const int64_t orow = t0 + r < tok_end ? out_row<decltype(scat)::value>(a, t0 + r) : -1;
+                    if (orow >= 0) {
 #pragma unroll
-                    for (int nt = 0; nt < 2; ++nt) {
-                        const int col = row0 + nt * 8 + 2 * t;
-                        const float2 ol = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(sOl + R::TV::off(r, col)));
-                        store_out2(a.o, a.qkv_dt, ((size_t)orow * H + h) * VD + col,
-                                   ol.x + tmp[nt][2 * hh], ol.y + tmp[nt][2 * hh + 1]);
+                        for (int nt = 0; nt < 2; ++nt) {
+                            const int col = row0 + nt * 8 + 2 * t;
+                            const float2 ol = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(sOl + R::TV::off(r, col)));
+                            store_out2(a.o, a.qkv_dt, ((size_t)orow * H + h) * VD + col,
+                                       ol.x + tmp[nt][2 * hh], ol.y + tmp[nt][2 * hh + 1]);
+                        }
                     }
                 }
             }
-        }
+        };
+        if (a.out_perm_rows > 0) emit(ScatterOn{}); else emit(ScatterOff{});
         if (i + 1 < nsteps) {
             load_slab_bf16<KD>(C, sBt, row0, lane);
             state_times_mt<KD, Tile<KD>>(C, sp, sM, lane);
@@ -626,22 +629,25 @@ __global__ void __launch_bounds__(NG * VD * 2, 1) gdn_out_hier_kernel(GdnArgs a)
                         for (int e = 0; e < 4; ++e) O[mt][nt][e] += rd[((mt * 2 + nt) * 4 + e) * 32];
             }
             const int64_t t0 = tok0 + (int64_t)i * CHUNK;
+            auto emit = [&](auto scat) {
 #pragma unroll
-            for (int mt = 0; mt < 4; ++mt)
+                for (int mt = 0; mt < 4; ++mt)
 #pragma unroll
-                for (int hh = 0; hh < 2; ++hh) {
-                    const int r = mt * 16 + g + hh * 8;
-                    const int64_t orow = t0 + r < tok_end ? out_row(a, t0 + r) : -1;
-                    if (orow >= 0) {
+                    for (int hh = 0; hh < 2; ++hh) {
+                        const int r = mt * 16 + g + hh * 8;
+                        const int64_t orow = t0 + r < tok_end ? out_row<decltype(scat)::value>(a, t0 + r) : -1;
+                        if (orow >= 0) {
 #pragma unroll
-                        for (int nt = 0; nt < 2; ++nt) {
-                            const int col = row0 + nt * 8 + 2 * t;
-                            const float2 ol = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(sOl + R::TV::off(r, col)));
-                            store_out2(a.o, a.qkv_dt, ((size_t)orow * H + h) * VD + col,
-                                       ol.x + O[mt][nt][2 * hh], ol.y + O[mt][nt][2 * hh + 1]);
+                            for (int nt = 0; nt < 2; ++nt) {
+                                const int col = row0 + nt * 8 + 2 * t;
+                                const float2 ol = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(sOl + R::TV::off(r, col)));
+                                store_out2(a.o, a.qkv_dt, ((size_t)orow * H + h) * VD + col,
+                                           ol.x + O[mt][nt][2 * hh], ol.y + O[mt][nt][2 * hh + 1]);
+                            }
                         }
                     }
-                }
+            };
+            if (a.out_perm_rows > 0) emit(ScatterOn{}); else emit(ScatterOff{});
         }
     }
     pipe.finish();

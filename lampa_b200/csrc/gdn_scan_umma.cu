@@ -311,10 +311,10 @@ __global__ void __launch_bounds__(UTHREADS, 1) gdn_out_hier_umma_kernel(GdnArgs 
                 case 2: asm volatile("bar.sync 3, 128;\n" ::: "memory"); break;
                 default: asm volatile("bar.sync 4, 128;\n" ::: "memory"); break;
             }
-            {
+            auto emit = [&](auto scat) {
                 const int tok = tid >> 3, col = (tid & 7) * 8;
                 const int64_t t_out = tok0 + (int64_t)i * CHUNK + tok;
-                const int64_t orow = t_out < tok_end ? out_row(a, t_out) : -1;
+                const int64_t orow = t_out < tok_end ? out_row<decltype(scat)::value>(a, t_out) : -1;
                 if (orow >= 0) {
                     const size_t idx = ((size_t)orow * H + h) * UVD + col;
                     float r[8];
@@ -342,7 +342,8 @@ __global__ void __launch_bounds__(UTHREADS, 1) gdn_out_hier_umma_kernel(GdnArgs 
                         *reinterpret_cast<uint4*>((uint16_t*)a.o + idx) = make_uint4(w[0], w[1], w[2], w[3]);
                     }
                 }
-            }
+            };
+            if (a.out_perm_rows > 0) emit(ScatterOn{}); else emit(ScatterOff{});
             __syncwarp();
             if (lane == 0) mbar_arrive(sfree + (i % UNST));   // B^T, lambda and O_local of this stage have been read
         }
@@ -534,7 +535,8 @@ __global__ void __launch_bounds__(UTHREADS, 1) gdn_out_plain_umma_kernel(GdnArgs
                 case 2: asm volatile("bar.sync 3, 128;\n" ::: "memory"); break;
                 default: asm volatile("bar.sync 4, 128;\n" ::: "memory"); break;
             }
-            const int64_t orow = t_out < tok_end ? out_row(a, t_out) : -1;
+            auto emit = [&](auto scat) {
+            const int64_t orow = t_out < tok_end ? out_row<decltype(scat)::value>(a, t_out) : -1;
             if (orow >= 0) {
 #pragma unroll
                 for (int hd = 0; hd < 2; ++hd) {
@@ -563,6 +565,8 @@ __global__ void __launch_bounds__(UTHREADS, 1) gdn_out_plain_umma_kernel(GdnArgs
                     }
                 }
             }
+            };
+            if (a.out_perm_rows > 0) emit(ScatterOn{}); else emit(ScatterOff{});
         }
     }
     tc_fence_before();
