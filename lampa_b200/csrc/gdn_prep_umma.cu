@@ -74,7 +74,7 @@ __device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap* map, int32_t 
 // tensor-memory columns (256 allocated): three 64-column accumulators and two 32-column A operands
 constexpr int T0 = 0, T1 = 64, T2 = 128, TA_P = 192, TA_R = 224;
 // one mbarrier per group of products issued together (commits complete in issue order, so the group's last one covers it)
-enum { B_G1 = 0, B_G2, B_G3, B_RK, B_PV, B_DRAIN, B_IN, NBAR };
+enum { B_G1 = 0, B_G2, B_G3, B_PV, B_DRAIN, B_IN, NBAR };
 
 constexpr uint32_t ID_KK = umma_idesc(64, 64, 0, 0);   // A, B K-major
 constexpr uint32_t ID_KN = umma_idesc(64, 64, 0, 1);   // A K-major (shared or tensor memory), B MN-major
@@ -449,21 +449,9 @@ __global__ void __launch_bounds__(8192 / NC, 2) gdn_prep_umma_kernel(GdnArgs a, 
     }
     pack_n<NC>(x, w);
     tmem_st_n<NC / 2>(tlane + TA_P + col0 / 2, w);
-    tc_fence_before();
-    __syncthreads();
 
     stage_tick(a, cta, 7);
-    // ---- product 8 ----------------------------------------------------------------------------------
-    if (issuer && !dead) {
-        tc_fence_after();
-        const uint64_t dKN = umma_desc_mn128(sK + isub * TILE);
-#pragma unroll
-        for (int kk = 0; kk < 4; ++kk) umma_f16_ts(dsub + T0, dsub + TA_R + 8 * kk, desc_adv(dKN, kk * 2048), ID_KN, kk > 0);
-        umma_commit(bars + B_RK);
-    }
-    __syncwarp();
-
-    // M[a][b] = e^{Gl} (delta_ab - (K^T W)[a][b]) -> record
+    // M[a][b] = e^{Gl} (delta_ab - (K^T W)[a][b]) -> record (products 6 and 7 ran while R was converted)
     mbar_wait(bars + B_G3, 0u, dead, a.status, 604, budget);
     tc_fence_after();
     tmem_ld_n<NC>(x, tlane + T1 + col0);
@@ -483,17 +471,19 @@ __global__ void __launch_bounds__(8192 / NC, 2) gdn_prep_umma_kernel(GdnArgs a, 
     }
 
     stage_tick(a, cta, 8);
-    // ---- product 9 ----------------------------------------------------------------------------------
+    // ---- products 8, 9: their A operands (R, R .* E .* lambda) are in tensor memory, accumulators T0 and T1 are read out
     if (issuer && !dead) {
         tc_fence_after();
-        const uint64_t dVN = umma_desc_mn128(sV + isub * TILE);
+        const uint64_t dKN = umma_desc_mn128(sK + isub * TILE), dVN = umma_desc_mn128(sV + isub * TILE);
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) umma_f16_ts(dsub + T0, dsub + TA_R + 8 * kk, desc_adv(dKN, kk * 2048), ID_KN, kk > 0);
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk) umma_f16_ts(dsub + T1, dsub + TA_P + 8 * kk, desc_adv(dVN, kk * 2048), ID_KN, kk > 0);
         umma_commit(bars + B_PV);
     }
     __syncwarp();
 
-    // (while product 9 runs)
+    // (while products 8 and 9 run)
     if (HIER) {   // lambda of the chunk levels, transposed to [level][token] for the scan
         for (int idx = tid; idx < 2 * a.LC * CHUNK; idx += PT) {
             const int sb = idx / (a.LC * CHUNK), rem = idx - sb * a.LC * CHUNK;
@@ -510,7 +500,7 @@ __global__ void __launch_bounds__(8192 / NC, 2) gdn_prep_umma_kernel(GdnArgs a, 
     store_cols_swz<NC>(smem + S_X + 2 * TILE + sub * TILE, i, col0 / 8, w);   // staged over U^ (product 7 is complete)
 
     // Q~ = s e^{G_i} (Q - R K) -> record
-    mbar_wait(bars + B_RK, 0u, dead, a.status, 606, budget);
+    mbar_wait(bars + B_PV, 0u, dead, a.status, 606, budget);
     tc_fence_after();
     tmem_ld_n<NC>(x, tlane + T0 + col0);
     {
@@ -530,8 +520,6 @@ __global__ void __launch_bounds__(8192 / NC, 2) gdn_prep_umma_kernel(GdnArgs a, 
     }
 
     // O_local = s Pm V -> record (bf16 [64][64], plain rows)
-    mbar_wait(bars + B_PV, 0u, dead, a.status, 607, budget);
-    tc_fence_after();
     tmem_ld_n<NC>(x, tlane + T1 + col0);
     if (!HIER) {
 #pragma unroll
