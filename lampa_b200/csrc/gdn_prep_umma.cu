@@ -403,9 +403,18 @@ __global__ void __launch_bounds__(8192 / NC, 2) gdn_prep_umma_kernel(GdnArgs a, 
 
     // R (product 3 is long complete) -> the two A operands of products 8 and 9
     const float osc = HIER ? 1.f : a.scale;
-    tmem_ld_n<NC>(x, tlane + T0 + col0);
+    // Column tiles (8 wide) of this phase: with 16 warps a thread takes tiles cq and 7 - cq instead of the adjacent pair
+    // 2 cq, 2 cq + 1 of the other epilogues, so that the two tiles on the diagonal of a row block (the expensive ones:
+    // eight exponentials and level look-ups per row) go to two different warps.
+    constexpr int NT = NC / 8;
+    int tile_of[NT];
+#pragma unroll
+    for (int b4 = 0; b4 < NT; ++b4) tile_of[b4] = (NC == 16) ? (b4 == 0 ? cq : 7 - cq) : col0 / 8 + b4;
+#pragma unroll
+    for (int b4 = 0; b4 < NT; ++b4) tmem_ld8(x + 8 * b4, tlane + T0 + 8 * tile_of[b4]);
     pack_n<NC>(x, w);                                 // R is lower triangular by construction: no mask
-    tmem_st_n<NC / 2>(tlane + TA_R + col0 / 2, w);
+#pragma unroll
+    for (int b4 = 0; b4 < NT; ++b4) tmem_st4(tlane + TA_R + 4 * tile_of[b4], w + 4 * b4);
     {
         // Pm = R .* E .* lambda[i][level(i, j)], E_ij = e^{G_i - G_j} for j <= i.  level(i, j) = bit_length(i ^ j):
         // off the diagonal 8x8 tile it depends on the tiles only, and there E_ij splits into a factor per (row, tile),
@@ -419,8 +428,8 @@ __global__ void __launch_bounds__(8192 / NC, 2) gdn_prep_umma_kernel(GdnArgs a, 
             for (int l = 0; l < 7; ++l) lrow[l] = l < a.L ? lam_at(sub, i, l) : 0.f;
         }
 #pragma unroll
-        for (int b4 = 0; b4 < NC / 8; ++b4) {
-            const int jb = col0 / 8 + b4;
+        for (int b4 = 0; b4 < NT; ++b4) {
+            const int jb = tile_of[b4];
             if (jb > ib) {
 #pragma unroll
                 for (int e = 0; e < 8; ++e) x[8 * b4 + e] = 0.f;
@@ -448,7 +457,8 @@ __global__ void __launch_bounds__(8192 / NC, 2) gdn_prep_umma_kernel(GdnArgs a, 
         }
     }
     pack_n<NC>(x, w);
-    tmem_st_n<NC / 2>(tlane + TA_P + col0 / 2, w);
+#pragma unroll
+    for (int b4 = 0; b4 < NT; ++b4) tmem_st4(tlane + TA_P + 4 * tile_of[b4], w + 4 * b4);
 
     stage_tick(a, cta, 7);
     // M[a][b] = e^{Gl} (delta_ab - (K^T W)[a][b]) -> record (products 6 and 7 ran while R was converted)
@@ -484,13 +494,13 @@ __global__ void __launch_bounds__(8192 / NC, 2) gdn_prep_umma_kernel(GdnArgs a, 
     __syncwarp();
 
     // (while products 8 and 9 run)
-    if (HIER) {   // lambda of the chunk levels, transposed to [level][token] for the scan
-        for (int idx = tid; idx < 2 * a.LC * CHUNK; idx += PT) {
-            const int sb = idx / (a.LC * CHUNK), rem = idx - sb * a.LC * CHUNK;
-            const int l = rem >> 6, r = rem & 63;
+    if (HIER) {   // lambda of the chunk levels, transposed to [level][token] for the scan: thread = (token, rows 8 apart)
+        const int r = tid & 63;
+        for (int row = tid >> 6; row < 2 * a.LC; row += PT / 64) {     // row = head of the pair * LC + level
+            const int sb = row >= a.LC ? 1 : 0, l = row - sb * a.LC;
             if (2 * pair + sb < H) {
                 float* lamc = reinterpret_cast<float*>(a.rec + ((size_t)c * H + 2 * pair + sb) * a.rec_bytes + R::LAM_OFF);
-                lamc[rem] = (ELL0 + l < a.L && r < len) ? lam_at(sb, r, ELL0 + l) : 0.f;
+                lamc[l * CHUNK + r] = (ELL0 + l < a.L && r < len) ? lam_at(sb, r, ELL0 + l) : 0.f;
             }
         }
     }

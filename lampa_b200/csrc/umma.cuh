@@ -77,6 +77,14 @@ __device__ __forceinline__ void tmem_ld16(float (&x)[16], uint32_t taddr) {
     tmem_ld16_issue(x, taddr);
     tmem_wait_ld();
 }
+// 8 consecutive fp32 columns
+__device__ __forceinline__ void tmem_ld8(float* x, uint32_t taddr) {
+    uint32_t* r = reinterpret_cast<uint32_t*>(x);
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                 : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+}
 __device__ __forceinline__ void tmem_ld32(float (&x)[32], uint32_t taddr) {
     uint32_t* r = reinterpret_cast<uint32_t*>(x);
     asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
@@ -89,6 +97,11 @@ __device__ __forceinline__ void tmem_ld32(float (&x)[32], uint32_t taddr) {
     asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
 }
 // write 8 / 16 packed words (16 / 32 bf16 of an A operand row) to consecutive columns of this thread's lane
+__device__ __forceinline__ void tmem_st4(uint32_t taddr, const uint32_t* w) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1,%2,%3,%4};\n"
+                 :: "r"(taddr), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]) : "memory");
+    asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
+}
 __device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t (&w)[8]) {
     asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};\n"
                  :: "r"(taddr), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7]) : "memory");
