@@ -76,16 +76,19 @@ __device__ __forceinline__ void tril_inverse_64(float* sA, int blk, int lane, bo
         float x[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
-            float sum = (i == cc) ? 1.f : 0.f;
+            float sum = (i == cc) ? 1.f : 0.f, sum2 = 0.f;    // two partial sums: half the dependent chain
 #pragma unroll
             for (int q = 0; q < (i + 3) / 4; ++q) {
                 const float4 av = *reinterpret_cast<const float4*>(sA + (m0 + i) * PA + m0 + 4 * q);
                 const float ae[4] = {av.x, av.y, av.z, av.w};
 #pragma unroll
                 for (int e = 0; e < 4; ++e)
-                    if (4 * q + e < i) sum -= ae[e] * x[4 * q + e];
+                    if (4 * q + e < i) {
+                        if (e & 1) sum2 -= ae[e] * x[4 * q + e];
+                        else sum -= ae[e] * x[4 * q + e];
+                    }
             }
-            x[i] = sum;
+            x[i] = sum + sum2;
         }
         __syncwarp();
         if (lane < 16) {
