@@ -518,7 +518,7 @@ def model_measure(ms_, dev, rank, world, steps, warmup, e2e=True, profile=True):
                 model(static_in, cu)
             torch.cuda.synchronize()
             g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g):
+            with torch.cuda.graph(g, capture_error_mode="thread_local"):     # NCCL's watchdog thread may touch CUDA meanwhile
                 static_out = model(static_in, cu)
             graph = g
         except Exception as exc:      # capture is an optimisation of the measurement loop, not a requirement
