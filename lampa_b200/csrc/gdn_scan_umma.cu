@@ -40,7 +40,7 @@ constexpr int UTHREADS = (UEPI_WARPS + 2) * 32;   // plus one control warp and o
 // The relay's own waits are bounded and it arrives whether or not they ran out, so nobody can be left waiting; once
 // a wait has run out it joins the barriers synchronously (relay_pass) so that it cannot run ahead of the epilogue and
 // arrive twice in one phase.
-constexpr int UNB_PAIR = 5, UNB_REC = 10, UNB_COUNT = (UEPI_WARPS + 1) * 32;
+constexpr int UNB_PAIR = 5, UNB_REC = 10, UNB_DFREE = 11, UNB_COUNT = (UEPI_WARPS + 1) * 32;
 __device__ __forceinline__ void named_arrive(int id) { asm volatile("bar.arrive %0, %1;\n" :: "r"(id), "n"(UNB_COUNT) : "memory"); }
 __device__ __forceinline__ void named_sync(int id) { asm volatile("bar.sync %0, %1;\n" :: "r"(id), "n"(UNB_COUNT) : "memory"); }
 __device__ __forceinline__ void relay_pass(int id, bool dead) { if (dead) named_sync(id); else named_arrive(id); }
@@ -74,10 +74,9 @@ __global__ void __launch_bounds__(UTHREADS, 1) gdn_out_hier_umma_kernel(GdnArgs 
     uint64_t* full = reinterpret_cast<uint64_t*>(smem + SM_BAR);      // record landed            (tx count)
     uint64_t* sfree = full + UNST;                                      // stage consumed           (16 warps)
     uint64_t* mdone = sfree + UNST;                                     // pair's MMA complete      (commit)
-    uint64_t* aready = mdone + UNP;                                     // pair's operand rewritten (16 warps)
-    uint64_t* dfree = aready + UNP;                                     // pair's accumulator read  (16 warps)
-    uint64_t* drainb = dfree + UNP;                                     // every MMA issued has completed (commit at the end)
+    uint64_t* drainb = mdone + UNP;                                     // every MMA issued has completed (commit at the end)
     uint32_t* tslot = reinterpret_cast<uint32_t*>(smem + SM_BAR + 256);
+    volatile uint32_t* sdead = reinterpret_cast<volatile uint32_t*>(smem + SM_BAR + 260);   // set once a bounded wait has run out
     float* sOT = reinterpret_cast<float*>(smem + SM_OT);
 
     const int H = a.H;
@@ -117,13 +116,16 @@ __global__ void __launch_bounds__(UTHREADS, 1) gdn_out_hier_umma_kernel(GdnArgs 
         if ((b >> lh) & 1) { live_pack |= (uint32_t)lh << (4 * nlive); ++nlive; }
     const int nslots = BLOCK_LOG + nlive;
     const int npairs = (nslots + 1) >> 1;
+    // accumulator buffers of 128 columns behind the operands: three where four pairs or fewer leave room for them
+    const int nbuf = npairs <= 4 ? 3 : 2, tm_d = npairs <= 4 ? 128 : TM_D;
 
     if (tid == 0) {
 #pragma unroll
         for (int s = 0; s < UNST; ++s) { mbar_init(full + s, 1); mbar_init(sfree + s, UEPI_WARPS); }
 #pragma unroll
-        for (int p = 0; p < UNP; ++p) { mbar_init(mdone + p, 1); mbar_init(aready + p, UEPI_WARPS); mbar_init(dfree + p, UEPI_WARPS); }
+        for (int p = 0; p < UNP; ++p) mbar_init(mdone + p, 1);
         mbar_init(drainb, 1);
+        *sdead = 0u;
         fence_mbar_init();
     }
     if (warp == 0) {
@@ -162,45 +164,52 @@ __global__ void __launch_bounds__(UTHREADS, 1) gdn_out_hier_umma_kernel(GdnArgs 
     const int budget = a.poll_budget;
 
     if (warp == UEPI_WARPS) {
-        // ---- control warp: one lane streams records and issues MMAs --------------------------------
-        if (lane == 0) {
-            int loaded = 0, landed = 0;              // records requested / records seen in shared memory
-            auto load_record = [&](int step) {
-                uint64_t* fb = full + (step % UNST);
-                unsigned char* dst = stage0 + (size_t)(step % UNST) * stage_bytes;
-                const char* src = rec0 + (size_t)step * rec_stride;
-                mbar_expect_tx(fb, (uint32_t)(STAGE_TILES + lam_bytes));
-                bulk_g2s(dst, src, (uint32_t)(STAGE_TILES + lam_bytes), fb);
-                loaded = step + 1;
-            };
+        // ---- control warp: lane 0 streams records and issues MMAs; the whole warp joins the named barriers ----
+        int loaded = 0, landed = 0;                  // records requested / records seen in shared memory (lane 0)
+        auto load_record = [&](int step) {
+            uint64_t* fb = full + (step % UNST);
+            unsigned char* dst = stage0 + (size_t)(step % UNST) * stage_bytes;
+            const char* src = rec0 + (size_t)step * rec_stride;
+            mbar_expect_tx(fb, (uint32_t)(STAGE_TILES + lam_bytes));
+            bulk_g2s(dst, src, (uint32_t)(STAGE_TILES + lam_bytes), fb);
+            loaded = step + 1;
+        };
+        if (lane == 0)
             for (int s = 0; s < UNST - 1 && s < nsteps; ++s) load_record(s);
-            for (int i = 0; i < nsteps && !dead; ++i) {
-                const unsigned char* st = stage0 + (size_t)(i % UNST) * stage_bytes;
-                if (mbar_wait(full + (i % UNST), (uint32_t)((i / UNST) & 1), dead, a.status, 200 + i, budget)) landed = i + 1;
-                for (int p = 0; p < npairs; ++p) {
-                    // the pair's operand rewritten by the previous chunk ...
-                    if (i > 0) mbar_wait(aready + p, (uint32_t)((i - 1) & 1), dead, a.status, 400 + p, budget);
-                    // ... and the accumulator buffer (p & 1) read out by the pair that used it last
-                    if (p >= 2) {
-                        mbar_wait(dfree + (p - 2), (uint32_t)(i & 1), dead, a.status, 410 + p, budget);
-                    } else if (i > 0) {
-                        const int q = ((npairs - 1) & 1) == p ? npairs - 1 : npairs - 2;
-                        mbar_wait(dfree + max(q, p), (uint32_t)((i - 1) & 1), dead, a.status, 420 + p, budget);
-                    }
-                    if (dead) break;                 // a wait ran out: nothing more is issued
+        // The MMAs are numbered through the chunks, m = i * npairs + p, and take the accumulator buffers in turn:
+        // MMA m overwrites the buffer MMA m - nbuf filled, once the epilogue has handed that one back.  The epilogue hands
+        // a pair's accumulator back after it has rewritten the pair's operand, and it works through chunks and pairs in
+        // order, so the same hand-back also covers the operand of pair p rewritten in the previous chunk (npairs >= nbuf).
+        // Every hand-back is joined exactly once and in the order it is given, whether or not anything is still issued.
+        int bufi = 0;
+        for (int i = 0; i < nsteps; ++i) {
+            const unsigned char* st = stage0 + (size_t)(i % UNST) * stage_bytes;
+            if (lane == 0 && !dead && mbar_wait(full + (i % UNST), (uint32_t)((i / UNST) & 1), dead, a.status, 200 + i, budget)) landed = i + 1;
+            for (int p = 0; p < npairs; ++p) {
+                __syncwarp();
+                if (p >= nbuf) named_sync(UNB_DFREE + p - nbuf);
+                else if (i > 0) named_sync(UNB_DFREE + npairs - nbuf + p);
+                const uint32_t dcol = (uint32_t)(tm_d + bufi * 128);
+                bufi = bufi + 1 == nbuf ? 0 : bufi + 1;
+                if (lane == 0 && !dead) {
                     tc_fence_after();
                     const uint32_t b_base = smem_u32(st + UR::M_OFF);
 #pragma unroll
                     for (int kk = 0; kk < 4; ++kk)
-                        umma_f16_ts(taddr + (uint32_t)(TM_D + (p & 1) * 128), taddr + (uint32_t)(TM_A + 32 * p + 8 * kk),
+                        umma_f16_ts(taddr + dcol, taddr + (uint32_t)(TM_A + 32 * p + 8 * kk),
                                     umma_desc_k128(b_base + kk * 32), UMMA_IDESC, kk > 0 ? 1u : 0u);
                     umma_commit(mdone + p);
                 }
-                if (!dead && i + UNST - 1 < nsteps) {       // refill the stage chunk i-1 used, once everyone is done with it
-                    if (i >= 1) mbar_wait(sfree + ((i - 1) % UNST), (uint32_t)(((i - 1) / UNST) & 1), dead, a.status, 500 + i, budget);
-                    if (!dead) load_record(i + UNST - 1);
-                }
             }
+            if (lane == 0 && !dead && i + UNST - 1 < nsteps) {       // refill the stage chunk i-1 used, once everyone is done with it
+                if (i >= 1) mbar_wait(sfree + ((i - 1) % UNST), (uint32_t)(((i - 1) / UNST) & 1), dead, a.status, 500 + i, budget);
+                if (!dead) load_record(i + UNST - 1);
+            }
+            if (lane == 0 && dead) *sdead = 1u;
+        }
+        __syncwarp();
+        for (int p = npairs - nbuf; p < npairs; ++p) named_sync(UNB_DFREE + p);      // the last chunk's outstanding hand-backs
+        if (lane == 0) {
             // nothing asynchronous may outlive the CTA: records still on their way land first, and one
             // last commit covers every MMA issued above
             for (int s = landed; s < loaded; ++s) mbar_drain(full + (s % UNST), (uint32_t)((s / UNST) & 1));
@@ -209,11 +218,13 @@ __global__ void __launch_bounds__(UTHREADS, 1) gdn_out_hier_umma_kernel(GdnArgs 
         }
     } else if (wg == 4) {
         // ---- relay warp (the second warp of this group): mbarrier completions -> named barriers ----
+        // "record landed" travels with the first pair of the chunk.  A pair's barrier cannot be reached a second time
+        // before every epilogue warp has left it: the pair's next MMA is only issued after its accumulator came back.
         for (int i = 0; i < nsteps; ++i) {
             mbar_wait(full + (i % UNST), (uint32_t)((i / UNST) & 1), dead, a.status, 250 + i, budget);
-            relay_pass(UNB_REC, dead);
             for (int p = 0; p < npairs; ++p) {
                 mbar_wait(mdone + p, (uint32_t)(i & 1), dead, a.status, 300 + p, budget);
+                if (dead) *sdead = 1u;
                 relay_pass(UNB_PAIR + p, dead);
             }
         }
@@ -231,6 +242,7 @@ __global__ void __launch_bounds__(UTHREADS, 1) gdn_out_hier_umma_kernel(GdnArgs 
             const int row = s < BLOCK_LOG ? s : BLOCK_LOG + (int)((live_pack >> (4 * (s - BLOCK_LOG))) & 15);
             if (row < a.LC) slot_ok |= 1u << s;      // a missing row is only reachable when the level check already failed
         }
+        int bufi = 0;                                // accumulator buffer of the next pair, in step with the control warp
         for (int i = 0; i < nsteps; ++i) {
             const unsigned char* st = stage0 + (size_t)(i % UNST) * stage_bytes;
             const float* sLam = reinterpret_cast<const float*>(st + STAGE_TILES);
@@ -243,10 +255,7 @@ __global__ void __launch_bounds__(UTHREADS, 1) gdn_out_hier_umma_kernel(GdnArgs 
             const uint32_t low = (uint32_t)n & (BLOCK_CHUNKS - 1);
             const uint32_t read_mask = (low | (~0u << BLOCK_LOG)) & slot_ok;
             const uint32_t clear_mask = low & ~(low + 1u) & (BLOCK_CHUNKS - 1);      // trailing ones of n
-            named_sync(UNB_REC);                       // record landed
-            // this row's 16 columns of B^T, shared by every level that collects in this chunk
-            const uint4 bq0 = *reinterpret_cast<const uint4*>(sBt + v * 128 + (((2 * part) ^ (v & 7)) << 4));
-            const uint4 bq1 = *reinterpret_cast<const uint4*>(sBt + v * 128 + (((2 * part + 1) ^ (v & 7)) << 4));
+            uint4 bq0, bq1;                            // this row's 16 columns of B^T, shared by every level that collects in this chunk
 
             float oacc[16];
 #pragma unroll
@@ -255,11 +264,17 @@ __global__ void __launch_bounds__(UTHREADS, 1) gdn_out_hier_umma_kernel(GdnArgs 
             for (int p = 0; p < npairs; ++p) {
                 named_sync(UNB_PAIR + p);              // pair's MMA complete
                 tc_fence_after();
+                const bool lockstep = *sdead != 0u;    // a wait ran out somewhere: nobody runs ahead of anybody from here on
+                if (p == 0) {                          // the record has landed too
+                    bq0 = *reinterpret_cast<const uint4*>(sBt + v * 128 + (((2 * part) ^ (v & 7)) << 4));
+                    bq1 = *reinterpret_cast<const uint4*>(sBt + v * 128 + (((2 * part + 1) ^ (v & 7)) << 4));
+                }
                 const int s = 2 * p + u;
                 const bool active = s < nslots;
                 const bool do_read = (read_mask >> s) & 1u, clear = (clear_mask >> s) & 1u, add_b = !((n >> s) & 1) && s < BLOCK_LOG;
                 const int lam_row = (int)((lam_pack >> (5 * p)) & 31u);
-                const uint32_t tcol = tlane + (uint32_t)(TM_D + (p & 1) * 128);
+                const uint32_t tcol = tlane + (uint32_t)(tm_d + bufi * 128);
+                bufi = bufi + 1 == nbuf ? 0 : bufi + 1;
                 // state path first: the next chunk's MMA of this pair waits for it
                 if (active && i + 1 < nsteps) {
                     float x[16];
@@ -279,9 +294,6 @@ __global__ void __launch_bounds__(UTHREADS, 1) gdn_out_hier_umma_kernel(GdnArgs 
                     }
                     tmem_st_bf16x16(tlane + TM_A + 32 * p + 8 * part, x);
                 }
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(aready + p);
                 // read path: lambda-weighted contribution of this level to 16 tokens
                 if (do_read) {
                     float y[16];
@@ -295,8 +307,8 @@ __global__ void __launch_bounds__(UTHREADS, 1) gdn_out_hier_umma_kernel(GdnArgs 
                     }
                 }
                 tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(dfree + p);
+                // operand rewritten, accumulator read: the control warp may go on
+                if (lockstep) named_sync(UNB_DFREE + p); else named_arrive(UNB_DFREE + p);
             }
             // output: sum the two rows (levels) of the pairs through shared memory, add O_local, store.
             // Tokens 16 wg .. 16 wg + 15 of the tile are written and read by warpgroup wg alone, so the barrier is the
