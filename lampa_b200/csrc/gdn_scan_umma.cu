@@ -16,11 +16,13 @@
 // Warp-specialised: 16 epilogue warps (warp = 32 rows x 16 state columns x 16 tokens; together they
 // also transpose the chunk's output through shared memory and store it with O_local added) and one
 // control warp whose first lane streams the records in (bulk async copies, three stages) and issues
-// the MMAs.  A pair's MMA for the next chunk is issued as soon as every warp has handed that pair's
-// operand back and the accumulator buffer it will overwrite has been read (two mbarriers per pair,
-// no block-wide barrier on the state path).  MMA completion is tracked by tcgen05.commit on one
-// mbarrier per pair; every wait is bounded, and a CTA whose wait ran out stops issuing copies and
-// MMAs, waits for the ones in flight and only then frees its tensor memory.
+// the MMAs.  The MMAs take the accumulator buffers in turn; one is issued as soon as every epilogue warp has
+// handed back the buffer it overwrites, which it does after rewriting the pair's operand and reading the
+// pair's contribution (a hardware named barrier per pair that the control warp joins: no block-wide barrier
+// and no polling on the state path).  MMA completion is tracked by tcgen05.commit on one mbarrier per
+// pair; every mbarrier wait is bounded, and a CTA whose wait ran out stops issuing copies and MMAs, lets
+// every warp walk through its remaining barriers in lockstep, waits for the copies and MMAs in flight
+// and only then frees its tensor memory.
 #include "gdn.cuh"
 #include "profile.cuh"
 #include "umma.cuh"
@@ -36,10 +38,14 @@ constexpr int UTHREADS = (UEPI_WARPS + 2) * 32;   // plus one control warp and o
 // An mbarrier poll costs the polling warp 200 - 300 cycles even when the phase is long complete, a hardware named
 // barrier that everybody else has already reached about 30.  So only the relay warp polls the mbarriers the epilogue
 // depends on ("record landed", "pair's MMA complete") and passes each completion on through a named barrier that the
-// sixteen epilogue warps join: ids 5 + p for the pairs, 10 for the record (ids 1..4 belong to the output transpose).
-// The relay's own waits are bounded and it arrives whether or not they ran out, so nobody can be left waiting; once
-// a wait has run out it joins the barriers synchronously (relay_pass) so that it cannot run ahead of the epilogue and
-// arrive twice in one phase.
+// sixteen epilogue warps join (ids 5 + p; ids 1..4 belong to the output transpose), and the epilogue hands a pair's
+// accumulator back to the control warp the same way (ids 11 + p: sixteen warps arrive, the control warp waits).
+// Nobody can be left waiting at a named barrier: the relay's and the control lane's own waits are bounded and both
+// walk through every barrier whether or not a wait ran out, and the epilogue never waits for anything else.  Nobody
+// can reach a barrier twice in one phase either: a pair's next MMA is issued only after its hand-back was joined, and
+// once a wait has run out (flag in shared memory) relay and epilogue join their barriers synchronously instead of
+// arriving and running on.  (The plain-rule kernel below has one MMA group per chunk and hands its operands back
+// through an mbarrier: there the named barrier measured slower; its records alternate between ids 10 and 11.)
 constexpr int UNB_PAIR = 5, UNB_REC = 10, UNB_DFREE = 11, UNB_COUNT = (UEPI_WARPS + 1) * 32;
 __device__ __forceinline__ void named_arrive(int id) { asm volatile("bar.arrive %0, %1;\n" :: "r"(id), "n"(UNB_COUNT) : "memory"); }
 __device__ __forceinline__ void named_sync(int id) { asm volatile("bar.sync %0, %1;\n" :: "r"(id), "n"(UNB_COUNT) : "memory"); }
@@ -50,8 +56,9 @@ using UR = Rec<UKD, UVD>;
 // shared-memory map (bytes); everything that tcgen05 reads is 1024-byte aligned
 constexpr int SM_BAR = 0;                    // full[UNST], mma[UNP] mbarriers, TMEM slot
 constexpr int SM_OT = 1024;                  // two buffers (chunk parity) of fp32 [2][64 tokens][64 v]: output transpose / pair-half sum
-// TMEM columns (512 allocated): the states as bf16 A operands, 32 columns per pair, then two
-// 128-column accumulator buffers used by the pairs in turn
+// TMEM columns (512 allocated): the states as bf16 A operands, 32 columns per pair, then the
+// 128-column accumulator buffers used by the MMAs in turn (three from column 128 when there are at
+// most four pairs, else two from column 192)
 constexpr int TM_A = 0;
 constexpr int TM_D = 192;
 constexpr int SM_STAGE = SM_OT + 2 * 2 * 64 * 64 * 4;
