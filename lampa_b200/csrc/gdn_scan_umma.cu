@@ -271,7 +271,7 @@ __global__ void __launch_bounds__(UTHREADS, 1) gdn_out_hier_umma_kernel(GdnArgs 
             for (int p = 0; p < npairs; ++p) {
                 named_sync(UNB_PAIR + p);              // pair's MMA complete
                 tc_fence_after();
-                const bool lockstep = *sdead != 0u;    // a wait ran out somewhere: nobody runs ahead of anybody from here on
+                const uint32_t lockstep = *sdead;      // non-zero: a wait ran out somewhere, nobody runs ahead of anybody from here on
                 if (p == 0) {                          // the record has landed too
                     bq0 = *reinterpret_cast<const uint4*>(sBt + v * 128 + (((2 * part) ^ (v & 7)) << 4));
                     bq1 = *reinterpret_cast<const uint4*>(sBt + v * 128 + (((2 * part + 1) ^ (v & 7)) << 4));
@@ -331,34 +331,31 @@ __global__ void __launch_bounds__(UTHREADS, 1) gdn_out_hier_umma_kernel(GdnArgs 
                 default: asm volatile("bar.sync 4, 128;\n" ::: "memory"); break;
             }
             auto emit = [&](auto scat) {
-                const int tok = tid >> 3, col = (tid & 7) * 8;
+                // thread = (token, 4 + 4 output columns: 4c.. and 32 + 4c..): the eight lanes of a token read 128
+                // contiguous bytes of the tile per load, which is what keeps the 16-byte loads free of bank conflicts
+                const int tok = tid >> 3, col = (tid & 7) * 4;
                 const int64_t t_out = tok0 + (int64_t)i * CHUNK + tok;
                 const int64_t orow = t_out < tok_end ? out_row<decltype(scat)::value>(a, t_out) : -1;
                 if (orow >= 0) {
                     const size_t idx = ((size_t)orow * H + h) * UVD + col;
-                    float r[8];
-                    const uint4 ol = *reinterpret_cast<const uint4*>(sOl + UR::TV::off(tok, col));      // 8 bf16 of O_local
-                    const uint32_t olw[4] = {ol.x, ol.y, ol.z, ol.w};
 #pragma unroll
                     for (int q = 0; q < 2; ++q) {
-                        const float4 p0 = *reinterpret_cast<const float4*>(sOTc + (0 * 64 + tok) * 64 + col + 4 * q);
-                        const float4 q0 = *reinterpret_cast<const float4*>(sOTc + (1 * 64 + tok) * 64 + col + 4 * q);
-                        const float2 oa = unpack_bf16x2(olw[2 * q]), ob = unpack_bf16x2(olw[2 * q + 1]);
-                        r[4 * q] = p0.x + q0.x + oa.x; r[4 * q + 1] = p0.y + q0.y + oa.y;
-                        r[4 * q + 2] = p0.z + q0.z + ob.x; r[4 * q + 3] = p0.w + q0.w + ob.y;
-                    }
-                    if (a.qkv_dt == LAMPA_F32) {
-                        float4* o4 = reinterpret_cast<float4*>((float*)a.o + idx);
-                        o4[0] = make_float4(r[0], r[1], r[2], r[3]);
-                        o4[1] = make_float4(r[4], r[5], r[6], r[7]);
-                    } else {
-                        uint32_t w[4];
-#pragma unroll
-                        for (int q = 0; q < 4; ++q) {
-                            if (a.qkv_dt == LAMPA_BF16) w[q] = pack_bf16x2(r[2 * q], r[2 * q + 1]);
-                            else { const __half2 hh = __floats2half2_rn(r[2 * q], r[2 * q + 1]); w[q] = *reinterpret_cast<const uint32_t*>(&hh); }
+                        const float4 p0 = *reinterpret_cast<const float4*>(sOTc + (0 * 64 + tok) * 64 + col + 32 * q);
+                        const float4 q0 = *reinterpret_cast<const float4*>(sOTc + (1 * 64 + tok) * 64 + col + 32 * q);
+                        const uint2 ol = *reinterpret_cast<const uint2*>(sOl + UR::TV::off(tok, col + 32 * q));      // 4 bf16 of O_local
+                        const float2 oa = unpack_bf16x2(ol.x), ob = unpack_bf16x2(ol.y);
+                        const float r0 = p0.x + q0.x + oa.x, r1 = p0.y + q0.y + oa.y, r2 = p0.z + q0.z + ob.x, r3 = p0.w + q0.w + ob.y;
+                        if (a.qkv_dt == LAMPA_F32) {
+                            *reinterpret_cast<float4*>((float*)a.o + idx + 32 * q) = make_float4(r0, r1, r2, r3);
+                        } else {
+                            uint2 w;
+                            if (a.qkv_dt == LAMPA_BF16) { w.x = pack_bf16x2(r0, r1); w.y = pack_bf16x2(r2, r3); }
+                            else {
+                                const __half2 ha = __floats2half2_rn(r0, r1), hb = __floats2half2_rn(r2, r3);
+                                w.x = *reinterpret_cast<const uint32_t*>(&ha); w.y = *reinterpret_cast<const uint32_t*>(&hb);
+                            }
+                            *reinterpret_cast<uint2*>((uint16_t*)a.o + idx + 32 * q) = w;
                         }
-                        *reinterpret_cast<uint4*>((uint16_t*)a.o + idx) = make_uint4(w[0], w[1], w[2], w[3]);
                     }
                 }
             };
