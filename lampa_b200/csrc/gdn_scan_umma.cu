@@ -504,6 +504,11 @@ __global__ void __launch_bounds__(UTHREADS, 1) gdn_out_plain_umma_kernel(GdnArgs
         // ---- epilogue warps: thread = (head sub, state row v, 16 state columns / 16 tokens) ----------
         const int lt = tid & 127;                      // position in the warpgroup that shares cq
         const int otok = 16 * cq + (lt >> 3), ocol = (lt & 7) * 8;
+        // Columns of the fp32 output tile are permuted so that neither side meets a bank conflict: bit 4 flips with the
+        // head (the two half-warps of a store write the two heads' tiles, 16 KB apart, at the same v) and bit 2 with
+        // bit 5 (the eight lanes of a token read 16 bytes every 32 bytes).
+        const int vsw = v ^ (16 * sub) ^ (4 * ((v >> 5) & 1));
+        const int osw = 4 * ((ocol >> 5) & 1);
         for (int i = 0; i < nsteps; ++i) {
             const unsigned char* sBt = stage0 + (size_t)(i % PNST) * PSTAGE + sub * PSTAGE_HEAD + UR::BT_OFF;
             // this thread's 2 x 8 values of O_local (one per head), from the records in global memory
@@ -544,7 +549,7 @@ __global__ void __launch_bounds__(UTHREADS, 1) gdn_out_plain_umma_kernel(GdnArgs
             tmem_loaded(y);
             float* sOTc = sOT + (i & 1) * (2 * 64 * 64);
 #pragma unroll
-            for (int j = 0; j < 16; ++j) sOTc[(sub * 64 + 16 * cq + j) * 64 + v] = y[j];
+            for (int j = 0; j < 16; ++j) sOTc[(sub * 64 + 16 * cq + j) * 64 + vsw] = y[j];
             switch (cq) {
                 case 0: asm volatile("bar.sync 1, 128;\n" ::: "memory"); break;
                 case 1: asm volatile("bar.sync 2, 128;\n" ::: "memory"); break;
@@ -562,7 +567,7 @@ __global__ void __launch_bounds__(UTHREADS, 1) gdn_out_plain_umma_kernel(GdnArgs
                     float r[8];
 #pragma unroll
                     for (int q = 0; q < 2; ++q) {
-                        const float4 p0 = *reinterpret_cast<const float4*>(sOTc + (hd * 64 + otok) * 64 + ocol + 4 * q);
+                        const float4 p0 = *reinterpret_cast<const float4*>(sOTc + (hd * 64 + otok) * 64 + ((ocol + 4 * q) ^ (16 * hd) ^ osw));
                         const float2 oa = unpack_bf16x2(olw[2 * q]), ob = unpack_bf16x2(olw[2 * q + 1]);
                         r[4 * q] = p0.x + oa.x; r[4 * q + 1] = p0.y + oa.y; r[4 * q + 2] = p0.z + ob.x; r[4 * q + 3] = p0.w + ob.y;
                     }
